@@ -1,0 +1,196 @@
+"""Generate the golden FLCE vectors in this directory from the reference itself.
+
+Run once, in a container that has the reference checkout and no GPU:
+
+    REFERENCE_SRC=<reference checkout>/src python tests/golden/make_golden.py
+
+For every case below the script
+  1. builds seeded inputs,
+  2. runs the reference's own ``fused_linear_cross_entropy_forward`` (and, for an
+     upstream gradient different from one, ``fused_linear_cross_entropy_backward``)
+     on CPU tensors with ``TRITON_INTERPRET=1``, so that the reference's Triton
+     kernels (``liger_cross_entropy_kernel``, ``element_mul_kernel``) are executed
+     unmodified by Triton's interpreter,
+  3. runs the torch ``Linear -> CrossEntropyLoss`` ground truth used by the
+     reference's tests through autograd (``ce_weight``/token-scaling cases excepted
+     where torch has no equivalent term),
+and stores inputs and both sets of outputs in ``<case>.npz``.
+
+Two shims are needed because the interpreter is not the compiler; neither touches
+the reference's arithmetic:
+  * Python floats passed as kernel arguments have no ``.to`` method in the
+    interpreter, so soft-cap values are passed as a ``float`` subclass whose
+    ``.to`` returns itself (for the class-weight sums, which the reference obtains
+    with ``Tensor.item()``, ``item`` is wrapped for the duration of the call so that
+    float results come back as that subclass);
+  * libdevice ``tanh`` has no interpreter implementation, so the module-level name
+    ``tanh`` of ``liger_kernel.ops.cross_entropy`` is bound to
+    ``2*sigmoid(2x)-1`` written with ``triton.language`` primitives.
+"""
+
+import os
+import sys
+
+os.environ["TRITON_INTERPRET"] = "1"
+sys.path.insert(0, os.environ.get("REFERENCE_SRC", "/root/reference/src"))
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "..", ".."))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import triton  # noqa: E402
+import triton.language as tl  # noqa: E402
+
+import liger_kernel.ops.cross_entropy as ref_ce  # noqa: E402
+from liger_kernel.ops.fused_linear_cross_entropy import fused_linear_cross_entropy_backward  # noqa: E402
+from liger_kernel.ops.fused_linear_cross_entropy import fused_linear_cross_entropy_forward  # noqa: E402
+
+from oracle.flce_oracle import torch_linear_ce_reference  # noqa: E402
+
+
+class _Float(float):
+    def to(self, *_a, **_k):
+        return self
+
+
+@triton.jit
+def _interp_tanh(x):
+    return 2 * tl.sigmoid(2 * x) - 1
+
+
+ref_ce.tanh = _interp_tanh
+
+_orig_item = torch.Tensor.item
+
+
+def _item_with_to(self):
+    v = _orig_item(self)
+    return _Float(v) if isinstance(v, float) else v
+
+# name -> (N, H, V, dtype, kwargs, extras)
+CASES = {
+    "mean_default": dict(N=96, H=64, V=257, ign=0.1),
+    "sum_default": dict(N=96, H=64, V=257, ign=0.1, reduction="sum"),
+    "ragged_odd": dict(N=47, H=31, V=123, ign=0.2),
+    "label_smoothing": dict(N=64, H=48, V=203, ign=0.1, label_smoothing=0.1),
+    "z_loss": dict(N=64, H=48, V=203, ign=0.1, lse_square_scale=1e-2, return_z_loss=True),
+    # V is a power of two here on purpose: the reference pads each vocabulary block with -inf *before*
+    # soft-capping, tanh(-inf) = -1 turns the padding into -softcap, and for a small softcap those lanes
+    # leak exp(-softcap - max) each into the row's sum-exp.  "softcap_padded_quirk" records that deviation
+    # from the torch ground truth (3e-3 on the loss at softcap=3); with softcap=30 it is below fp32 epsilon.
+    "softcap": dict(N=64, H=48, V=256, ign=0.1, softcap=3.0, wscale=0.5),
+    "softcap_padded_quirk": dict(N=64, H=48, V=203, ign=0.1, softcap=3.0, wscale=0.5),
+    "bias": dict(N=64, H=48, V=203, ign=0.1, bias=True),
+    "ignore_index_42": dict(N=64, H=48, V=203, ign=0.3, ignore_index=42),
+    "all_ignored": dict(N=32, H=48, V=203, ign=1.0),
+    "ce_weight": dict(N=64, H=48, V=203, ign=0.1, ce_weight=True, label_smoothing=0.1),
+    "token_scaling": dict(N=64, H=48, V=203, ign=0.1, use_token_scaling=True),
+    "all_features": dict(
+        N=64, H=48, V=203, ign=0.15, bias=True, ce_weight=True, label_smoothing=0.1, ignore_index=42,
+        lse_square_scale=1e-4, softcap=30.0, return_z_loss=True, wscale=0.5,
+    ),
+    "qwen_style": dict(N=128, H=64, V=515, ign=0.2, label_smoothing=0.1, lse_square_scale=1e-4, return_z_loss=True),
+    "gemma_style_sum": dict(N=128, H=64, V=515, ign=0.05, softcap=30.0, reduction="sum", wscale=1.0),
+    "none_reduction": dict(N=64, H=48, V=203, ign=0.1, reduction="none", token_grad=True),
+    "grad_output_2p5": dict(N=64, H=48, V=203, ign=0.1, grad_output=2.5),
+    "metrics": dict(N=64, H=48, V=203, ign=0.1, return_token_accuracy=True, return_predicted_tokens=True, wscale=2.0),
+    "bf16_mean": dict(N=96, H=64, V=257, ign=0.1, dtype="bfloat16"),
+}
+
+
+def build_inputs(name, spec):
+    seed = 1000 + sorted(CASES).index(name)
+    g = torch.Generator().manual_seed(seed)
+    N, H, V = spec["N"], spec["H"], spec["V"]
+    dtype = getattr(torch, spec.get("dtype", "float32"))
+    x = torch.randn(N, H, generator=g).to(dtype)
+    w = (torch.randn(V, H, generator=g) * spec.get("wscale", 0.1)).to(dtype)
+    ignore_index = spec.get("ignore_index", -100)
+    t = torch.randint(0, V, (N,), generator=g)
+    if ignore_index >= 0:
+        t[t == ignore_index] = (ignore_index + 1) % V
+    drop = torch.rand(N, generator=g) < spec["ign"]
+    if spec["ign"] >= 1.0:
+        drop[:] = True
+    t[drop] = ignore_index
+    bias = (torch.randn(V, generator=g) * 0.5).to(dtype) if spec.get("bias") else None
+    cw = (torch.rand(V, generator=g) + 0.5) if spec.get("ce_weight") else None
+    tg = (torch.rand(N, generator=g) + 0.5) if spec.get("token_grad") else None
+    return x, w, t, bias, cw, tg, ignore_index
+
+
+def run_case(name, spec):
+    x, w, t, bias, cw, tg, ignore_index = build_inputs(name, spec)
+    softcap = spec.get("softcap")
+    kw = dict(
+        ce_weight=cw,
+        bias=bias,
+        ignore_index=ignore_index,
+        lse_square_scale=spec.get("lse_square_scale", 0.0),
+        label_smoothing=spec.get("label_smoothing", 0.0),
+        reduction=spec.get("reduction", "mean"),
+        softcap=None if softcap is None else _Float(softcap),
+        return_z_loss=spec.get("return_z_loss", False),
+        use_token_scaling=spec.get("use_token_scaling", False),
+        return_token_accuracy=spec.get("return_token_accuracy", False),
+        return_predicted_tokens=spec.get("return_predicted_tokens", False),
+    )
+    xr = x.clone().requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    br = None if bias is None else bias.clone().requires_grad_(True)
+    kw["bias"] = br
+    torch.Tensor.item = _item_with_to
+    try:
+        with torch.no_grad():  # the operator runs inside an autograd.Function forward
+            out = fused_linear_cross_entropy_forward(xr, wr, t, token_grad_output=tg, compute_gradients=True,
+                                                     weight_requires_grad=True, **kw)
+    finally:
+        torch.Tensor.item = _orig_item
+    loss, z_loss, acc, pred, gx, gw, gb = out
+    go = spec.get("grad_output")
+    if go is not None:
+        gx, gw, gb = fused_linear_cross_entropy_backward(torch.tensor(go), gx, gw, gb)
+
+    rec = dict(
+        x=x.float().numpy(), w=w.float().numpy(), target=t.numpy(),
+        ref_loss=loss.float().numpy(), ref_grad_input=gx.float().numpy(), ref_grad_weight=gw.float().numpy(),
+    )
+    if bias is not None:
+        rec["bias"] = bias.float().numpy()
+        rec["ref_grad_bias"] = gb.float().numpy()
+    if cw is not None:
+        rec["ce_weight"] = cw.numpy()
+    if tg is not None:
+        rec["token_grad"] = tg.numpy()
+    if z_loss is not None:
+        rec["ref_z_loss"] = z_loss.float().numpy()
+    if acc is not None:
+        rec["ref_token_accuracy"] = acc.float().numpy()
+    if pred is not None:
+        rec["ref_predicted_tokens"] = pred.numpy()
+
+    # torch ground truth of the reference's tests (no token-scaling equivalent)
+    if not spec.get("use_token_scaling"):
+        tl_, tz, tgx, tgw, tgb = torch_linear_ce_reference(
+            x, w, t, bias=bias, ce_weight=cw, ignore_index=ignore_index,
+            lse_square_scale=kw["lse_square_scale"], label_smoothing=kw["label_smoothing"],
+            reduction=kw["reduction"], softcap=softcap, dtype=torch.float32,
+        )
+        if tg is None and go is None:
+            rec["torch_loss"] = tl_.numpy()
+            rec["torch_z_loss"] = tz.numpy()
+            if spec["ign"] < 1.0:
+                rec["torch_grad_input"] = tgx.numpy()
+                rec["torch_grad_weight"] = tgw.numpy()
+                if tgb is not None:
+                    rec["torch_grad_bias"] = tgb.numpy()
+    meta = {k: v for k, v in spec.items()}
+    meta["ignore_index"] = ignore_index
+    rec["meta"] = np.array(repr(meta))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+    print(f"{name}: loss={np.asarray(rec['ref_loss']).reshape(-1)[:1]}")
+
+
+if __name__ == "__main__":
+    for case_name in sorted(CASES):
+        run_case(case_name, CASES[case_name])
