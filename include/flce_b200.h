@@ -1,0 +1,155 @@
+/* C ABI of the B200 fused linear cross-entropy (FLCE) library, libflce_b200.so.
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer unless the
+ * comment says "host".  All functions return a flce_status_t, never throw, and leave a
+ * human-readable message retrievable with flce_b200_last_error() (thread local) when
+ * they fail.  Work is enqueued on the CUDA stream passed by the caller (a cudaStream_t
+ * cast to void*); nothing synchronises the host except flce_b200_check_device_status.
+ *
+ * The reference has no native interface for this path: its operator is the Python
+ * function pair fused_linear_cross_entropy_forward / fused_linear_cross_entropy_backward
+ * (src/liger_kernel/ops/fused_linear_cross_entropy.py:21-289, :292-336) wrapped by
+ * LigerFusedLinearCrossEntropyFunction (:339-487).  The entry points below are what a
+ * native binding of that operator needs; each one names the slice of the reference it
+ * replaces.  Status-code + last-error conventions follow the reference's only C ABI
+ * (liger_cute_kernels/csrc/core/include/liger_cute/liger_cute.h:19-42).
+ */
+#ifndef FLCE_B200_H_
+#define FLCE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum flce_status {
+  FLCE_OK = 0,
+  FLCE_ERR_INVALID_ARGUMENT = 1, /* null pointer, bad shape, misaligned pitch ... */
+  FLCE_ERR_UNSUPPORTED = 2,      /* combination not implemented / not an sm_100 device */
+  FLCE_ERR_WORKSPACE = 3,        /* workspace too small */
+  FLCE_ERR_CUDA = 4,             /* a CUDA runtime / driver call failed */
+  FLCE_ERR_DEVICE_TIMEOUT = 5    /* a bounded device-side wait expired (see check_device_status) */
+} flce_status_t;
+
+typedef enum flce_dtype { FLCE_BF16 = 0, FLCE_FP16 = 1, FLCE_FP32 = 2 } flce_dtype_t;
+typedef enum flce_reduction { FLCE_MEAN = 0, FLCE_SUM = 1, FLCE_NONE = 2 } flce_reduction_t;
+
+/* One FLCE problem: logits = x[n_rows, hidden] . w[vocab, hidden]^T (+ bias), then the
+ * cross-entropy family of src/liger_kernel/ops/cross_entropy.py:97-336 per row.
+ * Arguments mirror LigerFusedLinearCrossEntropyFunction.forward
+ * (src/liger_kernel/ops/fused_linear_cross_entropy.py:342-359). */
+typedef struct flce_problem {
+  int64_t n_rows;       /* N: tokens held by this rank                                        */
+  int64_t hidden;       /* H: must be a multiple of 8 (16-byte rows for the TMA engine)      */
+  int64_t vocab;        /* V: vocabulary rows of w held by this rank                          */
+  int64_t vocab_total;  /* vocabulary size used by label smoothing (== vocab when unsharded)  */
+  int64_t vocab_offset; /* global id of local row 0 of w (0 when unsharded)                   */
+  int64_t ld_x;         /* row pitch of x in elements (>= hidden, multiple of 8)              */
+  int64_t ld_w;         /* row pitch of w in elements (>= hidden, multiple of 8)              */
+  int32_t dtype;        /* flce_dtype_t of x and w: FLCE_BF16 or FLCE_FP16                    */
+  int32_t reduction;    /* flce_reduction_t                                                   */
+  int64_t ignore_index;
+  float label_smoothing;
+  float lse_square_scale;
+  float softcap;             /* 0 = off                                                       */
+  int32_t use_token_scaling; /* scale each row's loss and gradient by its detached p(target)  */
+  const void* x;             /* [n_rows, ld_x]                                                */
+  const void* w;             /* [vocab, ld_w]                                                 */
+  const int64_t* target;     /* [n_rows] global class ids or ignore_index                     */
+  const float* bias;         /* [vocab] fp32 or NULL                                          */
+  const float* ce_weight;    /* [vocab] fp32 class weights or NULL                            */
+} flce_problem_t;
+
+/* Number of fp32 planes in a row-statistics buffer ([FLCE_ROWSTAT_PLANES][n_rows]):
+ * 0 max, 1 sum-exp relative to max, 2 target logit (0 unless this rank owns the target),
+ * 3 sum of (class-weighted) soft-capped logits, 4 arg-max value, 5 arg-max index (int32 bits). */
+#define FLCE_ROWSTAT_PLANES 6
+
+/* Outputs of the forward pass.  Optional pointers may be NULL. */
+typedef struct flce_forward_out {
+  float* lse;               /* [n_rows] log-sum-exp of the soft-capped logits (saved for backward) */
+  float* target_prob;       /* [n_rows] p(target) (needed for token scaling), optional             */
+  float* loss_rows;         /* [n_rows] per-row loss incl. z-loss, 0 on ignored rows               */
+  float* z_loss_rows;       /* [n_rows] optional                                                    */
+  float* correct_rows;      /* [n_rows] 1.0 where arg-max == target, optional                       */
+  int64_t* predicted_tokens;/* [n_rows] arg-max class id, -1 on ignored rows, optional              */
+  float* scalars;           /* [4]: sum(loss_rows), sum(z_loss_rows), token accuracy, n_non_ignore  */
+} flce_forward_out_t;
+
+typedef struct flce_backward_args {
+  const float* lse;          /* [n_rows] from the forward pass                                      */
+  const float* target_prob;  /* [n_rows] from the forward pass; required with token scaling         */
+  const float* norm;         /* [4] normalisers, see flce_b200_count                                 */
+  const float* grad_output;  /* fp32 upstream gradient: 1 element, or [n_rows] when per_row != 0; NULL = 1 */
+  int32_t grad_output_per_row;
+  int32_t grad_dtype;        /* flce_dtype_t of grad_input / grad_weight (FLCE_FP32 allowed)        */
+  void* grad_input;          /* [n_rows, hidden] dense, or NULL                                     */
+  void* grad_weight;         /* [vocab, hidden] dense, or NULL                                      */
+  float* grad_bias;          /* [vocab] fp32, or NULL                                               */
+} flce_backward_args_t;
+
+enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1 };
+
+/* Bytes of scratch the given phase needs for this problem (0 on invalid input).
+ * `slab_budget_bytes` caps the logit-gradient slab of the backward pass (0 = default 1 GiB). */
+size_t flce_b200_workspace_bytes(const flce_problem_t* p, int phase, size_t slab_budget_bytes);
+
+/* norm is [4] fp32: norm[0] = number of rows whose target != ignore_index, norm[1] = sum of
+ * ce_weight[target] over those rows (== norm[0] without class weights), norm[2] = sum of all class
+ * weights (== vocab_total without class weights), norm[3] = 0.  Replaces the host-synchronising `.item()` reads at
+ * src/liger_kernel/ops/fused_linear_cross_entropy.py:92-104.  A token-sharded caller all-reduces
+ * norm across ranks before passing it on. */
+int flce_b200_count(const flce_problem_t* p, float* norm, void* stream);
+
+/* Sweep 1: logit tiles on the tensor cores, reduced on the fly to per-row statistics; the
+ * N x V logits never reach memory.  Replaces the `X_chunk @ W.t()` GEMM plus the first pass of
+ * liger_cross_entropy_kernel (src/liger_kernel/ops/fused_linear_cross_entropy.py:114,
+ * src/liger_kernel/ops/cross_entropy.py:138-189).  rowstats is [FLCE_ROWSTAT_PLANES][n_rows]. */
+int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* Per-row losses and metrics from (possibly cross-rank merged) statistics, and their sums.
+ * Replaces src/liger_kernel/ops/cross_entropy.py:289-336 and
+ * src/liger_kernel/ops/fused_linear_cross_entropy.py:272-283. */
+int flce_b200_forward_finalize(const flce_problem_t* p, const float* rowstats, const float* norm,
+                               const flce_forward_out_t* out, void* stream);
+
+/* count + forward_stats + forward_finalize for the unsharded case.  norm ([4]) and rowstats are
+ * caller-provided outputs as well. */
+int flce_b200_forward(const flce_problem_t* p, float* norm, float* rowstats, const flce_forward_out_t* out,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Sweep 2: recompute each logit tile, turn it into the logit gradient in the epilogue (bounded
+ * [n_rows, slab] workspace), and run grad_weight = dZ^T.X and grad_input += dZ.W on the tensor
+ * cores slab by slab.  Replaces the second pass of liger_cross_entropy_kernel
+ * (src/liger_kernel/ops/cross_entropy.py:205-283), the projections at
+ * src/liger_kernel/ops/fused_linear_cross_entropy.py:225-265 and the upstream-gradient scaling at
+ * :292-336 (folded into the logit gradient). */
+int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args, void* workspace,
+                       size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
+
+/* Plain D = A . B^T on the same main loop (fp32 or 16-bit output), for unit-testing the tensor-core
+ * path in isolation.  a_mn_major / b_mn_major select which dimension is contiguous in memory:
+ * 0: A is [M, K] (K contiguous), 1: A is [K, M] (M contiguous); likewise B is [N, K] or [K, N].
+ * Replaces nothing in the reference (its GEMMs are cuBLAS calls, fused_linear_cross_entropy.py:114,231,257). */
+int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                   int64_t ld_b, int64_t ld_d, int32_t ab_dtype, int32_t d_dtype, int32_t a_mn_major,
+                   int32_t b_mn_major, int32_t cta_pair, void* stream);
+
+/* Synchronises `stream`, then reports whether any kernel of this library abandoned a bounded wait
+ * since the last call (FLCE_ERR_DEVICE_TIMEOUT) and clears the record.  For tests and debugging. */
+int flce_b200_check_device_status(void* stream);
+
+/* Tunables (process-wide): raster group (m-tiles kept L2-resident per sweep), CTA pairing on/off. */
+int flce_b200_set_option(const char* name, int64_t value);
+
+const char* flce_b200_status_string(int status);
+const char* flce_b200_last_error(void);
+const char* flce_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLCE_B200_H_ */

@@ -1,0 +1,291 @@
+// Register epilogues plugged into the tcgen05 main loop (gemm_sm100.cuh).  Each epilogue
+// thread owns one output row of the tile and sees its 256 fp32 accumulators 32 at a time.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+
+namespace flce {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+enum OutFormat : int { kOutBf16 = 0, kOutFp16 = 1, kOutFp32 = 2 };
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
+  if (fmt == kOutBf16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// soft-capped logit and tanh (needed again by the chain rule)
+__device__ __forceinline__ float softcap_apply(float z, float cap, float inv_cap, float& th) {
+  th = tanhf(z * inv_cap);
+  return cap * th;
+}
+
+// =====================================================================================
+// Sweep 1: logits tile -> per-(row, tile) softmax statistics.  Nothing of size N x V is stored.
+// =====================================================================================
+struct StatsEpilogue {
+  struct Params {
+    const long long* target;  // [M] global class ids
+    const float* bias;        // [n_cols] or null
+    const float* col_weight;  // [n_cols] class weights or null (weights the logit sum only)
+    float softcap, inv_softcap;
+    int n_cols;               // valid columns (vocabulary rows held by this rank)
+    long long vocab_offset;   // global id of column 0
+    int m_rows;               // M
+    float* pmax;              // [n_tiles][M]
+    float* psum;              // [n_tiles][M]
+    float* plogit_sum;        // [n_tiles][M] or null
+    float* pamax_val;         // [n_tiles][M] or null
+    int* pamax_idx;           // [n_tiles][M] or null
+    float* target_logit;      // [M], written by the one tile that contains the target
+  };
+
+  float m, d, ssum, best;
+  int best_idx, row, nt, tgt_local;
+  bool row_ok;
+
+  __device__ __forceinline__ void begin(const Params& p, int row_, int /*col0*/, int n_tile, bool ok) {
+    row = row_;
+    nt = n_tile;
+    row_ok = ok;
+    m = -INFINITY;
+    d = 0.f;
+    ssum = 0.f;
+    best = -INFINITY;
+    best_idx = 0;
+    tgt_local = -1;
+    if (ok) {
+      const long long t = p.target[row] - p.vocab_offset;
+      if (t >= 0 && t < p.n_cols) tgt_local = static_cast<int>(t);
+    }
+  }
+
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+    float s[32];
+    const bool ragged = col + 32 > p.n_cols;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float z = __uint_as_float(acc[j]);
+      if (p.bias != nullptr && col + j < p.n_cols) z += __ldg(p.bias + col + j);
+      if (p.softcap > 0.f) {
+        float th;
+        z = softcap_apply(z, p.softcap, p.inv_softcap, th);
+      }
+      s[j] = (ragged && col + j >= p.n_cols) ? -INFINITY : z;
+    }
+    float cm = s[0];
+#pragma unroll
+    for (int j = 1; j < 32; ++j) cm = fmaxf(cm, s[j]);
+    if (p.pamax_val != nullptr && cm > best) {  // strictly greater: ties keep the lowest index
+      int idx = 31;
+#pragma unroll
+      for (int j = 30; j >= 0; --j) idx = (s[j] == cm) ? j : idx;
+      best = cm;
+      best_idx = col + idx;
+    }
+    if (p.plogit_sum != nullptr) {
+      float acc_s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (!ragged || col + j < p.n_cols) {
+          const float wj = (p.col_weight != nullptr) ? __ldg(p.col_weight + col + j) : 1.f;
+          acc_s = fmaf(s[j], wj, acc_s);
+        }
+      }
+      ssum += acc_s;
+    }
+    const float m_new = fmaxf(m, cm);
+    const float ml2 = m_new * kLog2e;
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) part += ex2_approx(fmaf(s[j], kLog2e, -ml2));
+    d = d * ex2_approx((m - m_new) * kLog2e) + part;
+    m = m_new;
+    const unsigned rel = static_cast<unsigned>(tgt_local - col);
+    if (rel < 32u) {
+      float sy = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sy = (rel == static_cast<unsigned>(j)) ? s[j] : sy;
+      p.target_logit[row] = sy;
+    }
+  }
+
+  __device__ __forceinline__ void end(const Params& p) {
+    if (!row_ok) return;
+    const size_t o = static_cast<size_t>(nt) * p.m_rows + row;
+    p.pmax[o] = m;
+    p.psum[o] = d;
+    if (p.plogit_sum != nullptr) p.plogit_sum[o] = ssum;
+    if (p.pamax_val != nullptr) {
+      p.pamax_val[o] = best;
+      p.pamax_idx[o] = best_idx;
+    }
+  }
+};
+
+// =====================================================================================
+// Sweep 2: recomputed logits tile -> logit gradient dZ (16-bit) in the slab workspace.
+//   dZ[r, j] = (p[r, j] * c1[r] - c2[r] * colw[j] - c3[r] * [j == target_r]) * (1 - tanh^2) ,
+// with p = exp(s - lse); c1/c2/c3 carry every per-row factor (normalisers, z-loss, smoothing,
+// class weight of the target, token scaling, upstream gradient, ignored rows = 0).
+// =====================================================================================
+struct DzEpilogue {
+  struct Params {
+    const long long* target;
+    const float* bias;
+    const float* col_weight;
+    float softcap, inv_softcap;
+    int n_cols;               // valid columns of this slab
+    long long vocab_offset;   // global id of slab column 0
+    int m_rows;
+    const float* lse;         // [M]
+    const float* c1;          // [M]
+    const float* c2;          // [M]
+    const float* c3;          // [M]
+    void* dz;                 // [M][ld_dz] 16-bit
+    long long ld_dz;
+    int out_fmt;              // kOutBf16 / kOutFp16
+  };
+
+  float l2, c1, c2, c3;
+  int row, tgt_local;
+  bool row_ok;
+
+  __device__ __forceinline__ void begin(const Params& p, int row_, int /*col0*/, int /*n_tile*/, bool ok) {
+    row = row_;
+    row_ok = ok;
+    tgt_local = -1;
+    l2 = 0.f;
+    c1 = c2 = c3 = 0.f;
+    if (ok) {
+      const long long t = p.target[row] - p.vocab_offset;
+      if (t >= 0 && t < p.n_cols) tgt_local = static_cast<int>(t);
+      l2 = p.lse[row] * kLog2e;
+      c1 = p.c1[row];
+      c2 = p.c2[row];
+      c3 = p.c3[row];
+    }
+  }
+
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+    if (!row_ok) return;
+    float g[32];
+    const unsigned rel = static_cast<unsigned>(tgt_local - col);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float z = __uint_as_float(acc[j]);
+      const bool in = col + j < p.n_cols;
+      if (p.bias != nullptr && in) z += __ldg(p.bias + col + j);
+      float chain = 1.f;
+      if (p.softcap > 0.f) {
+        float th;
+        z = softcap_apply(z, p.softcap, p.inv_softcap, th);
+        chain = 1.f - th * th;
+      }
+      const float prob = ex2_approx(fmaf(z, kLog2e, -l2));
+      const float wj = (p.col_weight != nullptr && in) ? __ldg(p.col_weight + col + j) : 1.f;
+      float v = fmaf(prob, c1, -c2 * wj);
+      if (rel == static_cast<unsigned>(j)) v -= c3;
+      v *= chain;
+      g[j] = in ? v : 0.f;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.dz) + static_cast<size_t>(row) * p.ld_dz + col);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 o;
+      o.x = pack2(g[8 * q + 0], g[8 * q + 1], p.out_fmt);
+      o.y = pack2(g[8 * q + 2], g[8 * q + 3], p.out_fmt);
+      o.z = pack2(g[8 * q + 4], g[8 * q + 5], p.out_fmt);
+      o.w = pack2(g[8 * q + 6], g[8 * q + 7], p.out_fmt);
+      dst[q] = o;
+    }
+  }
+
+  __device__ __forceinline__ void end(const Params&) {}
+};
+
+// =====================================================================================
+// Plain store / accumulate epilogue for the two gradient GEMMs.
+//   acc_in  != null : v += acc_in[row][col]     (fp32 partial from earlier slabs)
+//   acc_out != null : acc_out[row][col] = v     (fp32 partial for later slabs)
+//   out     != null : out[row][col] = cast(v)   (final result, out_fmt)
+// n_cols must be a multiple of 8 and ld_* keep rows 16-byte aligned.
+// =====================================================================================
+struct StoreEpilogue {
+  struct Params {
+    int m_rows, n_cols;
+    const float* acc_in;
+    float* acc_out;
+    long long ld_acc;
+    void* out;
+    long long ld_out;
+    int out_fmt;
+  };
+
+  int row;
+  bool row_ok;
+
+  __device__ __forceinline__ void begin(const Params&, int row_, int, int, bool ok) {
+    row = row_;
+    row_ok = ok;
+  }
+
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+    if (!row_ok) return;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+    if (p.acc_in != nullptr) {
+      const float4* src = reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(row) * p.ld_acc + col);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (col + 4 * q < p.n_cols) {
+          const float4 a = src[q];
+          v[4 * q + 0] += a.x;
+          v[4 * q + 1] += a.y;
+          v[4 * q + 2] += a.z;
+          v[4 * q + 3] += a.w;
+        }
+      }
+    }
+    if (p.acc_out != nullptr) {
+      float4* dst = reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(row) * p.ld_acc + col);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (col + 4 * q < p.n_cols) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+    if (p.out != nullptr) {
+      if (p.out_fmt == kOutFp32) {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (col + 4 * q < p.n_cols) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (col + 8 * q < p.n_cols) {
+            uint4 o;
+            o.x = pack2(v[8 * q + 0], v[8 * q + 1], p.out_fmt);
+            o.y = pack2(v[8 * q + 2], v[8 * q + 3], p.out_fmt);
+            o.z = pack2(v[8 * q + 4], v[8 * q + 5], p.out_fmt);
+            o.w = pack2(v[8 * q + 6], v[8 * q + 7], p.out_fmt);
+            dst[q] = o;
+          }
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ void end(const Params&) {}
+};
+
+}  // namespace flce

@@ -1,0 +1,761 @@
+// Host side of libflce_b200.so: argument checking, workspace carving, TMA tensor maps,
+// kernel launches and the small per-row kernels around the two tensor-core sweeps.
+// The exported functions are documented in include/flce_b200.h.
+#include "flce_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "epilogues.cuh"
+#include "gemm_sm100.cuh"
+
+namespace flce {
+
+// ------------------------------------------------------------------ errors
+static thread_local char g_last_error[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FLCE_CUDA(expr)                                                                             \
+  do {                                                                                              \
+    cudaError_t e__ = (expr);                                                                       \
+    if (e__ != cudaSuccess) return fail(FLCE_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+
+// ------------------------------------------------------------------ process-wide options
+static long long g_raster_bytes = 32ll << 20;  // bytes of A tiles kept hot per raster group
+static int g_cta_pair = 0;                      // use CTA pairs (cta_group::2) for the FLCE GEMMs
+
+// ------------------------------------------------------------------ per-device state
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  int* status = nullptr;  // device word written by abandoned waits
+};
+static DeviceState g_dev[64];
+static std::mutex g_dev_mutex;
+__device__ int g_device_status_word;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int device_state(DeviceState** out) {
+  int dev = 0;
+  FLCE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FLCE_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    FLCE_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    FLCE_CUDA(cudaDeviceGetAttribute(&st.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    FLCE_CUDA(cudaDeviceGetAttribute(&st.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    if (st.cc_major != 10)
+      return fail(FLCE_ERR_UNSUPPORTED, "this library is built for sm_100a only; device %d is sm_%d%d", dev,
+                  st.cc_major, st.cc_minor);
+    void* p = nullptr;
+    FLCE_CUDA(cudaGetSymbolAddress(&p, g_device_status_word));
+    st.status = static_cast<int*>(p);
+    FLCE_CUDA(cudaMemset(st.status, 0, sizeof(int)));
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      FLCE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+        return fail(FLCE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    st.ready = true;
+  }
+  *out = &st;
+  return FLCE_OK;
+}
+
+// 2-D tensor map over a row-major 16-bit matrix: `inner` contiguous elements per row, `outer` rows
+// `pitch` elements apart, boxes of box_inner x box_outer, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* base, int dtype, long long inner, long long outer, long long pitch,
+                    int box_inner, int box_outer) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "matrix base %p is not 16-byte aligned", base);
+  if ((pitch * 2) % 16 != 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "row pitch %lld elements is not a multiple of 8", pitch);
+  if (inner <= 0 || outer <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "empty matrix (%lld x %lld)", outer, inner);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = (dtype == FLCE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FLCE_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return FLCE_OK;
+}
+
+// An operand of D = A.B^T as the main loop wants it.
+struct Operand {
+  const void* base;
+  long long rows;   // extent along M (for A) or N (for B)
+  long long depth;  // extent along K
+  long long pitch;  // elements between consecutive rows of the *stored* matrix
+  int mn_major;     // 0: stored [rows][depth]; 1: stored [depth][rows]
+};
+
+static int operand_map(CUtensorMap* map, const Operand& op, int dtype, int tile_rows) {
+  if (op.mn_major == 0) return make_map(map, op.base, dtype, op.depth, op.rows, op.pitch, kBlockK, tile_rows);
+  return make_map(map, op.base, dtype, op.rows, op.depth, op.pitch, 64, kBlockK);
+}
+
+static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <int kCtas, int kAMajor, int kBMajor, class Epi>
+static int launch_gemm_impl(const DeviceState& dev, const Operand& a, const Operand& b, int dtype, long long M,
+                            long long N, long long K, long long raster_row_bytes, bool n_fastest,
+                            const typename Epi::Params& ep, cudaStream_t stream) {
+  using Cfg = StageCfg<kCtas>;
+  CUtensorMap map_a, map_b;
+  int rc = operand_map(&map_a, a, dtype, kBlockM);
+  if (rc != FLCE_OK) return rc;
+  rc = operand_map(&map_b, b, dtype, kBlockN / kCtas);
+  if (rc != FLCE_OK) return rc;
+  GemmShape shape;
+  shape.M = static_cast<int>(M);
+  shape.N = static_cast<int>(N);
+  shape.K = static_cast<int>(K);
+  shape.m_tiles = static_cast<int>(ceil_div(M, kBlockM * kCtas));
+  shape.n_tiles = static_cast<int>(ceil_div(N, kBlockN));
+  shape.k_blocks = static_cast<int>(ceil_div(K, kBlockK));
+  if (n_fastest) {
+    shape.group_along_m = 0;
+    shape.group = shape.n_tiles;
+  } else {
+    shape.group_along_m = 1;
+    long long g = g_raster_bytes / (raster_row_bytes > 0 ? raster_row_bytes : 1);
+    if (g < 1) g = 1;
+    if (g > shape.m_tiles) g = shape.m_tiles;
+    shape.group = static_cast<int>(g);
+  }
+  const long long tiles = static_cast<long long>(shape.m_tiles) * shape.n_tiles;
+  long long units = dev.sm_count / kCtas;
+  if (units > tiles) units = tiles;
+  auto kernel = gemm_tcgen05_kernel<kCtas, kAMajor, kBMajor, Epi>;
+  FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(units * kCtas), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = kCtas;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  const int fmt = (dtype == FLCE_BF16) ? 1 : 0;
+  FLCE_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, shape, fmt, ep, dev.status));
+  return FLCE_OK;
+}
+
+template <int kAMajor, int kBMajor, class Epi>
+static int launch_gemm(const DeviceState& dev, bool pair, const Operand& a, const Operand& b, int dtype, long long M,
+                       long long N, long long K, long long raster_row_bytes, bool n_fastest,
+                       const typename Epi::Params& ep, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "empty GEMM %lld x %lld x %lld", M, N, K);
+  if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "GEMM extent does not fit 32 bits");
+  if (pair)
+    return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream);
+  return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream);
+}
+
+// ------------------------------------------------------------------ small kernels
+constexpr int kRedThreads = 1024;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  // fixed-order tree: deterministic for a given block size
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (warp == 0) {
+    r = (lane < (blockDim.x >> 5)) ? scratch[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  }
+  return r;  // valid in warp 0
+}
+
+// norm[0] = #rows with target != ignore_index, norm[1] = sum of class weight of those targets,
+// norm[2] = sum of all class weights (vocab_total when unweighted).  One block: exact and ordered.
+__global__ void count_kernel(const long long* target, long long n_rows, long long ignore_index, const float* ce_weight,
+                             long long vocab, long long vocab_offset, float vocab_total, float* norm) {
+  __shared__ float scratch[32];
+  float cnt = 0.f, wy = 0.f, wall = 0.f;
+  for (long long i = threadIdx.x; i < n_rows; i += blockDim.x) {
+    const long long t = target[i];
+    if (t != ignore_index) {
+      cnt += 1.f;
+      if (ce_weight != nullptr) {
+        const long long l = t - vocab_offset;
+        if (l >= 0 && l < vocab) wy += ce_weight[l];
+      }
+    }
+  }
+  if (ce_weight != nullptr)
+    for (long long j = threadIdx.x; j < vocab; j += blockDim.x) wall += ce_weight[j];
+  const float c = block_sum(cnt, scratch);
+  const float w = block_sum(wy, scratch);
+  const float a = block_sum(wall, scratch);
+  if (threadIdx.x == 0) {
+    norm[0] = c;
+    norm[1] = (ce_weight != nullptr) ? w : c;
+    norm[2] = (ce_weight != nullptr) ? a : vocab_total;
+    norm[3] = 0.f;
+  }
+}
+
+// per-(row, tile) partials -> per-row statistics planes
+__global__ void merge_partials_kernel(int m_rows, int n_tiles, const float* pmax, const float* psum,
+                                      const float* plogit_sum, const float* pamax_val, const int* pamax_idx,
+                                      float* rowstats) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= m_rows) return;
+  float m = -INFINITY;
+  for (int t = 0; t < n_tiles; ++t) m = fmaxf(m, pmax[static_cast<size_t>(t) * m_rows + row]);
+  float d = 0.f, ss = 0.f, best = -INFINITY;
+  int best_idx = 0;
+  for (int t = 0; t < n_tiles; ++t) {
+    const size_t o = static_cast<size_t>(t) * m_rows + row;
+    d += psum[o] * expf(pmax[o] - m);
+    if (plogit_sum != nullptr) ss += plogit_sum[o];
+    if (pamax_val != nullptr) {
+      const float v = pamax_val[o];
+      if (v > best) {
+        best = v;
+        best_idx = pamax_idx[o];
+      }
+    }
+  }
+  const size_t n = static_cast<size_t>(m_rows);
+  rowstats[0 * n + row] = m;
+  rowstats[1 * n + row] = d;
+  // plane 2 (target logit) was written by the sweep itself
+  rowstats[3 * n + row] = ss;
+  rowstats[4 * n + row] = best;
+  reinterpret_cast<int*>(rowstats)[5 * n + row] = best_idx;
+}
+
+struct RowMath {
+  long long ignore_index;
+  float alpha, eps, lambda;
+  int mean, token_scaling, weighted;
+  long long vocab, vocab_offset;
+};
+
+// per-row loss / metrics (src/liger_kernel/ops/cross_entropy.py:289-336 of the reference)
+__global__ void finalize_rows_kernel(int m_rows, RowMath rm, const long long* target, const float* ce_weight,
+                                     const float* rowstats, const float* norm, float* lse_out, float* prob_out,
+                                     float* loss_rows, float* z_rows, float* correct_rows, long long* predicted) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= m_rows) return;
+  const size_t n = static_cast<size_t>(m_rows);
+  const float m = rowstats[0 * n + row], d = rowstats[1 * n + row], xy = rowstats[2 * n + row];
+  const float ss = rowstats[3 * n + row];
+  const int amax = reinterpret_cast<const int*>(rowstats)[5 * n + row];
+  const long long t = target[row];
+  const bool valid = t != rm.ignore_index;
+  const float lse = m + logf(d);
+  if (lse_out != nullptr) lse_out[row] = lse;
+  float loss = 0.f, z = 0.f, py = 0.f, correct = 0.f;
+  long long pred = -1;
+  if (valid) {
+    float wy = 1.f;
+    if (rm.weighted) {
+      const long long l = t - rm.vocab_offset;
+      wy = (l >= 0 && l < rm.vocab) ? ce_weight[l] : 0.f;
+    }
+    loss = (lse - xy) * wy;
+    if (rm.alpha > 0.f) {
+      const float smooth = -rm.eps * ss + (rm.weighted ? rm.eps * lse * norm[2] : rm.alpha * lse);
+      loss = loss * (1.f - rm.alpha) + smooth;
+    }
+    z = rm.lambda * lse * lse;
+    if (rm.mean) {
+      loss /= norm[1];
+      z /= norm[0];
+    }
+    loss += z;
+    py = expf(xy - lse);
+    if (rm.token_scaling) {
+      loss *= py;
+      z *= py;
+    }
+    pred = amax;
+    correct = (static_cast<long long>(amax) == t) ? 1.f : 0.f;
+  }
+  if (prob_out != nullptr) prob_out[row] = py;
+  if (loss_rows != nullptr) loss_rows[row] = loss;
+  if (z_rows != nullptr) z_rows[row] = z;
+  if (correct_rows != nullptr) correct_rows[row] = correct;
+  if (predicted != nullptr) predicted[row] = pred;
+}
+
+// scalars[0] = sum loss_rows, [1] = sum z_rows, [2] = sum correct / n_non_ignore, [3] = n_non_ignore
+__global__ void reduce_rows_kernel(int m_rows, const float* loss_rows, const float* z_rows, const float* correct_rows,
+                                   const float* norm, float* scalars) {
+  __shared__ float scratch[32];
+  float a = 0.f, b = 0.f, c = 0.f;
+  for (int i = threadIdx.x; i < m_rows; i += blockDim.x) {
+    if (loss_rows != nullptr) a += loss_rows[i];
+    if (z_rows != nullptr) b += z_rows[i];
+    if (correct_rows != nullptr) c += correct_rows[i];
+  }
+  const float sa = block_sum(a, scratch);
+  const float sb = block_sum(b, scratch);
+  const float sc = block_sum(c, scratch);
+  if (threadIdx.x == 0) {
+    scalars[0] = sa;
+    scalars[1] = sb;
+    scalars[2] = sc / norm[0];
+    scalars[3] = norm[0];
+  }
+}
+
+// per-row coefficients of the logit gradient (see DzEpilogue)
+__global__ void coef_kernel(int m_rows, RowMath rm, const long long* target, const float* ce_weight, const float* lse,
+                            const float* prob, const float* norm, const float* grad_output, int per_row, float* c1,
+                            float* c2, float* c3) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= m_rows) return;
+  const long long t = target[row];
+  float a = 0.f, b = 0.f, c = 0.f;
+  if (t != rm.ignore_index) {
+    float go = 1.f;
+    if (grad_output != nullptr) go = per_row ? grad_output[row] : grad_output[0];
+    if (rm.token_scaling) go *= prob[row];
+    float wy = 1.f;
+    if (rm.weighted) {
+      const long long l = t - rm.vocab_offset;
+      wy = (l >= 0 && l < rm.vocab) ? ce_weight[l] : 0.f;
+    }
+    const float inv_s = rm.mean ? 1.f / norm[1] : 1.f;
+    const float inv_n = rm.mean ? 1.f / norm[0] : 1.f;
+    const float sum_w = norm[2];
+    const float l = lse[row];
+    a = go * (((1.f - rm.alpha) * wy + rm.eps * sum_w) * inv_s + 2.f * rm.lambda * l * inv_n);
+    b = go * rm.eps * inv_s;
+    c = go * (1.f - rm.alpha) * wy * inv_s;
+  }
+  c1[row] = a;
+  c2[row] = b;
+  c3[row] = c;
+}
+
+// grad_bias[j] (+)= sum over rows of the 16-bit slab column j; one block per 64 columns, ordered sum
+__global__ void colsum_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out) {
+  __shared__ float part[16][64];
+  const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;  // 64 x 16
+  const int col = blockIdx.x * 64 + cx;
+  float s = 0.f;
+  if (col < n_cols) {
+    for (int r = ry; r < m_rows; r += 16) {
+      const uint16_t raw = dz[static_cast<size_t>(r) * ld + col];
+      s += (fmt == kOutBf16) ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw))
+                             : __half2float(*reinterpret_cast<const __half*>(&raw));
+    }
+  }
+  part[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < n_cols) {
+    float t = 0.f;
+    for (int i = 0; i < 16; ++i) t += part[i][cx];
+    out[col] = t;
+  }
+}
+
+// ------------------------------------------------------------------ problem checks / workspace plans
+static int check_problem(const flce_problem_t* p) {
+  if (p == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "problem is NULL");
+  if (p->n_rows <= 0 || p->hidden <= 0 || p->vocab <= 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "shapes must be positive (n_rows=%lld hidden=%lld vocab=%lld)",
+                (long long)p->n_rows, (long long)p->hidden, (long long)p->vocab);
+  if (p->n_rows > 0x7fffffffll || p->vocab > 0x7fffffffll || p->hidden > 0x7fffffffll)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "shapes must fit 32 bits");
+  if (p->dtype != FLCE_BF16 && p->dtype != FLCE_FP16)
+    return fail(FLCE_ERR_UNSUPPORTED, "x / w must be bf16 or fp16 (dtype code %d)", p->dtype);
+  if (p->hidden % 8 != 0 || p->ld_x % 8 != 0 || p->ld_w % 8 != 0 || p->ld_x < p->hidden || p->ld_w < p->hidden)
+    return fail(FLCE_ERR_INVALID_ARGUMENT,
+                "hidden (%lld) and row pitches (%lld, %lld) must be multiples of 8 elements (16-byte rows)",
+                (long long)p->hidden, (long long)p->ld_x, (long long)p->ld_w);
+  if (p->x == nullptr || p->w == nullptr || p->target == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "x, w and target must not be NULL");
+  if (p->reduction < FLCE_MEAN || p->reduction > FLCE_NONE) return fail(FLCE_ERR_INVALID_ARGUMENT, "bad reduction");
+  if (!(p->label_smoothing >= 0.f && p->label_smoothing <= 1.f))
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "label_smoothing must be in [0, 1]");
+  if (p->softcap < 0.f) return fail(FLCE_ERR_INVALID_ARGUMENT, "softcap must be positive (0 = off)");
+  if (p->vocab_total < p->vocab || p->vocab_offset < 0 || p->vocab_offset + p->vocab > p->vocab_total)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "vocabulary shard [%lld, %lld) does not fit vocab_total %lld",
+                (long long)p->vocab_offset, (long long)(p->vocab_offset + p->vocab), (long long)p->vocab_total);
+  if (p->ce_weight != nullptr && p->vocab != p->vocab_total)
+    return fail(FLCE_ERR_UNSUPPORTED, "class weights are not supported together with vocabulary sharding");
+  return FLCE_OK;
+}
+
+static RowMath row_math(const flce_problem_t* p) {
+  RowMath rm;
+  rm.ignore_index = p->ignore_index;
+  rm.alpha = p->label_smoothing;
+  rm.eps = p->label_smoothing / static_cast<float>(p->vocab_total);
+  rm.lambda = p->lse_square_scale;
+  rm.mean = p->reduction == FLCE_MEAN;
+  rm.token_scaling = p->use_token_scaling != 0;
+  rm.weighted = p->ce_weight != nullptr;
+  rm.vocab = p->vocab;
+  rm.vocab_offset = p->vocab_offset;
+  return rm;
+}
+
+struct ForwardPlan {
+  int n_tiles;
+  size_t plane;  // bytes of one [n_tiles][n_rows] fp32 plane
+  size_t total;
+};
+static ForwardPlan forward_plan(const flce_problem_t* p) {
+  ForwardPlan f;
+  f.n_tiles = static_cast<int>(ceil_div(p->vocab, kBlockN));
+  f.plane = align_up(static_cast<size_t>(f.n_tiles) * p->n_rows * sizeof(float), 256);
+  f.total = 5 * f.plane;
+  return f;
+}
+
+struct BackwardPlan {
+  long long slab_cols;  // vocabulary columns per slab
+  long long ld_dz;
+  int n_slabs;
+  size_t coef_bytes, slab_bytes, acc_bytes, total;
+};
+static BackwardPlan backward_plan(const flce_problem_t* p, size_t budget, bool need_acc) {
+  BackwardPlan b;
+  if (budget == 0) budget = size_t(1) << 30;
+  long long max_cols = static_cast<long long>(budget / (static_cast<size_t>(p->n_rows) * 2));
+  max_cols = max_cols / kBlockN * kBlockN;
+  if (max_cols < kBlockN) max_cols = kBlockN;
+  b.n_slabs = static_cast<int>(ceil_div(p->vocab, max_cols));
+  b.slab_cols = ceil_div(ceil_div(p->vocab, b.n_slabs), kBlockN) * kBlockN;
+  b.n_slabs = static_cast<int>(ceil_div(p->vocab, b.slab_cols));
+  b.ld_dz = b.slab_cols;
+  b.coef_bytes = align_up(static_cast<size_t>(p->n_rows) * 3 * sizeof(float), 256);
+  b.slab_bytes = align_up(static_cast<size_t>(p->n_rows) * b.ld_dz * 2, 256);
+  b.acc_bytes = (need_acc && b.n_slabs > 1) ? align_up(static_cast<size_t>(p->n_rows) * p->hidden * sizeof(float), 256) : 0;
+  b.total = b.coef_bytes + b.slab_bytes + b.acc_bytes;
+  return b;
+}
+
+}  // namespace flce
+
+using namespace flce;
+
+// ====================================================================================== C ABI
+extern "C" {
+
+const char* flce_b200_last_error(void) { return g_last_error; }
+const char* flce_b200_version(void) { return "flce_b200 0.1 (sm_100a, tcgen05/TMA)"; }
+
+const char* flce_b200_status_string(int status) {
+  switch (status) {
+    case FLCE_OK: return "ok";
+    case FLCE_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case FLCE_ERR_UNSUPPORTED: return "unsupported";
+    case FLCE_ERR_WORKSPACE: return "workspace too small";
+    case FLCE_ERR_CUDA: return "CUDA error";
+    case FLCE_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+int flce_b200_set_option(const char* name, int64_t value) {
+  if (name == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "option name is NULL");
+  if (strcmp(name, "raster_group_bytes") == 0) {
+    if (value <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "raster_group_bytes must be positive");
+    g_raster_bytes = value;
+    return FLCE_OK;
+  }
+  if (strcmp(name, "cta_pair") == 0) {
+    g_cta_pair = value != 0;
+    return FLCE_OK;
+  }
+  return fail(FLCE_ERR_INVALID_ARGUMENT, "unknown option '%s'", name);
+}
+
+size_t flce_b200_workspace_bytes(const flce_problem_t* p, int phase, size_t slab_budget_bytes) {
+  if (check_problem(p) != FLCE_OK) return 0;
+  if (phase == FLCE_PHASE_FORWARD) return forward_plan(p).total;
+  if (phase == FLCE_PHASE_BACKWARD) return backward_plan(p, slab_budget_bytes, true).total;
+  fail(FLCE_ERR_INVALID_ARGUMENT, "unknown phase %d", phase);
+  return 0;
+}
+
+int flce_b200_count(const flce_problem_t* p, float* norm, void* stream) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (norm == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "norm is NULL");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  count_kernel<<<1, kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(p->target), p->n_rows, p->ignore_index, p->ce_weight, p->vocab,
+      p->vocab_offset, static_cast<float>(p->vocab_total), norm);
+  FLCE_CUDA(cudaGetLastError());
+  return FLCE_OK;
+}
+
+int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* workspace, size_t workspace_bytes,
+                            void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (rowstats == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "rowstats is NULL");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const ForwardPlan plan = forward_plan(p);
+  if (workspace == nullptr || workspace_bytes < plan.total)
+    return fail(FLCE_ERR_WORKSPACE, "forward needs %zu bytes of workspace, got %zu", plan.total, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  const bool need_sum = p->label_smoothing > 0.f;
+  StatsEpilogue::Params ep;
+  ep.target = reinterpret_cast<const long long*>(p->target);
+  ep.bias = p->bias;
+  ep.col_weight = p->ce_weight;
+  ep.softcap = p->softcap;
+  ep.inv_softcap = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+  ep.n_cols = static_cast<int>(p->vocab);
+  ep.vocab_offset = p->vocab_offset;
+  ep.m_rows = static_cast<int>(p->n_rows);
+  ep.pmax = reinterpret_cast<float*>(ws);
+  ep.psum = reinterpret_cast<float*>(ws + plan.plane);
+  ep.plogit_sum = need_sum ? reinterpret_cast<float*>(ws + 2 * plan.plane) : nullptr;
+  ep.pamax_val = reinterpret_cast<float*>(ws + 3 * plan.plane);
+  ep.pamax_idx = reinterpret_cast<int*>(ws + 4 * plan.plane);
+  ep.target_logit = rowstats + 2 * static_cast<size_t>(p->n_rows);
+  FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
+  Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
+  Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
+  rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, g_cta_pair != 0, a, b, p->dtype, p->n_rows, p->vocab, p->hidden,
+                                                    static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
+  if (rc != FLCE_OK) return rc;
+  const int threads = 256;
+  merge_partials_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), plan.n_tiles, ep.pmax, ep.psum, ep.plogit_sum, ep.pamax_val, ep.pamax_idx, rowstats);
+  FLCE_CUDA(cudaGetLastError());
+  return FLCE_OK;
+}
+
+int flce_b200_forward_finalize(const flce_problem_t* p, const float* rowstats, const float* norm,
+                               const flce_forward_out_t* out, void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (rowstats == nullptr || norm == nullptr || out == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "rowstats, norm and out must not be NULL");
+  if (out->scalars != nullptr && out->loss_rows == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "scalars requires loss_rows");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int threads = 256;
+  finalize_rows_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), row_math(p), reinterpret_cast<const long long*>(p->target), p->ce_weight, rowstats,
+      norm, out->lse, out->target_prob, out->loss_rows, out->z_loss_rows, out->correct_rows,
+      reinterpret_cast<long long*>(out->predicted_tokens));
+  FLCE_CUDA(cudaGetLastError());
+  if (out->scalars != nullptr) {
+    reduce_rows_kernel<<<1, kRedThreads, 0, stream>>>(static_cast<int>(p->n_rows), out->loss_rows, out->z_loss_rows,
+                                                     out->correct_rows, norm, out->scalars);
+    FLCE_CUDA(cudaGetLastError());
+  }
+  return FLCE_OK;
+}
+
+int flce_b200_forward(const flce_problem_t* p, float* norm, float* rowstats, const flce_forward_out_t* out,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = flce_b200_count(p, norm, stream);
+  if (rc != FLCE_OK) return rc;
+  rc = flce_b200_forward_stats(p, rowstats, workspace, workspace_bytes, stream);
+  if (rc != FLCE_OK) return rc;
+  return flce_b200_forward_finalize(p, rowstats, norm, out, stream);
+}
+
+int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args, void* workspace,
+                       size_t workspace_bytes, size_t slab_budget_bytes, void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (args == nullptr || args->lse == nullptr || args->norm == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "args, args->lse and args->norm must not be NULL");
+  if (p->use_token_scaling && args->target_prob == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "token scaling needs target_prob from the forward pass");
+  if (args->grad_dtype != p->dtype && args->grad_dtype != FLCE_FP32)
+    return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool grads_fp32 = args->grad_dtype == FLCE_FP32;
+  const BackwardPlan plan = backward_plan(p, slab_budget_bytes, true);
+  const size_t needed = plan.coef_bytes + plan.slab_bytes + ((args->grad_input != nullptr && !grads_fp32) ? plan.acc_bytes : 0);
+  if (workspace == nullptr || workspace_bytes < needed)
+    return fail(FLCE_ERR_WORKSPACE, "backward needs %zu bytes of workspace, got %zu", needed, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* c1 = reinterpret_cast<float*>(ws);
+  float* c2 = c1 + p->n_rows;
+  float* c3 = c2 + p->n_rows;
+  uint16_t* dz = reinterpret_cast<uint16_t*>(ws + plan.coef_bytes);
+  float* dx_acc = reinterpret_cast<float*>(ws + plan.coef_bytes + plan.slab_bytes);
+
+  const int threads = 256;
+  coef_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), row_math(p), reinterpret_cast<const long long*>(p->target), p->ce_weight, args->lse,
+      args->target_prob, args->norm, args->grad_output, args->grad_output_per_row, c1, c2, c3);
+  FLCE_CUDA(cudaGetLastError());
+
+  const bool pair = g_cta_pair != 0;
+  const int esize_out = grads_fp32 ? 4 : 2;
+  for (int s = 0; s < plan.n_slabs; ++s) {
+    const long long v0 = static_cast<long long>(s) * plan.slab_cols;
+    const long long cols = (p->vocab - v0 < plan.slab_cols) ? p->vocab - v0 : plan.slab_cols;
+    const uint16_t* w_slab = static_cast<const uint16_t*>(p->w) + v0 * p->ld_w;
+    // ---- recompute logits of this slab -> dZ
+    {
+      DzEpilogue::Params ep;
+      ep.target = reinterpret_cast<const long long*>(p->target);
+      ep.bias = p->bias != nullptr ? p->bias + v0 : nullptr;
+      ep.col_weight = p->ce_weight != nullptr ? p->ce_weight + v0 : nullptr;
+      ep.softcap = p->softcap;
+      ep.inv_softcap = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+      ep.n_cols = static_cast<int>(cols);
+      ep.vocab_offset = p->vocab_offset + v0;
+      ep.m_rows = static_cast<int>(p->n_rows);
+      ep.lse = args->lse;
+      ep.c1 = c1;
+      ep.c2 = c2;
+      ep.c3 = c3;
+      ep.dz = dz;
+      ep.ld_dz = plan.ld_dz;
+      ep.out_fmt = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
+      Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
+      Operand b{w_slab, cols, p->hidden, p->ld_w, 0};
+      rc = launch_gemm<kMajorK, kMajorK, DzEpilogue>(*dev, pair, a, b, p->dtype, p->n_rows, cols, p->hidden,
+                                                     static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    // ---- grad_weight[slab] = dZ^T . X        (M = cols, N = hidden, K = n_rows; both operands MN-major)
+    if (args->grad_weight != nullptr) {
+      StoreEpilogue::Params ep;
+      ep.m_rows = static_cast<int>(cols);
+      ep.n_cols = static_cast<int>(p->hidden);
+      ep.acc_in = nullptr;
+      ep.acc_out = nullptr;
+      ep.ld_acc = 0;
+      ep.out = static_cast<uint8_t*>(args->grad_weight) + static_cast<size_t>(v0) * p->hidden * esize_out;
+      ep.ld_out = p->hidden;
+      ep.out_fmt = grads_fp32 ? kOutFp32 : (p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
+      Operand a{dz, cols, p->n_rows, plan.ld_dz, 1};
+      Operand b{p->x, p->hidden, p->n_rows, p->ld_x, 1};
+      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, pair, a, b, p->dtype, cols, p->hidden, p->n_rows, 0, true,
+                                                          ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    // ---- grad_input (+)= dZ . W[slab]        (M = n_rows, N = hidden, K = cols; B is MN-major)
+    if (args->grad_input != nullptr) {
+      StoreEpilogue::Params ep;
+      ep.m_rows = static_cast<int>(p->n_rows);
+      ep.n_cols = static_cast<int>(p->hidden);
+      const bool first = s == 0, last = s == plan.n_slabs - 1;
+      float* acc = grads_fp32 ? static_cast<float*>(args->grad_input) : dx_acc;
+      ep.acc_in = first ? nullptr : acc;
+      ep.acc_out = (last && !grads_fp32) ? nullptr : acc;
+      if (plan.n_slabs == 1 && !grads_fp32) ep.acc_out = nullptr;
+      ep.ld_acc = p->hidden;
+      ep.out = (last && !grads_fp32) ? args->grad_input : nullptr;
+      ep.ld_out = p->hidden;
+      ep.out_fmt = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
+      Operand a{dz, p->n_rows, cols, plan.ld_dz, 0};
+      Operand b{w_slab, p->hidden, cols, p->ld_w, 1};
+      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, pair, a, b, p->dtype, p->n_rows, p->hidden, cols, 0, true,
+                                                         ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    if (args->grad_bias != nullptr) {
+      colsum_kernel<<<static_cast<unsigned>(ceil_div(cols, 64)), 1024, 0, stream>>>(
+          dz, plan.ld_dz, static_cast<int>(p->n_rows), static_cast<int>(cols), p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16,
+          args->grad_bias + v0);
+      FLCE_CUDA(cudaGetLastError());
+    }
+  }
+  return FLCE_OK;
+}
+
+int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, int64_t k, int64_t ld_a, int64_t ld_b,
+                   int64_t ld_d, int32_t ab_dtype, int32_t d_dtype, int32_t a_mn_major, int32_t b_mn_major,
+                   int32_t cta_pair, void* stream_) {
+  if (a == nullptr || b == nullptr || d == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL matrix");
+  if (ab_dtype != FLCE_BF16 && ab_dtype != FLCE_FP16) return fail(FLCE_ERR_UNSUPPORTED, "A/B must be bf16 or fp16");
+  if (d_dtype != FLCE_FP32 && d_dtype != ab_dtype) return fail(FLCE_ERR_UNSUPPORTED, "D must be fp32 or the input dtype");
+  if (n % 8 != 0 || ld_d % 8 != 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "n and ld_d must be multiples of 8");
+  DeviceState* dev;
+  int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  StoreEpilogue::Params ep;
+  ep.m_rows = static_cast<int>(m);
+  ep.n_cols = static_cast<int>(n);
+  ep.acc_in = nullptr;
+  ep.acc_out = nullptr;
+  ep.ld_acc = 0;
+  ep.out = d;
+  ep.ld_out = ld_d;
+  ep.out_fmt = d_dtype == FLCE_FP32 ? kOutFp32 : (d_dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
+  Operand oa{a, m, k, ld_a, a_mn_major != 0};
+  Operand ob{b, n, k, ld_b, b_mn_major != 0};
+  const bool pair = cta_pair != 0;
+  const long long row_bytes = static_cast<long long>(kBlockM) * k * 2;
+  if (!a_mn_major && !b_mn_major)
+    return launch_gemm<kMajorK, kMajorK, StoreEpilogue>(*dev, pair, oa, ob, ab_dtype, m, n, k, row_bytes, false, ep, stream);
+  if (a_mn_major && b_mn_major)
+    return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
+  if (!a_mn_major && b_mn_major)
+    return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
+  return fail(FLCE_ERR_UNSUPPORTED, "A MN-major with B K-major is not instantiated");
+}
+
+int flce_b200_check_device_status(void* stream) {
+  DeviceState* dev;
+  int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  FLCE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  int word = 0;
+  FLCE_CUDA(cudaMemcpy(&word, dev->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (word != 0) {
+    FLCE_CUDA(cudaMemset(dev->status, 0, sizeof(int)));
+    return fail(FLCE_ERR_DEVICE_TIMEOUT, "a kernel abandoned a bounded wait (device status %d)", word);
+  }
+  return FLCE_OK;
+}
+
+}  // extern "C"

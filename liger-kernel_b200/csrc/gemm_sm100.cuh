@@ -1,0 +1,281 @@
+// Persistent, warp-specialised tcgen05 GEMM main loop with a pluggable register epilogue.
+//
+//   D[m, n] = sum_k A[m, k] * B[n, k]          (fp16/bf16 in, fp32 accumulate in tensor memory)
+//
+// * one CTA (kCtas = 1) or a pair of CTAs on neighbouring SMs (kCtas = 2) owns a
+//   (128 * kCtas) x 256 output tile; every CTA keeps its own 128 rows in its own tensor memory;
+// * warp 0 streams 64-wide K slices of A and B into a ring of shared-memory stages with TMA
+//   (each CTA of a pair loads only its own rows of A and its own half of B: no multicast);
+// * warp 1 (of the pair's leader) issues tcgen05.mma and hands stages back through
+//   tcgen05.commit -> mbarrier;
+// * warps 2..5 drain finished accumulators with tcgen05.ld, 32 columns at a time, one output row
+//   per thread, and feed them to the epilogue functor.  Two accumulators (2 x 256 columns)
+//   let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Either operand may be K-major (K contiguous in global memory) or MN-major (M or N
+// contiguous); the latter is what the weight-gradient GEMM (dZ^T X) and the B side of the
+// input-gradient GEMM (dZ W) need, so no transposed copies are ever made.
+//
+// Ragged edges are handled by TMA zero fill on loads (the tensor maps carry the exact extents)
+// and by bounds checks in the epilogues.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace flce {
+
+enum Major : int { kMajorK = 0, kMajorMN = 1 };
+
+constexpr int kBlockM = 128;      // rows per CTA
+constexpr int kBlockN = 256;      // columns per tile
+constexpr int kBlockK = 64;       // two-byte elements per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kNumThreads = 192;  // 6 warps
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kTmemCols = 512;    // two 256-column accumulators
+
+template <int kCtas>
+struct StageCfg {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = (kBlockN / kCtas) * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (kCtas == 1) ? 4 : 6;
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  // ring + barriers + bookkeeping, plus 1 KiB so the ring can be aligned to the swizzle atom
+  static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
+};
+
+struct GemmShape {
+  int M, N, K;         // logical extents
+  int m_tiles;         // ceil(M / (128 * kCtas))
+  int n_tiles;         // ceil(N / 256)
+  int k_blocks;        // ceil(K / 64)
+  int group;           // raster: tiles are walked in groups of `group` rows (or columns) of tiles
+  int group_along_m;   // 1: a group is `group` m-tiles x all n-tiles, m fastest; 0: the transpose
+};
+
+__device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& mt, int& nt) {
+  if (s.group_along_m) {
+    const int per_group = s.group * s.n_tiles;
+    const int g = tile / per_group;
+    const int r = tile - g * per_group;
+    const int first = g * s.group;
+    const int rows = min(s.group, s.m_tiles - first);
+    nt = r / rows;
+    mt = first + (r - nt * rows);
+  } else {
+    const int per_group = s.group * s.m_tiles;
+    const int g = tile / per_group;
+    const int r = tile - g * per_group;
+    const int first = g * s.group;
+    const int cols = min(s.group, s.n_tiles - first);
+    mt = r / cols;
+    nt = first + (r - mt * cols);
+  }
+}
+
+// Epilogue concept:
+//   struct Epi {
+//     struct Params {...};                                  // trivially copyable, passed by value
+//     __device__ void begin(const Params&, int row, int col0, int n_tile, bool row_ok);
+//     __device__ void chunk(const Params&, const uint32_t (&acc)[32], int col);   // fp32 bit patterns
+//     __device__ void end(const Params&);
+//   };
+template <int kCtas, int kAMajor, int kBMajor, class Epi>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmShape shape, const int ab_format, const typename Epi::Params ep, int* status) {
+  using Cfg = StageCfg<kCtas>;
+  constexpr int kStages = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  // the swizzle pattern is a function of the address: align the ring to 1024 B
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring_a = smem;
+  uint8_t* ring_b = smem + kStages * Cfg::kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes);
+  uint64_t* full_bar = bars;                    // [kStages]  TMA bytes landed
+  uint64_t* empty_bar = bars + kStages;         // [kStages]  MMAs that read the stage retired
+  uint64_t* tmem_full_bar = bars + 2 * kStages; // [2]        accumulator complete
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2; // [2]        accumulator drained
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (kCtas == 1) ? 0u : cluster_ctarank();
+  const bool is_leader = (cta_rank == 0);
+  const int unit = blockIdx.x / kCtas;          // tile-owning unit (CTA or CTA pair)
+  const int num_units = gridDim.x / kCtas;
+  const int num_tiles = shape.m_tiles * shape.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), kNumEpilogueWarps * kCtas);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<kCtas>(smem_u32(tmem_base_slot), kTmemCols);
+    tmem_relinquish<kCtas>();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_descriptor(&map_a);
+    tma_prefetch_descriptor(&map_b);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtas == 2) cluster_sync();   // partner's barriers are initialised before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        int mt, nt;
+        decode_tile(shape, tile, mt, nt);
+        const int m0 = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM;
+        const int n0 = nt * kBlockN + static_cast<int>(cta_rank) * (kBlockN / kCtas);
+        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, status, kDevTimeoutEmptyBarrier);
+          if (!ok) break;
+          const uint32_t local_full = smem_u32(&full_bar[stage]);
+          if (is_leader) mbar_arrive_expect_tx(local_full, Cfg::kStageBytes * kCtas);
+          uint32_t signal_bar = local_full;
+          if constexpr (kCtas == 2) {
+            asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(signal_bar) : "r"(local_full));
+          }
+          const int k0 = kb * kBlockK;
+          const uint32_t dst_a = smem_u32(ring_a + stage * Cfg::kABytes);
+          const uint32_t dst_b = smem_u32(ring_b + stage * Cfg::kBBytes);
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+            if constexpr (kCtas == 1) tma_load_2d(dst, map, signal_bar, x, y);
+            else tma_load_2d_pair(dst, map, signal_bar, x, y);
+          };
+          if constexpr (kAMajor == kMajorK) {
+            load(dst_a, &map_a, k0, m0);                          // box: 64 k x 128 rows
+          } else {
+#pragma unroll
+            for (int i = 0; i < kBlockM / 64; ++i)                 // boxes: 64 m x 64 k
+              load(dst_a + i * (64 * kBlockK * 2), &map_a, m0 + i * 64, k0);
+          }
+          if constexpr (kBMajor == kMajorK) {
+            load(dst_b, &map_b, k0, n0);                          // box: 64 k x (256 / kCtas) rows
+          } else {
+#pragma unroll
+            for (int i = 0; i < (kBlockN / kCtas) / 64; ++i)       // boxes: 64 n x 64 k
+              load(dst_b + i * (64 * kBlockK * 2), &map_b, n0 + i * 64, k0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // unwinding: give copies already in flight a bounded chance to land before the CTA exits
+        for (int s = 0; s < kStages; ++s)
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(&full_bar[s]), 0) &&
+                             !mbar_try_wait(smem_u32(&full_bar[s]), 1); ++spin) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && is_leader) {
+      const uint32_t idesc = make_idesc_f16(ab_format, kAMajor, kBMajor, kBlockM * kCtas, kBlockN);
+      // per-operand descriptor geometry
+      constexpr uint32_t kLboA = (kAMajor == kMajorK) ? 16u : 64u * kBlockK * 2u;
+      constexpr uint32_t kLboB = (kBMajor == kMajorK) ? 16u : 64u * kBlockK * 2u;
+      constexpr uint32_t kSbo = 1024u;
+      // start-address advance (in 16-byte units) per 16-deep MMA step
+      constexpr uint32_t kStepA = (kAMajor == kMajorK) ? (kUmmaK * 2) / 16 : (kUmmaK * 128) / 16;
+      constexpr uint32_t kStepB = (kBMajor == kMajorK) ? (kUmmaK * 2) / 16 : (kUmmaK * 128) / 16;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
+        const int acc = local_tile & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase[acc] ^ 1u, abort_flag, status, kDevTimeoutTmemEmpty);
+        if (!ok) break;
+        acc_phase[acc] ^= 1u;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
+        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, status, kDevTimeoutFullBarrier);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint64_t desc_a = make_smem_desc(smem_u32(ring_a + stage * Cfg::kABytes), kLboA, kSbo);
+          const uint64_t desc_b = make_smem_desc(smem_u32(ring_b + stage * Cfg::kBBytes), kLboB, kSbo);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            umma_f16<kCtas>(tmem_d, desc_a + static_cast<uint64_t>(k * kStepA),
+                            desc_b + static_cast<uint64_t>(k * kStepB), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          if constexpr (kCtas == 1) umma_commit(smem_u32(&empty_bar[stage]));
+          else umma_commit_pair(smem_u32(&empty_bar[stage]), 0x3);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if constexpr (kCtas == 1) umma_commit(smem_u32(&tmem_full_bar[acc]));
+        else umma_commit_pair(smem_u32(&tmem_full_bar[acc]), 0x3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;                         // tensor-memory lanes this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t acc_phase[2] = {0, 0};
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
+      int mt, nt;
+      decode_tile(shape, tile, mt, nt);
+      const int acc = local_tile & 1;
+      const int row = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM + row_in_tile;
+      const int col0 = nt * kBlockN;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase[acc], abort_flag, status, kDevTimeoutTmemFull);
+      if (!ok) break;
+      acc_phase[acc] ^= 1u;
+      tcgen05_fence_after();
+      Epi epi;
+      epi.begin(ep, row, col0, nt, row < shape.M);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kBlockN);
+#pragma unroll 1
+      for (int c = 0; c < kBlockN; c += 32) {
+        if (col0 + c >= shape.N) break;                   // whole chunk is padding (uniform across the CTA)
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + static_cast<uint32_t>(c), v);
+        tmem_ld_wait();
+        epi.chunk(ep, v, col0 + c);
+      }
+      epi.end(ep);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCtas == 1) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        else mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]), 0);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();  // the single-lane role loops above diverged; the cluster barrier and dealloc below are warp-wide
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtas == 2) cluster_sync();               // partner may still read our stages / signal our barriers
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc<kCtas>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace flce

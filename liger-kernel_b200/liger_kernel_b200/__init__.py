@@ -1,0 +1,19 @@
+"""B200-native fused linear cross-entropy with the call surface of Liger-Kernel's FLCE path.
+
+Importing this package loads ``libflce_b200.so``; if it has not been built the import fails
+(there is no fallback implementation).
+"""
+
+from . import _lib  # noqa: F401  (loads the shared library, raises if missing)
+from .ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction  # noqa: F401
+from .transformers.functional import CrossEntropyOutput  # noqa: F401
+from .transformers.functional import liger_fused_linear_cross_entropy  # noqa: F401
+from .transformers.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyLoss  # noqa: F401
+from .transformers.model.loss_utils import LigerForCausalLMLoss  # noqa: F401
+from .transformers.monkey_patch import _apply_liger_kernel_to_instance  # noqa: F401
+from .transformers.monkey_patch import apply_liger_kernel_to_gemma2  # noqa: F401
+from .transformers.monkey_patch import apply_liger_kernel_to_llama  # noqa: F401
+from .transformers.monkey_patch import apply_liger_kernel_to_qwen2  # noqa: F401
+from .transformers.monkey_patch import install  # noqa: F401
+
+__version__ = "0.1.0"

@@ -1,0 +1,106 @@
+"""ctypes binding of libflce_b200.so (declared in include/flce_b200.h).
+
+There is no fallback: if the shared library is missing, importing this module raises.
+"""
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libflce_b200.so")
+
+FLCE_BF16, FLCE_FP16, FLCE_FP32 = 0, 1, 2
+FLCE_MEAN, FLCE_SUM, FLCE_NONE = 0, 1, 2
+PHASE_FORWARD, PHASE_BACKWARD = 0, 1
+ROWSTAT_PLANES = 6
+
+EXPORTS = (
+    "flce_b200_workspace_bytes",
+    "flce_b200_count",
+    "flce_b200_forward_stats",
+    "flce_b200_forward_finalize",
+    "flce_b200_forward",
+    "flce_b200_backward",
+    "flce_b200_gemm",
+    "flce_b200_check_device_status",
+    "flce_b200_set_option",
+    "flce_b200_status_string",
+    "flce_b200_last_error",
+    "flce_b200_version",
+)
+
+
+class Problem(C.Structure):
+    _fields_ = [
+        ("n_rows", C.c_int64), ("hidden", C.c_int64), ("vocab", C.c_int64),
+        ("vocab_total", C.c_int64), ("vocab_offset", C.c_int64),
+        ("ld_x", C.c_int64), ("ld_w", C.c_int64),
+        ("dtype", C.c_int32), ("reduction", C.c_int32),
+        ("ignore_index", C.c_int64),
+        ("label_smoothing", C.c_float), ("lse_square_scale", C.c_float), ("softcap", C.c_float),
+        ("use_token_scaling", C.c_int32),
+        ("x", C.c_void_p), ("w", C.c_void_p), ("target", C.c_void_p),
+        ("bias", C.c_void_p), ("ce_weight", C.c_void_p),
+    ]
+
+
+class ForwardOut(C.Structure):
+    _fields_ = [
+        ("lse", C.c_void_p), ("target_prob", C.c_void_p), ("loss_rows", C.c_void_p),
+        ("z_loss_rows", C.c_void_p), ("correct_rows", C.c_void_p), ("predicted_tokens", C.c_void_p),
+        ("scalars", C.c_void_p),
+    ]
+
+
+class BackwardArgs(C.Structure):
+    _fields_ = [
+        ("lse", C.c_void_p), ("target_prob", C.c_void_p), ("norm", C.c_void_p), ("grad_output", C.c_void_p),
+        ("grad_output_per_row", C.c_int32), ("grad_dtype", C.c_int32),
+        ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
+    ]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python liger-kernel_b200/build.py` "
+            "(nvcc, sm_100a). This package has no CPU or PyTorch fallback."
+        )
+    lib = C.CDLL(LIB_PATH)
+    P, A, F = C.POINTER(Problem), C.POINTER(BackwardArgs), C.POINTER(ForwardOut)
+    vp, sz, i32, i64 = C.c_void_p, C.c_size_t, C.c_int32, C.c_int64
+    lib.flce_b200_workspace_bytes.argtypes = [P, C.c_int, sz]
+    lib.flce_b200_workspace_bytes.restype = sz
+    lib.flce_b200_count.argtypes = [P, vp, vp]
+    lib.flce_b200_forward_stats.argtypes = [P, vp, vp, sz, vp]
+    lib.flce_b200_forward_finalize.argtypes = [P, vp, vp, F, vp]
+    lib.flce_b200_forward.argtypes = [P, vp, vp, F, vp, sz, vp]
+    lib.flce_b200_backward.argtypes = [P, A, vp, sz, sz, vp]
+    lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]
+    lib.flce_b200_check_device_status.argtypes = [vp]
+    lib.flce_b200_set_option.argtypes = [C.c_char_p, i64]
+    for name in ("flce_b200_count", "flce_b200_forward_stats", "flce_b200_forward_finalize", "flce_b200_forward",
+                 "flce_b200_backward", "flce_b200_gemm", "flce_b200_check_device_status", "flce_b200_set_option"):
+        getattr(lib, name).restype = C.c_int
+    for name in ("flce_b200_status_string", "flce_b200_last_error", "flce_b200_version"):
+        getattr(lib, name).restype = C.c_char_p
+    lib.flce_b200_status_string.argtypes = [C.c_int]
+    return lib
+
+
+lib = _load()
+
+
+class FlceError(RuntimeError):
+    pass
+
+
+def check(status):
+    if status != 0:
+        raise FlceError(
+            f"libflce_b200: {lib.flce_b200_status_string(status).decode()}: {lib.flce_b200_last_error().decode()}"
+        )
+
+
+def set_option(name, value):
+    check(lib.flce_b200_set_option(name.encode(), int(value)))

@@ -1,0 +1,259 @@
+"""Fused linear cross-entropy on B200: host side of the operator.
+
+Same call surface as the reference's ``src/liger_kernel/ops/fused_linear_cross_entropy.py``
+(``fused_linear_cross_entropy_forward`` / ``..._backward`` /
+``LigerFusedLinearCrossEntropyFunction``), but every number is produced by
+``libflce_b200.so`` (tcgen05 + TMA kernels) through its C ABI.  torch is used for device
+memory and the current stream only.  There is no CPU or eager fallback.
+
+Differences from the reference that a caller can observe:
+* forward computes only the loss; gradients are produced in ``backward`` by a second sweep
+  that recomputes the logits tile by tile (the reference computes them in forward and keeps
+  them, ``ops/fused_linear_cross_entropy.py:395-435``).  A repeated backward therefore just
+  recomputes, and ``reduction="none"`` needs no special path.
+* logits stay fp32 from accumulator to loss (the reference rounds them to the input dtype).
+* there is no host synchronisation (the reference reads the non-ignored count with ``.item()``).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import BackwardArgs, ForwardOut, Problem, check, lib
+
+_DTYPES = {torch.bfloat16: _lib.FLCE_BF16, torch.float16: _lib.FLCE_FP16, torch.float32: _lib.FLCE_FP32}
+_REDUCTIONS = {"mean": _lib.FLCE_MEAN, "sum": _lib.FLCE_SUM, "none": _lib.FLCE_NONE}
+
+# bytes of logit-gradient slab the backward sweep may use (N x slab columns, 16-bit)
+SLAB_BUDGET_BYTES = 1 << 30
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _pad_hidden(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
+    """Rows must be 16-byte multiples for the TMA engine; zero-pad the hidden dimension if needed."""
+    h = t.shape[1]
+    if h % mult == 0 and t.is_contiguous():
+        return t
+    hp = (h + mult - 1) // mult * mult
+    if hp == h:
+        return t.contiguous()
+    out = t.new_zeros((t.shape[0], hp))
+    out[:, :h] = t
+    return out
+
+
+class _Prepared:
+    """Validated, device-resident operands of one FLCE call and the matching C struct."""
+
+    def __init__(self, _input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing,
+                 reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0):
+        if _input.device.type != "cuda":
+            raise RuntimeError("liger_kernel_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+        if _input.dim() != 2 or weight.dim() != 2 or _input.shape[1] != weight.shape[1]:
+            raise ValueError(f"expected _input [BT, H] and weight [V, H], got {tuple(_input.shape)} and {tuple(weight.shape)}")
+        if target.dim() != 1 or target.shape[0] != _input.shape[0]:
+            raise ValueError(f"target must be [BT]={_input.shape[0]}, got {tuple(target.shape)}")
+        if _input.dtype != weight.dtype:
+            raise TypeError(f"_input ({_input.dtype}) and weight ({weight.dtype}) must share a dtype")
+        if _input.dtype not in _DTYPES:
+            raise TypeError(f"unsupported dtype {_input.dtype}")
+        if reduction not in _REDUCTIONS:
+            raise ValueError(f"reduction must be 'mean', 'sum' or 'none'. Got: {reduction}")
+        if bias is not None and bias.shape != (weight.shape[0],):
+            raise ValueError(f"bias must be [V]={weight.shape[0]}, got {tuple(bias.shape)}")
+        if ce_weight is not None:
+            assert ce_weight.shape[0] == weight.shape[0], f"If given, weight has to be a Tensor of size V. Got: {ce_weight.shape}"
+            assert torch.is_floating_point(ce_weight), f"If given, weight has to be a Tensor of floating point dtype. Got: {ce_weight.dtype}"
+        self.device = _input.device
+        self.n_rows, self.hidden = _input.shape
+        self.vocab = weight.shape[0]
+        self.dtype = _input.dtype
+        self.reduction = reduction
+        self.x = _pad_hidden(_input.detach())
+        self.w = _pad_hidden(weight.detach())
+        self.target = target.detach().to(device=self.device, dtype=torch.int64).contiguous()
+        self.bias = None if bias is None else bias.detach().to(device=self.device, dtype=torch.float32).contiguous()
+        self.ce_weight = None if ce_weight is None else ce_weight.detach().to(device=self.device, dtype=torch.float32).contiguous()
+        p = Problem()
+        p.n_rows, p.hidden, p.vocab = self.n_rows, self.x.shape[1], self.vocab
+        p.vocab_total = self.vocab if vocab_total is None else int(vocab_total)
+        p.vocab_offset = int(vocab_offset)
+        p.ld_x, p.ld_w = self.x.stride(0), self.w.stride(0)
+        p.dtype = _DTYPES[self.dtype]
+        p.reduction = _REDUCTIONS[reduction]
+        p.ignore_index = int(ignore_index)
+        p.label_smoothing = float(label_smoothing)
+        p.lse_square_scale = float(lse_square_scale)
+        p.softcap = 0.0 if softcap is None else float(softcap)
+        p.use_token_scaling = int(bool(use_token_scaling))
+        p.x, p.w, p.target = self.x.data_ptr(), self.w.data_ptr(), self.target.data_ptr()
+        p.bias = None if self.bias is None else self.bias.data_ptr()
+        p.ce_weight = None if self.ce_weight is None else self.ce_weight.data_ptr()
+        self.problem = p
+
+    def workspace(self, phase: int, budget: int = 0) -> torch.Tensor:
+        nbytes = lib.flce_b200_workspace_bytes(C.byref(self.problem), phase, budget)
+        if nbytes == 0:
+            raise _lib.FlceError(f"libflce_b200: {lib.flce_b200_last_error().decode()}")
+        return torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+
+
+def _forward_outputs(prep: _Prepared):
+    n, dev = prep.n_rows, prep.device
+    f32 = dict(dtype=torch.float32, device=dev)
+    return dict(
+        lse=torch.empty(n, **f32), target_prob=torch.empty(n, **f32), loss_rows=torch.empty(n, **f32),
+        z_loss_rows=torch.empty(n, **f32), correct_rows=torch.empty(n, **f32),
+        predicted_tokens=torch.empty(n, dtype=torch.int64, device=dev), scalars=torch.empty(4, **f32),
+    )
+
+
+def _as_forward_out(o) -> ForwardOut:
+    f = ForwardOut()
+    for k, v in o.items():
+        setattr(f, k, v.data_ptr())
+    return f
+
+
+def flce_forward_device(prep: _Prepared):
+    """Run count + sweep 1 + finalize.  Returns (outputs dict, norm[4], rowstats[6, N])."""
+    with torch.cuda.device(prep.device):
+        norm = torch.empty(4, dtype=torch.float32, device=prep.device)
+        rowstats = torch.empty((_lib.ROWSTAT_PLANES, prep.n_rows), dtype=torch.float32, device=prep.device)
+        out = _forward_outputs(prep)
+        ws = prep.workspace(_lib.PHASE_FORWARD)
+        fo = _as_forward_out(out)
+        check(lib.flce_b200_forward(C.byref(prep.problem), _ptr(norm), _ptr(rowstats), C.byref(fo), _ptr(ws),
+                                    ws.numel(), _stream(prep.device)))
+    return out, norm, rowstats
+
+
+def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, need_input=True, need_weight=True,
+                         need_bias=False, grad_dtype=None, slab_budget=None):
+    """Run sweep 2.  Returns (grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``."""
+    dev = prep.device
+    gd = prep.dtype if grad_dtype is None else grad_dtype
+    budget = SLAB_BUDGET_BYTES if slab_budget is None else int(slab_budget)
+    hp = prep.x.shape[1]
+    with torch.cuda.device(dev):
+        gx = torch.empty((prep.n_rows, hp), dtype=gd, device=dev) if need_input else None
+        gw = torch.empty((prep.vocab, hp), dtype=gd, device=dev) if need_weight else None
+        gb = torch.empty(prep.vocab, dtype=torch.float32, device=dev) if need_bias else None
+        args = BackwardArgs()
+        args.lse, args.target_prob, args.norm = lse.data_ptr(), target_prob.data_ptr(), norm.data_ptr()
+        go = None
+        if grad_output is not None:
+            go = grad_output.detach().to(device=dev, dtype=torch.float32).contiguous().reshape(-1)
+            if go.numel() not in (1, prep.n_rows):
+                raise ValueError(f"grad_output must have 1 or {prep.n_rows} elements, got {go.numel()}")
+            args.grad_output = go.data_ptr()
+            args.grad_output_per_row = int(go.numel() == prep.n_rows and prep.reduction == "none")
+        args.grad_dtype = _DTYPES[gd]
+        args.grad_input = None if gx is None else gx.data_ptr()
+        args.grad_weight = None if gw is None else gw.data_ptr()
+        args.grad_bias = None if gb is None else gb.data_ptr()
+        ws = prep.workspace(_lib.PHASE_BACKWARD, budget)
+        check(lib.flce_b200_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
+    return gx, gw, gb
+
+
+def _autocast_operands(_input, weight, bias):
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
+        _input = _input.to(dt)
+        weight = weight.to(dt)
+        bias = None if bias is None else bias.to(dt)
+    return _input, weight, bias
+
+
+def fused_linear_cross_entropy_forward(
+    _input, weight, target, ce_weight=None, bias=None, ignore_index=-100, lse_square_scale=0.0, label_smoothing=0.0,
+    reduction="mean", softcap=None, return_z_loss=False, accum_dtype=None, use_token_scaling=False,
+    return_token_accuracy=False, return_predicted_tokens=False,
+):
+    """Loss side of the operator (``ops/fused_linear_cross_entropy.py:21-289`` of the reference).
+
+    Returns ``(loss, z_loss, token_accuracy, predicted_tokens, saved)`` where ``saved`` carries what
+    ``fused_linear_cross_entropy_backward`` needs.  ``accum_dtype`` is accepted for signature
+    compatibility: weight gradients here are reduced over all tokens in fp32 tensor memory and written
+    once, so there is no lower-precision accumulation to opt out of.
+    """
+    assert isinstance(return_z_loss, bool), f"return_z_loss must be True or False. Got: {return_z_loss}"
+    assert isinstance(return_token_accuracy, bool), f"return_token_accuracy must be True or False. Got: {return_token_accuracy}"
+    assert isinstance(return_predicted_tokens, bool), f"return_predicted_tokens must be True or False. Got: {return_predicted_tokens}"
+    prep = _Prepared(_input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction,
+                     softcap, use_token_scaling)
+    out, norm, _rowstats = flce_forward_device(prep)
+    if reduction == "none":
+        loss = out["loss_rows"]
+        z_loss = out["z_loss_rows"].to(prep.dtype) if return_z_loss else None
+        token_accuracy = out["correct_rows"] if return_token_accuracy else None
+    else:
+        loss = out["scalars"][0]
+        z_loss = out["scalars"][1].to(prep.dtype) if return_z_loss else None
+        token_accuracy = out["scalars"][2] if return_token_accuracy else None
+    predicted_tokens = out["predicted_tokens"] if return_predicted_tokens else None
+    saved = (prep, out["lse"], out["target_prob"], norm)
+    return loss, z_loss, token_accuracy, predicted_tokens, saved
+
+
+def fused_linear_cross_entropy_backward(grad_output, saved, need_input=True, need_weight=True, need_bias=False):
+    """Gradient side (``ops/fused_linear_cross_entropy.py:205-265,292-336`` of the reference): the upstream
+    gradient (scalar, or per token for ``reduction="none"``) is folded into the logit gradient before the
+    two projections, so no separate scaling pass exists."""
+    prep, lse, target_prob, norm = saved
+    gx, gw, gb = flce_backward_device(prep, lse, target_prob, norm, grad_output, need_input, need_weight, need_bias)
+    h = prep.hidden
+    if gx is not None and gx.shape[1] != h:
+        gx = gx[:, :h].contiguous()
+    if gw is not None and gw.shape[1] != h:
+        gw = gw[:, :h].contiguous()
+    return gx, gw, gb
+
+
+class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
+    """Drop-in for the reference class of the same name (``ops/fused_linear_cross_entropy.py:339-487``):
+    same 15 positional arguments, same 4-tuple result, same gradient slots."""
+
+    @staticmethod
+    def forward(
+        ctx, _input, weight, target, bias=None, ce_weight=None, ignore_index=-100, lse_square_scale=0.0,
+        label_smoothing=0.0, reduction="mean", softcap=None, return_z_loss: bool = False, accum_dtype=None,
+        use_token_scaling: bool = False, return_token_accuracy: bool = False, return_predicted_tokens: bool = False,
+    ):
+        ctx.in_dtypes = (_input.dtype, weight.dtype, None if bias is None else bias.dtype)
+        x, w, b = _autocast_operands(_input, weight, bias)
+        loss, z_loss, token_accuracy, predicted_tokens, saved = fused_linear_cross_entropy_forward(
+            x, w, target, ce_weight=ce_weight, bias=b, ignore_index=ignore_index, lse_square_scale=lse_square_scale,
+            label_smoothing=label_smoothing, reduction=reduction, softcap=softcap, return_z_loss=return_z_loss,
+            accum_dtype=accum_dtype, use_token_scaling=use_token_scaling, return_token_accuracy=return_token_accuracy,
+            return_predicted_tokens=return_predicted_tokens,
+        )
+        ctx.flce_saved = saved
+        ctx.has_bias = bias is not None
+        nondiff = [t for t in (z_loss, token_accuracy, predicted_tokens) if t is not None]
+        if nondiff:
+            ctx.mark_non_differentiable(*nondiff)
+        return loss, z_loss, token_accuracy, predicted_tokens
+
+    @staticmethod
+    def backward(ctx, grad_output, grad_output2=None, grad_output3=None, grad_output4=None):
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_b = ctx.has_bias and ctx.needs_input_grad[3]
+        gx, gw, gb = fused_linear_cross_entropy_backward(grad_output, ctx.flce_saved, need_x, need_w, need_b)
+        dx, dw, db = ctx.in_dtypes
+        gx = None if gx is None else gx.to(dx)
+        gw = None if gw is None else gw.to(dw)
+        gb = None if gb is None else gb.to(db)
+        return (gx, gw, None, gb) + (None,) * 11

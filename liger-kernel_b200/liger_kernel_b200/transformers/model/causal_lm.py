@@ -1,0 +1,118 @@
+"""``forward`` replacements for Hugging Face causal-LM heads that route the training loss through the
+fused operator instead of ``lm_head`` + cross-entropy, so the ``[B, T, V]`` logits are never built.
+
+One implementation serves the three model families in scope; they differ only in whether a final
+logit soft-cap is read from the config.  Behaviour follows the reference's per-model functions:
+``src/liger_kernel/transformers/model/llama.py:24-202``, ``model/qwen2.py:13-130`` and
+``model/gemma2.py:19-157`` (skip-logits default, ``logits_to_keep`` slicing, ``shift_labels``,
+PEFT ``modules_to_save`` unwrapping, FSDP forward redirection, extra ``token_accuracy`` /
+``predicted_tokens`` outputs).
+"""
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from transformers.modeling_outputs import CausalLMOutputWithPast
+
+from ..fsdp import run_inside_fsdp_forward
+from .loss_utils import LigerForCausalLMLoss, unpack_cross_entropy_result
+
+
+@dataclass
+class LigerCausalLMOutputWithPast(CausalLMOutputWithPast):
+    token_accuracy: Optional[torch.FloatTensor] = None
+    predicted_tokens: Optional[torch.LongTensor] = None
+
+
+def _head_loss(lm_head, hidden_states, hidden_size, labels, shift_labels, **loss_kwargs):
+    return LigerForCausalLMLoss(
+        hidden_states=hidden_states, lm_head_weight=lm_head.weight, labels=labels, hidden_size=hidden_size,
+        shift_labels=shift_labels, **loss_kwargs,
+    )
+
+
+def _loss_through_lm_head(model, hidden_states, labels, shift_labels, **loss_kwargs):
+    lm_head = model.lm_head
+    try:  # lm_head listed in LoRA's modules_to_save: read the trainable copy
+        from peft.utils.other import ModulesToSaveWrapper
+
+        if isinstance(lm_head, ModulesToSaveWrapper):
+            lm_head = lm_head.modules_to_save.default
+    except ImportError:
+        pass
+    from torch.distributed.fsdp import FullyShardedDataParallel
+
+    if isinstance(lm_head, FullyShardedDataParallel):
+        # the full weight only exists while FSDP's own forward runs: call the loss from inside it
+        return run_inside_fsdp_forward(
+            lm_head, _head_loss, lm_head.module, hidden_states, model.config.hidden_size, labels, shift_labels,
+            **loss_kwargs,
+        )
+    return _head_loss(lm_head, hidden_states, model.config.hidden_size, labels, shift_labels, **loss_kwargs)
+
+
+def _make_lce_forward(softcap_from_config: bool):
+    def lce_forward(
+        self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None, inputs_embeds=None,
+        labels=None, use_cache=None, output_attentions=None, output_hidden_states=None, return_dict=None,
+        cache_position=None, logits_to_keep=0, skip_logits=None, **kwargs,
+    ):
+        cfg = self.config
+        output_attentions = cfg.output_attentions if output_attentions is None else output_attentions
+        output_hidden_states = cfg.output_hidden_states if output_hidden_states is None else output_hidden_states
+        return_dict = cfg.use_return_dict if return_dict is None else return_dict
+        if getattr(cfg, "pretraining_tp", 1) > 1:
+            raise Exception("Liger Kernel does not support pretraining_tp!!")
+
+        outputs = self.model(
+            input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
+            past_key_values=past_key_values, inputs_embeds=inputs_embeds, use_cache=use_cache,
+            output_attentions=output_attentions, output_hidden_states=output_hidden_states, return_dict=return_dict,
+            cache_position=cache_position, **kwargs,
+        )
+        hidden_states = outputs[0]
+        keep = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep
+        kept = hidden_states[:, keep, :]
+        shift_labels = kwargs.pop("shift_labels", None)
+        have_labels = labels is not None or shift_labels is not None
+        if skip_logits and not have_labels:
+            raise ValueError("skip_logits is True, but labels and shift_labels are None")
+        if skip_logits is None:
+            skip_logits = self.training and have_labels
+        softcap = getattr(cfg, "final_logit_softcapping", None) if softcap_from_config else None
+
+        logits = loss = token_accuracy = predicted_tokens = None
+        if skip_logits:
+            extra = dict(final_logit_softcapping=softcap) if softcap_from_config else {}
+            result = _loss_through_lm_head(self, kept, labels, shift_labels, **extra, **kwargs)
+            loss, _, token_accuracy, predicted_tokens = unpack_cross_entropy_result(result)
+        else:
+            logits = self.lm_head(kept)
+            if softcap is not None:
+                logits = torch.tanh(logits / softcap) * softcap
+            if have_labels:
+                loss = self.loss_function(
+                    logits=logits, labels=labels, shift_labels=shift_labels, vocab_size=cfg.vocab_size, **kwargs
+                )
+        if not return_dict:
+            out = (logits,) + tuple(outputs[1:])
+            if loss is not None:
+                out = (loss,) + out
+            if token_accuracy is not None:
+                out = out + (token_accuracy,)
+            if predicted_tokens is not None:
+                out = out + (predicted_tokens,)
+            return out
+        return LigerCausalLMOutputWithPast(
+            loss=loss, logits=logits, past_key_values=outputs.past_key_values, hidden_states=outputs.hidden_states,
+            attentions=outputs.attentions, token_accuracy=token_accuracy, predicted_tokens=predicted_tokens,
+        )
+
+    return lce_forward
+
+
+llama_lce_forward = _make_lce_forward(softcap_from_config=False)
+qwen2_lce_forward = _make_lce_forward(softcap_from_config=False)
+gemma2_lce_forward = _make_lce_forward(softcap_from_config=True)

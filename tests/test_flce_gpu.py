@@ -1,0 +1,222 @@
+"""Parity of the CUDA path (through the public API and the C ABI below it) with the CPU oracle and with
+the golden vectors of the reference.  Case grid follows the reference's
+test/transformers/test_fused_linear_cross_entropy.py (shapes (8,128,1024,4096) and (4,47,31,123), feature
+rows, bias on/off, mean/sum/none) and test/cutedsl/test_fused_linear_cross_entropy.py (ragged row counts,
+odd vocabulary, all-ignored rows, upstream gradient != 1, repeated backward).
+
+Tolerances: loss 1e-4 relative, per-row lse 1e-5 (relative to max(1,|lse|)) against fp64 math on the same
+16-bit inputs; gradients atol 1e-2 / rtol 5e-2 of the bf16 bar, tightened by the gradient scale where noted;
+ignored rows and integer outputs exact.
+"""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from flce_cases import assert_close, make_inputs, oracle_for, run_cuda
+from golden_util import golden_grad_output, golden_kwargs, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(res, ora, dtype, reduction, n_rows):
+    scale = max(1.0, float(ora.loss.abs().max()))
+    assert_close(res["loss"], ora.loss.float(), 1e-4 * scale, 1e-4, "loss")
+    assert_close(res["z_loss"].float(), ora.z_loss.float(), 2e-2 * max(1e-3, float(ora.z_loss.abs().max())), 1e-2, "z_loss")
+    assert torch.equal(res["predicted_tokens"] == -1, ora.predicted_tokens == -1)
+    # gradient magnitude: mean divides by the row count, 16-bit storage rounds relative to the value
+    gscale = 1.0 if reduction != "mean" else 1.0 / max(1, ora.n_non_ignore)
+    assert_close(res["grad_input"].float(), ora.grad_input.float(), 1e-2 * gscale, 5e-2, "grad_input")
+    assert_close(res["grad_weight"].float(), ora.grad_weight.float(), 1e-2 * max(gscale, 1e-3), 5e-2, "grad_weight")
+    if res.get("grad_bias") is not None:
+        assert_close(res["grad_bias"].float(), ora.grad_bias.float(), 1e-2 * max(gscale, 1e-3), 5e-2, "grad_bias")
+
+
+FEATURES = [
+    dict(),
+    dict(label_smoothing=0.1),
+    dict(lse_square_scale=1e-4),
+    dict(softcap=30.0),
+    dict(label_smoothing=0.1, ignore_index=42, lse_square_scale=1e-4, softcap=30.0),
+]
+
+
+@pytest.mark.parametrize("B,T,H,V", [(8, 128, 1024, 4096), (4, 47, 31, 123)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("feat", FEATURES)
+def test_correctness(B, T, H, V, dtype, reduction, bias, feat):
+    x, w, t, b, _ = make_inputs(B * T, H, V, dtype, seed=B * T + V, bias=bias, ignore_index=feat.get("ignore_index", -100))
+    kw = dict(reduction=reduction, **feat)
+    res = run_cuda(x, w, t, bias=b, **kw)
+    ora = oracle_for(x, w, t, bias=b, **kw)
+    _check(res, ora, dtype, reduction, B * T)
+
+
+@pytest.mark.parametrize("N", [129, 640, 1269])
+@pytest.mark.parametrize("H,V", [(512, 4096), (127, 513), (2048, 32000)])
+def test_ragged_shapes_and_lse(N, H, V):
+    """Row tails, odd vocabulary (padding columns must never enter max / sum / arg-max) and per-row lse."""
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import _Prepared, flce_forward_device
+
+    x, w, t, _, _ = make_inputs(N, H, V, torch.bfloat16, seed=N + V, wscale=0.05)
+    ora = oracle_for(x, w, t)
+    prep = _Prepared(x.cuda(), w.cuda(), t.cuda(), None, None, -100, 0.0, 0.0, "mean", None, False)
+    out, norm, _ = flce_forward_device(prep)
+    lse = out["lse"].cpu().double()
+    valid = t != -100
+    want = ora.lse.double()
+    err = ((lse - want).abs() / want.abs().clamp(min=1.0))[valid]
+    assert float(err.max()) <= 1e-5, f"lse error {float(err.max()):.3e}"
+    assert int(norm[0].item()) == int(valid.sum())
+    assert torch.equal(out["predicted_tokens"].cpu(), ora.predicted_tokens)
+    assert_close(out["scalars"][0].cpu(), ora.loss.float(), 0, 1e-4, "loss")
+    res = run_cuda(x, w, t)
+    _check(res, ora, torch.bfloat16, "mean", N)
+
+
+def test_all_rows_ignored_exact_zero():
+    x, w, t, _, _ = make_inputs(256, 128, 1000, torch.bfloat16, seed=3, ignore_frac=1.1)
+    res = run_cuda(x, w, t)
+    assert float(res["loss"]) == 0.0
+    assert float(res["grad_input"].abs().max()) == 0.0 and float(res["grad_weight"].abs().max()) == 0.0
+    assert torch.all(res["predicted_tokens"] == -1)
+
+
+def test_ignored_rows_have_exact_zero_gradient():
+    x, w, t, _, _ = make_inputs(300, 256, 777, torch.bfloat16, seed=4, ignore_frac=0.4)
+    res = run_cuda(x, w, t, lse_square_scale=1e-3, label_smoothing=0.1)
+    assert float(res["grad_input"][t == -100].abs().max()) == 0.0
+
+
+def test_targets_at_vocab_edges():
+    x, w, t, _, _ = make_inputs(260, 64, 1030, torch.bfloat16, seed=5, ignore_frac=0.0)
+    t[::2] = 0
+    t[1::2] = 1029
+    res = run_cuda(x, w, t)
+    _check(res, oracle_for(x, w, t), torch.bfloat16, "mean", 260)
+
+
+@pytest.mark.parametrize("go", [2.0, 0.5])
+def test_grad_output_scalar(go):
+    x, w, t, _, _ = make_inputs(200, 96, 500, torch.bfloat16, seed=6)
+    res = run_cuda(x, w, t, grad_output=go)
+    ora = oracle_for(x, w, t, grad_output=go)
+    _check(res, ora, torch.bfloat16, "mean", 200)
+
+
+def test_reduction_none_per_token_grad():
+    x, w, t, _, _ = make_inputs(200, 96, 500, torch.bfloat16, seed=7)
+    go = torch.rand(200) + 0.5
+    res = run_cuda(x, w, t, reduction="none", grad_output=go)
+    ora = oracle_for(x, w, t, reduction="none", grad_output=go)
+    assert_close(res["loss"], ora.loss.float(), 1e-4, 1e-4, "loss rows")
+    assert_close(res["grad_input"].float(), ora.grad_input.float(), 1e-2, 5e-2, "grad_input")
+    assert_close(res["grad_weight"].float(), ora.grad_weight.float(), 1e-2, 5e-2, "grad_weight")
+
+
+def test_token_scaling_and_class_weights():
+    x, w, t, _, cw = make_inputs(200, 96, 500, torch.bfloat16, seed=8, ce_weight=True)
+    for kw in (dict(use_token_scaling=True), dict(label_smoothing=0.1), dict()):
+        use_cw = None if kw.get("use_token_scaling") else cw
+        res = run_cuda(x, w, t, ce_weight=use_cw, **kw)
+        ora = oracle_for(x, w, t, ce_weight=use_cw, **kw)
+        _check(res, ora, torch.bfloat16, "mean", 200)
+
+
+def test_repeated_backward_doubles_exactly():
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Fn
+
+    x, w, t, _, _ = make_inputs(200, 96, 500, torch.bfloat16, seed=9)
+    xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    loss = Fn.apply(xd, wd, t.cuda())[0]
+    loss.backward(retain_graph=True)
+    g1x, g1w = xd.grad.clone(), wd.grad.clone()
+    loss.backward()
+    assert torch.equal(xd.grad, 2 * g1x) and torch.equal(wd.grad, 2 * g1w)
+
+
+def test_run_to_run_bitwise_determinism():
+    x, w, t, _, _ = make_inputs(700, 256, 3000, torch.bfloat16, seed=10)
+    a = run_cuda(x, w, t, label_smoothing=0.1)
+    b = run_cuda(x, w, t, label_smoothing=0.1)
+    for k in ("loss", "grad_input", "grad_weight"):
+        assert torch.equal(a[k], b[k]), k
+
+
+def test_multi_slab_backward_matches_single_slab():
+    """A small slab budget forces several vocabulary slabs: dX is accumulated across them in fp32."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+
+    x, w, t, b, _ = make_inputs(384, 128, 2000, torch.bfloat16, seed=11, bias=True)
+    one = run_cuda(x, w, t, bias=b)
+    old = mod.SLAB_BUDGET_BYTES
+    mod.SLAB_BUDGET_BYTES = 384 * 2 * 512  # 512 columns per slab -> 4 slabs
+    try:
+        many = run_cuda(x, w, t, bias=b)
+    finally:
+        mod.SLAB_BUDGET_BYTES = old
+    assert torch.equal(one["grad_weight"], many["grad_weight"])
+    assert torch.equal(one["grad_bias"], many["grad_bias"])
+    assert_close(many["grad_input"].float(), one["grad_input"].float(), 1e-5, 2e-2, "grad_input")
+    _check(many, oracle_for(x, w, t, bias=b), torch.bfloat16, "mean", 384)
+
+
+def test_cta_pair_matches_single_cta():
+    from liger_kernel_b200 import _lib
+
+    x, w, t, _, _ = make_inputs(700, 256, 3000, torch.bfloat16, seed=12)
+    a = run_cuda(x, w, t)
+    _lib.set_option("cta_pair", 1)
+    try:
+        b = run_cuda(x, w, t)
+    finally:
+        _lib.set_option("cta_pair", 0)
+    assert_close(b["loss"], a["loss"], 0, 1e-6, "loss")
+    assert_close(b["grad_weight"].float(), a["grad_weight"].float(), 1e-6, 1e-2, "grad_weight")
+    _check(b, oracle_for(x, w, t), torch.bfloat16, "mean", 700)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_against_reference_golden(name):
+    rec, meta = load_golden(name)
+    x, w, t = torch.from_numpy(rec["x"]).bfloat16(), torch.from_numpy(rec["w"]).bfloat16(), torch.from_numpy(rec["target"])
+    kw = golden_kwargs(rec, meta)
+    bias, cw = kw.pop("bias"), kw.pop("ce_weight")
+    bias = None if bias is None else bias.bfloat16()
+    go = golden_grad_output(rec, meta)
+    res = run_cuda(x, w, t, bias=bias, ce_weight=cw, grad_output=go, **kw)
+    # the golden outputs were produced from the fp32 inputs: bf16 rounding of x and w bounds the agreement
+    scale = max(1.0, float(np.abs(rec["ref_loss"]).max()))
+    tol = 5e-2 if name == "token_scaling" else 2e-2
+    assert_close(res["loss"], torch.from_numpy(rec["ref_loss"]), tol * scale, tol, "loss vs reference")
+    gs = max(float(np.abs(rec["ref_grad_weight"]).max()), 1e-6)
+    assert_close(res["grad_weight"].float(), torch.from_numpy(rec["ref_grad_weight"]), 5e-2 * gs, 1e-1, "grad_weight vs reference")
+    gs = max(float(np.abs(rec["ref_grad_input"]).max()), 1e-6)
+    assert_close(res["grad_input"].float(), torch.from_numpy(rec["ref_grad_input"]), 5e-2 * gs, 1e-1, "grad_input vs reference")
+    # and tightly against the oracle on the same rounded inputs
+    ora = oracle_for(x, w, t, bias=bias, ce_weight=cw, grad_output=go, **kw)
+    _check(res, ora, torch.bfloat16, kw["reduction"], x.shape[0])
+
+
+def test_error_paths():
+    from liger_kernel_b200 import _lib
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Fn
+
+    x = torch.randn(16, 64, dtype=torch.bfloat16)
+    w = torch.randn(100, 64, dtype=torch.bfloat16)
+    t = torch.randint(0, 100, (16,))
+    with pytest.raises(RuntimeError):  # CPU tensors: no fallback
+        Fn.apply(x, w, t)
+    with pytest.raises(ValueError):
+        Fn.apply(x.cuda(), w.cuda(), t.cuda(), None, None, -100, 0.0, 0.0, "median")
+    with pytest.raises(TypeError):
+        Fn.apply(x.cuda().half(), w.cuda(), t.cuda())
+    rc = _lib.lib.flce_b200_gemm(None, None, None, 1, 8, 8, 8, 8, 8, 0, 2, 0, 0, 0, None)
+    assert rc == 1 and b"NULL" in _lib.lib.flce_b200_last_error()
+    loss = Fn.apply(x.cuda(), w.cuda(), t.cuda())[0]
+    with pytest.raises(RuntimeError, match="does not require grad"):
+        loss.backward()

@@ -1,0 +1,49 @@
+"""The tcgen05 main loop in isolation, through the C ABI (flce_b200_gemm), against torch matmul.
+
+Inputs are small integers, so every product and partial sum is exact in fp32 and the comparison
+is bit-exact for every operand layout (K-major / MN-major) and for single CTAs and CTA pairs.
+"""
+
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+VARIANTS = [(0, 0), (0, 1), (1, 1)]  # (A MN-major?, B MN-major?) as used by logits / dX / dW
+SHAPES = [(128, 256, 64), (256, 512, 256), (1000, 1304, 520), (129, 8, 72), (2048, 4096, 1024)]
+
+
+def _run(a_mn, b_mn, pair, M, N, K, dtype=torch.bfloat16, out_dtype=torch.float32):
+    from liger_kernel_b200 import _lib
+
+    lib = _lib.lib
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
+    A = torch.randint(-3, 4, (M, K), device="cuda", generator=g).to(dtype)
+    B = torch.randint(-3, 4, (N, K), device="cuda", generator=g).to(dtype)
+    As = A.t().contiguous() if a_mn else A
+    Bs = B.t().contiguous() if b_mn else B
+    D = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+    _lib.check(lib.flce_b200_gemm(C.c_void_p(As.data_ptr()), C.c_void_p(Bs.data_ptr()), C.c_void_p(D.data_ptr()),
+                                  M, N, K, As.stride(0), Bs.stride(0), D.stride(0), code[dtype], code[out_dtype],
+                                  a_mn, b_mn, pair, st))
+    _lib.check(lib.flce_b200_check_device_status(st))
+    ref = A.float() @ B.float().t()
+    return D, ref
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("a_mn,b_mn", VARIANTS)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_exact(M, N, K, a_mn, b_mn, pair):
+    D, ref = _run(a_mn, b_mn, pair, M, N, K)
+    assert torch.equal(D, ref), f"{int((D != ref).sum())} of {D.numel()} entries differ"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_gemm_16bit_output(dtype):
+    D, ref = _run(0, 0, 0, 300, 264, 136, dtype=dtype, out_dtype=dtype)
+    assert torch.equal(D.float(), ref.to(dtype).float())
