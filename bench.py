@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""FLCE forward+backward throughput on B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5|small]
+
+One step = one fused-linear-cross-entropy forward + backward over one batch of synthetic tokens
+(default workload: the Llama-3-8B head, N=32768 tokens, H=4096, V=128256, bf16, 5 % ignored targets,
+mean reduction, returning grad_input and grad_weight).  With N GPUs (launched under torchrun, one rank
+per GPU) every rank processes its own N tokens against a replicated weight and the weight gradient is
+all-reduced over NCCL inside the step: weak scaling, `value` is the sum over ranks.
+
+Rank 0 prints one JSON line (see README / DESIGN for the keys).  `--impl reference` times the torch
+Linear+CrossEntropy ground truth of the reference's tests on the host cores instead.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "liger-kernel_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: N, H, V, ignored fraction, kwargs
+    "small": dict(N=4096, H=1024, V=32000, ign=0.10, kw=dict()),
+    "c2": dict(N=32768, H=4096, V=128256, ign=0.05, kw=dict()),
+    "c3": dict(N=32768, H=3584, V=152064, ign=0.20, kw=dict(label_smoothing=0.1, lse_square_scale=1e-4, return_z_loss=True)),
+    "c4": dict(N=16384, H=3584, V=256000, ign=0.05, kw=dict(softcap=30.0, reduction="sum")),
+    "c5": dict(N=65536, H=8192, V=128256, ign=0.05, kw=dict()),
+}
+NAMES = {
+    "small": "FLCE small head N=4096 H=1024 V=32000 bf16",
+    "c2": "Llama-3-8B LM head FLCE bf16: N=32768 (B=8,T=4096) H=4096 V=128256, 5% ignored, mean, fwd+bwd",
+    "c3": "Qwen2.5-7B-style head FLCE bf16: N=32768 H=3584 V=152064, label_smoothing 0.1, z-loss 1e-4, 20% ignored",
+    "c4": "Gemma-2-9B-style head FLCE bf16: N=16384 H=3584 V=256000, softcap 30, sum, 5% ignored",
+    "c5": "Llama-3-70B LM head FLCE bf16: N=65536 H=8192 V=128256, 5% ignored, mean",
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(burst=float(d["bf16_tflops"]), sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def make_inputs(spec, device, seed):
+    g = torch.Generator(device=device).manual_seed(seed)
+    N, H, V = spec["N"], spec["H"], spec["V"]
+    x = torch.randn(N, H, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    w = (torch.randn(V, H, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    t = torch.randint(0, V, (N,), generator=g, device=device)
+    drop = torch.rand(N, generator=g, device=device) < spec["ign"]
+    t = torch.where(drop, torch.full_like(t, -100), t)
+    return x, w, t
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.out.close()
+
+    def summary(self):
+        res = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.path is None or not os.path.exists(self.path):
+            return res
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[3:7]):
+                    if val.lower() == "active":
+                        reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            busy = [v for v in sm if v > 0.5 * max(sm)] or sm
+            res.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return res
+
+
+def cpu_reference_rate(spec, seconds_budget, rows_per_chunk=256, max_rows=1024, seed=99):
+    """tokens/s of the torch Linear+CrossEntropy ground truth (fp32, autograd) on the host cores, measured
+    on the first rows of the workload with the full H and V."""
+    from oracle.flce_oracle import torch_linear_ce_reference
+
+    g = torch.Generator().manual_seed(seed)
+    H, V = spec["H"], spec["V"]
+    w = torch.randn(V, H, generator=g) * 0.02
+    kw = {k: v for k, v in spec["kw"].items() if k in ("label_smoothing", "lse_square_scale", "softcap", "reduction")}
+    done, t0 = 0, time.perf_counter()
+    while done < max_rows:
+        x = torch.randn(rows_per_chunk, H, generator=g)
+        t = torch.randint(0, V, (rows_per_chunk,), generator=g)
+        t[::20] = -100
+        torch_linear_ce_reference(x, w, t, **kw)
+        done += rows_per_chunk
+        if time.perf_counter() - t0 > seconds_budget:
+            break
+    dt = time.perf_counter() - t0
+    return done / dt, done, dt
+
+
+def run_reference(args, spec, rank, world):
+    if rank != 0:
+        return
+    rows = 256
+    for _ in range(args.warmup):
+        cpu_reference_rate(spec, 1e9, rows, rows)
+    t0 = time.perf_counter()
+    total = 0
+    for _ in range(args.steps):
+        _, done, _ = cpu_reference_rate(spec, 1e9, rows, rows)
+        total += done
+    dt = time.perf_counter() - t0
+    value = total / dt
+    cores = torch.get_num_threads()
+    sample = f"{rows} rows per step with the full H={spec['H']} and V={spec['V']} (fp32 torch Linear+CrossEntropy, autograd backward)"
+    print(json.dumps({
+        "impl": "reference", "metric": "flce_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": NAMES[args.workload], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "host_cpus": os.cpu_count(),
+    }))
+
+
+def run_ours(args, spec, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from liger_kernel_b200 import _lib
+    from liger_kernel_b200.transformers.functional import liger_fused_linear_cross_entropy
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if args.cta_pair is not None:
+        _lib.set_option("cta_pair", args.cta_pair)
+    peaks = load_peaks()
+    x, w, t = make_inputs(spec, device, 1234 + rank)
+    if world > 1:
+        dist.broadcast(w, 0)
+    w.requires_grad_(True)
+    x_host = x.cpu().pin_memory()
+    t_host = t.cpu().pin_memory()
+    x_dev = torch.empty_like(x)
+    t_dev = torch.empty_like(t)
+    kw = dict(spec["kw"])
+    N, H, V = spec["N"], spec["H"], spec["V"]
+
+    def step(xin, tin):
+        xin = xin.detach().requires_grad_(True)
+        w.grad = None
+        out = liger_fused_linear_cross_entropy(xin, w, tin, **kw)
+        loss = out if torch.is_tensor(out) else out.loss
+        loss.backward()
+        if world > 1:
+            dist.all_reduce(w.grad)
+        return loss, xin.grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        v = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    for _ in range(args.warmup):
+        step(x, t)
+    torch.cuda.reset_peak_memory_stats()
+    launches0 = _lib.lib.flce_b200_kernel_launches()
+    _lib.profile_enable(True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step(x, t)
+        e1.record()
+        barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    prof = _lib.profile_read(reset=True)
+    _lib.profile_enable(False)
+    launches = _lib.lib.flce_b200_kernel_launches() - launches0
+    peak_mem = torch.cuda.max_memory_allocated()
+    clock_info = clocks.summary()
+
+    # end to end: host buffers in, loss out, every step
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        t_dev.copy_(t_host, non_blocking=True)
+        loss, _ = step(x_dev, t_dev)
+        return float(loss.item())
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e3.record()
+    barrier()
+    ms_e2e = max_over_ranks(e2.elapsed_time(e3))
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_step = ms_total / args.steps
+    tokens = N * world
+    value = tokens / (ms_step * 1e-3)
+    flops_step = 8.0 * N * H * V  # per rank
+    tflops = flops_step / (ms_step * 1e-3) / 1e12
+    kind_flops = 2.0 * N * H * V * args.steps  # algorithmic flops of each kernel kind over the timed region
+    dom = max(("stats", "dz", "dw", "dx"), key=lambda k: prof[k][0])
+    dom_ms, dom_launches = prof[dom]
+    achieved = kind_flops / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+    per_kind = {k: {"ms_per_step": prof[k][0] / args.steps, "launches_per_step": prof[k][1] / args.steps,
+                    "tflops": (kind_flops / (prof[k][0] * 1e-3) / 1e12) if prof[k][0] > 0 else None}
+                for k in ("stats", "dz", "dw", "dx")}
+    result = {
+        "metric": "flce_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": NAMES[args.workload], "tokens_per_gpu": N, "hidden": H, "vocab": V,
+                   "parallelism": "single GPU" if world == 1 else f"token-sharded x{world}, NCCL all-reduce of grad_weight",
+                   "l2_policy": "inputs larger than L2 (weight alone is %.2f GB)" % (V * H * 2 / 1e9),
+                   "cta_pair": args.cta_pair},
+        "tflops_per_gpu": tflops,
+        "frac_of_bf16_peak": {"burst": tflops / peaks["burst"], "sustained": tflops / peaks["sustained"], "peaks": peaks["source"]},
+        "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["sustained"], "frac_of_burst": achieved / peaks["burst"],
+                     "launches": dom_launches, "avg_launch_ms": dom_ms / max(1, dom_launches),
+                     "peak_kind": f"sustained bf16 GEMM, {peaks['source']}", "traffic": None},
+        "kernels": per_kind,
+        "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": x_host.numel() * 2 + t_host.numel() * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+        "peak_mem_gb": peak_mem / 1e9,
+        "clocks": {"sm_mhz": clock_info["sm_mhz"], "sm_max_mhz": clock_info["sm_max_mhz"], "reasons": clock_info["reasons"],
+                   "samples": clock_info["samples"]},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        rate, rows, secs = cpu_reference_rate(spec, seconds_budget=12.0)
+        result["cpu_baseline"] = {
+            "value": rate, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"first {rows} rows with the full H and V, fp32 torch Linear+CrossEntropy with autograd, {secs:.1f} s",
+        }
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--cta-pair", type=int, default=None, dest="cta_pair")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    spec = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, spec, rank, world)
+    else:
+        run_ours(args, spec, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

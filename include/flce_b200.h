@@ -142,6 +142,19 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
  * since the last call (FLCE_ERR_DEVICE_TIMEOUT) and clears the record.  For tests and debugging. */
 int flce_b200_check_device_status(void* stream);
 
+/* Per-kernel timing for benchmarks; no counterpart in the reference (its benchmarks time whole calls,
+ * benchmark/scripts/utils.py:115-172).  While enabled, each tensor-core launch is bracketed by CUDA
+ * events on the caller's stream.  profile_read waits for the recorded events and returns, per kernel
+ * kind (0 forward statistics sweep, 1 logit-gradient sweep, 2 grad_weight GEMM, 3 grad_input GEMM,
+ * 4 plain GEMM), the summed device time in milliseconds and the number of launches; both arrays have
+ * FLCE_NUM_KERNEL_KINDS entries. */
+#define FLCE_NUM_KERNEL_KINDS 5
+int flce_b200_profile_enable(int on);
+int flce_b200_profile_read(double* ms_by_kind, int64_t* launches_by_kind, int reset);
+
+/* Kernels launched by this library in this process so far (host-side counter). */
+int64_t flce_b200_kernel_launches(void);
+
 /* Tunables (process-wide): raster group (m-tiles kept L2-resident per sweep), CTA pairing on/off. */
 int flce_b200_set_option(const char* name, int64_t value);
 

@@ -34,6 +34,40 @@ static int fail(int code, const char* fmt, ...) {
 static long long g_raster_bytes = 32ll << 20;  // bytes of A tiles kept hot per raster group
 static int g_cta_pair = 0;                      // use CTA pairs (cta_group::2) for the FLCE GEMMs
 
+// ------------------------------------------------------------------ optional per-kernel timing
+// When enabled, every tensor-core launch is bracketed by a pair of CUDA events on the caller's stream;
+// flce_b200_profile_read sums the elapsed times per kernel kind.  Off by default (no events, no cost).
+enum KernelKind : int { kKindStats = 0, kKindDz = 1, kKindDw = 2, kKindDx = 3, kKindOther = 4, kNumKinds = 5 };
+struct ProfileSlot {
+  cudaEvent_t start, stop;
+  int kind;
+};
+constexpr int kMaxProfileSlots = 8192;
+static bool g_profile_on = false;
+static ProfileSlot g_profile[kMaxProfileSlots];
+static int g_profile_created = 0;  // events exist for slots [0, created)
+static int g_profile_used = 0;
+static long long g_kernel_launches = 0;
+static std::mutex g_profile_mutex;
+
+static ProfileSlot* profile_begin(int kind, cudaStream_t stream) {
+  if (!g_profile_on) return nullptr;
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  if (g_profile_used >= kMaxProfileSlots) return nullptr;
+  if (g_profile_used >= g_profile_created) {
+    ProfileSlot& fresh = g_profile[g_profile_created];
+    if (cudaEventCreate(&fresh.start) != cudaSuccess || cudaEventCreate(&fresh.stop) != cudaSuccess) return nullptr;
+    ++g_profile_created;
+  }
+  ProfileSlot* slot = &g_profile[g_profile_used++];
+  slot->kind = kind;
+  cudaEventRecord(slot->start, stream);
+  return slot;
+}
+static void profile_end(ProfileSlot* slot, cudaStream_t stream) {
+  if (slot != nullptr) cudaEventRecord(slot->stop, stream);
+}
+
 // ------------------------------------------------------------------ per-device state
 struct DeviceState {
   bool ready = false;
@@ -119,7 +153,7 @@ static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 template <int kCtas, int kAMajor, int kBMajor, class Epi>
-static int launch_gemm_impl(const DeviceState& dev, const Operand& a, const Operand& b, int dtype, long long M,
+static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, const Operand& b, int dtype, long long M,
                             long long N, long long K, long long raster_row_bytes, bool n_fastest,
                             const typename Epi::Params& ep, cudaStream_t stream) {
   using Cfg = StageCfg<kCtas>;
@@ -164,20 +198,24 @@ static int launch_gemm_impl(const DeviceState& dev, const Operand& a, const Oper
   cfg.attrs = attrs;
   cfg.numAttrs = 1;
   const int fmt = (dtype == FLCE_BF16) ? 1 : 0;
-  FLCE_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, shape, fmt, ep, dev.status));
+  ProfileSlot* slot = profile_begin(kind, stream);
+  const cudaError_t launched = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, shape, fmt, ep, dev.status);
+  profile_end(slot, stream);
+  if (launched != cudaSuccess) return fail(FLCE_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(launched));
+  ++g_kernel_launches;
   return FLCE_OK;
 }
 
 template <int kAMajor, int kBMajor, class Epi>
-static int launch_gemm(const DeviceState& dev, bool pair, const Operand& a, const Operand& b, int dtype, long long M,
+static int launch_gemm(const DeviceState& dev, int kind, bool pair, const Operand& a, const Operand& b, int dtype, long long M,
                        long long N, long long K, long long raster_row_bytes, bool n_fastest,
                        const typename Epi::Params& ep, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "empty GEMM %lld x %lld x %lld", M, N, K);
   if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "GEMM extent does not fit 32 bits");
   if (pair)
-    return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream);
-  return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream);
+    return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream);
+  return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream);
 }
 
 // ------------------------------------------------------------------ small kernels
@@ -521,6 +559,7 @@ int flce_b200_count(const flce_problem_t* p, float* norm, void* stream) {
       reinterpret_cast<const long long*>(p->target), p->n_rows, p->ignore_index, p->ce_weight, p->vocab,
       p->vocab_offset, static_cast<float>(p->vocab_total), norm);
   FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   return FLCE_OK;
 }
 
@@ -558,13 +597,14 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
   FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
   Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
   Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
-  rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, g_cta_pair != 0, a, b, p->dtype, p->n_rows, p->vocab, p->hidden,
+  rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, kKindStats, g_cta_pair != 0, a, b, p->dtype, p->n_rows, p->vocab, p->hidden,
                                                     static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
   if (rc != FLCE_OK) return rc;
   const int threads = 256;
   merge_partials_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
       static_cast<int>(p->n_rows), plan.n_tiles, ep.pmax, ep.psum, ep.plogit_sum, ep.pamax_val, ep.pamax_idx, rowstats);
   FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   return FLCE_OK;
 }
 
@@ -583,10 +623,12 @@ int flce_b200_forward_finalize(const flce_problem_t* p, const float* rowstats, c
       norm, out->lse, out->target_prob, out->loss_rows, out->z_loss_rows, out->correct_rows,
       reinterpret_cast<long long*>(out->predicted_tokens));
   FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   if (out->scalars != nullptr) {
     reduce_rows_kernel<<<1, kRedThreads, 0, stream>>>(static_cast<int>(p->n_rows), out->loss_rows, out->z_loss_rows,
                                                      out->correct_rows, norm, out->scalars);
     FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   }
   return FLCE_OK;
 }
@@ -633,6 +675,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       static_cast<int>(p->n_rows), row_math(p), reinterpret_cast<const long long*>(p->target), p->ce_weight, args->lse,
       args->target_prob, args->norm, args->grad_output, args->grad_output_per_row, c1, c2, c3);
   FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
 
   const bool pair = g_cta_pair != 0;
   const int esize_out = grads_fp32 ? 4 : 2;
@@ -660,7 +703,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       ep.out_fmt = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
       Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
       Operand b{w_slab, cols, p->hidden, p->ld_w, 0};
-      rc = launch_gemm<kMajorK, kMajorK, DzEpilogue>(*dev, pair, a, b, p->dtype, p->n_rows, cols, p->hidden,
+      rc = launch_gemm<kMajorK, kMajorK, DzEpilogue>(*dev, kKindDz, pair, a, b, p->dtype, p->n_rows, cols, p->hidden,
                                                      static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
       if (rc != FLCE_OK) return rc;
     }
@@ -677,7 +720,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       ep.out_fmt = grads_fp32 ? kOutFp32 : (p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
       Operand a{dz, cols, p->n_rows, plan.ld_dz, 1};
       Operand b{p->x, p->hidden, p->n_rows, p->ld_x, 1};
-      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, pair, a, b, p->dtype, cols, p->hidden, p->n_rows, 0, true,
+      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, cols, p->hidden, p->n_rows, 0, true,
                                                           ep, stream);
       if (rc != FLCE_OK) return rc;
     }
@@ -697,7 +740,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       ep.out_fmt = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
       Operand a{dz, p->n_rows, cols, plan.ld_dz, 0};
       Operand b{w_slab, p->hidden, cols, p->ld_w, 1};
-      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, pair, a, b, p->dtype, p->n_rows, p->hidden, cols, 0, true,
+      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, p->n_rows, p->hidden, cols, 0, true,
                                                          ep, stream);
       if (rc != FLCE_OK) return rc;
     }
@@ -706,6 +749,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
           dz, plan.ld_dz, static_cast<int>(p->n_rows), static_cast<int>(cols), p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16,
           args->grad_bias + v0);
       FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
     }
   }
   return FLCE_OK;
@@ -736,13 +780,40 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
   const bool pair = cta_pair != 0;
   const long long row_bytes = static_cast<long long>(kBlockM) * k * 2;
   if (!a_mn_major && !b_mn_major)
-    return launch_gemm<kMajorK, kMajorK, StoreEpilogue>(*dev, pair, oa, ob, ab_dtype, m, n, k, row_bytes, false, ep, stream);
+    return launch_gemm<kMajorK, kMajorK, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, false, ep, stream);
   if (a_mn_major && b_mn_major)
-    return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
+    return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
   if (!a_mn_major && b_mn_major)
-    return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
+    return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
   return fail(FLCE_ERR_UNSUPPORTED, "A MN-major with B K-major is not instantiated");
 }
+
+int flce_b200_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  g_profile_on = on != 0;
+  g_profile_used = 0;
+  return FLCE_OK;
+}
+
+int flce_b200_profile_read(double* ms_by_kind, int64_t* launches_by_kind, int reset) {
+  if (ms_by_kind == nullptr || launches_by_kind == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL output");
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  for (int k = 0; k < kNumKinds; ++k) {
+    ms_by_kind[k] = 0.0;
+    launches_by_kind[k] = 0;
+  }
+  for (int i = 0; i < g_profile_used; ++i) {
+    FLCE_CUDA(cudaEventSynchronize(g_profile[i].stop));
+    float ms = 0.f;
+    FLCE_CUDA(cudaEventElapsedTime(&ms, g_profile[i].start, g_profile[i].stop));
+    ms_by_kind[g_profile[i].kind] += ms;
+    launches_by_kind[g_profile[i].kind] += 1;
+  }
+  if (reset) g_profile_used = 0;
+  return FLCE_OK;
+}
+
+int64_t flce_b200_kernel_launches(void) { return g_kernel_launches; }
 
 int flce_b200_check_device_status(void* stream) {
   DeviceState* dev;

@@ -23,6 +23,9 @@ EXPORTS = (
     "flce_b200_backward",
     "flce_b200_gemm",
     "flce_b200_check_device_status",
+    "flce_b200_profile_enable",
+    "flce_b200_profile_read",
+    "flce_b200_kernel_launches",
     "flce_b200_set_option",
     "flce_b200_status_string",
     "flce_b200_last_error",
@@ -79,6 +82,12 @@ def _load():
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]
     lib.flce_b200_check_device_status.argtypes = [vp]
     lib.flce_b200_set_option.argtypes = [C.c_char_p, i64]
+    lib.flce_b200_profile_enable.argtypes = [C.c_int]
+    lib.flce_b200_profile_enable.restype = C.c_int
+    lib.flce_b200_profile_read.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_int64), C.c_int]
+    lib.flce_b200_profile_read.restype = C.c_int
+    lib.flce_b200_kernel_launches.argtypes = []
+    lib.flce_b200_kernel_launches.restype = C.c_int64
     for name in ("flce_b200_count", "flce_b200_forward_stats", "flce_b200_forward_finalize", "flce_b200_forward",
                  "flce_b200_backward", "flce_b200_gemm", "flce_b200_check_device_status", "flce_b200_set_option"):
         getattr(lib, name).restype = C.c_int
@@ -100,6 +109,21 @@ def check(status):
         raise FlceError(
             f"libflce_b200: {lib.flce_b200_status_string(status).decode()}: {lib.flce_b200_last_error().decode()}"
         )
+
+
+KERNEL_KINDS = ("stats", "dz", "dw", "dx", "gemm")
+
+
+def profile_enable(on=True):
+    check(lib.flce_b200_profile_enable(int(on)))
+
+
+def profile_read(reset=True):
+    """{kind: (milliseconds, launches)} of the tensor-core kernels recorded since the last reset."""
+    ms = (C.c_double * len(KERNEL_KINDS))()
+    n = (C.c_int64 * len(KERNEL_KINDS))()
+    check(lib.flce_b200_profile_read(ms, n, int(reset)))
+    return {k: (ms[i], n[i]) for i, k in enumerate(KERNEL_KINDS)}
 
 
 def set_option(name, value):
