@@ -31,6 +31,7 @@ import torch  # noqa: E402
 WORKLOADS = {
     # name: N, H, V, ignored fraction, kwargs
     "small": dict(N=4096, H=1024, V=32000, ign=0.10, kw=dict()),
+    "profile": dict(N=8192, H=4096, V=32768, ign=0.05, kw=dict()),  # small case for ncu captures (W = 268 MB > L2)
     "c2": dict(N=32768, H=4096, V=128256, ign=0.05, kw=dict()),
     "c3": dict(N=32768, H=3584, V=152064, ign=0.20, kw=dict(label_smoothing=0.1, lse_square_scale=1e-4, return_z_loss=True)),
     "c4": dict(N=16384, H=3584, V=256000, ign=0.05, kw=dict(softcap=30.0, reduction="sum")),
@@ -38,6 +39,7 @@ WORKLOADS = {
 }
 NAMES = {
     "small": "FLCE small head N=4096 H=1024 V=32000 bf16",
+    "profile": "FLCE profiling case N=8192 H=4096 V=32768 bf16 (one vocabulary slab)",
     "c2": "Llama-3-8B LM head FLCE bf16: N=32768 (B=8,T=4096) H=4096 V=128256, 5% ignored, mean, fwd+bwd",
     "c3": "Qwen2.5-7B-style head FLCE bf16: N=32768 H=3584 V=152064, label_smoothing 0.1, z-loss 1e-4, 20% ignored",
     "c4": "Gemma-2-9B-style head FLCE bf16: N=16384 H=3584 V=256000, softcap 30, sum, 5% ignored",
@@ -185,6 +187,8 @@ def run_ours(args, spec, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=device)
     if args.cta_pair is not None:
         _lib.set_option("cta_pair", args.cta_pair)
+    if args.raster_mb is not None:
+        _lib.set_option("raster_group_bytes", args.raster_mb << 20)
     peaks = load_peaks()
     x, w, t = make_inputs(spec, device, 1234 + rank)
     if world > 1:
@@ -280,7 +284,7 @@ def run_ours(args, spec, rank, world, local_rank):
         "config": {"workload": NAMES[args.workload], "tokens_per_gpu": N, "hidden": H, "vocab": V,
                    "parallelism": "single GPU" if world == 1 else f"token-sharded x{world}, NCCL all-reduce of grad_weight",
                    "l2_policy": "inputs larger than L2 (weight alone is %.2f GB)" % (V * H * 2 / 1e9),
-                   "cta_pair": args.cta_pair},
+                   "cta_pair": args.cta_pair, "raster_mb": args.raster_mb},
         "tflops_per_gpu": tflops,
         "frac_of_bf16_peak": {"burst": tflops / peaks["burst"], "sustained": tflops / peaks["sustained"], "peaks": peaks["source"]},
         "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
@@ -314,6 +318,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cta-pair", type=int, default=None, dest="cta_pair")
+    ap.add_argument("--raster-mb", type=int, default=None, dest="raster_mb")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -55,12 +55,17 @@ typedef struct flce_problem {
   float lse_square_scale;
   float softcap;             /* 0 = off                                                       */
   int32_t use_token_scaling; /* scale each row's loss and gradient by its detached p(target)  */
+  int32_t flags;             /* FLCE_FLAG_* bits                                              */
   const void* x;             /* [n_rows, ld_x]                                                */
   const void* w;             /* [vocab, ld_w]                                                 */
   const int64_t* target;     /* [n_rows] global class ids or ignore_index                     */
   const float* bias;         /* [vocab] fp32 or NULL                                          */
   const float* ce_weight;    /* [vocab] fp32 class weights or NULL                            */
 } flce_problem_t;
+
+/* flce_problem_t.flags: track the arg-max of every row in the forward sweep (needed for token accuracy
+ * and predicted tokens; rowstats planes 4 and 5 are only meaningful with it). */
+#define FLCE_FLAG_ARGMAX 1
 
 /* Number of fp32 planes in a row-statistics buffer ([FLCE_ROWSTAT_PLANES][n_rows]):
  * 0 max, 1 sum-exp relative to max, 2 target logit (0 unless this rank owns the target),

@@ -22,14 +22,50 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// soft-capped logit and tanh (needed again by the chain rule)
-__device__ __forceinline__ float softcap_apply(float z, float cap, float inv_cap, float& th) {
-  th = tanhf(z * inv_cap);
-  return cap * th;
+// 32 fp32 values -> 32 16-bit values (64 bytes) at dst; one format branch for the whole row segment
+__device__ __forceinline__ void store32_16bit(uint4* dst, const float (&g)[32], int fmt) {
+  if (fmt == kOutBf16) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(g[8 * q + 0], g[8 * q + 1]);
+      __nv_bfloat162 h1 = __floats2bfloat162_rn(g[8 * q + 2], g[8 * q + 3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(g[8 * q + 4], g[8 * q + 5]);
+      __nv_bfloat162 h3 = __floats2bfloat162_rn(g[8 * q + 6], g[8 * q + 7]);
+      dst[q] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                          *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      __half2 h0 = __floats2half2_rn(g[8 * q + 0], g[8 * q + 1]);
+      __half2 h1 = __floats2half2_rn(g[8 * q + 2], g[8 * q + 3]);
+      __half2 h2 = __floats2half2_rn(g[8 * q + 4], g[8 * q + 5]);
+      __half2 h3 = __floats2half2_rn(g[8 * q + 6], g[8 * q + 7]);
+      dst[q] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                          *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+    }
+  }
+}
+
+// tanh without branches: exp-based form away from zero, odd polynomial near zero (where the
+// exp form cancels).  Absolute error stays below ~2e-7, so a soft-cap of 30 moves a logit by < 1e-5.
+__device__ __forceinline__ float tanh_accurate(float x) {
+  const float t = ex2_approx(x * (2.f * kLog2e));
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + t));
+  const float big = fmaf(-2.f, r, 1.f);
+  const float x2 = x * x;
+  float poly = fmaf(x2, 62.f / 2835.f, -17.f / 315.f);
+  poly = fmaf(x2, poly, 2.f / 15.f);
+  poly = fmaf(x2, poly, -1.f / 3.f);
+  poly = fmaf(x2 * x, poly, x);
+  return (fabsf(x) < 0.3f) ? poly : big;
 }
 
 // =====================================================================================
 // Sweep 1: logits tile -> per-(row, tile) softmax statistics.  Nothing of size N x V is stored.
+// Feature tests are hoisted out of the per-element loops: each optional stage is one uniform
+// branch around a fully unrolled, branch-free pass over the 32 values.
 // =====================================================================================
 struct StatsEpilogue {
   struct Params {
@@ -70,20 +106,31 @@ struct StatsEpilogue {
 
   __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
     float s[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(acc[j]);
     const bool ragged = col + 32 > p.n_cols;
+    if (p.bias != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float z = __uint_as_float(acc[j]);
-      if (p.bias != nullptr && col + j < p.n_cols) z += __ldg(p.bias + col + j);
-      if (p.softcap > 0.f) {
-        float th;
-        z = softcap_apply(z, p.softcap, p.inv_softcap, th);
-      }
-      s[j] = (ragged && col + j >= p.n_cols) ? -INFINITY : z;
+      for (int j = 0; j < 32; ++j) s[j] += __ldg(p.bias + min(col + j, p.n_cols - 1));
     }
-    float cm = s[0];
+    if (p.softcap > 0.f) {
 #pragma unroll
-    for (int j = 1; j < 32; ++j) cm = fmaxf(cm, s[j]);
+      for (int j = 0; j < 32; ++j) s[j] = p.softcap * tanh_accurate(s[j] * p.inv_softcap);
+    }
+    if (ragged) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) s[j] = (col + j < p.n_cols) ? s[j] : -INFINITY;
+    }
+    // chunk maximum: four independent chains
+    float c0 = fmaxf(s[0], s[4]), c1 = fmaxf(s[1], s[5]), c2 = fmaxf(s[2], s[6]), c3 = fmaxf(s[3], s[7]);
+#pragma unroll
+    for (int j = 8; j < 32; j += 4) {
+      c0 = fmaxf(c0, s[j]);
+      c1 = fmaxf(c1, s[j + 1]);
+      c2 = fmaxf(c2, s[j + 2]);
+      c3 = fmaxf(c3, s[j + 3]);
+    }
+    const float cm = fmaxf(fmaxf(c0, c1), fmaxf(c2, c3));
     if (p.pamax_val != nullptr && cm > best) {  // strictly greater: ties keep the lowest index
       int idx = 31;
 #pragma unroll
@@ -92,22 +139,41 @@ struct StatsEpilogue {
       best_idx = col + idx;
     }
     if (p.plogit_sum != nullptr) {
-      float acc_s = 0.f;
+      float a0 = 0.f, a1 = 0.f;
+      if (p.col_weight != nullptr) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        if (!ragged || col + j < p.n_cols) {
-          const float wj = (p.col_weight != nullptr) ? __ldg(p.col_weight + col + j) : 1.f;
-          acc_s = fmaf(s[j], wj, acc_s);
+        for (int j = 0; j < 32; j += 2) {
+          const float w0 = __ldg(p.col_weight + min(col + j, p.n_cols - 1));
+          const float w1 = __ldg(p.col_weight + min(col + j + 1, p.n_cols - 1));
+          a0 = fmaf((col + j < p.n_cols) ? s[j] : 0.f, w0, a0);
+          a1 = fmaf((col + j + 1 < p.n_cols) ? s[j + 1] : 0.f, w1, a1);
+        }
+      } else if (ragged) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          a0 += (col + j < p.n_cols) ? s[j] : 0.f;
+          a1 += (col + j + 1 < p.n_cols) ? s[j + 1] : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          a0 += s[j];
+          a1 += s[j + 1];
         }
       }
-      ssum += acc_s;
+      ssum += a0 + a1;
     }
     const float m_new = fmaxf(m, cm);
     const float ml2 = m_new * kLog2e;
-    float part = 0.f;
+    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) part += ex2_approx(fmaf(s[j], kLog2e, -ml2));
-    d = d * ex2_approx((m - m_new) * kLog2e) + part;
+    for (int j = 0; j < 32; j += 4) {
+      p0 += ex2_approx(fmaf(s[j], kLog2e, -ml2));
+      p1 += ex2_approx(fmaf(s[j + 1], kLog2e, -ml2));
+      p2 += ex2_approx(fmaf(s[j + 2], kLog2e, -ml2));
+      p3 += ex2_approx(fmaf(s[j + 3], kLog2e, -ml2));
+    }
+    d = fmaf(d, ex2_approx((m - m_new) * kLog2e), (p0 + p1) + (p2 + p3));
     m = m_new;
     const unsigned rel = static_cast<unsigned>(tgt_local - col);
     if (rel < 32u) {
@@ -178,35 +244,61 @@ struct DzEpilogue {
   __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
     if (!row_ok) return;
     float g[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(acc[j]);
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] += __ldg(p.bias + min(col + j, p.n_cols - 1));
+    }
+    const bool capped = p.softcap > 0.f;
+    if (capped) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = p.softcap * tanh_accurate(g[j] * p.inv_softcap);
+    }
+    // true-class correction, formed in fp32 before rounding: c3, times the soft-cap chain factor at the target
     const unsigned rel = static_cast<unsigned>(tgt_local - col);
+    float corr = c3;
+    if (rel < 32u && capped) {
+      float sy = 0.f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float z = __uint_as_float(acc[j]);
-      const bool in = col + j < p.n_cols;
-      if (p.bias != nullptr && in) z += __ldg(p.bias + col + j);
-      float chain = 1.f;
-      if (p.softcap > 0.f) {
-        float th;
-        z = softcap_apply(z, p.softcap, p.inv_softcap, th);
-        chain = 1.f - th * th;
+      for (int j = 0; j < 32; ++j) sy = (rel == static_cast<unsigned>(j)) ? g[j] : sy;
+      const float thy = sy * p.inv_softcap;
+      corr = c3 * fmaf(-thy, thy, 1.f);
+    }
+    // g holds the soft-capped logits s; turn them into gradients in place
+    if (p.col_weight != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float wj = __ldg(p.col_weight + min(col + j, p.n_cols - 1));
+        const float s = g[j];
+        float v = fmaf(ex2_approx(fmaf(s, kLog2e, -l2)), c1, -c2 * wj);
+        if (capped) {
+          const float th = s * p.inv_softcap;
+          v *= fmaf(-th, th, 1.f);
+        }
+        g[j] = v;
       }
-      const float prob = ex2_approx(fmaf(z, kLog2e, -l2));
-      const float wj = (p.col_weight != nullptr && in) ? __ldg(p.col_weight + col + j) : 1.f;
-      float v = fmaf(prob, c1, -c2 * wj);
-      if (rel == static_cast<unsigned>(j)) v -= c3;
-      v *= chain;
-      g[j] = in ? v : 0.f;
-    }
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.dz) + static_cast<size_t>(row) * p.ld_dz + col);
+    } else if (capped) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint4 o;
-      o.x = pack2(g[8 * q + 0], g[8 * q + 1], p.out_fmt);
-      o.y = pack2(g[8 * q + 2], g[8 * q + 3], p.out_fmt);
-      o.z = pack2(g[8 * q + 4], g[8 * q + 5], p.out_fmt);
-      o.w = pack2(g[8 * q + 6], g[8 * q + 7], p.out_fmt);
-      dst[q] = o;
+      for (int j = 0; j < 32; ++j) {
+        const float s = g[j];
+        const float th = s * p.inv_softcap;
+        g[j] = fmaf(ex2_approx(fmaf(s, kLog2e, -l2)), c1, -c2) * fmaf(-th, th, 1.f);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = fmaf(ex2_approx(fmaf(g[j], kLog2e, -l2)), c1, -c2);
     }
+    if (rel < 32u) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = (rel == static_cast<unsigned>(j)) ? g[j] - corr : g[j];
+    }
+    if (col + 32 > p.n_cols) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = (col + j < p.n_cols) ? g[j] : 0.f;
+    }
+    store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.dz) + static_cast<size_t>(row) * p.ld_dz + col), g,
+                  p.out_fmt);
   }
 
   __device__ __forceinline__ void end(const Params&) {}
@@ -268,6 +360,9 @@ struct StoreEpilogue {
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           if (col + 4 * q < p.n_cols) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else if (col + 32 <= p.n_cols) {
+        store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col),
+                      v, p.out_fmt);
       } else {
         uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
 #pragma unroll

@@ -32,7 +32,7 @@ static int fail(int code, const char* fmt, ...) {
 
 // ------------------------------------------------------------------ process-wide options
 static long long g_raster_bytes = 32ll << 20;  // bytes of A tiles kept hot per raster group
-static int g_cta_pair = 0;                      // use CTA pairs (cta_group::2) for the FLCE GEMMs
+static int g_cta_pair = 1;                      // use CTA pairs (cta_group::2) for the FLCE GEMMs
 
 // ------------------------------------------------------------------ optional per-kernel timing
 // When enabled, every tensor-core launch is bracketed by a pair of CUDA events on the caller's stream;
@@ -591,8 +591,9 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
   ep.pmax = reinterpret_cast<float*>(ws);
   ep.psum = reinterpret_cast<float*>(ws + plan.plane);
   ep.plogit_sum = need_sum ? reinterpret_cast<float*>(ws + 2 * plan.plane) : nullptr;
-  ep.pamax_val = reinterpret_cast<float*>(ws + 3 * plan.plane);
-  ep.pamax_idx = reinterpret_cast<int*>(ws + 4 * plan.plane);
+  const bool need_argmax = (p->flags & FLCE_FLAG_ARGMAX) != 0;
+  ep.pamax_val = need_argmax ? reinterpret_cast<float*>(ws + 3 * plan.plane) : nullptr;
+  ep.pamax_idx = need_argmax ? reinterpret_cast<int*>(ws + 4 * plan.plane) : nullptr;
   ep.target_logit = rowstats + 2 * static_cast<size_t>(p->n_rows);
   FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
   Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
@@ -814,6 +815,14 @@ int flce_b200_profile_read(double* ms_by_kind, int64_t* launches_by_kind, int re
 }
 
 int64_t flce_b200_kernel_launches(void) { return g_kernel_launches; }
+
+#ifdef FLCE_CLOCK_TRACE
+int flce_b200_debug_clock_trace(unsigned long long* out, int n_words) {
+  FLCE_CUDA(cudaDeviceSynchronize());
+  FLCE_CUDA(cudaMemcpyFromSymbol(out, g_clock_trace, sizeof(unsigned long long) * n_words));
+  return FLCE_OK;
+}
+#endif
 
 int flce_b200_check_device_status(void* stream) {
   DeviceState* dev;

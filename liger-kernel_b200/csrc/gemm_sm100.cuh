@@ -26,6 +26,21 @@ namespace flce {
 
 enum Major : int { kMajorK = 0, kMajorMN = 1 };
 
+// Optional cycle accounting for tuning (compile with -DFLCE_CLOCK_TRACE): per CTA, cycles the three roles
+// spend waiting on each barrier and cycles the epilogue is busy.  Off in the shipped library.
+#ifdef FLCE_CLOCK_TRACE
+__device__ unsigned long long g_clock_trace[1024 * 8];
+#define FLCE_TRACE_DECL(name) long long name = 0
+#define FLCE_TRACE_BEGIN(t) const long long t = clock64()
+#define FLCE_TRACE_ADD(acc, t) acc += clock64() - t
+#define FLCE_TRACE_STORE(slot, v) g_clock_trace[(blockIdx.x & 1023) * 8 + slot] = static_cast<unsigned long long>(v)
+#else
+#define FLCE_TRACE_DECL(name)
+#define FLCE_TRACE_BEGIN(t)
+#define FLCE_TRACE_ADD(acc, t)
+#define FLCE_TRACE_STORE(slot, v)
+#endif
+
 constexpr int kBlockM = 128;      // rows per CTA
 constexpr int kBlockN = 256;      // columns per tile
 constexpr int kBlockK = 64;       // two-byte elements per stage = one 128-byte swizzle row
@@ -141,13 +156,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      FLCE_TRACE_DECL(wait_empty);
+      FLCE_TRACE_BEGIN(t_kernel);
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
         int mt, nt;
         decode_tile(shape, tile, mt, nt);
         const int m0 = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM;
         const int n0 = nt * kBlockN + static_cast<int>(cta_rank) * (kBlockN / kCtas);
         for (int kb = 0; kb < shape.k_blocks; ++kb) {
+          FLCE_TRACE_BEGIN(t_w);
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, status, kDevTimeoutEmptyBarrier);
+          FLCE_TRACE_ADD(wait_empty, t_w);
           if (!ok) break;
           const uint32_t local_full = smem_u32(&full_bar[stage]);
           if (is_leader) mbar_arrive_expect_tx(local_full, Cfg::kStageBytes * kCtas);
@@ -179,6 +198,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      FLCE_TRACE_STORE(4, wait_empty);
+      FLCE_TRACE_DECL(total);
+      FLCE_TRACE_ADD(total, t_kernel);
+      FLCE_TRACE_STORE(5, total);
       if (!ok) {
         // unwinding: give copies already in flight a bounded chance to land before the CTA exits
         for (int s = 0; s < kStages; ++s)
@@ -202,15 +225,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t acc_phase[2] = {0, 0};
       int local_tile = 0;
       bool ok = true;
+      FLCE_TRACE_DECL(wait_full);
+      FLCE_TRACE_DECL(wait_tmem_empty);
       for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
         const int acc = local_tile & 1;
+        FLCE_TRACE_BEGIN(t_e);
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase[acc] ^ 1u, abort_flag, status, kDevTimeoutTmemEmpty);
+        FLCE_TRACE_ADD(wait_tmem_empty, t_e);
         if (!ok) break;
         acc_phase[acc] ^= 1u;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
         for (int kb = 0; kb < shape.k_blocks; ++kb) {
+          FLCE_TRACE_BEGIN(t_f);
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, status, kDevTimeoutFullBarrier);
+          FLCE_TRACE_ADD(wait_full, t_f);
           if (!ok) break;
           tcgen05_fence_after();
           const uint64_t desc_a = make_smem_desc(smem_u32(ring_a + stage * Cfg::kABytes), kLboA, kSbo);
@@ -228,6 +257,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if constexpr (kCtas == 1) umma_commit(smem_u32(&tmem_full_bar[acc]));
         else umma_commit_pair(smem_u32(&tmem_full_bar[acc]), 0x3);
       }
+      FLCE_TRACE_STORE(0, wait_full);
+      FLCE_TRACE_STORE(1, wait_tmem_empty);
+      FLCE_TRACE_STORE(6, local_tile);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -236,26 +268,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t acc_phase[2] = {0, 0};
     int local_tile = 0;
     bool ok = true;
+    FLCE_TRACE_DECL(wait_tmem_full);
+    FLCE_TRACE_DECL(busy);
     for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
       int mt, nt;
       decode_tile(shape, tile, mt, nt);
       const int acc = local_tile & 1;
       const int row = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM + row_in_tile;
       const int col0 = nt * kBlockN;
+      FLCE_TRACE_BEGIN(t_w);
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase[acc], abort_flag, status, kDevTimeoutTmemFull);
+      FLCE_TRACE_ADD(wait_tmem_full, t_w);
       if (!ok) break;
+      FLCE_TRACE_BEGIN(t_b);
       acc_phase[acc] ^= 1u;
       tcgen05_fence_after();
       Epi epi;
       epi.begin(ep, row, col0, nt, row < shape.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kBlockN);
+      // two register buffers: the load of the next 32 columns is in flight while the current ones are consumed
+      const int n_chunks = min(kBlockN / 32, (shape.N - col0 + 31) / 32);   // uniform across the CTA
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(taddr, va);
 #pragma unroll 1
-      for (int c = 0; c < kBlockN; c += 32) {
-        if (col0 + c >= shape.N) break;                   // whole chunk is padding (uniform across the CTA)
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + static_cast<uint32_t>(c), v);
+      for (int c = 0; c < n_chunks; c += 2) {
         tmem_ld_wait();
-        epi.chunk(ep, v, col0 + c);
+        tmem_ld_fence(va);
+        if (c + 1 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 1) * 32), vb);
+        epi.chunk(ep, va, col0 + c * 32);
+        if (c + 1 < n_chunks) {
+          tmem_ld_wait();
+          tmem_ld_fence(vb);
+          if (c + 2 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 2) * 32), va);
+          epi.chunk(ep, vb, col0 + (c + 1) * 32);
+        }
       }
       epi.end(ep);
       tcgen05_fence_before();
@@ -264,6 +310,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if constexpr (kCtas == 1) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
         else mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]), 0);
       }
+      FLCE_TRACE_ADD(busy, t_b);
+    }
+    if (threadIdx.x == 64) {
+      FLCE_TRACE_STORE(2, wait_tmem_full);
+      FLCE_TRACE_STORE(3, busy);
     }
   }
 

@@ -13,6 +13,7 @@ FLCE_BF16, FLCE_FP16, FLCE_FP32 = 0, 1, 2
 FLCE_MEAN, FLCE_SUM, FLCE_NONE = 0, 1, 2
 PHASE_FORWARD, PHASE_BACKWARD = 0, 1
 ROWSTAT_PLANES = 6
+FLAG_ARGMAX = 1
 
 EXPORTS = (
     "flce_b200_workspace_bytes",
@@ -41,7 +42,7 @@ class Problem(C.Structure):
         ("dtype", C.c_int32), ("reduction", C.c_int32),
         ("ignore_index", C.c_int64),
         ("label_smoothing", C.c_float), ("lse_square_scale", C.c_float), ("softcap", C.c_float),
-        ("use_token_scaling", C.c_int32),
+        ("use_token_scaling", C.c_int32), ("flags", C.c_int32),
         ("x", C.c_void_p), ("w", C.c_void_p), ("target", C.c_void_p),
         ("bias", C.c_void_p), ("ce_weight", C.c_void_p),
     ]

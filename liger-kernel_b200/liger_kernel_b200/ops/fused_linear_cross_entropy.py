@@ -57,7 +57,7 @@ class _Prepared:
     """Validated, device-resident operands of one FLCE call and the matching C struct."""
 
     def __init__(self, _input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing,
-                 reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0):
+                 reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=True):
         if _input.device.type != "cuda":
             raise RuntimeError("liger_kernel_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
         if _input.dim() != 2 or weight.dim() != 2 or _input.shape[1] != weight.shape[1]:
@@ -97,6 +97,7 @@ class _Prepared:
         p.lse_square_scale = float(lse_square_scale)
         p.softcap = 0.0 if softcap is None else float(softcap)
         p.use_token_scaling = int(bool(use_token_scaling))
+        p.flags = _lib.FLAG_ARGMAX if want_argmax else 0
         p.x, p.w, p.target = self.x.data_ptr(), self.w.data_ptr(), self.target.data_ptr()
         p.bias = None if self.bias is None else self.bias.data_ptr()
         p.ce_weight = None if self.ce_weight is None else self.ce_weight.data_ptr()
@@ -193,7 +194,7 @@ def fused_linear_cross_entropy_forward(
     assert isinstance(return_token_accuracy, bool), f"return_token_accuracy must be True or False. Got: {return_token_accuracy}"
     assert isinstance(return_predicted_tokens, bool), f"return_predicted_tokens must be True or False. Got: {return_predicted_tokens}"
     prep = _Prepared(_input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction,
-                     softcap, use_token_scaling)
+                     softcap, use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)
     out, norm, _rowstats = flce_forward_device(prep)
     if reduction == "none":
         loss = out["loss_rows"]

@@ -172,11 +172,11 @@ def test_cta_pair_matches_single_cta():
 
     x, w, t, _, _ = make_inputs(700, 256, 3000, torch.bfloat16, seed=12)
     a = run_cuda(x, w, t)
-    _lib.set_option("cta_pair", 1)
+    _lib.set_option("cta_pair", 0)
     try:
         b = run_cuda(x, w, t)
     finally:
-        _lib.set_option("cta_pair", 0)
+        _lib.set_option("cta_pair", 1)
     assert_close(b["loss"], a["loss"], 0, 1e-6, "loss")
     assert_close(b["grad_weight"].float(), a["grad_weight"].float(), 1e-6, 1e-2, "grad_weight")
     _check(b, oracle_for(x, w, t), torch.bfloat16, "mean", 700)
