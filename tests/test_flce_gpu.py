@@ -222,3 +222,57 @@ def test_error_paths():
     loss = Fn.apply(x.cuda(), w.cuda(), t.cuda())[0]
     with pytest.raises(RuntimeError, match="does not require grad"):
         loss.backward()
+
+
+def test_full_size_properties():
+    """Llama-3-8B head size (N=32768, H=4096, V=128256): size-independent properties plus sampled rows and
+    sampled vocabulary rows against fp64 math on the CPU."""
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Fn
+
+    if torch.cuda.get_device_properties(0).total_memory < 40e9:
+        pytest.skip("needs ~10 GB of device memory")
+    N, H, V = 32768, 4096, 128256
+    g = torch.Generator(device="cuda").manual_seed(2024)
+    x = torch.randn(N, H, generator=g, device="cuda").bfloat16()
+    w = (torch.randn(V, H, generator=g, device="cuda") * 0.02).bfloat16()
+    t = torch.randint(0, V, (N,), generator=g, device="cuda")
+    t[torch.rand(N, generator=g, device="cuda") < 0.05] = -100
+    xd, wd = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    loss = Fn.apply(xd, wd, t)[0]
+    loss.backward()
+    rows = Fn.apply(x, w, t, None, None, -100, 0.0, 0.0, "none")[0]
+    n_valid = int((t != -100).sum())
+    # mean == sum of per-row losses / count
+    assert abs(float(rows.double().sum()) / n_valid - float(loss)) <= 1e-5 * abs(float(loss))
+    # ignored rows: exact zeros
+    assert float(xd.grad[t == -100].abs().max()) == 0.0 and float(rows[t == -100].abs().max()) == 0.0
+    # linearity in the upstream gradient (power of two: bit exact)
+    x2, w2 = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    Fn.apply(x2, w2, t)[0].backward(torch.tensor(2.0, device="cuda"))
+    assert torch.equal(x2.grad, 2 * xd.grad) and torch.equal(w2.grad, 2 * wd.grad)
+    del x2, w2
+    # sampled token rows against fp64
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import _Prepared, flce_forward_device
+
+    out, _, _ = flce_forward_device(_Prepared(x, w, t, None, None, -100, 0.0, 0.0, "mean", None, False))
+    lse = out["lse"]
+    pick = torch.arange(0, N, 509, device="cuda")[:64]
+    wf = w.double()
+    z = x[pick].double() @ wf.t()
+    lse_ref = torch.logsumexp(z, dim=1)
+    assert float(((lse[pick].double() - lse_ref).abs() / lse_ref.abs().clamp(min=1)).max()) <= 1e-5
+    p = torch.exp(z - lse_ref[:, None])
+    valid = (t[pick] != -100)
+    onehot = torch.zeros_like(p)
+    onehot[torch.arange(len(pick), device="cuda")[valid], t[pick][valid]] = 1.0
+    gz = (p - onehot) * valid[:, None] / n_valid
+    dx_ref = gz @ wf
+    assert_close(xd.grad[pick].float().cpu(), dx_ref.float().cpu(), 8e-3 * float(dx_ref.abs().max()), 5e-2, "grad_input rows")
+    # sampled vocabulary rows of grad_weight (uses the per-row lse validated above)
+    vs = torch.tensor([0, 1, 4097, 65000, 128000, 128255], device="cuda")
+    zc = x.double() @ wf[vs].t()                                  # [N, 6]
+    pc = torch.exp(zc - lse.double()[:, None])
+    hit = (t[:, None] == vs[None, :]).double()
+    gc = (pc - hit) * (t != -100)[:, None] / n_valid
+    dw_ref = gc.t() @ x.double()
+    assert_close(wd.grad[vs].float().cpu(), dw_ref.float().cpu(), 8e-3 * float(dw_ref.abs().max()), 5e-2, "grad_weight rows")
