@@ -179,6 +179,7 @@ def run_ours(args, spec, rank, world, local_rank):
     import torch.distributed as dist
 
     from liger_kernel_b200 import _lib
+    from liger_kernel_b200.sharded import token_sharded_fused_linear_cross_entropy
     from liger_kernel_b200.transformers.functional import liger_fused_linear_cross_entropy
 
     device = torch.device("cuda", local_rank)
@@ -204,11 +205,14 @@ def run_ours(args, spec, rank, world, local_rank):
     def step(xin, tin):
         xin = xin.detach().requires_grad_(True)
         w.grad = None
-        out = liger_fused_linear_cross_entropy(xin, w, tin, **kw)
-        loss = out if torch.is_tensor(out) else out.loss
-        loss.backward()
         if world > 1:
-            dist.all_reduce(w.grad)
+            # global-batch loss; grad_weight is all-reduced slab by slab on a side stream inside backward
+            skw = {k: v for k, v in kw.items() if k != "return_z_loss"}
+            loss = token_sharded_fused_linear_cross_entropy(xin, w, tin, **skw)
+        else:
+            out = liger_fused_linear_cross_entropy(xin, w, tin, **kw)
+            loss = out if torch.is_tensor(out) else out.loss
+        loss.backward()
         return loss, xin.grad
 
     def barrier():

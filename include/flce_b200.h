@@ -93,6 +93,8 @@ typedef struct flce_backward_args {
   void* grad_input;          /* [n_rows, hidden] dense, or NULL                                     */
   void* grad_weight;         /* [vocab, hidden] dense, or NULL                                      */
   float* grad_bias;          /* [vocab] fp32, or NULL                                               */
+  int32_t slab_begin;        /* run only vocabulary slabs [slab_begin, slab_end) of the plan reported by  */
+  int32_t slab_end;          /* flce_b200_backward_plan; 0,0 = all slabs                                  */
 } flce_backward_args_t;
 
 enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1 };
@@ -134,6 +136,13 @@ int flce_b200_forward(const flce_problem_t* p, float* norm, float* rowstats, con
  * :292-336 (folded into the logit gradient). */
 int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args, void* workspace,
                        size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
+
+/* The vocabulary slabs flce_b200_backward will use for this problem and slab budget: slab s covers rows
+ * [s * slab_cols, min(vocab, (s+1) * slab_cols)) of w / grad_weight.  A caller that wants to overlap work with
+ * the backward pass (e.g. an all-reduce of finished grad_weight rows) calls flce_b200_backward once per slab
+ * range, in increasing order, with the same workspace; grad_input is complete after the last slab.
+ * No counterpart in the reference (its loop is over token chunks, ops/fused_linear_cross_entropy.py:108). */
+int flce_b200_backward_plan(const flce_problem_t* p, size_t slab_budget_bytes, int32_t* n_slabs, int64_t* slab_cols);
 
 /* Plain D = A . B^T on the same main loop (fp32 or 16-bit output), for unit-testing the tensor-core
  * path in isolation.  a_mn_major / b_mn_major select which dimension is contiguous in memory:

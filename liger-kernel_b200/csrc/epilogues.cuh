@@ -136,7 +136,7 @@ struct StatsEpilogue {
 #pragma unroll
       for (int j = 30; j >= 0; --j) idx = (s[j] == cm) ? j : idx;
       best = cm;
-      best_idx = col + idx;
+      best_idx = static_cast<int>(p.vocab_offset) + col + idx;  // global class id
     }
     if (p.plogit_sum != nullptr) {
       float a0 = 0.f, a1 = 0.f;

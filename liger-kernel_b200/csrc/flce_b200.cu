@@ -671,6 +671,11 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
   uint16_t* dz = reinterpret_cast<uint16_t*>(ws + plan.coef_bytes);
   float* dx_acc = reinterpret_cast<float*>(ws + plan.coef_bytes + plan.slab_bytes);
 
+  int slab_begin = args->slab_begin, slab_end = args->slab_end;
+  if (slab_begin == 0 && slab_end == 0) slab_end = plan.n_slabs;
+  if (slab_begin < 0 || slab_end > plan.n_slabs || slab_begin >= slab_end)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "slab range [%d, %d) outside the plan's %d slabs", slab_begin, slab_end,
+                plan.n_slabs);
   const int threads = 256;
   coef_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
       static_cast<int>(p->n_rows), row_math(p), reinterpret_cast<const long long*>(p->target), p->ce_weight, args->lse,
@@ -680,7 +685,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
 
   const bool pair = g_cta_pair != 0;
   const int esize_out = grads_fp32 ? 4 : 2;
-  for (int s = 0; s < plan.n_slabs; ++s) {
+  for (int s = slab_begin; s < slab_end; ++s) {
     const long long v0 = static_cast<long long>(s) * plan.slab_cols;
     const long long cols = (p->vocab - v0 < plan.slab_cols) ? p->vocab - v0 : plan.slab_cols;
     const uint16_t* w_slab = static_cast<const uint16_t*>(p->w) + v0 * p->ld_w;
@@ -753,6 +758,16 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
   ++g_kernel_launches;
     }
   }
+  return FLCE_OK;
+}
+
+int flce_b200_backward_plan(const flce_problem_t* p, size_t slab_budget_bytes, int32_t* n_slabs, int64_t* slab_cols) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (n_slabs == nullptr || slab_cols == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL output");
+  const BackwardPlan plan = backward_plan(p, slab_budget_bytes, true);
+  *n_slabs = plan.n_slabs;
+  *slab_cols = plan.slab_cols;
   return FLCE_OK;
 }
 

@@ -22,6 +22,7 @@ EXPORTS = (
     "flce_b200_forward_finalize",
     "flce_b200_forward",
     "flce_b200_backward",
+    "flce_b200_backward_plan",
     "flce_b200_gemm",
     "flce_b200_check_device_status",
     "flce_b200_profile_enable",
@@ -61,6 +62,7 @@ class BackwardArgs(C.Structure):
         ("lse", C.c_void_p), ("target_prob", C.c_void_p), ("norm", C.c_void_p), ("grad_output", C.c_void_p),
         ("grad_output_per_row", C.c_int32), ("grad_dtype", C.c_int32),
         ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
+        ("slab_begin", C.c_int32), ("slab_end", C.c_int32),
     ]
 
 
@@ -80,6 +82,8 @@ def _load():
     lib.flce_b200_forward_finalize.argtypes = [P, vp, vp, F, vp]
     lib.flce_b200_forward.argtypes = [P, vp, vp, F, vp, sz, vp]
     lib.flce_b200_backward.argtypes = [P, A, vp, sz, sz, vp]
+    lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
+    lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]
     lib.flce_b200_check_device_status.argtypes = [vp]
     lib.flce_b200_set_option.argtypes = [C.c_char_p, i64]

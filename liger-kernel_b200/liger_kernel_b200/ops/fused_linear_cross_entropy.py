@@ -141,8 +141,11 @@ def flce_forward_device(prep: _Prepared):
 
 
 def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, need_input=True, need_weight=True,
-                         need_bias=False, grad_dtype=None, slab_budget=None):
-    """Run sweep 2.  Returns (grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``."""
+                         need_bias=False, grad_dtype=None, slab_budget=None, slab_hook=None):
+    """Run sweep 2.  Returns (grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``.
+
+    ``slab_hook(first_row, last_row, grad_weight)``, if given, is called after the kernels of each vocabulary slab
+    have been enqueued, with the range of ``grad_weight`` rows that slab completes (used to overlap an all-reduce)."""
     dev = prep.device
     gd = prep.dtype if grad_dtype is None else grad_dtype
     budget = SLAB_BUDGET_BYTES if slab_budget is None else int(slab_budget)
@@ -165,7 +168,16 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
         args.grad_weight = None if gw is None else gw.data_ptr()
         args.grad_bias = None if gb is None else gb.data_ptr()
         ws = prep.workspace(_lib.PHASE_BACKWARD, budget)
-        check(lib.flce_b200_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
+        if slab_hook is None:
+            check(lib.flce_b200_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
+        else:
+            n_slabs, slab_cols = C.c_int32(0), C.c_int64(0)
+            check(lib.flce_b200_backward_plan(C.byref(prep.problem), budget, C.byref(n_slabs), C.byref(slab_cols)))
+            for s in range(n_slabs.value):
+                args.slab_begin, args.slab_end = s, s + 1
+                check(lib.flce_b200_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget,
+                                             _stream(dev)))
+                slab_hook(s * slab_cols.value, min(prep.vocab, (s + 1) * slab_cols.value), gw)
     return gx, gw, gb
 
 

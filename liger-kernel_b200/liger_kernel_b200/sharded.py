@@ -1,0 +1,205 @@
+"""FLCE across the GPUs of one box: token-sharded and vocabulary-sharded operators.
+
+One process per GPU, collectives through ``torch.distributed`` (NCCL on GPUs).  Nothing in here reads a
+peer's memory: the collectives land in local HBM and the kernels only ever see local pointers.
+
+Token-sharded (data parallel; the reference leaves this to DDP/FSDP, ``README.md:117``): every rank holds its
+own rows of X / target and the whole W.  Exchanges: the normalisers (count of non-ignored rows, class-weight
+sum) before the per-row losses are formed, the scalar loss, and grad_weight (summed; issued slab by slab on
+a side stream so it overlaps the remaining slabs' GEMMs).
+
+Vocabulary-sharded (tensor parallel; the math and collective pattern follow the reference's
+``ops/vocab_parallel_cross_entropy.py:235-303``): every rank holds rows ``[vocab_start, vocab_start+V_r)`` of W and
+the whole X / target (global class ids).  Exchanges: one all-gather of the ``[6, N]`` per-row statistics after
+sweep 1 (max, sum-exp, target logit, logit sum, arg-max value and index) merged locally in rank order — instead
+of the reference's all-reduce(MAX) + 2 x all-reduce(SUM) — and an all-reduce(SUM) of the partial grad_input.
+Label smoothing uses the global vocabulary size.
+
+The local computation is reached through a small backend object so that the exchange logic can be exercised
+on CPU ranks (gloo) with a stand-in backend in the tests; the default backend is the CUDA library.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import check, lib
+from .ops import fused_linear_cross_entropy as _op
+
+
+class CudaBackend:
+    """Local FLCE pieces on the current GPU through libflce_b200.so."""
+
+    def prepare(self, x, w, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
+                use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=False):
+        return _op._Prepared(x, w, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction,
+                             softcap, use_token_scaling, vocab_total=vocab_total, vocab_offset=vocab_offset,
+                             want_argmax=want_argmax)
+
+    def count(self, prep):
+        norm = torch.empty(4, dtype=torch.float32, device=prep.device)
+        with torch.cuda.device(prep.device):
+            check(lib.flce_b200_count(C.byref(prep.problem), _op._ptr(norm), _op._stream(prep.device)))
+        return norm
+
+    def forward_stats(self, prep):
+        rowstats = torch.empty((_lib.ROWSTAT_PLANES, prep.n_rows), dtype=torch.float32, device=prep.device)
+        with torch.cuda.device(prep.device):
+            ws = prep.workspace(_lib.PHASE_FORWARD)
+            check(lib.flce_b200_forward_stats(C.byref(prep.problem), _op._ptr(rowstats), _op._ptr(ws), ws.numel(),
+                                              _op._stream(prep.device)))
+        return rowstats
+
+    def finalize(self, prep, rowstats, norm):
+        out = _op._forward_outputs(prep)
+        fo = _op._as_forward_out(out)
+        with torch.cuda.device(prep.device):
+            check(lib.flce_b200_forward_finalize(C.byref(prep.problem), _op._ptr(rowstats), _op._ptr(norm), C.byref(fo),
+                                                 _op._stream(prep.device)))
+        return out
+
+    def backward(self, prep, lse, target_prob, norm, grad_output, need_input, need_weight, grad_dtype=None, slab_hook=None):
+        gx, gw, _ = _op.flce_backward_device(prep, lse, target_prob, norm, grad_output, need_input, need_weight, False,
+                                             grad_dtype=grad_dtype, slab_hook=slab_hook)
+        return gx, gw
+
+
+def merge_rowstats(gathered: torch.Tensor) -> torch.Tensor:
+    """Merge per-rank row statistics ``[G, 6, N]`` (ranks ordered by vocabulary offset) into ``[6, N]``.
+
+    max: max over ranks; sum-exp: rescaled to the global max; target logit and logit sum: added (only the owner rank
+    has a non-zero target logit); arg-max: largest value, lowest rank (= lowest class id) on ties."""
+    m_r, d_r = gathered[:, 0], gathered[:, 1]
+    m = m_r.max(dim=0).values
+    d = (d_r * torch.exp(m_r - m[None, :])).sum(dim=0)
+    xy = gathered[:, 2].sum(dim=0)
+    ss = gathered[:, 3].sum(dim=0)
+    best_val, best_rank = gathered[:, 4].max(dim=0)  # torch returns the first (lowest-rank) maximum
+    idx_bits = gathered[:, 5].gather(0, best_rank[None, :])[0]
+    return torch.stack([m, d, xy, ss, best_val, idx_bits], dim=0).contiguous()
+
+
+def _world(group):
+    return dist.get_world_size(group) if dist.is_initialized() else 1
+
+
+class _TokenSharded(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, target, group, backend, overlap, kw):
+        prep = backend.prepare(x.detach(), w.detach(), target, None, kw.get("ce_weight"), kw["ignore_index"],
+                               kw["lse_square_scale"], kw["label_smoothing"], kw["reduction"], kw["softcap"], False)
+        norm = backend.count(prep)
+        if _world(group) > 1:
+            counts = norm[:2].clone()          # norm[2] (sum of all class weights) is the same on every rank
+            dist.all_reduce(counts, group=group)
+            norm = torch.cat([counts, norm[2:]])
+        out = backend.finalize(prep, backend.forward_stats(prep), norm)
+        ctx.saved = (prep, out["lse"], out["target_prob"], norm)
+        ctx.group, ctx.backend, ctx.overlap = group, backend, overlap
+        ctx.in_dtypes = (x.dtype, w.dtype)
+        if kw["reduction"] == "none":
+            return out["loss_rows"]
+        loss = out["scalars"][0].clone()
+        if _world(group) > 1:
+            dist.all_reduce(loss, group=group)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        prep, lse, prob, norm = ctx.saved
+        group, backend = ctx.group, ctx.backend
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        world = _world(group)
+        hook = None
+        pending = []
+        if world > 1 and need_w and ctx.overlap and prep.device.type == "cuda":
+            comm = torch.cuda.Stream(device=prep.device)
+
+            def hook(first_row, last_row, gw):
+                ev = torch.cuda.Event()
+                ev.record()
+                comm.wait_event(ev)
+                with torch.cuda.stream(comm):
+                    pending.append(dist.all_reduce(gw[first_row:last_row], group=group, async_op=True))
+
+        gx, gw = backend.backward(prep, lse, prob, norm, grad_output, need_x, need_w, slab_hook=hook)
+        if world > 1 and need_w:
+            if hook is None:
+                dist.all_reduce(gw, group=group)
+            else:
+                for work in pending:
+                    work.wait()
+                torch.cuda.current_stream(prep.device).wait_stream(comm)
+        h = prep.hidden
+        gx = None if gx is None else gx[:, :h].to(ctx.in_dtypes[0])
+        gw = None if gw is None else gw[:, :h].to(ctx.in_dtypes[1])
+        return gx, gw, None, None, None, None, None
+
+
+class _VocabSharded(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_shard, target, vocab_start, vocab_total, group, backend, kw):
+        prep = backend.prepare(x.detach(), w_shard.detach(), target, None, None, kw["ignore_index"], kw["lse_square_scale"],
+                               kw["label_smoothing"], kw["reduction"], kw["softcap"], False, vocab_total=vocab_total,
+                               vocab_offset=vocab_start, want_argmax=True)
+        norm = backend.count(prep)              # targets are replicated: identical on every rank
+        stats = backend.forward_stats(prep)
+        world = _world(group)
+        if world > 1:
+            planes, n = stats.shape
+            gathered = torch.empty((world * planes, n), dtype=stats.dtype, device=stats.device)
+            dist.all_gather_into_tensor(gathered, stats.contiguous(), group=group)
+            stats = merge_rowstats(gathered.view(world, planes, n))
+        out = backend.finalize(prep, stats, norm)
+        ctx.saved = (prep, out["lse"], out["target_prob"], norm)
+        ctx.group, ctx.backend = group, backend
+        ctx.in_dtypes = (x.dtype, w_shard.dtype)
+        ctx.extra = dict(predicted_tokens=out["predicted_tokens"], z_loss=out["scalars"][1])
+        return out["loss_rows"] if kw["reduction"] == "none" else out["scalars"][0].clone()
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        prep, lse, prob, norm = ctx.saved
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        # partial grad_input in fp32 so that the cross-rank sum is formed before the single rounding
+        gx, gw = ctx.backend.backward(prep, lse, prob, norm, grad_output, need_x, need_w, grad_dtype=torch.float32)
+        if need_x and _world(ctx.group) > 1:
+            dist.all_reduce(gx, group=ctx.group)
+        h = prep.hidden
+        gx = None if gx is None else gx[:, :h].to(ctx.in_dtypes[0])
+        gw = None if gw is None else gw[:, :h].to(ctx.in_dtypes[1])
+        return gx, gw, None, None, None, None, None, None
+
+
+def _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap, ce_weight=None):
+    assert reduction in ("mean", "sum", "none"), f"reduction must be 'mean' or 'sum' or 'none'. Got: {reduction}"
+    return dict(ignore_index=ignore_index, lse_square_scale=lse_square_scale, label_smoothing=label_smoothing,
+                reduction=reduction, softcap=softcap, ce_weight=ce_weight)
+
+
+def token_sharded_fused_linear_cross_entropy(input, weight, target, ignore_index=-100, lse_square_scale=0.0,
+                                             label_smoothing=0.0, reduction="mean", softcap=None, ce_weight=None,
+                                             group=None, overlap_grad_weight=True, backend=None):
+    """FLCE where each rank passes its own rows of ``input`` / ``target`` and the full ``weight``.
+
+    Returns the loss over the *global* batch (identical on every rank; per-row for ``reduction="none"``).
+    ``weight.grad`` receives the sum over ranks; ``input.grad`` is local."""
+    return _TokenSharded.apply(input, weight, target, group, backend or CudaBackend(), overlap_grad_weight,
+                               _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap, ce_weight))
+
+
+def vocab_sharded_fused_linear_cross_entropy(input, weight_shard, target, vocab_start, vocab_total, ignore_index=-100,
+                                             lse_square_scale=0.0, label_smoothing=0.0, reduction="mean", softcap=None,
+                                             group=None, backend=None):
+    """FLCE where each rank passes rows ``[vocab_start, vocab_start + V_r)`` of the weight and the full, replicated
+    ``input`` / ``target`` (global class ids).  Shards must be passed in rank order of increasing ``vocab_start``.
+
+    Returns the loss of the full problem on every rank; ``weight_shard.grad`` is local, ``input.grad`` is the sum over
+    ranks (all-reduced)."""
+    return _VocabSharded.apply(input, weight_shard, target, int(vocab_start), int(vocab_total), group,
+                               backend or CudaBackend(),
+                               _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap))

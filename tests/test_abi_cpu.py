@@ -1,0 +1,82 @@
+"""The C-ABI library loads without a GPU and exports every function include/flce_b200.h declares.
+No compute entry point is called here."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "flce_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(flce_b200_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    from liger_kernel_b200 import _lib
+
+    names = _declared_functions()
+    assert len(names) >= 15
+    raw = C.CDLL(_lib.LIB_PATH)
+    missing = [n for n in names if not hasattr(raw, n)]
+    assert not missing, missing
+    assert set(_lib.EXPORTS) <= set(names)
+
+
+def test_struct_sizes_match_header_layout():
+    from liger_kernel_b200 import _lib
+
+    # 7 int64 + 2 int32 + int64 + 3 float + 2 int32 (+pad) + 5 pointers
+    assert C.sizeof(_lib.Problem) == 7 * 8 + 8 + 8 + 12 + 8 + 4 + 5 * 8
+    assert C.sizeof(_lib.ForwardOut) == 7 * 8
+    assert C.sizeof(_lib.BackwardArgs) == 4 * 8 + 8 + 3 * 8 + 8
+
+
+def test_host_side_argument_errors_without_gpu():
+    from liger_kernel_b200 import _lib
+
+    lib = _lib.lib
+    assert lib.flce_b200_version().decode().startswith("flce_b200")
+    assert lib.flce_b200_status_string(3).decode() == "workspace too small"
+    p = _lib.Problem()
+    assert lib.flce_b200_workspace_bytes(C.byref(p), 0, 0) == 0          # empty problem is rejected
+    assert b"shapes must be positive" in lib.flce_b200_last_error()
+    p.n_rows, p.hidden, p.vocab, p.vocab_total, p.ld_x, p.ld_w = 64, 60, 100, 100, 60, 60
+    p.x = p.w = p.target = 16
+    assert lib.flce_b200_workspace_bytes(C.byref(p), 0, 0) == 0          # hidden not a multiple of 8
+    assert b"multiples of 8" in lib.flce_b200_last_error()
+    p.hidden = p.ld_x = p.ld_w = 64
+    assert lib.flce_b200_workspace_bytes(C.byref(p), 0, 0) > 0
+    n_slabs, cols = C.c_int32(), C.c_int64()
+    assert lib.flce_b200_backward_plan(C.byref(p), 64 * 2 * 256, C.byref(n_slabs), C.byref(cols)) == 0
+    assert (n_slabs.value, cols.value) == (1, 256)
+    p.dtype = _lib.FLCE_FP32 + 5
+    assert lib.flce_b200_workspace_bytes(C.byref(p), 0, 0) == 0
+    assert lib.flce_b200_set_option(b"no_such_option", 1) == 1
+    with pytest.raises(_lib.FlceError):
+        _lib.set_option("raster_group_bytes", -1)
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    from liger_kernel_b200 import LigerFusedLinearCrossEntropyLoss
+
+    x = torch.randn(8, 16, dtype=torch.bfloat16)
+    w = torch.randn(32, 16, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        LigerFusedLinearCrossEntropyLoss()(w, x, torch.zeros(8, dtype=torch.long))
+
+
+def test_module_argument_checks_follow_the_reference():
+    from liger_kernel_b200 import LigerFusedLinearCrossEntropyLoss
+
+    with pytest.raises(AssertionError, match="label_smoothing must be between"):
+        LigerFusedLinearCrossEntropyLoss(label_smoothing=1.5)
+    with pytest.raises(AssertionError, match="reduction must be"):
+        LigerFusedLinearCrossEntropyLoss(reduction="median")
+    with pytest.raises(AssertionError, match="softcap must greater than"):
+        LigerFusedLinearCrossEntropyLoss(softcap=0.0)

@@ -1,0 +1,77 @@
+"""Token-sharded and vocabulary-sharded FLCE on real GPUs (NCCL), one process per GPU, against the single-GPU
+operator on the whole problem.  Skipped when fewer than two GPUs are visible (as the reference skips its
+multi-GPU test, test/megatron/test_cross_entropy.py:691-715)."""
+
+import os
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _worker(rank, world, init_file, mode, kw, result_file):
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.join(os.path.dirname(HERE), "liger-kernel_b200"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from liger_kernel_b200 import sharded
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Fn
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        g = torch.Generator().manual_seed(17)
+        N, H, V = 1024, 256, 5000
+        x = torch.randn(N, H, generator=g).bfloat16().cuda()
+        w = (torch.randn(V, H, generator=g) * 0.05).bfloat16().cuda()
+        t = torch.randint(0, V, (N,), generator=g)
+        t[::9] = -100
+        t = t.cuda()
+        xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        ref = Fn.apply(xr, wr, t, None, None, -100, kw.get("lse_square_scale", 0.0), kw.get("label_smoothing", 0.0),
+                       kw.get("reduction", "mean"), kw.get("softcap"))[0]
+        ref.backward()
+        if mode == "token":
+            lo, hi = rank * N // world, (rank + 1) * N // world
+            xs, ws = x[lo:hi].clone().requires_grad_(True), w.clone().requires_grad_(True)
+            import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+            mod.SLAB_BUDGET_BYTES = (hi - lo) * 2 * 1024      # several slabs: exercises the overlapped all-reduce
+            loss = sharded.token_sharded_fused_linear_cross_entropy(xs, ws, t[lo:hi], **kw)
+            loss.backward()
+            ok = torch.allclose(loss, ref, rtol=1e-5)
+            ok &= torch.allclose(xs.grad.float(), xr.grad[lo:hi].float(), rtol=2e-2, atol=1e-6)
+            ok &= torch.allclose(ws.grad.float(), wr.grad.float(), rtol=5e-2, atol=2e-6)
+        else:
+            per = (V + world - 1) // world
+            lo, hi = rank * per, min(V, (rank + 1) * per)
+            xs, ws = x.clone().requires_grad_(True), w[lo:hi].clone().requires_grad_(True)
+            loss = sharded.vocab_sharded_fused_linear_cross_entropy(xs, ws, t, lo, V, **kw)
+            loss.backward()
+            ok = torch.allclose(loss, ref, rtol=1e-5)
+            ok &= torch.allclose(xs.grad.float(), xr.grad.float(), rtol=5e-2, atol=2e-6)
+            ok &= torch.allclose(ws.grad.float(), wr.grad[lo:hi].float(), rtol=2e-2, atol=1e-6)
+        torch.cuda.synchronize()
+        with open(f"{result_file}.{rank}", "w") as f:
+            f.write("ok" if bool(ok) else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["token", "vocab"])
+@pytest.mark.parametrize("kw", [dict(), dict(label_smoothing=0.1, lse_square_scale=1e-3, softcap=30.0, reduction="sum")])
+def test_sharded_equals_single_gpu(mode, kw):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    with tempfile.TemporaryDirectory() as tmp:
+        init_file, result = os.path.join(tmp, "rdv"), os.path.join(tmp, "res")
+        mp.spawn(_worker, args=(world, init_file, mode, kw, result), nprocs=world, join=True)
+        for r in range(world):
+            with open(f"{result}.{r}") as f:
+                assert f.read() == "ok", f"rank {r}"
