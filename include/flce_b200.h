@@ -117,6 +117,24 @@ int flce_b200_count(const flce_problem_t* p, float* norm, void* stream);
 int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* workspace, size_t workspace_bytes,
                             void* stream);
 
+/* The same sweep as flce_b200_forward_stats for callers that must not allocate device memory and have no
+ * workspace to lend: a host whose memory plan is fixed (for example a server that has handed the whole GPU to
+ * its own arena, where a late cudaMalloc fails or fragments the plan), or a latency-critical loop that cannot
+ * afford the device-wide synchronisation an allocation implies.  It has no counterpart in the reference, which
+ * allocates its scratch through torch on every call.
+ *   - The per-tile partial statistics go to a 32 MiB array built into the library (held by every GPU that loads
+ *     the library until the process exits).  Limit: planes x ceil(vocab/256) x n_rows <= 8 Mi floats, where planes
+ *     = 2, +1 with label smoothing, +2 with FLCE_FLAG_ARGMAX (e.g. 4096 rows x 128256 classes without extras);
+ *     larger problems get FLCE_ERR_WORKSPACE and a message naming the limit.
+ *   - Inputs and the rowstats output are still the caller's.  The call itself performs no cudaMalloc / cudaFree
+ *     and calls no allocating library routine.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a GPU share the one array, and it keeps the previous call's contents; nothing in it needs to
+ *     start at zero.  Two calls whose kernels overlap on the same GPU (different streams or threads) race on it:
+ *     serialise them. */
+int flce_b200_forward_stats_static(const flce_problem_t* p, float* rowstats, void* stream);
+
 /* Per-row losses and metrics from (possibly cross-rank merged) statistics, and their sums.
  * Replaces src/liger_kernel/ops/cross_entropy.py:289-336 and
  * src/liger_kernel/ops/fused_linear_cross_entropy.py:272-283. */

@@ -609,6 +609,83 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
   return FLCE_OK;
 }
 
+// ------------------------------------------------------------------ forward statistics without any allocation
+// Scratch for flce_b200_forward_stats_static: lives in the library image, one copy per GPU that loads the library,
+// for the life of the process.  In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress (once per device, below).
+constexpr size_t kStaticScratchFloats = size_t(8) << 20;  // 8 Mi floats = 32 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static float* g_static_scratch_addr[64] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+int flce_b200_forward_stats_static(const flce_problem_t* p, float* rowstats, void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (rowstats == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "rowstats is NULL");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool need_sum = p->label_smoothing > 0.f;
+  const bool need_argmax = (p->flags & FLCE_FLAG_ARGMAX) != 0;
+  const size_t n_tiles = static_cast<size_t>(ceil_div(p->vocab, kBlockN));
+  const size_t plane = align_up(n_tiles * static_cast<size_t>(p->n_rows), 64);  // floats; keeps planes 256-byte aligned
+  const size_t n_planes = 2 + (need_sum ? 1 : 0) + (need_argmax ? 2 : 0);
+  if (n_planes * plane > kStaticScratchFloats)
+    return fail(FLCE_ERR_WORKSPACE,
+                "problem too large for the built-in scratch: %zu planes x %zu vocabulary tiles x %lld rows = %zu floats, "
+                "limit %zu floats (32 MiB); use flce_b200_forward_stats with caller-provided workspace",
+                n_planes, n_tiles, (long long)p->n_rows, n_planes * plane, kStaticScratchFloats);
+  // one-time set-up for the current device: resolve the array's device address
+  int ordinal = 0;
+  FLCE_CUDA(cudaGetDevice(&ordinal));
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[ordinal] == nullptr) {
+      void* addr = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
+      if (e != cudaSuccess || addr == nullptr)
+        return fail(FLCE_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch) failed on device %d: %s", ordinal,
+                    cudaGetErrorString(e));
+      g_static_scratch_addr[ordinal] = static_cast<float*>(addr);
+    }
+    scratch = g_static_scratch_addr[ordinal];
+  }
+  // Every (row, tile) entry that the merge below reads is written by the sweep first, so nothing in the shared
+  // array has to start at zero; only the caller's target-logit plane does.
+  size_t next = 0;
+  StatsEpilogue::Params ep;
+  ep.target = reinterpret_cast<const long long*>(p->target);
+  ep.bias = p->bias;
+  ep.col_weight = p->ce_weight;
+  ep.softcap = p->softcap;
+  ep.inv_softcap = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+  ep.n_cols = static_cast<int>(p->vocab);
+  ep.vocab_offset = p->vocab_offset;
+  ep.m_rows = static_cast<int>(p->n_rows);
+  ep.pmax = scratch + plane * next++;
+  ep.psum = scratch + plane * next++;
+  ep.plogit_sum = need_sum ? scratch + plane * next++ : nullptr;
+  ep.pamax_val = need_argmax ? scratch + plane * next++ : nullptr;
+  ep.pamax_idx = need_argmax ? reinterpret_cast<int*>(scratch + plane * next++) : nullptr;
+  ep.target_logit = rowstats + 2 * static_cast<size_t>(p->n_rows);
+  FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
+  Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
+  Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
+  rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, kKindStats, g_cta_pair != 0, a, b, p->dtype, p->n_rows, p->vocab,
+                                                    p->hidden, static_cast<long long>(kBlockM) * p->hidden * 2, false, ep,
+                                                    stream);
+  if (rc != FLCE_OK) return rc;
+  const int threads = 256;
+  merge_partials_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), static_cast<int>(n_tiles), ep.pmax, ep.psum, ep.plogit_sum, ep.pamax_val, ep.pamax_idx,
+      rowstats);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
 int flce_b200_forward_finalize(const flce_problem_t* p, const float* rowstats, const float* norm,
                                const flce_forward_out_t* out, void* stream_) {
   int rc = check_problem(p);

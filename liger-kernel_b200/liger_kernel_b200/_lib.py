@@ -19,6 +19,7 @@ EXPORTS = (
     "flce_b200_workspace_bytes",
     "flce_b200_count",
     "flce_b200_forward_stats",
+    "flce_b200_forward_stats_static",
     "flce_b200_forward_finalize",
     "flce_b200_forward",
     "flce_b200_backward",
@@ -79,6 +80,8 @@ def _load():
     lib.flce_b200_workspace_bytes.restype = sz
     lib.flce_b200_count.argtypes = [P, vp, vp]
     lib.flce_b200_forward_stats.argtypes = [P, vp, vp, sz, vp]
+    lib.flce_b200_forward_stats_static.argtypes = [P, vp, vp]
+    lib.flce_b200_forward_stats_static.restype = C.c_int
     lib.flce_b200_forward_finalize.argtypes = [P, vp, vp, F, vp]
     lib.flce_b200_forward.argtypes = [P, vp, vp, F, vp, sz, vp]
     lib.flce_b200_backward.argtypes = [P, A, vp, sz, sz, vp]
