@@ -243,7 +243,7 @@ def test_full_size_properties():
     rows = Fn.apply(x, w, t, None, None, -100, 0.0, 0.0, "none")[0]
     n_valid = int((t != -100).sum())
     # mean == sum of per-row losses / count
-    assert abs(float(rows.double().sum()) / n_valid - float(loss)) <= 1e-5 * abs(float(loss))
+    assert abs(float(rows.double().sum()) / n_valid - float(loss.detach())) <= 1e-5 * abs(float(loss.detach()))
     # ignored rows: exact zeros
     assert float(xd.grad[t == -100].abs().max()) == 0.0 and float(rows[t == -100].abs().max()) == 0.0
     # linearity in the upstream gradient (power of two: bit exact)
