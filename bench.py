@@ -47,6 +47,13 @@ NAMES = {
 }
 
 
+# DRAM bytes per (token row x vocabulary column) of one launch, from the ncu --set full capture of the profiling case
+# (dram__bytes_read.sum + dram__bytes_write.sum over N x V = 8192 x 32768 units; summary under profiles/).  Traffic of a
+# full-size launch is this figure times the units that launch covers; it grows with the units for a fixed raster.
+NCU_DRAM_BYTES_PER_UNIT = {"stats": 0.7325e9 / (8192 * 32768), "dz": 1.4562e9 / (8192 * 32768),
+                           "dw": 2.9133e9 / (8192 * 32768), "dx": 3.4928e9 / (8192 * 32768)}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -175,6 +182,67 @@ def run_reference(args, spec, rank, world):
     }))
 
 
+def run_liger(args, spec, rank, world, local_rank):
+    """The reference's own GPU operator (installed unmodified under baseline/_ref) on the same workload and
+    timing, for the side-by-side number.  `--impl liger_triton`: its default Triton path; `--impl liger_cutedsl`:
+    its CuTe-DSL sm_100 path (LIGER_KERNEL_IMPL=cutedsl), which needs a newer nvidia-cutlass-dsl than some images have."""
+    if rank != 0:
+        return
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "liger_kernel")):
+        print(json.dumps({"impl": args.impl, "unavailable": "baseline/_ref/liger_kernel is not installed"}))
+        return
+    if args.impl == "liger_cutedsl":
+        os.environ["LIGER_KERNEL_IMPL"] = "cutedsl"
+    sys.path.insert(0, ref_dir)
+    try:
+        from liger_kernel.transformers.functional import liger_fused_linear_cross_entropy as ref_flce
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"impl": args.impl, "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}))
+        return
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    x, w, t = make_inputs(spec, device, 1234)
+    w.requires_grad_(True)
+    kw = dict(spec["kw"])
+    if args.accum_fp32:
+        kw["accum_dtype"] = torch.float32
+    N, H, V = spec["N"], spec["H"], spec["V"]
+
+    def step():
+        xin = x.detach().requires_grad_(True)
+        w.grad = None
+        out = ref_flce(xin, w, t, **kw)
+        loss = out if torch.is_tensor(out) else out.loss
+        loss.backward()
+        return loss
+
+    try:
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"impl": args.impl, "unavailable": f"run failed: {type(e).__name__}: {e}"[:300]}))
+        return
+    ms = e0.elapsed_time(e1) / args.steps
+    peaks = load_peaks()
+    tflops = 8.0 * N * H * V / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "impl": args.impl, "metric": "flce_fwd_bwd_tokens_per_s", "value": N / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": NAMES[args.workload], "accum_dtype": "fp32" if args.accum_fp32 else None},
+        "tflops_credited_8NHV": tflops, "frac_of_burst": tflops / peaks["burst"],
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+    }))
+
+
 def run_ours(args, spec, rank, world, local_rank):
     import torch.distributed as dist
 
@@ -294,7 +362,9 @@ def run_ours(args, spec, rank, world, local_rank):
         "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["sustained"], "frac_of_burst": achieved / peaks["burst"],
                      "launches": dom_launches, "avg_launch_ms": dom_ms / max(1, dom_launches),
-                     "peak_kind": f"sustained bf16 GEMM, {peaks['source']}", "traffic": None},
+                     "peak_kind": f"sustained bf16 GEMM, {peaks['source']}",
+                     "traffic": NCU_DRAM_BYTES_PER_UNIT[dom] * N * V * args.steps / max(1, dom_launches),
+                     "traffic_note": "ncu capture of the N=8192,V=32768 case scaled by rows x columns per launch"},
         "kernels": per_kind,
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * 2 + t_host.numel() * 8, "d2h_bytes_per_step": 4},
@@ -319,7 +389,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "liger_triton", "liger_cutedsl"])
+    ap.add_argument("--accum-fp32", action="store_true", dest="accum_fp32")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cta-pair", type=int, default=None, dest="cta_pair")
     ap.add_argument("--raster-mb", type=int, default=None, dest="raster_mb")
@@ -331,6 +402,8 @@ def main():
     spec = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, spec, rank, world)
+    elif args.impl in ("liger_triton", "liger_cutedsl"):
+        run_liger(args, spec, rank, world, local_rank)
     else:
         run_ours(args, spec, rank, world, local_rank)
 
