@@ -258,6 +258,9 @@ def run_ours(args, spec, rank, world, local_rank):
         _lib.set_option("cta_pair", args.cta_pair)
     if args.raster_mb is not None:
         _lib.set_option("raster_group_bytes", args.raster_mb << 20)
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as flce_op
+    if args.mode is not None:
+        flce_op.MODE = args.mode
     peaks = load_peaks()
     x, w, t = make_inputs(spec, device, 1234 + rank)
     if world > 1:
@@ -356,7 +359,7 @@ def run_ours(args, spec, rank, world, local_rank):
         "config": {"workload": NAMES[args.workload], "tokens_per_gpu": N, "hidden": H, "vocab": V,
                    "parallelism": "single GPU" if world == 1 else f"token-sharded x{world}, NCCL all-reduce of grad_weight",
                    "l2_policy": "inputs larger than L2 (weight alone is %.2f GB)" % (V * H * 2 / 1e9),
-                   "cta_pair": args.cta_pair, "raster_mb": args.raster_mb},
+                   "cta_pair": args.cta_pair, "raster_mb": args.raster_mb, "mode": flce_op.MODE},
         "tflops_per_gpu": tflops,
         "frac_of_bf16_peak": {"burst": tflops / peaks["burst"], "sustained": tflops / peaks["sustained"], "peaks": peaks["source"]},
         "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
@@ -394,6 +397,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cta-pair", type=int, default=None, dest="cta_pair")
     ap.add_argument("--raster-mb", type=int, default=None, dest="raster_mb")
+    ap.add_argument("--mode", default=None, choices=["recompute", "single_sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -97,7 +97,16 @@ typedef struct flce_backward_args {
   int32_t slab_end;          /* flce_b200_backward_plan; 0,0 = all slabs                                  */
 } flce_backward_args_t;
 
-enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1 };
+typedef struct flce_fused_args {
+  const flce_forward_out_t* out; /* lse, target_prob and loss_rows are required here                         */
+  float* norm;                   /* [4] output, see flce_b200_count                                           */
+  int32_t grad_dtype;            /* flce_dtype_t of grad_input / grad_weight (FLCE_FP32 allowed)              */
+  void* grad_input;              /* [n_rows, hidden] dense, or NULL                                           */
+  void* grad_weight;             /* [vocab, hidden] dense, or NULL                                            */
+  float* grad_bias;              /* [vocab] fp32, or NULL                                                     */
+} flce_fused_args_t;
+
+enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1, FLCE_PHASE_FUSED = 2 };
 
 /* Bytes of scratch the given phase needs for this problem (0 on invalid input).
  * `slab_budget_bytes` caps the logit-gradient slab of the backward pass (0 = default 1 GiB). */
@@ -154,6 +163,21 @@ int flce_b200_forward(const flce_problem_t* p, float* norm, float* rowstats, con
  * :292-336 (folded into the logit gradient). */
 int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args, void* workspace,
                        size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
+
+/* Single-sweep mode: loss and gradients in one call, for an upstream gradient of 1, without recomputing the
+ * logits: per token chunk the logit tiles are reduced to statistics AND kept as a 16-bit copy ([chunk, vocab],
+ * bounded by slab_budget_bytes, default 2.5 GiB), turned into the logit gradient in place once the chunk's lse is
+ * known, and projected (grad_input chunk written once, grad_weight accumulated over chunks in fp32).  This is the
+ * structure of the reference's operator (src/liger_kernel/ops/fused_linear_cross_entropy.py:108-265: gradients
+ * are formed inside forward, 6.N.H.V tensor FLOPs instead of 8.N.H.V) on this library's kernels.  reduction
+ * 'none' is not available here.  Workspace: flce_b200_workspace_bytes(p, FLCE_PHASE_FUSED, budget). */
+int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t* args, void* workspace,
+                               size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
+
+/* data[i] *= *scale for n elements of the given dtype; a no-op when the device-resident scale equals 1 (tested on
+ * the device, no host synchronisation).  Replaces element_mul_kernel and the torch.equal test before it
+ * (src/liger_kernel/ops/utils.py:108-141, ops/fused_linear_cross_entropy.py:292-336). */
+int flce_b200_scale_gradient(void* data, int64_t n, int32_t dtype, const float* scale, void* stream);
 
 /* The vocabulary slabs flce_b200_backward will use for this problem and slab budget: slab s covers rows
  * [s * slab_cols, min(vocab, (s+1) * slab_cols)) of w / grad_weight.  A caller that wants to overlap work with

@@ -82,6 +82,9 @@ struct StatsEpilogue {
     float* pamax_val;         // [n_tiles][M] or null
     int* pamax_idx;           // [n_tiles][M] or null
     float* target_logit;      // [M], written by the one tile that contains the target
+    void* logits_out;         // optional [M][ld_logits] 16-bit copy of the soft-capped logits (single-sweep mode) or null
+    long long ld_logits;
+    int logits_fmt;           // kOutBf16 / kOutFp16
   };
 
   float m, d, ssum, best;
@@ -117,6 +120,9 @@ struct StatsEpilogue {
 #pragma unroll
       for (int j = 0; j < 32; ++j) s[j] = p.softcap * tanh_accurate(s[j] * p.inv_softcap);
     }
+    if (p.logits_out != nullptr && row_ok)
+      store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.logits_out) + static_cast<size_t>(row) * p.ld_logits + col),
+                    s, p.logits_fmt);
     if (ragged) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) s[j] = (col + j < p.n_cols) ? s[j] : -INFINITY;

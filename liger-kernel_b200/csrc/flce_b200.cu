@@ -404,6 +404,90 @@ __global__ void coef_kernel(int m_rows, RowMath rm, const long long* target, con
   c3[row] = c;
 }
 
+// Single-sweep mode: turn the stored 16-bit soft-capped logits of a token chunk into the logit gradient, in place.
+//   dZ = (exp(s - lse) * c1 - c2 * colw - c3 * [j == target]) * (1 - (s/softcap)^2)
+// One block per (row, segment of 8 * blockDim columns); HBM-bound (reads and writes each element once).
+__global__ void dz_inplace_kernel(uint16_t* slab, long long ld, int n_rows, int n_cols, int fmt, const long long* target,
+                                  long long vocab_offset, const float* lse, const float* c1, const float* c2,
+                                  const float* c3, const float* col_weight, float inv_softcap) {
+  const int row = blockIdx.y;
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (row >= n_rows || col >= n_cols) return;
+  const float l2 = lse[row] * kLog2e, a = c1[row], b = c2[row], c = c3[row];
+  const long long t = target[row] - vocab_offset;
+  uint4* ptr = reinterpret_cast<uint4*>(slab + static_cast<size_t>(row) * ld + col);
+  const uint4 raw = *ptr;
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  float g[8];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 f;
+    if (fmt == kOutBf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[q]));
+    else f = __half22float2(*reinterpret_cast<const __half2*>(&words[q]));
+    g[2 * q] = f.x;
+    g[2 * q + 1] = f.y;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float s = g[j];
+    const float wj = (col_weight != nullptr && col + j < n_cols) ? col_weight[col + j] : 1.f;
+    float v = fmaf(ex2_approx(fmaf(s, kLog2e, -l2)), a, -b * wj);
+    if (static_cast<long long>(col + j) == t) v -= c;
+    if (inv_softcap > 0.f) {
+      const float th = s * inv_softcap;
+      v *= fmaf(-th, th, 1.f);
+    }
+    g[j] = (col + j < n_cols) ? v : 0.f;
+  }
+  uint4 o;
+  o.x = pack2(g[0], g[1], fmt);
+  o.y = pack2(g[2], g[3], fmt);
+  o.z = pack2(g[4], g[5], fmt);
+  o.w = pack2(g[6], g[7], fmt);
+  *ptr = o;
+}
+
+// data[i] *= *scale unless *scale == 1 (checked on the device: no host synchronisation); 16-bit or fp32 elements
+__global__ void scale_inplace_kernel(void* data, long long n, int fmt, const float* scale) {
+  const float s = *scale;
+  if (s == 1.f) return;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    if (fmt == kOutFp32) {
+      static_cast<float*>(data)[i] *= s;
+    } else if (fmt == kOutBf16) {
+      __nv_bfloat16* p = static_cast<__nv_bfloat16*>(data) + i;
+      *p = __float2bfloat16_rn(__bfloat162float(*p) * s);
+    } else {
+      __half* p = static_cast<__half*>(data) + i;
+      *p = __float2half_rn(__half2float(*p) * s);
+    }
+  }
+}
+
+// out[j] += sum over rows of slab column j (bias gradient across token chunks); one block per 64 columns
+__global__ void colsum_accumulate_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out,
+                                         int accumulate) {
+  __shared__ float part[16][64];
+  const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
+  const int col = blockIdx.x * 64 + cx;
+  float s = 0.f;
+  if (col < n_cols) {
+    for (int r = ry; r < m_rows; r += 16) {
+      const uint16_t raw = dz[static_cast<size_t>(r) * ld + col];
+      s += (fmt == kOutBf16) ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw))
+                             : __half2float(*reinterpret_cast<const __half*>(&raw));
+    }
+  }
+  part[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < n_cols) {
+    float t = 0.f;
+    for (int i = 0; i < 16; ++i) t += part[i][cx];
+    out[col] = accumulate ? out[col] + t : t;
+  }
+}
+
 // grad_bias[j] (+)= sum over rows of the 16-bit slab column j; one block per 64 columns, ordered sum
 __global__ void colsum_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out) {
   __shared__ float part[16][64];
@@ -504,6 +588,32 @@ static BackwardPlan backward_plan(const flce_problem_t* p, size_t budget, bool n
   return b;
 }
 
+// single-sweep mode: token chunks with the chunk's soft-capped logits kept in a 16-bit slab [chunk][ld]
+struct FusedPlan {
+  long long chunk_rows, ld_slab;
+  int n_chunks, n_tiles;
+  size_t plane, rowstats_bytes, coef_bytes, slab_bytes, acc_bytes, total;
+};
+static FusedPlan fused_plan(const flce_problem_t* p, size_t budget, bool need_acc) {
+  FusedPlan f;
+  if (budget == 0) budget = size_t(5) << 29;  // 2.5 GiB
+  f.ld_slab = ceil_div(p->vocab, 64) * 64;
+  long long max_rows = static_cast<long long>(budget / (static_cast<size_t>(f.ld_slab) * 2));
+  max_rows = max_rows / 256 * 256;
+  if (max_rows < 256) max_rows = 256;
+  f.n_chunks = static_cast<int>(ceil_div(p->n_rows, max_rows));
+  f.chunk_rows = ceil_div(ceil_div(p->n_rows, f.n_chunks), 256) * 256;
+  f.n_chunks = static_cast<int>(ceil_div(p->n_rows, f.chunk_rows));
+  f.n_tiles = static_cast<int>(ceil_div(p->vocab, kBlockN));
+  f.plane = align_up(static_cast<size_t>(f.n_tiles) * f.chunk_rows * sizeof(float), 256);
+  f.rowstats_bytes = align_up(static_cast<size_t>(FLCE_ROWSTAT_PLANES) * f.chunk_rows * sizeof(float), 256);
+  f.coef_bytes = align_up(static_cast<size_t>(f.chunk_rows) * 3 * sizeof(float), 256);
+  f.slab_bytes = align_up(static_cast<size_t>(f.chunk_rows) * f.ld_slab * 2, 256);
+  f.acc_bytes = (need_acc && f.n_chunks > 1) ? align_up(static_cast<size_t>(p->vocab) * p->hidden * sizeof(float), 256) : 0;
+  f.total = 5 * f.plane + f.rowstats_bytes + f.coef_bytes + f.slab_bytes + f.acc_bytes;
+  return f;
+}
+
 }  // namespace flce
 
 using namespace flce;
@@ -544,6 +654,7 @@ size_t flce_b200_workspace_bytes(const flce_problem_t* p, int phase, size_t slab
   if (check_problem(p) != FLCE_OK) return 0;
   if (phase == FLCE_PHASE_FORWARD) return forward_plan(p).total;
   if (phase == FLCE_PHASE_BACKWARD) return backward_plan(p, slab_budget_bytes, true).total;
+  if (phase == FLCE_PHASE_FUSED) return fused_plan(p, slab_budget_bytes, true).total;
   fail(FLCE_ERR_INVALID_ARGUMENT, "unknown phase %d", phase);
   return 0;
 }
@@ -595,6 +706,9 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
   ep.pamax_val = need_argmax ? reinterpret_cast<float*>(ws + 3 * plan.plane) : nullptr;
   ep.pamax_idx = need_argmax ? reinterpret_cast<int*>(ws + 4 * plan.plane) : nullptr;
   ep.target_logit = rowstats + 2 * static_cast<size_t>(p->n_rows);
+  ep.logits_out = nullptr;
+  ep.ld_logits = 0;
+  ep.logits_fmt = kOutBf16;
   FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
   Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
   Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
@@ -670,6 +784,9 @@ int flce_b200_forward_stats_static(const flce_problem_t* p, float* rowstats, voi
   ep.pamax_val = need_argmax ? scratch + plane * next++ : nullptr;
   ep.pamax_idx = need_argmax ? reinterpret_cast<int*>(scratch + plane * next++) : nullptr;
   ep.target_logit = rowstats + 2 * static_cast<size_t>(p->n_rows);
+  ep.logits_out = nullptr;
+  ep.ld_logits = 0;
+  ep.logits_fmt = kOutBf16;
   FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
   Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
   Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
@@ -835,6 +952,176 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
   ++g_kernel_launches;
     }
   }
+  return FLCE_OK;
+}
+
+int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t* args, void* workspace,
+                               size_t workspace_bytes, size_t slab_budget_bytes, void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (args == nullptr || args->out == nullptr || args->norm == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "args, args->out and args->norm must not be NULL");
+  const flce_forward_out_t* out = args->out;
+  if (out->lse == nullptr || out->loss_rows == nullptr || out->target_prob == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "single-sweep mode needs out->lse, out->target_prob and out->loss_rows");
+  if (p->reduction == FLCE_NONE)
+    return fail(FLCE_ERR_UNSUPPORTED, "single-sweep mode forms gradients before the upstream gradient is known; "
+                                      "reduction 'none' needs the two-sweep path");
+  if (args->grad_dtype != p->dtype && args->grad_dtype != FLCE_FP32)
+    return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool grads_fp32 = args->grad_dtype == FLCE_FP32;
+  const FusedPlan plan = fused_plan(p, slab_budget_bytes, true);
+  const bool use_acc = args->grad_weight != nullptr && !grads_fp32 && plan.n_chunks > 1;
+  const size_t needed = plan.total - (use_acc ? 0 : plan.acc_bytes);
+  if (workspace == nullptr || workspace_bytes < needed)
+    return fail(FLCE_ERR_WORKSPACE, "single-sweep mode needs %zu bytes of workspace, got %zu", needed, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* planes = reinterpret_cast<float*>(ws);
+  float* chunk_stats = reinterpret_cast<float*>(ws + 5 * plan.plane);
+  float* c1 = reinterpret_cast<float*>(ws + 5 * plan.plane + plan.rowstats_bytes);
+  uint16_t* slab = reinterpret_cast<uint16_t*>(ws + 5 * plan.plane + plan.rowstats_bytes + plan.coef_bytes);
+  float* dw_acc = reinterpret_cast<float*>(ws + 5 * plan.plane + plan.rowstats_bytes + plan.coef_bytes + plan.slab_bytes);
+
+  rc = flce_b200_count(p, args->norm, stream_);
+  if (rc != FLCE_OK) return rc;
+  const bool pair = g_cta_pair != 0;
+  const bool need_sum = p->label_smoothing > 0.f;
+  const bool need_argmax = (p->flags & FLCE_FLAG_ARGMAX) != 0;
+  const int fmt16 = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
+  const int esize_out = grads_fp32 ? 4 : 2;
+  const RowMath rm = row_math(p);
+  const int threads = 256;
+  const size_t plane_floats = plan.plane / sizeof(float);
+  for (int c = 0; c < plan.n_chunks; ++c) {
+    const long long r0 = static_cast<long long>(c) * plan.chunk_rows;
+    const long long rows = (p->n_rows - r0 < plan.chunk_rows) ? p->n_rows - r0 : plan.chunk_rows;
+    const uint16_t* x_chunk = static_cast<const uint16_t*>(p->x) + r0 * p->ld_x;
+    const long long* tgt = reinterpret_cast<const long long*>(p->target) + r0;
+    float* c2 = c1 + rows;
+    float* c3 = c2 + rows;
+    // ---- logits of the chunk: statistics + 16-bit copy
+    {
+      StatsEpilogue::Params ep;
+      ep.target = tgt;
+      ep.bias = p->bias;
+      ep.col_weight = p->ce_weight;
+      ep.softcap = p->softcap;
+      ep.inv_softcap = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+      ep.n_cols = static_cast<int>(p->vocab);
+      ep.vocab_offset = p->vocab_offset;
+      ep.m_rows = static_cast<int>(rows);
+      ep.pmax = planes;
+      ep.psum = planes + plane_floats;
+      ep.plogit_sum = need_sum ? planes + 2 * plane_floats : nullptr;
+      ep.pamax_val = need_argmax ? planes + 3 * plane_floats : nullptr;
+      ep.pamax_idx = need_argmax ? reinterpret_cast<int*>(planes + 4 * plane_floats) : nullptr;
+      ep.target_logit = chunk_stats + 2 * static_cast<size_t>(rows);
+      ep.logits_out = slab;
+      ep.ld_logits = plan.ld_slab;
+      ep.logits_fmt = fmt16;
+      FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(rows) * sizeof(float), stream));
+      Operand a{x_chunk, rows, p->hidden, p->ld_x, 0};
+      Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
+      rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, kKindStats, pair, a, b, p->dtype, rows, p->vocab, p->hidden,
+                                                        static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
+      if (rc != FLCE_OK) return rc;
+      merge_partials_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
+          static_cast<int>(rows), plan.n_tiles, ep.pmax, ep.psum, ep.plogit_sum, ep.pamax_val, ep.pamax_idx, chunk_stats);
+      FLCE_CUDA(cudaGetLastError());
+      ++g_kernel_launches;
+    }
+    // ---- per-row losses, then the gradient coefficients (upstream gradient = 1)
+    finalize_rows_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
+        static_cast<int>(rows), rm, tgt, p->ce_weight, chunk_stats, args->norm, out->lse + r0, out->target_prob + r0,
+        out->loss_rows + r0, out->z_loss_rows != nullptr ? out->z_loss_rows + r0 : nullptr,
+        out->correct_rows != nullptr ? out->correct_rows + r0 : nullptr,
+        out->predicted_tokens != nullptr ? reinterpret_cast<long long*>(out->predicted_tokens) + r0 : nullptr);
+    FLCE_CUDA(cudaGetLastError());
+    ++g_kernel_launches;
+    coef_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
+        static_cast<int>(rows), rm, tgt, p->ce_weight, out->lse + r0, out->target_prob + r0, args->norm, nullptr, 0, c1, c2, c3);
+    FLCE_CUDA(cudaGetLastError());
+    ++g_kernel_launches;
+    // ---- logits -> logit gradient, in place
+    {
+      const int tpb = 256;
+      dim3 grid(static_cast<unsigned>(ceil_div(ceil_div(p->vocab, 8), tpb)), static_cast<unsigned>(rows), 1);
+      ProfileSlot* slot = profile_begin(kKindOther, stream);
+      dz_inplace_kernel<<<grid, tpb, 0, stream>>>(slab, plan.ld_slab, static_cast<int>(rows), static_cast<int>(p->vocab), fmt16,
+                                                  tgt, p->vocab_offset, out->lse + r0, c1, c2, c3, p->ce_weight,
+                                                  p->softcap > 0.f ? 1.f / p->softcap : 0.f);
+      profile_end(slot, stream);
+      FLCE_CUDA(cudaGetLastError());
+      ++g_kernel_launches;
+    }
+    // ---- grad_input[chunk] = dZ . W          (M = rows, N = hidden, K = vocab; B is MN-major)
+    if (args->grad_input != nullptr) {
+      StoreEpilogue::Params ep;
+      ep.m_rows = static_cast<int>(rows);
+      ep.n_cols = static_cast<int>(p->hidden);
+      ep.acc_in = nullptr;
+      ep.acc_out = nullptr;
+      ep.ld_acc = 0;
+      ep.out = static_cast<uint8_t*>(args->grad_input) + static_cast<size_t>(r0) * p->hidden * esize_out;
+      ep.ld_out = p->hidden;
+      ep.out_fmt = grads_fp32 ? kOutFp32 : fmt16;
+      Operand a{slab, rows, p->vocab, plan.ld_slab, 0};
+      Operand b{p->w, p->hidden, p->vocab, p->ld_w, 1};
+      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, rows, p->hidden, p->vocab, 0, true,
+                                                         ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    // ---- grad_weight (+)= dZ^T . X[chunk]    (M = vocab, N = hidden, K = rows; both operands MN-major)
+    if (args->grad_weight != nullptr) {
+      StoreEpilogue::Params ep;
+      ep.m_rows = static_cast<int>(p->vocab);
+      ep.n_cols = static_cast<int>(p->hidden);
+      const bool first = c == 0, last = c == plan.n_chunks - 1;
+      float* acc = grads_fp32 ? static_cast<float*>(args->grad_weight) : dw_acc;
+      ep.acc_in = first ? nullptr : acc;
+      ep.acc_out = (grads_fp32 || !last) ? acc : nullptr;
+      ep.ld_acc = p->hidden;
+      ep.out = (!grads_fp32 && last) ? args->grad_weight : nullptr;
+      ep.ld_out = p->hidden;
+      ep.out_fmt = fmt16;
+      Operand a{slab, p->vocab, rows, plan.ld_slab, 1};
+      Operand b{x_chunk, p->hidden, rows, p->ld_x, 1};
+      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0, true,
+                                                          ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    if (args->grad_bias != nullptr) {
+      colsum_accumulate_kernel<<<static_cast<unsigned>(ceil_div(p->vocab, 64)), 1024, 0, stream>>>(
+          slab, plan.ld_slab, static_cast<int>(rows), static_cast<int>(p->vocab), fmt16, args->grad_bias, c != 0);
+      FLCE_CUDA(cudaGetLastError());
+      ++g_kernel_launches;
+    }
+  }
+  if (out->scalars != nullptr) {
+    reduce_rows_kernel<<<1, kRedThreads, 0, stream>>>(static_cast<int>(p->n_rows), out->loss_rows, out->z_loss_rows,
+                                                     out->correct_rows, args->norm, out->scalars);
+    FLCE_CUDA(cudaGetLastError());
+    ++g_kernel_launches;
+  }
+  return FLCE_OK;
+}
+
+int flce_b200_scale_gradient(void* data, int64_t n, int32_t dtype, const float* scale, void* stream_) {
+  if (data == nullptr || scale == nullptr || n <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "bad scale_gradient arguments");
+  if (dtype < FLCE_BF16 || dtype > FLCE_FP32) return fail(FLCE_ERR_INVALID_ARGUMENT, "bad dtype");
+  DeviceState* dev;
+  int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  const int fmt = dtype == FLCE_FP32 ? kOutFp32 : (dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
+  scale_inplace_kernel<<<dev->sm_count * 8, 256, 0, static_cast<cudaStream_t>(stream_)>>>(data, n, fmt, scale);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   return FLCE_OK;
 }
 

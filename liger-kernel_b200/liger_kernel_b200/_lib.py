@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libflce_b200.so")
 
 FLCE_BF16, FLCE_FP16, FLCE_FP32 = 0, 1, 2
 FLCE_MEAN, FLCE_SUM, FLCE_NONE = 0, 1, 2
-PHASE_FORWARD, PHASE_BACKWARD = 0, 1
+PHASE_FORWARD, PHASE_BACKWARD, PHASE_FUSED = 0, 1, 2
 ROWSTAT_PLANES = 6
 FLAG_ARGMAX = 1
 
@@ -24,6 +24,8 @@ EXPORTS = (
     "flce_b200_forward",
     "flce_b200_backward",
     "flce_b200_backward_plan",
+    "flce_b200_forward_backward",
+    "flce_b200_scale_gradient",
     "flce_b200_gemm",
     "flce_b200_check_device_status",
     "flce_b200_profile_enable",
@@ -67,6 +69,13 @@ class BackwardArgs(C.Structure):
     ]
 
 
+class FusedArgs(C.Structure):
+    _fields_ = [
+        ("out", C.POINTER(ForwardOut)), ("norm", C.c_void_p), ("grad_dtype", C.c_int32),
+        ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
+    ]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -85,6 +94,10 @@ def _load():
     lib.flce_b200_forward_finalize.argtypes = [P, vp, vp, F, vp]
     lib.flce_b200_forward.argtypes = [P, vp, vp, F, vp, sz, vp]
     lib.flce_b200_backward.argtypes = [P, A, vp, sz, sz, vp]
+    lib.flce_b200_forward_backward.argtypes = [P, C.POINTER(FusedArgs), vp, sz, sz, vp]
+    lib.flce_b200_forward_backward.restype = C.c_int
+    lib.flce_b200_scale_gradient.argtypes = [vp, i64, i32, vp, vp]
+    lib.flce_b200_scale_gradient.restype = C.c_int
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]

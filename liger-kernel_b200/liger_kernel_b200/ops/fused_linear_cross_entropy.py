@@ -6,11 +6,15 @@ Same call surface as the reference's ``src/liger_kernel/ops/fused_linear_cross_e
 ``libflce_b200.so`` (tcgen05 + TMA kernels) through its C ABI.  torch is used for device
 memory and the current stream only.  There is no CPU or eager fallback.
 
+Two execution modes (``MODE`` below, or the environment variable ``LIGER_B200_FLCE_MODE``):
+* ``"recompute"``: forward computes only the loss (sweep 1); ``backward`` recomputes the logits tile by tile
+  (sweep 2) with the upstream gradient folded in.  8.N.H.V tensor FLOPs, smallest memory, any reduction.
+* ``"single_sweep"``: when a gradient is required and the reduction is mean or sum, forward also forms the
+  gradients, as the reference does (``ops/fused_linear_cross_entropy.py:395-435``), from a bounded 16-bit copy of each
+  token chunk's logits: 6.N.H.V tensor FLOPs.  The first ``backward`` hands the stored gradients off (scaled on the
+  device if the upstream gradient is not 1); a repeated ``backward`` falls back to the recompute sweep.
+
 Differences from the reference that a caller can observe:
-* forward computes only the loss; gradients are produced in ``backward`` by a second sweep
-  that recomputes the logits tile by tile (the reference computes them in forward and keeps
-  them, ``ops/fused_linear_cross_entropy.py:395-435``).  A repeated backward therefore just
-  recomputes, and ``reduction="none"`` needs no special path.
 * logits stay fp32 from accumulator to loss (the reference rounds them to the input dtype).
 * there is no host synchronisation (the reference reads the non-ignored count with ``.item()``).
 """
@@ -18,18 +22,22 @@ Differences from the reference that a caller can observe:
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
 
 from .. import _lib
-from .._lib import BackwardArgs, ForwardOut, Problem, check, lib
+from .._lib import BackwardArgs, ForwardOut, FusedArgs, Problem, check, lib
 
 _DTYPES = {torch.bfloat16: _lib.FLCE_BF16, torch.float16: _lib.FLCE_FP16, torch.float32: _lib.FLCE_FP32}
 _REDUCTIONS = {"mean": _lib.FLCE_MEAN, "sum": _lib.FLCE_SUM, "none": _lib.FLCE_NONE}
 
 # bytes of logit-gradient slab the backward sweep may use (N x slab columns, 16-bit)
 SLAB_BUDGET_BYTES = 1 << 30
+# bytes of logits copy the single-sweep mode may use (chunk rows x V, 16-bit)
+CHUNK_BUDGET_BYTES = 5 << 29
+MODE = os.environ.get("LIGER_B200_FLCE_MODE", "recompute")
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -181,6 +189,42 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
     return gx, gw, gb
 
 
+def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True, need_bias=False, grad_dtype=None,
+                             chunk_budget=None):
+    """Loss and gradients (for an upstream gradient of 1) in one pass over token chunks.
+    Returns (outputs dict, norm, grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``."""
+    dev = prep.device
+    gd = prep.dtype if grad_dtype is None else grad_dtype
+    budget = CHUNK_BUDGET_BYTES if chunk_budget is None else int(chunk_budget)
+    hp = prep.x.shape[1]
+    with torch.cuda.device(dev):
+        norm = torch.empty(4, dtype=torch.float32, device=dev)
+        out = _forward_outputs(prep)
+        fo = _as_forward_out(out)
+        gx = torch.empty((prep.n_rows, hp), dtype=gd, device=dev) if need_input else None
+        gw = torch.empty((prep.vocab, hp), dtype=gd, device=dev) if need_weight else None
+        gb = torch.empty(prep.vocab, dtype=torch.float32, device=dev) if need_bias else None
+        args = FusedArgs()
+        args.out = C.pointer(fo)
+        args.norm = norm.data_ptr()
+        args.grad_dtype = _DTYPES[gd]
+        args.grad_input = None if gx is None else gx.data_ptr()
+        args.grad_weight = None if gw is None else gw.data_ptr()
+        args.grad_bias = None if gb is None else gb.data_ptr()
+        ws = prep.workspace(_lib.PHASE_FUSED, budget)
+        check(lib.flce_b200_forward_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
+    return out, norm, gx, gw, gb
+
+
+def scale_gradient_(t: Optional[torch.Tensor], scale: torch.Tensor):
+    """In-place ``t *= scale`` with a device-resident fp32 scalar; a no-op on the device when the scalar is 1."""
+    if t is None:
+        return None
+    with torch.cuda.device(t.device):
+        check(lib.flce_b200_scale_gradient(_ptr(t), t.numel(), _DTYPES[t.dtype], _ptr(scale), _stream(t.device)))
+    return t
+
+
 def _autocast_operands(_input, weight, bias):
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
@@ -247,6 +291,24 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
     ):
         ctx.in_dtypes = (_input.dtype, weight.dtype, None if bias is None else bias.dtype)
         x, w, b = _autocast_operands(_input, weight, bias)
+        ctx.stored_grads = None
+        needs = (_input.requires_grad, weight.requires_grad, bias is not None and bias.requires_grad)
+        if MODE == "single_sweep" and reduction in ("mean", "sum") and any(needs):
+            assert isinstance(return_z_loss, bool), f"return_z_loss must be True or False. Got: {return_z_loss}"
+            prep = _Prepared(x, w, target, b, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
+                             use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)
+            out, norm, gx, gw, gb = flce_single_sweep_device(prep, needs[0], needs[1], needs[2])
+            ctx.stored_grads = (gx, gw, gb)
+            ctx.flce_saved = (prep, out["lse"], out["target_prob"], norm)
+            ctx.has_bias = bias is not None
+            loss = out["scalars"][0]
+            z_loss = out["scalars"][1].to(prep.dtype) if return_z_loss else None
+            token_accuracy = out["scalars"][2] if return_token_accuracy else None
+            predicted_tokens = out["predicted_tokens"] if return_predicted_tokens else None
+            nondiff = [t for t in (z_loss, token_accuracy, predicted_tokens) if t is not None]
+            if nondiff:
+                ctx.mark_non_differentiable(*nondiff)
+            return loss, z_loss, token_accuracy, predicted_tokens
         loss, z_loss, token_accuracy, predicted_tokens, saved = fused_linear_cross_entropy_forward(
             x, w, target, ce_weight=ce_weight, bias=b, ignore_index=ignore_index, lse_square_scale=lse_square_scale,
             label_smoothing=label_smoothing, reduction=reduction, softcap=softcap, return_z_loss=return_z_loss,
@@ -264,7 +326,22 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
     def backward(ctx, grad_output, grad_output2=None, grad_output3=None, grad_output4=None):
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         need_b = ctx.has_bias and ctx.needs_input_grad[3]
-        gx, gw, gb = fused_linear_cross_entropy_backward(grad_output, ctx.flce_saved, need_x, need_w, need_b)
+        if ctx.stored_grads is not None:
+            # single-sweep mode, first backward: hand the stored gradients off (scaled on the device when needed)
+            gx, gw, gb = ctx.stored_grads
+            ctx.stored_grads = None
+            prep = ctx.flce_saved[0]
+            go = grad_output.detach().to(device=prep.device, dtype=torch.float32).reshape(1)
+            h = prep.hidden
+            gx = scale_gradient_(gx, go)
+            gw = scale_gradient_(gw, go)
+            gb = scale_gradient_(gb, go)
+            if gx is not None and gx.shape[1] != h:
+                gx = gx[:, :h].contiguous()
+            if gw is not None and gw.shape[1] != h:
+                gw = gw[:, :h].contiguous()
+        else:
+            gx, gw, gb = fused_linear_cross_entropy_backward(grad_output, ctx.flce_saved, need_x, need_w, need_b)
         dx, dw, db = ctx.in_dtypes
         gx = None if gx is None else gx.to(dx)
         gw = None if gw is None else gw.to(dw)

@@ -276,3 +276,54 @@ def test_full_size_properties():
     gc = (pc - hit) * (t != -100)[:, None] / n_valid
     dw_ref = gc.t() @ x.double()
     assert_close(wd.grad[vs].float().cpu(), dw_ref.float().cpu(), 8e-3 * float(dw_ref.abs().max()), 5e-2, "grad_weight rows")
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# single-sweep mode (gradients formed in forward from a 16-bit copy of each token chunk's logits)
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.fixture
+def single_sweep(monkeypatch):
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+
+    monkeypatch.setattr(mod, "MODE", "single_sweep")
+    return mod
+
+
+@pytest.mark.parametrize("B,T,H,V", [(8, 128, 1024, 4096), (4, 47, 31, 123)])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("feat", FEATURES)
+def test_single_sweep_correctness(single_sweep, B, T, H, V, reduction, bias, feat):
+    x, w, t, b, _ = make_inputs(B * T, H, V, torch.bfloat16, seed=B * T + V + 1, bias=bias,
+                                ignore_index=feat.get("ignore_index", -100))
+    kw = dict(reduction=reduction, **feat)
+    res = run_cuda(x, w, t, bias=b, **kw)
+    _check(res, oracle_for(x, w, t, bias=b, **kw), torch.bfloat16, reduction, B * T)
+
+
+def test_single_sweep_many_chunks_weights_scaling_and_upstream_gradient(single_sweep, monkeypatch):
+    x, w, t, b, cw = make_inputs(1100, 96, 700, torch.bfloat16, seed=21, bias=True, ce_weight=True)
+    monkeypatch.setattr(single_sweep, "CHUNK_BUDGET_BYTES", 256 * 704 * 2)      # 256-row chunks -> 5 chunks
+    for kw, use_cw, go in ((dict(label_smoothing=0.1), cw, None), (dict(use_token_scaling=True), None, None),
+                           (dict(lse_square_scale=1e-3), None, 2.5)):
+        res = run_cuda(x, w, t, bias=b, ce_weight=use_cw, grad_output=go, **kw)
+        ora = oracle_for(x, w, t, bias=b, ce_weight=use_cw, grad_output=go, **kw)
+        _check(res, ora, torch.bfloat16, "mean", 1100)
+
+
+def test_single_sweep_all_ignored_and_repeated_backward(single_sweep):
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Fn
+
+    x, w, t, _, _ = make_inputs(256, 128, 1000, torch.bfloat16, seed=3, ignore_frac=1.1)
+    res = run_cuda(x, w, t)
+    assert float(res["loss"]) == 0.0 and float(res["grad_input"].abs().max()) == 0.0 and float(res["grad_weight"].abs().max()) == 0.0
+    x, w, t, _, _ = make_inputs(200, 96, 500, torch.bfloat16, seed=9)
+    xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    loss = Fn.apply(xd, wd, t.cuda())[0]
+    loss.backward(retain_graph=True)          # stored gradients
+    g1 = wd.grad.clone()
+    loss.backward()                           # second time: recompute sweep
+    assert_close((wd.grad - g1).float().cpu(), g1.float().cpu(), 8e-3 * float(g1.abs().max()), 5e-2, "second backward")
+    # reduction "none" is served by the two-sweep path even in this mode
+    res = run_cuda(x, w, t, reduction="none", grad_output=torch.rand(200) + 0.5)
+    assert res["grad_input"].shape == (200, 96)
