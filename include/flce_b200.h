@@ -95,6 +95,16 @@ typedef struct flce_backward_args {
   float* grad_bias;          /* [vocab] fp32, or NULL                                               */
   int32_t slab_begin;        /* run only vocabulary slabs [slab_begin, slab_end) of the plan reported by  */
   int32_t slab_end;          /* flce_b200_backward_plan; 0,0 = all slabs                                  */
+  /* Optional, for callers that fed 16-bit term splits of fp32 tensors to the logits GEMM (all zero = off):
+   * grad_weight = dZ^T . proj_x ([vocab, proj_x_cols]) and grad_input = dZ . proj_w ([n_rows, proj_w_cols]) are then
+   * formed against these narrower term matrices instead of x / w, in fp32; with split_logit_grad the 16-bit
+   * rounding residual of dZ is kept in a second slab and its products with the first lo_cols_* columns are added. */
+  const void* proj_x;        /* [n_rows, ld_proj_x] 16-bit, or NULL = x                                    */
+  int64_t proj_x_cols, ld_proj_x;
+  const void* proj_w;        /* [vocab, ld_proj_w] 16-bit, or NULL = w                                     */
+  int64_t proj_w_cols, ld_proj_w;
+  int32_t split_logit_grad;
+  int64_t lo_cols_x, lo_cols_w;
 } flce_backward_args_t;
 
 typedef struct flce_fused_args {
@@ -106,7 +116,7 @@ typedef struct flce_fused_args {
   float* grad_bias;              /* [vocab] fp32, or NULL                                                     */
 } flce_fused_args_t;
 
-enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1, FLCE_PHASE_FUSED = 2 };
+enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1, FLCE_PHASE_FUSED = 2, FLCE_PHASE_BACKWARD_SPLIT = 3 };
 
 /* Bytes of scratch the given phase needs for this problem (0 on invalid input).
  * `slab_budget_bytes` caps the logit-gradient slab of the backward pass (0 = default 1 GiB). */
@@ -173,6 +183,14 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
  * 'none' is not available here.  Workspace: flce_b200_workspace_bytes(p, FLCE_PHASE_FUSED, budget). */
 int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t* args, void* workspace,
                                size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
+
+/* fp32 inputs on 16-bit tensor cores: writes 16-bit terms of src (term 0 = round(v), term 1 = round(v - term 0),
+ * term 2 = round of what is left) side by side: block b of dst, columns [b*block_cols, b*block_cols + cols), holds
+ * term pattern[b] (host array of n_blocks <= 8 entries in {0,1,2}); padding columns are zero.  With X split as
+ * (0,0,0,1,1,2) and W as (0,1,2,0,1,0) the product of the two wide matrices is x.w to about 2^-24.  No counterpart
+ * in the reference, whose fp32 path is a cuBLAS fp32 GEMM (ops/fused_linear_cross_entropy.py:114). */
+int flce_b200_split_fp32(const float* src, int64_t rows, int64_t cols, int64_t ld_src, void* dst, int64_t ld_dst,
+                         int64_t block_cols, const int32_t* pattern, int32_t n_blocks, int32_t dst_dtype, void* stream);
 
 /* data[i] *= *scale for n elements of the given dtype; a no-op when the device-resident scale equals 1 (tested on
  * the device, no host synchronisation).  Replaces element_mul_kernel and the torch.equal test before it

@@ -223,6 +223,7 @@ struct DzEpilogue {
     const float* c2;          // [M]
     const float* c3;          // [M]
     void* dz;                 // [M][ld_dz] 16-bit
+    void* dz_lo;              // optional second slab: 16-bit rounding residual of dz (fp32-input path), or null
     long long ld_dz;
     int out_fmt;              // kOutBf16 / kOutFp16
   };
@@ -305,6 +306,15 @@ struct DzEpilogue {
     }
     store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.dz) + static_cast<size_t>(row) * p.ld_dz + col), g,
                   p.out_fmt);
+    if (p.dz_lo != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float hi = (p.out_fmt == kOutBf16) ? __bfloat162float(__float2bfloat16_rn(g[j])) : __half2float(__float2half_rn(g[j]));
+        g[j] -= hi;
+      }
+      store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.dz_lo) + static_cast<size_t>(row) * p.ld_dz + col), g,
+                    p.out_fmt);
+    }
   }
 
   __device__ __forceinline__ void end(const Params&) {}

@@ -33,6 +33,9 @@ static int fail(int code, const char* fmt, ...) {
 // ------------------------------------------------------------------ process-wide options
 static long long g_raster_bytes = 32ll << 20;  // bytes of A tiles kept hot per raster group
 static int g_cta_pair = 1;                      // use CTA pairs (cta_group::2) for the FLCE GEMMs
+static int g_poll_sleep_ns = 0;                 // epilogue back-off while waiting for an accumulator
+static int g_l2_hints = 0;                      // 1: mark streamed operands evict-first and re-read ones evict-last
+static int g_n_group = 0;                       // n-fastest raster: n-tiles per group (0 = all)
 
 // ------------------------------------------------------------------ optional per-kernel timing
 // When enabled, every tensor-core launch is bracketed by a pair of CUDA events on the caller's stream;
@@ -169,9 +172,17 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   shape.m_tiles = static_cast<int>(ceil_div(M, kBlockM * kCtas));
   shape.n_tiles = static_cast<int>(ceil_div(N, kBlockN));
   shape.k_blocks = static_cast<int>(ceil_div(K, kBlockK));
+  shape.poll_sleep_ns = g_poll_sleep_ns;
+  shape.hint_a = 0;
+  shape.hint_b = 0;
+  if (g_l2_hints) {
+    // sweeps over the vocabulary re-read X tiles (A) and stream W (B); the gradient GEMMs stream dZ (A) and re-read B
+    shape.hint_a = n_fastest ? 1 : 2;
+    shape.hint_b = n_fastest ? 2 : 1;
+  }
   if (n_fastest) {
     shape.group_along_m = 0;
-    shape.group = shape.n_tiles;
+    shape.group = (g_n_group > 0 && g_n_group < shape.n_tiles) ? g_n_group : shape.n_tiles;
   } else {
     shape.group_along_m = 1;
     long long g = g_raster_bytes / (raster_row_bytes > 0 ? raster_row_bytes : 1);
@@ -488,6 +499,39 @@ __global__ void colsum_accumulate_kernel(const uint16_t* dz, long long ld, int m
   }
 }
 
+// fp32 -> sum of 16-bit terms: term 0 = round(v), term 1 = round(v - term0), term 2 = round(v - term0 - term1).
+// Block b of the destination (columns [b * block_cols, (b+1) * block_cols)) receives term pattern[b]; columns beyond
+// `cols` inside a block are zero.
+struct SplitPattern { int term[8]; };
+__global__ void split_fp32_kernel(const float* src, long long rows, long long cols, long long ld_src, uint16_t* dst,
+                                  long long ld_dst, long long block_cols, SplitPattern pat, int n_blocks, int fmt) {
+  const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = blockIdx.y;
+  if (row >= rows || col >= block_cols) return;
+  float term[3] = {0.f, 0.f, 0.f};
+  if (col < cols) {
+    float v = src[row * ld_src + col];
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+      const float r = (fmt == kOutBf16) ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
+      term[t] = r;
+      v -= r;
+    }
+  }
+  for (int b = 0; b < n_blocks; ++b) {
+    const float t = term[pat.term[b]];
+    uint16_t bits;
+    if (fmt == kOutBf16) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(t);
+      bits = *reinterpret_cast<const uint16_t*>(&h);
+    } else {
+      const __half h = __float2half_rn(t);
+      bits = *reinterpret_cast<const uint16_t*>(&h);
+    }
+    dst[row * ld_dst + b * block_cols + col] = bits;
+  }
+}
+
 // grad_bias[j] (+)= sum over rows of the 16-bit slab column j; one block per 64 columns, ordered sum
 __global__ void colsum_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out) {
   __shared__ float part[16][64];
@@ -647,6 +691,20 @@ int flce_b200_set_option(const char* name, int64_t value) {
     g_cta_pair = value != 0;
     return FLCE_OK;
   }
+  if (strcmp(name, "poll_sleep_ns") == 0) {
+    if (value < 0 || value > 100000) return fail(FLCE_ERR_INVALID_ARGUMENT, "poll_sleep_ns out of range");
+    g_poll_sleep_ns = static_cast<int>(value);
+    return FLCE_OK;
+  }
+  if (strcmp(name, "l2_hints") == 0) {
+    g_l2_hints = value != 0;
+    return FLCE_OK;
+  }
+  if (strcmp(name, "raster_n_group") == 0) {
+    if (value < 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "raster_n_group must be >= 0");
+    g_n_group = static_cast<int>(value);
+    return FLCE_OK;
+  }
   return fail(FLCE_ERR_INVALID_ARGUMENT, "unknown option '%s'", name);
 }
 
@@ -655,6 +713,10 @@ size_t flce_b200_workspace_bytes(const flce_problem_t* p, int phase, size_t slab
   if (phase == FLCE_PHASE_FORWARD) return forward_plan(p).total;
   if (phase == FLCE_PHASE_BACKWARD) return backward_plan(p, slab_budget_bytes, true).total;
   if (phase == FLCE_PHASE_FUSED) return fused_plan(p, slab_budget_bytes, true).total;
+  if (phase == FLCE_PHASE_BACKWARD_SPLIT) {
+    const BackwardPlan b = backward_plan(p, slab_budget_bytes, false);
+    return b.coef_bytes + 2 * b.slab_bytes;
+  }
   fail(FLCE_ERR_INVALID_ARGUMENT, "unknown phase %d", phase);
   return 0;
 }
@@ -852,8 +914,26 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const bool grads_fp32 = args->grad_dtype == FLCE_FP32;
+  // projection operands: by default the problem's own x and w; a caller that fed split high/low 16-bit terms of
+  // fp32 tensors to the logits GEMM projects onto narrower term matrices instead
+  const void* px = args->proj_x != nullptr ? args->proj_x : p->x;
+  const long long px_cols = args->proj_x != nullptr ? args->proj_x_cols : p->hidden;
+  const long long ld_px = args->proj_x != nullptr ? args->ld_proj_x : p->ld_x;
+  const void* pw = args->proj_w != nullptr ? args->proj_w : p->w;
+  const long long pw_cols = args->proj_w != nullptr ? args->proj_w_cols : p->hidden;
+  const long long ld_pw = args->proj_w != nullptr ? args->ld_proj_w : p->ld_w;
+  const bool split = args->split_logit_grad != 0;
+  if (px_cols <= 0 || pw_cols <= 0 || px_cols % 8 != 0 || pw_cols % 8 != 0 || ld_px % 8 != 0 || ld_pw % 8 != 0 ||
+      ld_px < px_cols || ld_pw < pw_cols)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "projection operands need column counts and pitches that are multiples of 8");
+  if ((args->proj_x != nullptr || args->proj_w != nullptr || split) && !grads_fp32)
+    return fail(FLCE_ERR_UNSUPPORTED, "projection operands and the split logit gradient need fp32 gradient outputs");
+  if (split && (args->lo_cols_x <= 0 || args->lo_cols_x > px_cols || args->lo_cols_w <= 0 || args->lo_cols_w > pw_cols ||
+                args->lo_cols_x % 8 != 0 || args->lo_cols_w % 8 != 0))
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "lo_cols_x / lo_cols_w must be positive multiples of 8 within the projection widths");
   const BackwardPlan plan = backward_plan(p, slab_budget_bytes, true);
-  const size_t needed = plan.coef_bytes + plan.slab_bytes + ((args->grad_input != nullptr && !grads_fp32) ? plan.acc_bytes : 0);
+  const size_t needed = plan.coef_bytes + plan.slab_bytes * (split ? 2 : 1) +
+                        ((args->grad_input != nullptr && !grads_fp32) ? plan.acc_bytes : 0);
   if (workspace == nullptr || workspace_bytes < needed)
     return fail(FLCE_ERR_WORKSPACE, "backward needs %zu bytes of workspace, got %zu", needed, workspace_bytes);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
@@ -863,7 +943,8 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
   float* c2 = c1 + p->n_rows;
   float* c3 = c2 + p->n_rows;
   uint16_t* dz = reinterpret_cast<uint16_t*>(ws + plan.coef_bytes);
-  float* dx_acc = reinterpret_cast<float*>(ws + plan.coef_bytes + plan.slab_bytes);
+  uint16_t* dz_lo = split ? reinterpret_cast<uint16_t*>(ws + plan.coef_bytes + plan.slab_bytes) : nullptr;
+  float* dx_acc = reinterpret_cast<float*>(ws + plan.coef_bytes + plan.slab_bytes);   // unused with fp32 gradients
 
   int slab_begin = args->slab_begin, slab_end = args->slab_end;
   if (slab_begin == 0 && slab_end == 0) slab_end = plan.n_slabs;
@@ -899,6 +980,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       ep.c2 = c2;
       ep.c3 = c3;
       ep.dz = dz;
+      ep.dz_lo = dz_lo;
       ep.ld_dz = plan.ld_dz;
       ep.out_fmt = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
       Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
@@ -911,45 +993,77 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
     if (args->grad_weight != nullptr) {
       StoreEpilogue::Params ep;
       ep.m_rows = static_cast<int>(cols);
-      ep.n_cols = static_cast<int>(p->hidden);
+      ep.n_cols = static_cast<int>(px_cols);
       ep.acc_in = nullptr;
       ep.acc_out = nullptr;
       ep.ld_acc = 0;
-      ep.out = static_cast<uint8_t*>(args->grad_weight) + static_cast<size_t>(v0) * p->hidden * esize_out;
-      ep.ld_out = p->hidden;
+      ep.out = static_cast<uint8_t*>(args->grad_weight) + static_cast<size_t>(v0) * px_cols * esize_out;
+      ep.ld_out = px_cols;
       ep.out_fmt = grads_fp32 ? kOutFp32 : (p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
       Operand a{dz, cols, p->n_rows, plan.ld_dz, 1};
-      Operand b{p->x, p->hidden, p->n_rows, p->ld_x, 1};
-      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, cols, p->hidden, p->n_rows, 0, true,
+      Operand b{px, px_cols, p->n_rows, ld_px, 1};
+      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, cols, px_cols, p->n_rows, 0, true,
                                                           ep, stream);
       if (rc != FLCE_OK) return rc;
+      if (split) {  // rounding residual of dZ against the leading (high-order) columns of the projection operand
+        float* acc = reinterpret_cast<float*>(ep.out);
+        ep.n_cols = static_cast<int>(args->lo_cols_x);
+        ep.acc_in = acc;
+        ep.acc_out = acc;
+        ep.ld_acc = px_cols;
+        ep.out = nullptr;
+        Operand a2{dz_lo, cols, p->n_rows, plan.ld_dz, 1};
+        Operand b2{px, args->lo_cols_x, p->n_rows, ld_px, 1};
+        rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a2, b2, p->dtype, cols, args->lo_cols_x,
+                                                            p->n_rows, 0, true, ep, stream);
+        if (rc != FLCE_OK) return rc;
+      }
     }
     // ---- grad_input (+)= dZ . W[slab]        (M = n_rows, N = hidden, K = cols; B is MN-major)
     if (args->grad_input != nullptr) {
       StoreEpilogue::Params ep;
       ep.m_rows = static_cast<int>(p->n_rows);
-      ep.n_cols = static_cast<int>(p->hidden);
+      ep.n_cols = static_cast<int>(pw_cols);
       const bool first = s == 0, last = s == plan.n_slabs - 1;
       float* acc = grads_fp32 ? static_cast<float*>(args->grad_input) : dx_acc;
       ep.acc_in = first ? nullptr : acc;
       ep.acc_out = (last && !grads_fp32) ? nullptr : acc;
       if (plan.n_slabs == 1 && !grads_fp32) ep.acc_out = nullptr;
-      ep.ld_acc = p->hidden;
+      ep.ld_acc = pw_cols;
       ep.out = (last && !grads_fp32) ? args->grad_input : nullptr;
-      ep.ld_out = p->hidden;
+      ep.ld_out = pw_cols;
       ep.out_fmt = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
+      const uint16_t* pw_slab = static_cast<const uint16_t*>(pw) + v0 * ld_pw;
       Operand a{dz, p->n_rows, cols, plan.ld_dz, 0};
-      Operand b{w_slab, p->hidden, cols, p->ld_w, 1};
-      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, p->n_rows, p->hidden, cols, 0, true,
+      Operand b{pw_slab, pw_cols, cols, ld_pw, 1};
+      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, p->n_rows, pw_cols, cols, 0, true,
                                                          ep, stream);
       if (rc != FLCE_OK) return rc;
+      if (split) {
+        ep.n_cols = static_cast<int>(args->lo_cols_w);
+        ep.acc_in = acc;
+        ep.acc_out = acc;
+        ep.out = nullptr;
+        Operand a2{dz_lo, p->n_rows, cols, plan.ld_dz, 0};
+        Operand b2{pw_slab, args->lo_cols_w, cols, ld_pw, 1};
+        rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a2, b2, p->dtype, p->n_rows, args->lo_cols_w,
+                                                           cols, 0, true, ep, stream);
+        if (rc != FLCE_OK) return rc;
+      }
     }
     if (args->grad_bias != nullptr) {
       colsum_kernel<<<static_cast<unsigned>(ceil_div(cols, 64)), 1024, 0, stream>>>(
           dz, plan.ld_dz, static_cast<int>(p->n_rows), static_cast<int>(cols), p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16,
           args->grad_bias + v0);
       FLCE_CUDA(cudaGetLastError());
-  ++g_kernel_launches;
+      ++g_kernel_launches;
+      if (split) {
+        colsum_accumulate_kernel<<<static_cast<unsigned>(ceil_div(cols, 64)), 1024, 0, stream>>>(
+            dz_lo, plan.ld_dz, static_cast<int>(p->n_rows), static_cast<int>(cols),
+            p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16, args->grad_bias + v0, 1);
+        FLCE_CUDA(cudaGetLastError());
+        ++g_kernel_launches;
+      }
     }
   }
   return FLCE_OK;
@@ -1109,6 +1223,28 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
     FLCE_CUDA(cudaGetLastError());
     ++g_kernel_launches;
   }
+  return FLCE_OK;
+}
+
+int flce_b200_split_fp32(const float* src, int64_t rows, int64_t cols, int64_t ld_src, void* dst, int64_t ld_dst,
+                         int64_t block_cols, const int32_t* pattern, int32_t n_blocks, int32_t dst_dtype, void* stream_) {
+  if (src == nullptr || dst == nullptr || pattern == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL argument");
+  if (rows <= 0 || cols <= 0 || block_cols < cols || n_blocks < 1 || n_blocks > 8 || ld_dst < block_cols * n_blocks)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad split shape (rows %lld cols %lld block_cols %lld blocks %d ld_dst %lld)",
+                (long long)rows, (long long)cols, (long long)block_cols, n_blocks, (long long)ld_dst);
+  if (dst_dtype != FLCE_BF16 && dst_dtype != FLCE_FP16) return fail(FLCE_ERR_UNSUPPORTED, "terms must be bf16 or fp16");
+  if (rows > 65535) return fail(FLCE_ERR_INVALID_ARGUMENT, "split_fp32 handles at most 65535 rows per call");
+  SplitPattern pat;
+  for (int b = 0; b < 8; ++b) {
+    pat.term[b] = b < n_blocks ? pattern[b] : 0;
+    if (pat.term[b] < 0 || pat.term[b] > 2) return fail(FLCE_ERR_INVALID_ARGUMENT, "pattern entries must be 0, 1 or 2");
+  }
+  dim3 grid(static_cast<unsigned>(ceil_div(block_cols, 256)), static_cast<unsigned>(rows), 1);
+  split_fp32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(src, rows, cols, ld_src, static_cast<uint16_t*>(dst),
+                                                                       ld_dst, block_cols, pat, n_blocks,
+                                                                       dst_dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   return FLCE_OK;
 }
 

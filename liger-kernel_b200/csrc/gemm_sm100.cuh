@@ -67,6 +67,8 @@ struct GemmShape {
   int k_blocks;        // ceil(K / 64)
   int group;           // raster: tiles are walked in groups of `group` rows (or columns) of tiles
   int group_along_m;   // 1: a group is `group` m-tiles x all n-tiles, m fastest; 0: the transpose
+  int hint_a, hint_b;  // L2 eviction priority of the A / B loads: 0 default, 1 evict first, 2 evict last
+  int poll_sleep_ns;   // back-off of the epilogue warps while they wait for an accumulator
 };
 
 __device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& mt, int& nt) {
@@ -156,6 +158,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t policy_a = make_l2_policy(shape.hint_a);
+      const uint64_t policy_b = make_l2_policy(shape.hint_b);
       FLCE_TRACE_DECL(wait_empty);
       FLCE_TRACE_BEGIN(t_kernel);
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
@@ -178,8 +182,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t dst_a = smem_u32(ring_a + stage * Cfg::kABytes);
           const uint32_t dst_b = smem_u32(ring_b + stage * Cfg::kBBytes);
           auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
-            if constexpr (kCtas == 1) tma_load_2d(dst, map, signal_bar, x, y);
-            else tma_load_2d_pair(dst, map, signal_bar, x, y);
+            const bool is_a = (map == &map_a);
+            const int hint = is_a ? shape.hint_a : shape.hint_b;
+            if (hint == 0) {
+              if constexpr (kCtas == 1) tma_load_2d(dst, map, signal_bar, x, y);
+              else tma_load_2d_pair(dst, map, signal_bar, x, y);
+            } else {
+              const uint64_t pol = is_a ? policy_a : policy_b;
+              if constexpr (kCtas == 1) tma_load_2d_hint(dst, map, signal_bar, x, y, pol);
+              else tma_load_2d_pair_hint(dst, map, signal_bar, x, y, pol);
+            }
           };
           if constexpr (kAMajor == kMajorK) {
             load(dst_a, &map_a, k0, m0);                          // box: 64 k x 128 rows
@@ -277,7 +289,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM + row_in_tile;
       const int col0 = nt * kBlockN;
       FLCE_TRACE_BEGIN(t_w);
-      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase[acc], abort_flag, status, kDevTimeoutTmemFull);
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase[acc], abort_flag, status, kDevTimeoutTmemFull,
+                     static_cast<uint32_t>(shape.poll_sleep_ns));
       FLCE_TRACE_ADD(wait_tmem_full, t_w);
       if (!ok) break;
       FLCE_TRACE_BEGIN(t_b);

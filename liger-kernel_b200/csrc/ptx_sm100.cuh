@@ -86,10 +86,11 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // thread ran out of time (it then raises *abort_flag and records `code`) or
 // because another thread of the CTA already raised the flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+                                          int code, uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
+    if (sleep_ns != 0) __nanosleep(sleep_ns);   // back off: waits that are not latency-critical need not burn issue slots
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 0xFFu) == 0) {
       if (*abort_flag) return false;
@@ -110,6 +111,32 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// L2 eviction-priority policies for TMA loads: 1 = evict first (streamed once), 2 = evict last (re-read soon)
+__device__ __forceinline__ uint64_t make_l2_policy(int kind) {
+  uint64_t pol = 0;
+  if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  else if (kind == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int x, int y,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], "
+      "[%2], %5;" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t leader_bar, int x,
+                                                      int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, "
+      "{%3, %4}], [%2], %5;" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
 

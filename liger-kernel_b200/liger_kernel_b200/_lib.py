@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libflce_b200.so")
 
 FLCE_BF16, FLCE_FP16, FLCE_FP32 = 0, 1, 2
 FLCE_MEAN, FLCE_SUM, FLCE_NONE = 0, 1, 2
-PHASE_FORWARD, PHASE_BACKWARD, PHASE_FUSED = 0, 1, 2
+PHASE_FORWARD, PHASE_BACKWARD, PHASE_FUSED, PHASE_BACKWARD_SPLIT = 0, 1, 2, 3
 ROWSTAT_PLANES = 6
 FLAG_ARGMAX = 1
 
@@ -26,6 +26,7 @@ EXPORTS = (
     "flce_b200_backward_plan",
     "flce_b200_forward_backward",
     "flce_b200_scale_gradient",
+    "flce_b200_split_fp32",
     "flce_b200_gemm",
     "flce_b200_check_device_status",
     "flce_b200_profile_enable",
@@ -66,6 +67,9 @@ class BackwardArgs(C.Structure):
         ("grad_output_per_row", C.c_int32), ("grad_dtype", C.c_int32),
         ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
         ("slab_begin", C.c_int32), ("slab_end", C.c_int32),
+        ("proj_x", C.c_void_p), ("proj_x_cols", C.c_int64), ("ld_proj_x", C.c_int64),
+        ("proj_w", C.c_void_p), ("proj_w_cols", C.c_int64), ("ld_proj_w", C.c_int64),
+        ("split_logit_grad", C.c_int32), ("lo_cols_x", C.c_int64), ("lo_cols_w", C.c_int64),
     ]
 
 
@@ -98,6 +102,8 @@ def _load():
     lib.flce_b200_forward_backward.restype = C.c_int
     lib.flce_b200_scale_gradient.argtypes = [vp, i64, i32, vp, vp]
     lib.flce_b200_scale_gradient.restype = C.c_int
+    lib.flce_b200_split_fp32.argtypes = [vp, i64, i64, i64, vp, i64, i64, C.POINTER(C.c_int32), i32, i32, vp]
+    lib.flce_b200_split_fp32.restype = C.c_int
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]

@@ -61,6 +61,25 @@ def _pad_hidden(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
     return out
 
 
+_X_TERMS = (0, 0, 0, 1, 1, 2)   # paired with _W_TERMS: x0w0 + x0w1 + x0w2 + x1w0 + x1w1 + x2w0 = x.w to ~2^-24
+_W_TERMS = (0, 1, 2, 0, 1, 0)
+_PROJ_TERMS = (0, 1)            # projections use the two leading terms (2^-16)
+
+
+def _split_fp32(t: torch.Tensor, pattern, block_cols: int) -> torch.Tensor:
+    """[rows, cols] fp32 -> [rows, len(pattern) * block_cols] bf16 term blocks (see flce_b200_split_fp32)."""
+    t = t.contiguous()
+    rows, cols = t.shape
+    out = torch.empty((rows, len(pattern) * block_cols), dtype=torch.bfloat16, device=t.device)
+    pat = (C.c_int32 * len(pattern))(*pattern)
+    with torch.cuda.device(t.device):
+        for r0 in range(0, rows, 65535):
+            n = min(65535, rows - r0)
+            check(lib.flce_b200_split_fp32(_ptr(t[r0:r0 + n]), n, cols, t.stride(0), _ptr(out[r0:r0 + n]), out.stride(0),
+                                           block_cols, pat, len(pattern), _lib.FLCE_BF16, _stream(t.device)))
+    return out
+
+
 class _Prepared:
     """Validated, device-resident operands of one FLCE call and the matching C struct."""
 
@@ -88,8 +107,18 @@ class _Prepared:
         self.vocab = weight.shape[0]
         self.dtype = _input.dtype
         self.reduction = reduction
-        self.x = _pad_hidden(_input.detach())
-        self.w = _pad_hidden(weight.detach())
+        self.split = self.dtype == torch.float32
+        if self.split:
+            # fp32 inputs: 16-bit term splits side by side, so the same bf16 tensor-core kernels give fp32-level logits
+            self.block = (self.hidden + 7) // 8 * 8
+            x32, w32 = _input.detach(), weight.detach()
+            self.x = _split_fp32(x32, _X_TERMS, self.block)
+            self.w = _split_fp32(w32, _W_TERMS, self.block)
+            self.proj_x = _split_fp32(x32, _PROJ_TERMS, self.block)
+            self.proj_w = _split_fp32(w32, _PROJ_TERMS, self.block)
+        else:
+            self.x = _pad_hidden(_input.detach())
+            self.w = _pad_hidden(weight.detach())
         self.target = target.detach().to(device=self.device, dtype=torch.int64).contiguous()
         self.bias = None if bias is None else bias.detach().to(device=self.device, dtype=torch.float32).contiguous()
         self.ce_weight = None if ce_weight is None else ce_weight.detach().to(device=self.device, dtype=torch.float32).contiguous()
@@ -98,7 +127,7 @@ class _Prepared:
         p.vocab_total = self.vocab if vocab_total is None else int(vocab_total)
         p.vocab_offset = int(vocab_offset)
         p.ld_x, p.ld_w = self.x.stride(0), self.w.stride(0)
-        p.dtype = _DTYPES[self.dtype]
+        p.dtype = _lib.FLCE_BF16 if self.split else _DTYPES[self.dtype]
         p.reduction = _REDUCTIONS[reduction]
         p.ignore_index = int(ignore_index)
         p.label_smoothing = float(label_smoothing)
@@ -158,11 +187,18 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
     gd = prep.dtype if grad_dtype is None else grad_dtype
     budget = SLAB_BUDGET_BYTES if slab_budget is None else int(slab_budget)
     hp = prep.x.shape[1]
+    if prep.split:
+        gd = torch.float32
+        hp = prep.proj_x.shape[1]
     with torch.cuda.device(dev):
         gx = torch.empty((prep.n_rows, hp), dtype=gd, device=dev) if need_input else None
         gw = torch.empty((prep.vocab, hp), dtype=gd, device=dev) if need_weight else None
         gb = torch.empty(prep.vocab, dtype=torch.float32, device=dev) if need_bias else None
         args = BackwardArgs()
+        if prep.split:
+            args.proj_x, args.proj_x_cols, args.ld_proj_x = prep.proj_x.data_ptr(), hp, prep.proj_x.stride(0)
+            args.proj_w, args.proj_w_cols, args.ld_proj_w = prep.proj_w.data_ptr(), hp, prep.proj_w.stride(0)
+            args.split_logit_grad, args.lo_cols_x, args.lo_cols_w = 1, prep.block, prep.block
         args.lse, args.target_prob, args.norm = lse.data_ptr(), target_prob.data_ptr(), norm.data_ptr()
         go = None
         if grad_output is not None:
@@ -175,7 +211,7 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
         args.grad_input = None if gx is None else gx.data_ptr()
         args.grad_weight = None if gw is None else gw.data_ptr()
         args.grad_bias = None if gb is None else gb.data_ptr()
-        ws = prep.workspace(_lib.PHASE_BACKWARD, budget)
+        ws = prep.workspace(_lib.PHASE_BACKWARD_SPLIT if prep.split else _lib.PHASE_BACKWARD, budget)
         if slab_hook is None:
             check(lib.flce_b200_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
         else:
@@ -186,6 +222,10 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
                 check(lib.flce_b200_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget,
                                              _stream(dev)))
                 slab_hook(s * slab_cols.value, min(prep.vocab, (s + 1) * slab_cols.value), gw)
+        if prep.split:  # sum the term blocks: (dZ_hi + dZ_lo).t0 + dZ_hi.t1
+            b = prep.block
+            gx = None if gx is None else gx[:, :b] + gx[:, b:2 * b]
+            gw = None if gw is None else gw[:, :b] + gw[:, b:2 * b]
     return gx, gw, gb
 
 
@@ -293,7 +333,7 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
         x, w, b = _autocast_operands(_input, weight, bias)
         ctx.stored_grads = None
         needs = (_input.requires_grad, weight.requires_grad, bias is not None and bias.requires_grad)
-        if MODE == "single_sweep" and reduction in ("mean", "sum") and any(needs):
+        if MODE == "single_sweep" and reduction in ("mean", "sum") and any(needs) and x.dtype != torch.float32:
             assert isinstance(return_z_loss, bool), f"return_z_loss must be True or False. Got: {return_z_loss}"
             prep = _Prepared(x, w, target, b, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
                              use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)

@@ -327,3 +327,62 @@ def test_single_sweep_all_ignored_and_repeated_backward(single_sweep):
     # reduction "none" is served by the two-sweep path even in this mode
     res = run_cuda(x, w, t, reduction="none", grad_output=torch.rand(200) + 0.5)
     assert res["grad_input"].shape == (200, 96)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# fp32 inputs: 16-bit term splits on the same tensor-core kernels
+# ---------------------------------------------------------------------------------------------------------------
+def _check_fp32(res, ora, reduction):
+    scale = max(1.0, float(ora.loss.abs().max()))
+    # reference bars for fp32: mean 1e-5 / 5e-4, sum 1e-3 / 5e-2 (test_fused_linear_cross_entropy.py:115-123)
+    assert_close(res["loss"], ora.loss.float(), 1e-5 * scale, 2e-5, "loss")
+    for key, want in (("grad_input", ora.grad_input), ("grad_weight", ora.grad_weight), ("grad_bias", ora.grad_bias)):
+        if res.get(key) is None:
+            continue
+        atol = 2e-5 * max(float(want.abs().max()), 1e-30)
+        assert_close(res[key].float(), want.float(), atol, 5e-4, key)
+
+
+@pytest.mark.parametrize("B,T,H,V", [(8, 128, 1024, 4096), (4, 47, 31, 123)])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("feat", FEATURES)
+def test_correctness_fp32(B, T, H, V, reduction, bias, feat):
+    x, w, t, b, _ = make_inputs(B * T, H, V, torch.float32, seed=B * T + V + 2, bias=bias,
+                                ignore_index=feat.get("ignore_index", -100))
+    kw = dict(reduction=reduction, **feat)
+    res = run_cuda(x, w, t, bias=b, **kw)
+    assert res["grad_input"].dtype == torch.float32 and res["z_loss"].dtype == torch.float32
+    _check_fp32(res, oracle_for(x, w, t, bias=b, **kw), reduction)
+
+
+def test_config_c1_small_fp32_head():
+    """BASELINE config 1: N=1024 (B=2, T=512), H=1024, V=32000, fp32, X~N(0,1), W~N(0,1/H), 10 % ignored, mean."""
+    from liger_kernel_b200.ops.fused_linear_cross_entropy import _Prepared, flce_forward_device
+
+    x, w, t, _, _ = make_inputs(1024, 1024, 32000, torch.float32, seed=1234 + 1, ignore_frac=0.10, wscale=1024 ** -0.5)
+    ora = oracle_for(x, w, t)
+    res = run_cuda(x, w, t)
+    _check_fp32(res, ora, "mean")
+    prep = _Prepared(x.cuda(), w.cuda(), t.cuda(), None, None, -100, 0.0, 0.0, "mean", None, False)
+    out, _, _ = flce_forward_device(prep)
+    valid = t != -100
+    err = ((out["lse"].cpu().double() - ora.lse) .abs() / ora.lse.abs().clamp(min=1.0))[valid]
+    assert float(err.max()) <= 1e-5, float(err.max())
+    assert torch.equal(out["predicted_tokens"].cpu(), ora.predicted_tokens)
+
+
+@pytest.mark.parametrize("name", ["mean_default", "all_features", "qwen_style", "gemma_style_sum", "none_reduction", "ce_weight"])
+def test_golden_fp32_inputs_against_reference_outputs(name):
+    """fp32 inputs exactly as the reference saw them: outputs must agree with the reference's own to fp32 accuracy."""
+    rec, meta = load_golden(name)
+    x, w, t = torch.from_numpy(rec["x"]), torch.from_numpy(rec["w"]), torch.from_numpy(rec["target"])
+    kw = golden_kwargs(rec, meta)
+    bias, cw = kw.pop("bias"), kw.pop("ce_weight")
+    go = golden_grad_output(rec, meta)
+    res = run_cuda(x, w, t, bias=bias, ce_weight=cw, grad_output=go, **kw)
+    scale = max(1.0, float(np.abs(rec["ref_loss"]).max()))
+    assert_close(res["loss"], torch.from_numpy(rec["ref_loss"]), 2e-5 * scale, 2e-4, "loss vs reference")
+    for key in ("grad_input", "grad_weight"):
+        want = torch.from_numpy(rec["ref_" + key])
+        assert_close(res[key].float(), want, 5e-5 * float(want.abs().max()), 1e-3, key + " vs reference")
