@@ -134,46 +134,54 @@ class ClockSampler:
         return res
 
 
-def cpu_reference_rate(spec, seconds_budget, rows_per_chunk=256, max_rows=1024, seed=99):
-    """tokens/s of the torch Linear+CrossEntropy ground truth (fp32, autograd) on the host cores, measured
-    on the first rows of the workload with the full H and V."""
-    from oracle.flce_oracle import torch_linear_ce_reference
+class CpuReference:
+    """The torch Linear+CrossEntropy ground truth of the reference's tests (fp32, autograd backward) on the host cores,
+    fed with rows of the workload's shape at the full H and V.  The weight is built once, outside any timing."""
 
-    g = torch.Generator().manual_seed(seed)
-    H, V = spec["H"], spec["V"]
-    w = torch.randn(V, H, generator=g) * 0.02
-    kw = {k: v for k, v in spec["kw"].items() if k in ("label_smoothing", "lse_square_scale", "softcap", "reduction")}
-    done, t0 = 0, time.perf_counter()
-    while done < max_rows:
-        x = torch.randn(rows_per_chunk, H, generator=g)
-        t = torch.randint(0, V, (rows_per_chunk,), generator=g)
+    def __init__(self, spec, seed=99):
+        self.g = torch.Generator().manual_seed(seed)
+        self.H, self.V = spec["H"], spec["V"]
+        self.w = torch.randn(self.V, self.H, generator=self.g) * 0.02
+        self.kw = {k: v for k, v in spec["kw"].items() if k in ("label_smoothing", "lse_square_scale", "softcap", "reduction")}
+
+    def run_rows(self, rows):
+        from oracle.flce_oracle import torch_linear_ce_reference
+
+        x = torch.randn(rows, self.H, generator=self.g)
+        t = torch.randint(0, self.V, (rows,), generator=self.g)
         t[::20] = -100
-        torch_linear_ce_reference(x, w, t, **kw)
+        t0 = time.perf_counter()
+        torch_linear_ce_reference(x, self.w, t, **self.kw)
+        return time.perf_counter() - t0
+
+
+def cpu_reference_rate(spec, seconds_budget, rows_per_chunk=256, max_rows=1024):
+    """tokens/s over up to max_rows rows in chunks, stopping early once the time budget is spent."""
+    ref = CpuReference(spec)
+    ref.run_rows(32)  # warm the thread pool
+    done, busy = 0, 0.0
+    while done < max_rows and busy < seconds_budget:
+        busy += ref.run_rows(rows_per_chunk)
         done += rows_per_chunk
-        if time.perf_counter() - t0 > seconds_budget:
-            break
-    dt = time.perf_counter() - t0
-    return done / dt, done, dt
+    return done / busy, done, busy
 
 
 def run_reference(args, spec, rank, world):
     if rank != 0:
         return
     rows = 256
+    ref = CpuReference(spec)
     for _ in range(args.warmup):
-        cpu_reference_rate(spec, 1e9, rows, rows)
-    t0 = time.perf_counter()
-    total = 0
+        ref.run_rows(rows)
+    busy = 0.0
     for _ in range(args.steps):
-        _, done, _ = cpu_reference_rate(spec, 1e9, rows, rows)
-        total += done
-    dt = time.perf_counter() - t0
-    value = total / dt
+        busy += ref.run_rows(rows)
+    value = rows * args.steps / busy
     cores = torch.get_num_threads()
     sample = f"{rows} rows per step with the full H={spec['H']} and V={spec['V']} (fp32 torch Linear+CrossEntropy, autograd backward)"
     print(json.dumps({
         "impl": "reference", "metric": "flce_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * busy / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": NAMES[args.workload], "sample": sample},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
@@ -262,9 +270,24 @@ def run_ours(args, spec, rank, world, local_rank):
     if args.mode is not None:
         flce_op.MODE = args.mode
     peaks = load_peaks()
-    x, w, t = make_inputs(spec, device, 1234 + rank)
-    if world > 1:
-        dist.broadcast(w, 0)
+    from liger_kernel_b200.sharded import vocab_sharded_fused_linear_cross_entropy
+
+    vocab_lo = 0
+    if args.sharding == "vocab" and world > 1:
+        # replicated tokens, each rank owns a slice of the vocabulary (strong scaling of one problem)
+        x, w, t = make_inputs(spec, device, 1234)
+        per = (spec["V"] + world - 1) // world
+        vocab_lo = rank * per
+        w = w[vocab_lo:min(spec["V"], vocab_lo + per)].clone()
+    elif args.strong and world > 1:
+        # one global batch split by rows
+        x, w, t = make_inputs(spec, device, 1234)
+        n_loc = spec["N"] // world
+        x, t = x[rank * n_loc:(rank + 1) * n_loc].clone(), t[rank * n_loc:(rank + 1) * n_loc].clone()
+    else:
+        x, w, t = make_inputs(spec, device, 1234 + rank)
+        if world > 1:
+            dist.broadcast(w, 0)
     w.requires_grad_(True)
     x_host = x.cpu().pin_memory()
     t_host = t.cpu().pin_memory()
@@ -276,7 +299,10 @@ def run_ours(args, spec, rank, world, local_rank):
     def step(xin, tin):
         xin = xin.detach().requires_grad_(True)
         w.grad = None
-        if world > 1:
+        if world > 1 and args.sharding == "vocab":
+            skw = {k: v for k, v in kw.items() if k != "return_z_loss"}
+            loss = vocab_sharded_fused_linear_cross_entropy(xin, w, tin, vocab_lo, spec["V"], **skw)
+        elif world > 1:
             # global-batch loss; grad_weight is all-reduced slab by slab on a side stream inside backward
             skw = {k: v for k, v in kw.items() if k != "return_z_loss"}
             loss = token_sharded_fused_linear_cross_entropy(xin, w, tin, **skw)
@@ -341,11 +367,12 @@ def run_ours(args, spec, rank, world, local_rank):
             dist.destroy_process_group()
         return
     ms_step = ms_total / args.steps
-    tokens = N * world
+    strong = world > 1 and (args.strong or args.sharding == "vocab")
+    tokens = N if strong else N * world
     value = tokens / (ms_step * 1e-3)
-    flops_step = 8.0 * N * H * V  # per rank
+    flops_step = 8.0 * N * H * V / (world if strong else 1)  # per rank
     tflops = flops_step / (ms_step * 1e-3) / 1e12
-    kind_flops = 2.0 * N * H * V * args.steps  # algorithmic flops of each kernel kind over the timed region
+    kind_flops = 2.0 * N * H * V * args.steps / (world if strong else 1)  # algorithmic flops of each kernel kind, per rank
     dom = max(("stats", "dz", "dw", "dx"), key=lambda k: prof[k][0])
     dom_ms, dom_launches = prof[dom]
     achieved = kind_flops / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
@@ -355,9 +382,11 @@ def run_ours(args, spec, rank, world, local_rank):
     result = {
         "metric": "flce_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": NAMES[args.workload], "tokens_per_gpu": N, "hidden": H, "vocab": V,
-                   "parallelism": "single GPU" if world == 1 else f"token-sharded x{world}, NCCL all-reduce of grad_weight",
+        "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": NAMES[args.workload], "tokens_per_gpu": x.shape[0], "hidden": H, "vocab_per_gpu": w.shape[0],
+                   "parallelism": "single GPU" if world == 1 else (
+                       f"vocab-sharded x{world}: all-gather of row statistics, all-reduce of grad_input" if args.sharding == "vocab"
+                       else f"token-sharded x{world}, NCCL all-reduce of grad_weight"),
                    "l2_policy": "inputs larger than L2 (weight alone is %.2f GB)" % (V * H * 2 / 1e9),
                    "cta_pair": args.cta_pair, "raster_mb": args.raster_mb, "mode": flce_op.MODE},
         "tflops_per_gpu": tflops,
@@ -366,16 +395,39 @@ def run_ours(args, spec, rank, world, local_rank):
                      "frac": achieved / peaks["sustained"], "frac_of_burst": achieved / peaks["burst"],
                      "launches": dom_launches, "avg_launch_ms": dom_ms / max(1, dom_launches),
                      "peak_kind": f"sustained bf16 GEMM, {peaks['source']}",
-                     "traffic": NCU_DRAM_BYTES_PER_UNIT[dom] * N * V * args.steps / max(1, dom_launches),
+                     "traffic": NCU_DRAM_BYTES_PER_UNIT[dom] * N * V / (world if strong else 1) * args.steps / max(1, dom_launches),
                      "traffic_note": "ncu capture of the N=8192,V=32768 case scaled by rows x columns per launch"},
         "kernels": per_kind,
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * 2 + t_host.numel() * 8, "d2h_bytes_per_step": 4},
+        "global_tokens_per_step": tokens,
         "gpu_launches": int(launches),
         "peak_mem_gb": peak_mem / 1e9,
         "clocks": {"sm_mhz": clock_info["sm_mhz"], "sm_max_mhz": clock_info["sm_max_mhz"], "reasons": clock_info["reasons"],
                    "samples": clock_info["samples"]},
     }
+    if world == 1 and args.mode is None and not args.no_variants:
+        # the same workload with gradients formed in forward from a bounded 16-bit logits copy (6.N.H.V executed FLOPs)
+        flce_op.MODE = "single_sweep"
+        for _ in range(args.warmup):
+            step(x, t)
+        torch.cuda.reset_peak_memory_stats()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            step(x, t)
+        s1.record()
+        barrier()
+        ms_ss = s0.elapsed_time(s1) / args.steps
+        flce_op.MODE = "recompute"
+        result["single_sweep"] = {
+            "ms_per_step": ms_ss, "value": tokens / (ms_ss * 1e-3), "unit": "tokens/s",
+            "tflops_executed_6NHV": 6.0 * N * H * V / (ms_ss * 1e-3) / 1e12,
+            "tflops_credited_8NHV": 8.0 * N * H * V / (ms_ss * 1e-3) / 1e12,
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            "note": "opt-in mode LIGER_B200_FLCE_MODE=single_sweep; the headline value above is the recompute mode",
+        }
     if world == 1 and not args.no_cpu_baseline:
         rate, rows, secs = cpu_reference_rate(spec, seconds_budget=12.0)
         result["cpu_baseline"] = {
@@ -399,6 +451,9 @@ def main():
     ap.add_argument("--raster-mb", type=int, default=None, dest="raster_mb")
     ap.add_argument("--mode", default=None, choices=["recompute", "single_sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-variants", action="store_true", dest="no_variants")
+    ap.add_argument("--sharding", default="token", choices=["token", "vocab"])
+    ap.add_argument("--strong", action="store_true", help="fixed global batch split over the ranks (token sharding)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
