@@ -184,6 +184,34 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
 int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t* args, void* workspace,
                                size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
 
+/* ---- Stand-alone cross-entropy on materialised logits (the operator beside the fused path) ----------------------
+ * Replaces cross_entropy_forward / cross_entropy_backward and the same Triton kernel
+ * (src/liger_kernel/ops/cross_entropy.py:351-502).  Forward reads the logits once and leaves them untouched;
+ * backward reads them again and writes the gradient with the upstream gradient folded in (grad may be the logits
+ * buffer itself, which is how the reference saves memory).  HBM-bound: 3 * n_rows * vocab * sizeof(element) bytes. */
+typedef struct flce_ce_problem {
+  int64_t n_rows, vocab;
+  int64_t ld;               /* row pitch of logits in elements                                  */
+  int32_t dtype;            /* flce_dtype_t of the logits: bf16, fp16 or fp32                   */
+  int32_t reduction;        /* flce_reduction_t                                                 */
+  int64_t ignore_index;
+  float label_smoothing, lse_square_scale, softcap; /* softcap 0 = off                          */
+  int32_t flags;            /* reserved, 0                                                      */
+  const void* logits;       /* [n_rows, ld]                                                     */
+  const int64_t* target;    /* [n_rows]                                                         */
+  const float* ce_weight;   /* [vocab] fp32 or NULL                                             */
+} flce_ce_problem_t;
+
+/* norm: [4] output (see flce_b200_count); rowstats: [FLCE_ROWSTAT_PLANES][n_rows] output; out as in the fused path. */
+int flce_b200_ce_forward(const flce_ce_problem_t* p, float* norm, float* rowstats, const flce_forward_out_t* out,
+                         void* stream);
+
+/* grad_logits: [n_rows, ld_grad] in the logits' dtype, may alias p->logits.  coef_scratch: [3 * n_rows] fp32 scratch.
+ * grad_output as in flce_backward_args_t. */
+int flce_b200_ce_backward(const flce_ce_problem_t* p, const float* lse, const float* norm, const float* grad_output,
+                          int32_t grad_output_per_row, void* grad_logits, int64_t ld_grad, float* coef_scratch,
+                          void* stream);
+
 /* fp32 inputs on 16-bit tensor cores: writes 16-bit terms of src (term 0 = round(v), term 1 = round(v - term 0),
  * term 2 = round of what is left) side by side: block b of dst, columns [b*block_cols, b*block_cols + cols), holds
  * term pattern[b] (host array of n_blocks <= 8 entries in {0,1,2}); padding columns are zero.  With X split as

@@ -8,6 +8,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "ce_kernels.cuh"
 #include "epilogues.cuh"
 #include "gemm_sm100.cuh"
 
@@ -658,6 +659,74 @@ static FusedPlan fused_plan(const flce_problem_t* p, size_t budget, bool need_ac
   return f;
 }
 
+// ------------------------------------------------------------------ stand-alone cross-entropy
+static int check_ce_problem(const flce_ce_problem_t* p) {
+  if (p == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "problem is NULL");
+  if (p->n_rows <= 0 || p->vocab <= 0 || p->ld < p->vocab)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad logits shape (n_rows=%lld vocab=%lld ld=%lld)", (long long)p->n_rows,
+                (long long)p->vocab, (long long)p->ld);
+  if (p->n_rows > 0x7fffffffll || p->vocab > 0x7fffffffll) return fail(FLCE_ERR_INVALID_ARGUMENT, "shapes must fit 32 bits");
+  if (p->dtype < FLCE_BF16 || p->dtype > FLCE_FP32) return fail(FLCE_ERR_UNSUPPORTED, "logits must be bf16, fp16 or fp32");
+  if (p->logits == nullptr || p->target == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "logits and target must not be NULL");
+  if (p->reduction < FLCE_MEAN || p->reduction > FLCE_NONE) return fail(FLCE_ERR_INVALID_ARGUMENT, "bad reduction");
+  if (!(p->label_smoothing >= 0.f && p->label_smoothing <= 1.f))
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "label_smoothing must be in [0, 1]");
+  if (p->softcap < 0.f) return fail(FLCE_ERR_INVALID_ARGUMENT, "softcap must be positive (0 = off)");
+  return FLCE_OK;
+}
+
+static RowMath ce_row_math(const flce_ce_problem_t* p) {
+  RowMath rm;
+  rm.ignore_index = p->ignore_index;
+  rm.alpha = p->label_smoothing;
+  rm.eps = p->label_smoothing / static_cast<float>(p->vocab);
+  rm.lambda = p->lse_square_scale;
+  rm.mean = p->reduction == FLCE_MEAN;
+  rm.token_scaling = 0;
+  rm.weighted = p->ce_weight != nullptr;
+  rm.vocab = p->vocab;
+  rm.vocab_offset = 0;
+  return rm;
+}
+
+static bool ce_rows_vectorisable(const void* base, long long ld, int dtype) {
+  const long long esize = dtype == FLCE_FP32 ? 4 : 2;
+  return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && (ld * esize) % 16 == 0;
+}
+
+template <typename T>
+static void launch_ce_stats(const flce_ce_problem_t* p, float* rowstats, cudaStream_t stream) {
+  const float inv = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+  const T* x = static_cast<const T*>(p->logits);
+  const long long* tgt = reinterpret_cast<const long long*>(p->target);
+  const unsigned grid = static_cast<unsigned>(p->n_rows);
+  if (ce_rows_vectorisable(p->logits, p->ld, p->dtype))
+    ce_stats_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(x, p->ld, static_cast<int>(p->n_rows), static_cast<int>(p->vocab),
+                                                             tgt, p->ce_weight, p->softcap, inv, rowstats);
+  else
+    ce_stats_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(x, p->ld, static_cast<int>(p->n_rows), static_cast<int>(p->vocab),
+                                                              tgt, p->ce_weight, p->softcap, inv, rowstats);
+}
+
+template <typename T>
+static void launch_ce_grad(const flce_ce_problem_t* p, void* grad, long long ld_grad, const float* lse, const float* c1,
+                           const float* c2, const float* c3, cudaStream_t stream) {
+  const float inv = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+  const T* x = static_cast<const T*>(p->logits);
+  const long long* tgt = reinterpret_cast<const long long*>(p->target);
+  const bool vec = ce_rows_vectorisable(p->logits, p->ld, p->dtype) && ce_rows_vectorisable(grad, ld_grad, p->dtype);
+  const long long per_thread = vec ? CeElem<T>::kVec : 1;
+  dim3 grid(static_cast<unsigned>(p->n_rows), static_cast<unsigned>(ceil_div(ceil_div(p->vocab, per_thread), kCeThreads)), 1);
+  if (vec)
+    ce_grad_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(x, p->ld, static_cast<T*>(grad), ld_grad, static_cast<int>(p->n_rows),
+                                                            static_cast<int>(p->vocab), tgt, p->ce_weight, p->softcap, inv, lse,
+                                                            c1, c2, c3);
+  else
+    ce_grad_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(x, p->ld, static_cast<T*>(grad), ld_grad,
+                                                             static_cast<int>(p->n_rows), static_cast<int>(p->vocab), tgt,
+                                                             p->ce_weight, p->softcap, inv, lse, c1, c2, c3);
+}
+
 }  // namespace flce
 
 using namespace flce;
@@ -1223,6 +1292,71 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
     FLCE_CUDA(cudaGetLastError());
     ++g_kernel_launches;
   }
+  return FLCE_OK;
+}
+
+int flce_b200_ce_forward(const flce_ce_problem_t* p, float* norm, float* rowstats, const flce_forward_out_t* out,
+                         void* stream_) {
+  int rc = check_ce_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (norm == nullptr || rowstats == nullptr || out == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "norm, rowstats and out must not be NULL");
+  if (out->scalars != nullptr && out->loss_rows == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "scalars requires loss_rows");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long* tgt = reinterpret_cast<const long long*>(p->target);
+  count_kernel<<<1, kRedThreads, 0, stream>>>(tgt, p->n_rows, p->ignore_index, p->ce_weight, p->vocab, 0,
+                                             static_cast<float>(p->vocab), norm);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  if (p->dtype == FLCE_FP32) launch_ce_stats<float>(p, rowstats, stream);
+  else if (p->dtype == FLCE_BF16) launch_ce_stats<__nv_bfloat16>(p, rowstats, stream);
+  else launch_ce_stats<__half>(p, rowstats, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  const int threads = 256;
+  finalize_rows_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), ce_row_math(p), tgt, p->ce_weight, rowstats, norm, out->lse, out->target_prob,
+      out->loss_rows, out->z_loss_rows, out->correct_rows, reinterpret_cast<long long*>(out->predicted_tokens));
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  if (out->scalars != nullptr) {
+    reduce_rows_kernel<<<1, kRedThreads, 0, stream>>>(static_cast<int>(p->n_rows), out->loss_rows, out->z_loss_rows,
+                                                     out->correct_rows, norm, out->scalars);
+    FLCE_CUDA(cudaGetLastError());
+    ++g_kernel_launches;
+  }
+  return FLCE_OK;
+}
+
+int flce_b200_ce_backward(const flce_ce_problem_t* p, const float* lse, const float* norm, const float* grad_output,
+                          int32_t grad_output_per_row, void* grad_logits, int64_t ld_grad, float* coef_scratch,
+                          void* stream_) {
+  int rc = check_ce_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (lse == nullptr || norm == nullptr || grad_logits == nullptr || coef_scratch == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "lse, norm, grad_logits and coef_scratch must not be NULL");
+  if (ld_grad < p->vocab) return fail(FLCE_ERR_INVALID_ARGUMENT, "ld_grad smaller than vocab");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  float* c1 = coef_scratch;
+  float* c2 = c1 + p->n_rows;
+  float* c3 = c2 + p->n_rows;
+  const int threads = 256;
+  coef_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), ce_row_math(p), reinterpret_cast<const long long*>(p->target), p->ce_weight, lse, nullptr,
+      norm, grad_output, grad_output_per_row, c1, c2, c3);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  if (p->dtype == FLCE_FP32) launch_ce_grad<float>(p, grad_logits, ld_grad, lse, c1, c2, c3, stream);
+  else if (p->dtype == FLCE_BF16) launch_ce_grad<__nv_bfloat16>(p, grad_logits, ld_grad, lse, c1, c2, c3, stream);
+  else launch_ce_grad<__half>(p, grad_logits, ld_grad, lse, c1, c2, c3, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
   return FLCE_OK;
 }
 

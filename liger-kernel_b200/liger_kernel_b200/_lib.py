@@ -27,6 +27,8 @@ EXPORTS = (
     "flce_b200_forward_backward",
     "flce_b200_scale_gradient",
     "flce_b200_split_fp32",
+    "flce_b200_ce_forward",
+    "flce_b200_ce_backward",
     "flce_b200_gemm",
     "flce_b200_check_device_status",
     "flce_b200_profile_enable",
@@ -73,6 +75,15 @@ class BackwardArgs(C.Structure):
     ]
 
 
+class CeProblem(C.Structure):
+    _fields_ = [
+        ("n_rows", C.c_int64), ("vocab", C.c_int64), ("ld", C.c_int64),
+        ("dtype", C.c_int32), ("reduction", C.c_int32), ("ignore_index", C.c_int64),
+        ("label_smoothing", C.c_float), ("lse_square_scale", C.c_float), ("softcap", C.c_float), ("flags", C.c_int32),
+        ("logits", C.c_void_p), ("target", C.c_void_p), ("ce_weight", C.c_void_p),
+    ]
+
+
 class FusedArgs(C.Structure):
     _fields_ = [
         ("out", C.POINTER(ForwardOut)), ("norm", C.c_void_p), ("grad_dtype", C.c_int32),
@@ -104,6 +115,11 @@ def _load():
     lib.flce_b200_scale_gradient.restype = C.c_int
     lib.flce_b200_split_fp32.argtypes = [vp, i64, i64, i64, vp, i64, i64, C.POINTER(C.c_int32), i32, i32, vp]
     lib.flce_b200_split_fp32.restype = C.c_int
+    CP = C.POINTER(CeProblem)
+    lib.flce_b200_ce_forward.argtypes = [CP, vp, vp, F, vp]
+    lib.flce_b200_ce_forward.restype = C.c_int
+    lib.flce_b200_ce_backward.argtypes = [CP, vp, vp, vp, i32, vp, i64, vp, vp]
+    lib.flce_b200_ce_backward.restype = C.c_int
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]

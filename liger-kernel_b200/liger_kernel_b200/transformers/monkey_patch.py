@@ -3,9 +3,10 @@
 Signatures follow ``apply_liger_kernel_to_llama`` / ``_qwen2`` / ``_gemma2`` and
 ``_apply_liger_kernel_to_instance`` of the reference
 (``src/liger_kernel/transformers/monkey_patch.py:221-285, 990-1060, 1598-1660, 3588-3650``).
-Only the ``fused_linear_cross_entropy`` switch is implemented by this package; the other flags
-(rope, rms_norm, swiglu / geglu, cross_entropy) belong to kernels outside this package and are
-accepted so existing call sites keep working: when set they are reported once and otherwise ignored.
+The ``fused_linear_cross_entropy`` switch and the ``cross_entropy`` switch (logits kept, loss through the
+stand-alone cross-entropy operator) are implemented by this package; the other flags (rope, rms_norm,
+swiglu / geglu) belong to kernels outside this package and are accepted so existing call sites keep
+working: when set they are reported once and otherwise ignored.
 
 ``install()`` additionally rebinds the operator symbol inside an installed ``liger_kernel`` so that
 code which imports Liger directly (e.g. ``Trainer(use_liger_kernel=True)``) reaches this
@@ -31,6 +32,16 @@ def _report_unhandled(**flags):
             logger.info("liger_kernel_b200 only provides the fused linear cross-entropy path; '%s=True' is ignored", name)
 
 
+def _patch_cross_entropy():
+    """What the reference does for ``cross_entropy=True`` (``monkey_patch.py:191-194``): the function that Hugging
+    Face's loss helpers reach as ``nn.functional.cross_entropy`` becomes ``liger_cross_entropy``."""
+    from transformers.loss.loss_utils import nn
+
+    from .functional import liger_cross_entropy
+
+    nn.functional.cross_entropy = liger_cross_entropy
+
+
 def _patch_forward(modeling_module, class_name, forward_fn, model):
     if model is not None:
         model.forward = MethodType(forward_fn, model)
@@ -45,7 +56,9 @@ def apply_liger_kernel_to_llama(rope: bool = True, cross_entropy: bool = False, 
     )
     from transformers.models.llama import modeling_llama
 
-    _report_unhandled(rope=rope, cross_entropy=cross_entropy, rms_norm=rms_norm, swiglu=swiglu)
+    _report_unhandled(rope=rope, rms_norm=rms_norm, swiglu=swiglu)
+    if cross_entropy:
+        _patch_cross_entropy()
     if fused_linear_cross_entropy:
         _patch_forward(modeling_llama, "LlamaForCausalLM", llama_lce_forward, model)
 
@@ -57,7 +70,9 @@ def apply_liger_kernel_to_qwen2(rope: bool = True, cross_entropy: bool = False, 
     )
     from transformers.models.qwen2 import modeling_qwen2
 
-    _report_unhandled(rope=rope, cross_entropy=cross_entropy, rms_norm=rms_norm, swiglu=swiglu)
+    _report_unhandled(rope=rope, rms_norm=rms_norm, swiglu=swiglu)
+    if cross_entropy:
+        _patch_cross_entropy()
     if fused_linear_cross_entropy:
         _patch_forward(modeling_qwen2, "Qwen2ForCausalLM", qwen2_lce_forward, model)
 
@@ -69,7 +84,9 @@ def apply_liger_kernel_to_gemma2(rope: bool = True, cross_entropy: bool = False,
     )
     from transformers.models.gemma2 import modeling_gemma2
 
-    _report_unhandled(rope=rope, cross_entropy=cross_entropy, rms_norm=rms_norm, geglu=geglu)
+    _report_unhandled(rope=rope, rms_norm=rms_norm, geglu=geglu)
+    if cross_entropy:
+        _patch_cross_entropy()
     if fused_linear_cross_entropy:
         _patch_forward(modeling_gemma2, "Gemma2ForCausalLM", gemma2_lce_forward, model)
 

@@ -69,6 +69,7 @@ def flce_oracle(
     row_chunk: int = 256,
     vocab_total: Optional[int] = None,
     n_non_ignore_override: Optional[int] = None,
+    _given_logits: Optional[torch.Tensor] = None,
 ) -> OracleResult:
     """Closed-form FLCE.
 
@@ -82,6 +83,11 @@ def flce_oracle(
     """
     assert reduction in ("mean", "sum", "none")
     cd = compute_dtype
+    direct = _given_logits is not None  # stand-alone cross-entropy: logits are the input, no projection
+    if direct:
+        z_all = _as(_given_logits, cd)
+        _input = torch.zeros(z_all.shape[0], 1)
+        weight = torch.zeros(z_all.shape[1], 1)
     x = _as(_input, cd)
     w = _as(weight, cd)
     b = _as(bias, cd)
@@ -126,7 +132,7 @@ def flce_oracle(
     for r0 in range(0, n_rows, row_chunk):
         r1 = min(r0 + row_chunk, n_rows)
         xs = x[r0:r1]
-        z = xs @ w.t()
+        z = z_all[r0:r1] if direct else xs @ w.t()
         if b is not None:
             z = z + b
         if softcap is not None:
@@ -191,6 +197,11 @@ def flce_oracle(
         g = g * (scale_tok * vz * go_rows[r0:r1])[:, None]
         if round_dlogits_to is not None:
             g = g.to(round_dlogits_to).to(cd)
+        if direct:
+            if r0 == 0:
+                dx = torch.zeros_like(z_all)
+            dx[r0:r1] = g
+            continue
         dx[r0:r1] = g @ w
         dw += g.t() @ xs
         if db is not None:
@@ -202,6 +213,15 @@ def flce_oracle(
         loss, zl = loss_rows.sum(), z_rows.sum()
         acc = correct.sum() / n_valid if n_valid != 0 else correct.sum() * float("nan")
     return OracleResult(loss, zl, lse_rows, acc, pred, dx, dw, db, n_valid)
+
+
+def ce_oracle(logits, target, weight=None, ignore_index=-100, lse_square_scale=0.0, label_smoothing=0.0, reduction="mean",
+              softcap=None, grad_output=None, compute_dtype=torch.float64) -> OracleResult:
+    """Stand-alone cross-entropy on given logits (``src/liger_kernel/ops/cross_entropy.py:97-336, 351-502``):
+    same closed form as above without the linear layer; ``grad_input`` is the gradient with respect to the logits."""
+    return flce_oracle(None, None, target, ce_weight=weight, ignore_index=ignore_index, lse_square_scale=lse_square_scale,
+                       label_smoothing=label_smoothing, reduction=reduction, softcap=softcap, grad_output=grad_output,
+                       compute_dtype=compute_dtype, _given_logits=logits)
 
 
 def torch_linear_ce_reference(

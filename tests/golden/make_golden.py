@@ -191,6 +191,71 @@ def run_case(name, spec):
     print(f"{name}: loss={np.asarray(rec['ref_loss']).reshape(-1)[:1]}")
 
 
+# ---- stand-alone cross-entropy on materialised logits: the reference's cross_entropy_forward / _backward ---------
+CE_CASES = {
+    "xent_mean_default": dict(N=64, V=203, ign=0.1),
+    "xent_sum_bf16": dict(N=64, V=256, ign=0.1, reduction="sum", dtype="bfloat16"),
+    "xent_none_token_grad": dict(N=48, V=131, ign=0.2, reduction="none", token_grad=True),
+    "xent_all_features": dict(N=64, V=256, ign=0.15, weight=True, label_smoothing=0.1, ignore_index=42, lse_square_scale=1e-3,
+                            softcap=30.0, return_z_loss=True, scale=4.0),
+    "xent_metrics_grad_output": dict(N=64, V=515, ign=0.1, return_token_accuracy=True, return_predicted_tokens=True,
+                                   grad_output=0.5, scale=3.0),
+}
+
+
+def run_ce_case(name, spec):
+    from liger_kernel.ops.cross_entropy import cross_entropy_backward, cross_entropy_forward
+
+    seed = 2000 + sorted(CE_CASES).index(name)
+    g = torch.Generator().manual_seed(seed)
+    N, V = spec["N"], spec["V"]
+    dtype = getattr(torch, spec.get("dtype", "float32"))
+    logits = (torch.randn(N, V, generator=g) * spec.get("scale", 2.0)).to(dtype)
+    ignore_index = spec.get("ignore_index", -100)
+    t = torch.randint(0, V, (N,), generator=g)
+    if ignore_index >= 0:
+        t[t == ignore_index] = (ignore_index + 1) % V
+    t[torch.rand(N, generator=g) < spec["ign"]] = ignore_index
+    weight = (torch.rand(V, generator=g) + 0.5) if spec.get("weight") else None
+    tg = (torch.rand(N, generator=g) + 0.5) if spec.get("token_grad") else None
+    softcap = spec.get("softcap")
+    work = logits.clone().requires_grad_(True)
+    torch.Tensor.item = _item_with_to
+    try:
+        with torch.no_grad():
+            loss, z_loss, acc, pred, grad = cross_entropy_forward(
+                work, t, weight, ignore_index, spec.get("lse_square_scale", 0.0), spec.get("label_smoothing", 0.0),
+                spec.get("reduction", "mean"), None if softcap is None else _Float(softcap), spec.get("return_z_loss", False),
+                spec.get("return_token_accuracy", False), spec.get("return_predicted_tokens", False))
+            if tg is not None:
+                grad = cross_entropy_backward(grad, tg.to(dtype))
+            elif spec.get("grad_output") is not None:
+                grad = cross_entropy_backward(grad, torch.tensor(spec["grad_output"], dtype=dtype))
+    finally:
+        torch.Tensor.item = _orig_item
+    rec = dict(logits=logits.float().numpy(), target=t.numpy(), ref_loss=loss.float().numpy(),
+               ref_grad_logits=grad.detach().float().numpy())
+    if weight is not None:
+        rec["weight"] = weight.numpy()
+    if tg is not None:
+        rec["token_grad"] = tg.numpy()
+    if z_loss is not None:
+        rec["ref_z_loss"] = z_loss.float().numpy()
+    if acc is not None:
+        rec["ref_token_accuracy"] = acc.float().numpy()
+    if pred is not None:
+        rec["ref_predicted_tokens"] = pred.numpy()
+    meta = dict(spec)
+    meta["ignore_index"] = ignore_index
+    rec["meta"] = np.array(repr(meta))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+    print(f"{name}: loss={np.asarray(rec['ref_loss']).reshape(-1)[:1]}")
+
+
 if __name__ == "__main__":
-    for case_name in sorted(CASES):
-        run_case(case_name, CASES[case_name])
+    only_ce = len(sys.argv) > 1 and sys.argv[1] == "ce"
+    if not only_ce:
+        for case_name in sorted(CASES):
+            run_case(case_name, CASES[case_name])
+    for case_name in sorted(CE_CASES):
+        run_ce_case(case_name, CE_CASES[case_name])

@@ -10,8 +10,18 @@ import torch
 GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-def golden_names():
+def _all_names():
     return sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+
+
+def golden_names():
+    """Fused linear cross-entropy cases."""
+    return [n for n in _all_names() if not n.startswith("xent_")]
+
+
+def ce_golden_names():
+    """Stand-alone cross-entropy cases (logits given)."""
+    return [n for n in _all_names() if n.startswith("xent_")]
 
 
 def load_golden(name):

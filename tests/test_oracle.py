@@ -87,3 +87,31 @@ def test_closed_form_equals_autograd_fp64():
             assert (res.grad_input - gx).abs().max() < 1e-11
             assert (res.grad_weight - gw).abs().max() < 1e-11
             assert (res.grad_bias - gb).abs().max() < 1e-11
+
+
+# ---- stand-alone cross-entropy -----------------------------------------------------------------------------------
+from golden_util import ce_golden_names  # noqa: E402
+from oracle.flce_oracle import ce_oracle  # noqa: E402
+
+
+@pytest.mark.parametrize("name", ce_golden_names())
+def test_ce_oracle_matches_reference_golden(name):
+    rec, meta = load_golden(name)
+    bf16 = meta.get("dtype") == "bfloat16"
+    logits, t = torch.from_numpy(rec["logits"]), torch.from_numpy(rec["target"])
+    go = golden_grad_output(rec, meta)
+    res = ce_oracle(logits, t, weight=None if "weight" not in rec else torch.from_numpy(rec["weight"]),
+                    ignore_index=meta["ignore_index"], lse_square_scale=meta.get("lse_square_scale", 0.0),
+                    label_smoothing=meta.get("label_smoothing", 0.0), reduction=meta.get("reduction", "mean"),
+                    softcap=meta.get("softcap"), grad_output=go)
+    # the reference keeps loss rows in the logits' dtype: bf16 rounding for the bf16 case
+    atol, rtol = (0.0, 1e-2) if bf16 else (2e-5 * max(1.0, float(np.abs(rec["ref_loss"]).max())), 2e-4)
+    _close(res.loss, rec["ref_loss"], atol, rtol, "loss")
+    if "ref_z_loss" in rec:
+        _close(res.z_loss, rec["ref_z_loss"], 2e-5, 2e-4, "z_loss")
+    gmax = float(np.abs(rec["ref_grad_logits"]).max())
+    _close(res.grad_input, rec["ref_grad_logits"], (8e-3 if bf16 else 2e-6) * gmax, 1e-2 if bf16 else 1e-3, "grad_logits")
+    if "ref_token_accuracy" in rec:
+        _close(res.token_accuracy, rec["ref_token_accuracy"], 1e-6, 0, "token_accuracy")
+    if "ref_predicted_tokens" in rec:
+        assert np.array_equal(res.predicted_tokens.numpy(), rec["ref_predicted_tokens"])
