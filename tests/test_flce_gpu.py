@@ -387,23 +387,3 @@ def test_golden_fp32_inputs_against_reference_outputs(name):
         want = torch.from_numpy(rec["ref_" + key])
         assert_close(res[key].float(), want, 5e-5 * float(want.abs().max()), 1e-3, key + " vs reference")
 
-
-@pytest.mark.parametrize("amp_dtype", [torch.bfloat16, torch.float16])
-def test_amp_autocast_with_fp32_parameters(amp_dtype):
-    """fp32 master weights and inputs under torch.autocast: operands are cast to the autocast dtype, gradients come back
-    in fp32 (reference: test/transformers/test_fused_linear_cross_entropy.py:558-604)."""
-    from liger_kernel_b200 import LigerFusedLinearCrossEntropyLoss
-
-    x, w, t, b, _ = make_inputs(256, 128, 1000, torch.float32, seed=31, bias=True)
-    xd = x.cuda().requires_grad_(True)
-    wd = w.cuda().requires_grad_(True)
-    bd = b.cuda().requires_grad_(True)
-    with torch.autocast(device_type="cuda", dtype=amp_dtype):
-        loss = LigerFusedLinearCrossEntropyLoss()(wd, xd, t.cuda(), bd)
-    loss.backward()
-    assert loss.dtype == torch.float32 and xd.grad.dtype == torch.float32 and wd.grad.dtype == torch.float32
-    assert bd.grad.dtype == torch.float32
-    ora = oracle_for(x.to(amp_dtype), w.to(amp_dtype), t, bias=b.to(amp_dtype))
-    res = dict(loss=loss.detach().cpu(), z_loss=torch.zeros(()), predicted_tokens=ora.predicted_tokens,
-               grad_input=xd.grad.cpu(), grad_weight=wd.grad.cpu(), grad_bias=bd.grad.cpu())
-    _check(res, ora, amp_dtype, "mean", 256)
