@@ -9,7 +9,7 @@ mean reduction, returning grad_input and grad_weight).  With N GPUs (launched un
 per GPU) every rank processes its own N tokens against a replicated weight and the weight gradient is
 all-reduced over NCCL inside the step: weak scaling, `value` is the sum over ranks.
 
-Rank 0 prints one JSON line (see README / DESIGN for the keys).  `--impl reference` times the torch
+Rank 0 prints one JSON line.  `--impl reference` times the torch
 Linear+CrossEntropy ground truth of the reference's tests on the host cores instead.
 """
 

@@ -32,7 +32,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-sys.path.insert(0, os.environ.get("REFERENCE_SRC", "/root/reference/src"))
+if "REFERENCE_SRC" not in os.environ:
+    raise SystemExit("set REFERENCE_SRC to the src/ directory of the reference checkout")
+sys.path.insert(0, os.environ["REFERENCE_SRC"])
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 

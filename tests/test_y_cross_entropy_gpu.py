@@ -3,9 +3,8 @@ reference's golden vectors.  Case grid follows test/transformers/test_cross_entr
 (shapes incl. V=128256-like wide rows and odd sizes, dtypes, reductions, label smoothing, z-loss, soft-cap,
 class weights, ignore_index, not-last-layer upstream gradients, per-row gradients for reduction "none").
 
-These kernels were written after this build's GPU budget was spent: they compile, their host logic is tested on
-the CPU, but they have not run on a GPU yet.  Until they have, this file only runs when
-LIGER_B200_RUN_UNVALIDATED=1 is set, so that the validated suite stays a clean signal."""
+These kernels compile and their host logic is tested on the CPU, but they have not run on a GPU yet.  Until they
+have, this file only runs when LIGER_B200_RUN_UNVALIDATED=1 is set, so that the validated suite stays a clean signal."""
 
 import os
 
