@@ -124,7 +124,8 @@ size_t flce_b200_workspace_bytes(const flce_problem_t* p, int phase, size_t slab
 
 /* norm is [4] fp32: norm[0] = number of rows whose target != ignore_index, norm[1] = sum of
  * ce_weight[target] over those rows (== norm[0] without class weights), norm[2] = sum of all class
- * weights (== vocab_total without class weights), norm[3] = 0.  Replaces the host-synchronising `.item()` reads at
+ * weights (== vocab_total without class weights), norm[3] = number of targets that are neither ignore_index nor
+ * inside [0, vocab_total) (such rows match no class; a caller may read it to report them).  Replaces the host-synchronising `.item()` reads at
  * src/liger_kernel/ops/fused_linear_cross_entropy.py:92-104.  A token-sharded caller all-reduces
  * norm across ranks before passing it on. */
 int flce_b200_count(const flce_problem_t* p, float* norm, void* stream);

@@ -251,15 +251,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 // norm[0] = #rows with target != ignore_index, norm[1] = sum of class weight of those targets,
-// norm[2] = sum of all class weights (vocab_total when unweighted).  One block: exact and ordered.
+// norm[2] = sum of all class weights (vocab_total when unweighted), norm[3] = #targets outside [0, vocab_total).
+// One block: exact and ordered.
 __global__ void count_kernel(const long long* target, long long n_rows, long long ignore_index, const float* ce_weight,
                              long long vocab, long long vocab_offset, float vocab_total, float* norm) {
   __shared__ float scratch[32];
-  float cnt = 0.f, wy = 0.f, wall = 0.f;
+  float cnt = 0.f, wy = 0.f, wall = 0.f, bad = 0.f;
+  const long long classes = static_cast<long long>(vocab_total);
   for (long long i = threadIdx.x; i < n_rows; i += blockDim.x) {
     const long long t = target[i];
     if (t != ignore_index) {
       cnt += 1.f;
+      if (t < 0 || t >= classes) bad += 1.f;   // matches no class; reported, never dereferenced
       if (ce_weight != nullptr) {
         const long long l = t - vocab_offset;
         if (l >= 0 && l < vocab) wy += ce_weight[l];
@@ -271,11 +274,12 @@ __global__ void count_kernel(const long long* target, long long n_rows, long lon
   const float c = block_sum(cnt, scratch);
   const float w = block_sum(wy, scratch);
   const float a = block_sum(wall, scratch);
+  const float o = block_sum(bad, scratch);
   if (threadIdx.x == 0) {
     norm[0] = c;
     norm[1] = (ce_weight != nullptr) ? w : c;
     norm[2] = (ce_weight != nullptr) ? a : vocab_total;
-    norm[3] = 0.f;
+    norm[3] = o;
   }
 }
 

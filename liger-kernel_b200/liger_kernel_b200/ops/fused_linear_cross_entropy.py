@@ -38,6 +38,14 @@ SLAB_BUDGET_BYTES = 1 << 30
 # bytes of logits copy the single-sweep mode may use (chunk rows x V, 16-bit)
 CHUNK_BUDGET_BYTES = 5 << 29
 MODE = os.environ.get("LIGER_B200_FLCE_MODE", "recompute")
+# Read back the count of out-of-range targets after forward and raise, as the reference's stand-alone cross-entropy and
+# its sm_100 FLCE do (``ops/cross_entropy.py:389-392``).  Costs a host synchronisation, so it is off by default.
+CHECK_TARGETS = os.environ.get("LIGER_B200_CHECK_TARGETS", "0") == "1"
+
+
+def _raise_on_bad_targets(norm, vocab):
+    bad = int(norm[3].item())
+    assert bad == 0, f"Target out of bounds: {bad} targets are neither ignore_index nor in [0, {vocab})"
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -292,6 +300,8 @@ def fused_linear_cross_entropy_forward(
     prep = _Prepared(_input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction,
                      softcap, use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)
     out, norm, _rowstats = flce_forward_device(prep)
+    if CHECK_TARGETS:
+        _raise_on_bad_targets(norm, prep.vocab)
     if reduction == "none":
         loss = out["loss_rows"]
         z_loss = out["z_loss_rows"].to(prep.dtype) if return_z_loss else None

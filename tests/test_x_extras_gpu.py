@@ -1,5 +1,5 @@
-"""Automatic mixed precision: fp32 parameters and inputs under torch.autocast (kept in a file of its own, collected
-after the core parity files)."""
+"""Behaviour around the core operator, kept in a file of its own that is collected after the core parity files:
+automatic mixed precision (fp32 parameters and inputs under torch.autocast) and the out-of-range-target report."""
 
 import pytest
 import torch
@@ -29,3 +29,20 @@ def test_amp_autocast_with_fp32_parameters(amp_dtype):
     res = dict(loss=loss.detach().cpu(), z_loss=torch.zeros(()), predicted_tokens=ora.predicted_tokens,
                grad_input=xd.grad.cpu(), grad_weight=wd.grad.cpu(), grad_bias=bd.grad.cpu())
     _check(res, ora, amp_dtype, "mean", 256)
+
+
+def test_out_of_range_targets_are_counted_and_optionally_raised(monkeypatch):
+    """Targets that are neither ignore_index nor a class id never touch memory; they are counted on the device and a caller
+    can ask for the reference's assertion (ops/cross_entropy.py:389-392) at the price of a host synchronisation."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+
+    x, w, t, _, _ = make_inputs(200, 64, 300, torch.bfloat16, seed=41)
+    t[5], t[9] = 303, -7
+    prep = mod._Prepared(x.cuda(), w.cuda(), t.cuda(), None, None, -100, 0.0, 0.0, "mean", None, False)
+    out, norm, _ = mod.flce_forward_device(prep)
+    assert int(norm[3].item()) == 2 and bool(torch.isfinite(out["scalars"][0]))
+    monkeypatch.setattr(mod, "CHECK_TARGETS", True)
+    with pytest.raises(AssertionError, match="out of bounds"):
+        mod.LigerFusedLinearCrossEntropyFunction.apply(x.cuda(), w.cuda(), t.cuda())
+    t[5], t[9] = 1, 2
+    mod.LigerFusedLinearCrossEntropyFunction.apply(x.cuda(), w.cuda(), t.cuda())
