@@ -348,6 +348,8 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
             prep = _Prepared(x, w, target, b, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
                              use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)
             out, norm, gx, gw, gb = flce_single_sweep_device(prep, needs[0], needs[1], needs[2])
+            if CHECK_TARGETS:
+                _raise_on_bad_targets(norm, prep.vocab)
             ctx.stored_grads = (gx, gw, gb)
             ctx.flce_saved = (prep, out["lse"], out["target_prob"], norm)
             ctx.has_bias = bias is not None

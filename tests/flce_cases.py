@@ -64,3 +64,66 @@ def assert_close(got, want, atol, rtol, what):
         f"{what}: {int((excess > 0).sum())}/{excess.size} out of tolerance, max |diff| {np.abs(got - want).max():.3e}, "
         f"max |want| {np.abs(want).max():.3e}"
     )
+
+
+def sampled_fp64_check(x, w, t, lse, grad_input, grad_weight, *, reduction="mean", label_smoothing=0.0, lse_square_scale=0.0,
+                       softcap=None, ignore_index=-100, n_row_samples=64, vocab_samples=(0, 1, 4097), row_chunk=8192,
+                       vocab_chunk=16384):
+    """Size-independent check of a full-size result against fp64 math on a sample, on whatever device the tensors live:
+    * for sampled token rows: lse and the row of grad_input, from the whole vocabulary (streamed in chunks);
+    * for sampled vocabulary rows: the row of grad_weight, from all tokens (streamed in chunks), using the per-row lse
+      under test (which the first part validates on its sample).
+    Returns the largest relative lse error seen; raises AssertionError on a mismatch."""
+    N, H = x.shape
+    V = w.shape[0]
+    dev = x.device
+    alpha, lam = float(label_smoothing), float(lse_square_scale)
+    eps = alpha / V
+    valid = t != ignore_index
+    n_valid = int(valid.sum())
+    inv_n = 1.0 / n_valid if reduction == "mean" else 1.0
+
+    def capped(z):
+        if softcap is None:
+            return z, torch.ones_like(z)
+        th = torch.tanh(z / softcap)
+        return softcap * th, 1 - th * th
+
+    # ---- sampled token rows
+    rows = torch.arange(0, N, max(1, N // n_row_samples), device=dev)[:n_row_samples]
+    xr = x[rows].double()
+    s_parts, chain_parts = [], []
+    for v0 in range(0, V, vocab_chunk):
+        s, ch = capped(xr @ w[v0:v0 + vocab_chunk].double().t())
+        s_parts.append(s)
+        chain_parts.append(ch)
+    s = torch.cat(s_parts, dim=1)
+    chain = torch.cat(chain_parts, dim=1)
+    lse_ref = torch.logsumexp(s, dim=1)
+    lse_err = float(((lse[rows].double() - lse_ref).abs() / lse_ref.abs().clamp(min=1.0)).max())
+    assert lse_err <= 1e-5, f"lse error {lse_err:.3e}"
+    tr = t[rows]
+    vr = valid[rows]
+    g = torch.exp(s - lse_ref[:, None]) * (1 + 2 * lam * lse_ref)[:, None] - eps
+    hit_rows = torch.arange(len(rows), device=dev)[vr]
+    g[hit_rows, tr[vr]] -= (1 - alpha)
+    g = g * chain * (vr.double() * inv_n)[:, None]
+    dx_ref = torch.zeros(len(rows), H, dtype=torch.float64, device=dev)
+    for v0 in range(0, V, vocab_chunk):
+        dx_ref += g[:, v0:v0 + vocab_chunk] @ w[v0:v0 + vocab_chunk].double()
+    assert_close(grad_input[rows].float().cpu(), dx_ref.float().cpu(), 8e-3 * float(dx_ref.abs().max()), 5e-2, "grad_input rows")
+
+    # ---- sampled vocabulary rows
+    vs = torch.tensor([v for v in vocab_samples if v < V] + [V - 1], device=dev)
+    wv = w[vs].double()
+    dw_ref = torch.zeros(len(vs), H, dtype=torch.float64, device=dev)
+    for r0 in range(0, N, row_chunk):
+        xc = x[r0:r0 + row_chunk].double()
+        lc = lse[r0:r0 + row_chunk].double()
+        sc, chc = capped(xc @ wv.t())
+        gc = torch.exp(sc - lc[:, None]) * (1 + 2 * lam * lc)[:, None] - eps
+        gc = gc - (1 - alpha) * (t[r0:r0 + row_chunk, None] == vs[None, :]).double()
+        gc = gc * chc * (valid[r0:r0 + row_chunk].double() * inv_n)[:, None]
+        dw_ref += gc.t() @ xc
+    assert_close(grad_weight[vs].float().cpu(), dw_ref.float().cpu(), 8e-3 * float(dw_ref.abs().max()), 5e-2, "grad_weight rows")
+    return lse_err

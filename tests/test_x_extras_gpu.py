@@ -46,3 +46,42 @@ def test_out_of_range_targets_are_counted_and_optionally_raised(monkeypatch):
         mod.LigerFusedLinearCrossEntropyFunction.apply(x.cuda(), w.cuda(), t.cuda())
     t[5], t[9] = 1, 2
     mod.LigerFusedLinearCrossEntropyFunction.apply(x.cuda(), w.cuda(), t.cuda())
+
+
+FULL_SIZE = {
+    # BASELINE configs 3-5 at their full sizes (config 2 is covered by test_flce_gpu.py::test_full_size_properties)
+    "c3_qwen_style": (32768, 3584, 152064, 0.20, dict(label_smoothing=0.1, lse_square_scale=1e-4)),
+    "c4_gemma_style": (16384, 3584, 256000, 0.05, dict(softcap=30.0, reduction="sum")),
+    "c5_llama70b_head": (65536, 8192, 128256, 0.05, dict()),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FULL_SIZE))
+def test_full_size_configs_sampled_against_fp64(name):
+    """Full-size heads: loss consistency, exact zeros on ignored rows, and sampled rows of lse / grad_input / grad_weight
+    against fp64 math streamed over the whole vocabulary and all tokens."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+    from flce_cases import sampled_fp64_check
+
+    N, H, V, ign, kw = FULL_SIZE[name]
+    if torch.cuda.get_device_properties(0).total_memory < 60e9:
+        pytest.skip("needs ~25 GB of device memory")
+    g = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn(N, H, generator=g, device="cuda").bfloat16()
+    w = (torch.randn(V, H, generator=g, device="cuda") * 0.02).bfloat16()
+    t = torch.randint(0, V, (N,), generator=g, device="cuda")
+    t[torch.rand(N, generator=g, device="cuda") < ign] = -100
+    red = kw.get("reduction", "mean")
+    xd, wd = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    loss = mod.LigerFusedLinearCrossEntropyFunction.apply(
+        xd, wd, t, None, None, -100, kw.get("lse_square_scale", 0.0), kw.get("label_smoothing", 0.0), red, kw.get("softcap"))[0]
+    loss.backward()
+    prep = mod._Prepared(x, w, t, None, None, -100, kw.get("lse_square_scale", 0.0), kw.get("label_smoothing", 0.0), red,
+                         kw.get("softcap"), False, want_argmax=False)
+    out, norm, _ = mod.flce_forward_device(prep)
+    n_valid = int((t != -100).sum())
+    assert int(norm[0].item()) == n_valid
+    # the scalar loss is the ordered sum of the per-row losses; ignored rows contribute exact zeros everywhere
+    assert abs(float(out["loss_rows"].double().sum()) - float(loss.detach())) <= 1e-5 * abs(float(loss.detach()))
+    assert float(out["loss_rows"][t == -100].abs().max()) == 0.0 and float(xd.grad[t == -100].abs().max()) == 0.0
+    sampled_fp64_check(x, w, t, out["lse"], xd.grad, wd.grad, vocab_samples=(0, 1, 4097, V // 2), **kw)
