@@ -61,6 +61,9 @@ typedef struct flce_problem {
   const int64_t* target;     /* [n_rows] global class ids or ignore_index                     */
   const float* bias;         /* [vocab] fp32 or NULL                                          */
   const float* ce_weight;    /* [vocab] fp32 class weights or NULL                            */
+  const int32_t* active_rows;/* NULL, or a device word: only the first *active_rows rows matter (the others are
+                              * ignored targets moved to the end by flce_b200_compact_rows); the sweeps then skip
+                              * the token tiles that hold none of them                                 */
 } flce_problem_t;
 
 /* flce_problem_t.flags: track the arg-max of every row in the forward sweep (needed for token accuracy
@@ -220,6 +223,20 @@ int flce_b200_ce_backward(const flce_ce_problem_t* p, const float* lse, const fl
  * in the reference, whose fp32 path is a cuBLAS fp32 GEMM (ops/fused_linear_cross_entropy.py:114). */
 int flce_b200_split_fp32(const float* src, int64_t rows, int64_t cols, int64_t ld_src, void* dst, int64_t ld_dst,
                          int64_t block_cols, const int32_t* pattern, int32_t n_blocks, int32_t dst_dtype, void* stream);
+
+/* Ignored tokens cost nothing once they are out of the way: stable-partition the rows of p->x / p->target so that
+ * rows whose target is not ignore_index come first.  Outputs: x_compact [n_rows, hidden] dense, target_compact [n_rows],
+ * perm [n_rows] (original row of each compact row) and *active_rows (how many rows matter), all on the device, no host
+ * synchronisation.  Run the forward / backward entry points on a problem that points at the compact arrays and at
+ * active_rows; per-row results come out in compact order.  The reference multiplies every row through all three GEMMs and
+ * only skips ignored rows inside its cross-entropy kernel (src/liger_kernel/ops/cross_entropy.py:104-116). */
+int flce_b200_compact_rows(const flce_problem_t* p, void* x_compact, int64_t* target_compact, int32_t* perm,
+                           int32_t* active_rows, void* stream);
+
+/* dst[perm[i]] = src[i] for i < *active_rows and zeros for the other rows (row_bytes a multiple of 16): puts a compact
+ * grad_input back into token order. */
+int flce_b200_scatter_rows(const void* src, int64_t row_bytes, const int32_t* perm, const int32_t* active_rows,
+                           int64_t n_rows, void* dst, void* stream);
 
 /* data[i] *= *scale for n elements of the given dtype; a no-op when the device-resident scale equals 1 (tested on
  * the device, no host synchronisation).  Replaces element_mul_kernel and the torch.equal test before it

@@ -159,7 +159,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 template <int kCtas, int kAMajor, int kBMajor, class Epi>
 static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, const Operand& b, int dtype, long long M,
                             long long N, long long K, long long raster_row_bytes, bool n_fastest,
-                            const typename Epi::Params& ep, cudaStream_t stream) {
+                            const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows, int active_role) {
   using Cfg = StageCfg<kCtas>;
   CUtensorMap map_a, map_b;
   int rc = operand_map(&map_a, a, dtype, kBlockM);
@@ -174,6 +174,8 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   shape.n_tiles = static_cast<int>(ceil_div(N, kBlockN));
   shape.k_blocks = static_cast<int>(ceil_div(K, kBlockK));
   shape.poll_sleep_ns = g_poll_sleep_ns;
+  shape.active_rows = active_rows;
+  shape.active_role = active_rows != nullptr ? active_role : 0;
   shape.hint_a = 0;
   shape.hint_b = 0;
   if (g_l2_hints) {
@@ -221,13 +223,16 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
 template <int kAMajor, int kBMajor, class Epi>
 static int launch_gemm(const DeviceState& dev, int kind, bool pair, const Operand& a, const Operand& b, int dtype, long long M,
                        long long N, long long K, long long raster_row_bytes, bool n_fastest,
-                       const typename Epi::Params& ep, cudaStream_t stream) {
+                       const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows = nullptr,
+                       int active_role = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "empty GEMM %lld x %lld x %lld", M, N, K);
   if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "GEMM extent does not fit 32 bits");
   if (pair)
-    return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream);
-  return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream);
+    return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream,
+                                                      active_rows, active_role);
+  return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream,
+                                                    active_rows, active_role);
 }
 
 // ------------------------------------------------------------------ small kernels
@@ -502,6 +507,80 @@ __global__ void colsum_accumulate_kernel(const uint16_t* dz, long long ld, int m
     for (int i = 0; i < 16; ++i) t += part[i][cx];
     out[col] = accumulate ? out[col] + t : t;
   }
+}
+
+// ---- moving ignored rows out of the way -----------------------------------------------------------------------
+// Stable partition of the row indices: rows whose target is not ignore_index first (in order), the others after them.
+// perm[i] = original row of compact row i; *active = number of rows that matter.  One block, ordered.
+__global__ void compact_plan_kernel(const long long* target, int n_rows, long long ignore_index, int* perm, int* active) {
+  __shared__ int warp_tot[32];
+  __shared__ int s_total;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  // pass 1: how many rows matter
+  int cnt = 0;
+  for (int i = threadIdx.x; i < n_rows; i += blockDim.x) cnt += target[i] != ignore_index;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if (lane == 0) warp_tot[warp] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int w = 0; w < n_warps; ++w) t += warp_tot[w];
+    s_total = t;
+    *active = t;
+  }
+  __syncthreads();
+  const int total = s_total;
+  // pass 2: block-wide exclusive scan, one chunk of blockDim.x rows at a time
+  int base_valid = 0, base_other = 0;
+  for (int c0 = 0; c0 < n_rows; c0 += blockDim.x) {
+    const int row = c0 + threadIdx.x;
+    const int flag = (row < n_rows) && (target[row] != ignore_index);
+    int incl = flag;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    __syncthreads();   // warp_tot is reused
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int warp_base = 0, chunk_valid = 0;
+    for (int w = 0; w < n_warps; ++w) {
+      const int v = warp_tot[w];
+      if (w < warp) warp_base += v;
+      chunk_valid += v;
+    }
+    const int before = warp_base + incl - flag;   // rows that matter before this one inside the chunk
+    if (row < n_rows) {
+      if (flag) perm[base_valid + before] = row;
+      else perm[total + base_other + (threadIdx.x - before)] = row;
+    }
+    const int chunk_rows = min(static_cast<int>(blockDim.x), n_rows - c0);
+    base_valid += chunk_valid;
+    base_other += chunk_rows - chunk_valid;
+  }
+}
+
+// dst row i = src row perm[i] (row_bytes a multiple of 16); targets are permuted alongside
+__global__ void gather_rows_kernel(const uint8_t* src, long long src_pitch_bytes, const int* perm, uint8_t* dst,
+                                   long long row_bytes, const long long* target, long long* target_out) {
+  const int i = blockIdx.x;
+  const int from = perm[i];
+  const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<size_t>(from) * src_pitch_bytes);
+  uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(i) * row_bytes);
+  for (long long v = threadIdx.x; v < row_bytes / 16; v += blockDim.x) d[v] = s[v];
+  if (threadIdx.x == 0 && target != nullptr) target_out[i] = target[from];
+}
+
+// dst row perm[i] = src row i for i < *active, zeros for the rest (row_bytes a multiple of 16)
+__global__ void scatter_rows_kernel(const uint8_t* src, const int* perm, const int* active, uint8_t* dst, long long row_bytes) {
+  const int i = blockIdx.x;
+  const bool live = i < *active;
+  const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<size_t>(i) * row_bytes);
+  uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(perm[i]) * row_bytes);
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (long long v = threadIdx.x; v < row_bytes / 16; v += blockDim.x) d[v] = live ? s[v] : zero;
 }
 
 // fp32 -> sum of 16-bit terms: term 0 = round(v), term 1 = round(v - term0), term 2 = round(v - term0 - term1).
@@ -848,7 +927,8 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
   Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
   Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
   rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, kKindStats, g_cta_pair != 0, a, b, p->dtype, p->n_rows, p->vocab, p->hidden,
-                                                    static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
+                                                    static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream,
+                                                    p->active_rows, 1);
   if (rc != FLCE_OK) return rc;
   const int threads = 256;
   merge_partials_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
@@ -1059,7 +1139,8 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
       Operand b{w_slab, cols, p->hidden, p->ld_w, 0};
       rc = launch_gemm<kMajorK, kMajorK, DzEpilogue>(*dev, kKindDz, pair, a, b, p->dtype, p->n_rows, cols, p->hidden,
-                                                     static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
+                                                     static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream,
+                                                     p->active_rows, 1);
       if (rc != FLCE_OK) return rc;
     }
     // ---- grad_weight[slab] = dZ^T . X        (M = cols, N = hidden, K = n_rows; both operands MN-major)
@@ -1076,7 +1157,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       Operand a{dz, cols, p->n_rows, plan.ld_dz, 1};
       Operand b{px, px_cols, p->n_rows, ld_px, 1};
       rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, cols, px_cols, p->n_rows, 0, true,
-                                                          ep, stream);
+                                                          ep, stream, p->active_rows, 2);
       if (rc != FLCE_OK) return rc;
       if (split) {  // rounding residual of dZ against the leading (high-order) columns of the projection operand
         float* acc = reinterpret_cast<float*>(ep.out);
@@ -1088,7 +1169,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
         Operand a2{dz_lo, cols, p->n_rows, plan.ld_dz, 1};
         Operand b2{px, args->lo_cols_x, p->n_rows, ld_px, 1};
         rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a2, b2, p->dtype, cols, args->lo_cols_x,
-                                                            p->n_rows, 0, true, ep, stream);
+                                                            p->n_rows, 0, true, ep, stream, p->active_rows, 2);
         if (rc != FLCE_OK) return rc;
       }
     }
@@ -1110,7 +1191,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
       Operand a{dz, p->n_rows, cols, plan.ld_dz, 0};
       Operand b{pw_slab, pw_cols, cols, ld_pw, 1};
       rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, p->n_rows, pw_cols, cols, 0, true,
-                                                         ep, stream);
+                                                         ep, stream, p->active_rows, 1);
       if (rc != FLCE_OK) return rc;
       if (split) {
         ep.n_cols = static_cast<int>(args->lo_cols_w);
@@ -1120,7 +1201,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
         Operand a2{dz_lo, p->n_rows, cols, plan.ld_dz, 0};
         Operand b2{pw_slab, args->lo_cols_w, cols, ld_pw, 1};
         rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a2, b2, p->dtype, p->n_rows, args->lo_cols_w,
-                                                           cols, 0, true, ep, stream);
+                                                           cols, 0, true, ep, stream, p->active_rows, 1);
         if (rc != FLCE_OK) return rc;
       }
     }
@@ -1151,6 +1232,7 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
   const flce_forward_out_t* out = args->out;
   if (out->lse == nullptr || out->loss_rows == nullptr || out->target_prob == nullptr)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "single-sweep mode needs out->lse, out->target_prob and out->loss_rows");
+  if (p->active_rows != nullptr) return fail(FLCE_ERR_UNSUPPORTED, "active_rows is not supported in single-sweep mode");
   if (p->reduction == FLCE_NONE)
     return fail(FLCE_ERR_UNSUPPORTED, "single-sweep mode forms gradients before the upstream gradient is known; "
                                       "reduction 'none' needs the two-sweep path");
@@ -1381,6 +1463,46 @@ int flce_b200_split_fp32(const float* src, int64_t rows, int64_t cols, int64_t l
   split_fp32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(src, rows, cols, ld_src, static_cast<uint16_t*>(dst),
                                                                        ld_dst, block_cols, pat, n_blocks,
                                                                        dst_dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_compact_rows(const flce_problem_t* p, void* x_compact, int64_t* target_compact, int32_t* perm,
+                           int32_t* active_rows, void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (x_compact == nullptr || target_compact == nullptr || perm == nullptr || active_rows == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL output");
+  if ((reinterpret_cast<uintptr_t>(x_compact) & 15) != 0 || (reinterpret_cast<uintptr_t>(p->x) & 15) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "x and x_compact must be 16-byte aligned");
+  DeviceState* dev;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  compact_plan_kernel<<<1, kRedThreads, 0, stream>>>(reinterpret_cast<const long long*>(p->target), static_cast<int>(p->n_rows),
+                                                    p->ignore_index, perm, active_rows);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  gather_rows_kernel<<<static_cast<unsigned>(p->n_rows), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(p->x), p->ld_x * 2, perm, static_cast<uint8_t*>(x_compact), p->hidden * 2,
+      reinterpret_cast<const long long*>(p->target), reinterpret_cast<long long*>(target_compact));
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_scatter_rows(const void* src, int64_t row_bytes, const int32_t* perm, const int32_t* active_rows,
+                           int64_t n_rows, void* dst, void* stream_) {
+  if (src == nullptr || perm == nullptr || active_rows == nullptr || dst == nullptr || n_rows <= 0 || row_bytes <= 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad scatter_rows arguments");
+  if (row_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (reinterpret_cast<uintptr_t>(dst) & 15) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "rows must be 16-byte multiples and 16-byte aligned");
+  DeviceState* dev;
+  int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  scatter_rows_kernel<<<static_cast<unsigned>(n_rows), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint8_t*>(src), perm, active_rows, static_cast<uint8_t*>(dst), row_bytes);
   FLCE_CUDA(cudaGetLastError());
   ++g_kernel_launches;
   return FLCE_OK;

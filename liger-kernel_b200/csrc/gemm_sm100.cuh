@@ -69,6 +69,10 @@ struct GemmShape {
   int group_along_m;   // 1: a group is `group` m-tiles x all n-tiles, m fastest; 0: the transpose
   int hint_a, hint_b;  // L2 eviction priority of the A / B loads: 0 default, 1 evict first, 2 evict last
   int poll_sleep_ns;   // back-off of the epilogue warps while they wait for an accumulator
+  // Optional device-resident row count (rows that matter come first, e.g. after ignored tokens were moved to the end):
+  // role 1 limits the m-tiles to those that contain such rows, role 2 limits the k-blocks (when K runs over rows).
+  const int* active_rows;
+  int active_role;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& mt, int& nt) {
@@ -101,8 +105,14 @@ __device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& m
 template <int kCtas, int kAMajor, int kBMajor, class Epi>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmShape shape, const int ab_format, const typename Epi::Params ep, int* status) {
+                    const GemmShape shape_arg, const int ab_format, const typename Epi::Params ep, int* status) {
   using Cfg = StageCfg<kCtas>;
+  GemmShape shape = shape_arg;
+  if (shape.active_rows != nullptr) {   // uniform across the grid: every CTA reads the same word
+    const int rows = max(0, *shape.active_rows);
+    if (shape.active_role == 1) shape.m_tiles = min(shape.m_tiles, (rows + kBlockM * kCtas - 1) / (kBlockM * kCtas));
+    else if (shape.active_role == 2) shape.k_blocks = min(shape.k_blocks, (rows + kBlockK - 1) / kBlockK);
+  }
   constexpr int kStages = Cfg::kStages;
 
   extern __shared__ uint8_t smem_raw[];
@@ -308,11 +318,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tmem_ld_wait();
         tmem_ld_fence(va);
         if (c + 1 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 1) * 32), vb);
+        if (shape.k_blocks == 0) {   // nothing was accumulated (no active rows): the product is zero
+#pragma unroll
+          for (int j = 0; j < 32; ++j) va[j] = 0u;
+        }
         epi.chunk(ep, va, col0 + c * 32);
         if (c + 1 < n_chunks) {
           tmem_ld_wait();
           tmem_ld_fence(vb);
           if (c + 2 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 2) * 32), va);
+          if (shape.k_blocks == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) vb[j] = 0u;
+          }
           epi.chunk(ep, vb, col0 + (c + 1) * 32);
         }
       }

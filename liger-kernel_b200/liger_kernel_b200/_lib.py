@@ -27,6 +27,8 @@ EXPORTS = (
     "flce_b200_forward_backward",
     "flce_b200_scale_gradient",
     "flce_b200_split_fp32",
+    "flce_b200_compact_rows",
+    "flce_b200_scatter_rows",
     "flce_b200_ce_forward",
     "flce_b200_ce_backward",
     "flce_b200_gemm",
@@ -51,7 +53,7 @@ class Problem(C.Structure):
         ("label_smoothing", C.c_float), ("lse_square_scale", C.c_float), ("softcap", C.c_float),
         ("use_token_scaling", C.c_int32), ("flags", C.c_int32),
         ("x", C.c_void_p), ("w", C.c_void_p), ("target", C.c_void_p),
-        ("bias", C.c_void_p), ("ce_weight", C.c_void_p),
+        ("bias", C.c_void_p), ("ce_weight", C.c_void_p), ("active_rows", C.c_void_p),
     ]
 
 
@@ -120,6 +122,10 @@ def _load():
     lib.flce_b200_ce_forward.restype = C.c_int
     lib.flce_b200_ce_backward.argtypes = [CP, vp, vp, vp, i32, vp, i64, vp, vp]
     lib.flce_b200_ce_backward.restype = C.c_int
+    lib.flce_b200_compact_rows.argtypes = [P, vp, vp, vp, vp, vp]
+    lib.flce_b200_compact_rows.restype = C.c_int
+    lib.flce_b200_scatter_rows.argtypes = [vp, i64, vp, vp, i64, vp, vp]
+    lib.flce_b200_scatter_rows.restype = C.c_int
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]

@@ -41,6 +41,9 @@ MODE = os.environ.get("LIGER_B200_FLCE_MODE", "recompute")
 # Read back the count of out-of-range targets after forward and raise, as the reference's stand-alone cross-entropy and
 # its sm_100 FLCE do (``ops/cross_entropy.py:389-392``).  Costs a host synchronisation, so it is off by default.
 CHECK_TARGETS = os.environ.get("LIGER_B200_CHECK_TARGETS", "0") == "1"
+# Move rows whose target is ignore_index to the end (on the device, no host sync) and let the sweeps skip the token
+# tiles that hold none of the others: the tensor work shrinks by the ignored fraction.  Recompute mode, 16-bit inputs.
+SKIP_IGNORED = os.environ.get("LIGER_B200_FLCE_SKIP_IGNORED", "0") == "1"
 
 
 def _raise_on_bad_targets(norm, vocab):
@@ -92,7 +95,8 @@ class _Prepared:
     """Validated, device-resident operands of one FLCE call and the matching C struct."""
 
     def __init__(self, _input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing,
-                 reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=True):
+                 reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=True,
+                 allow_compact=False):
         if _input.device.type != "cuda":
             raise RuntimeError("liger_kernel_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
         if _input.dim() != 2 or weight.dim() != 2 or _input.shape[1] != weight.shape[1]:
@@ -147,6 +151,46 @@ class _Prepared:
         p.bias = None if self.bias is None else self.bias.data_ptr()
         p.ce_weight = None if self.ce_weight is None else self.ce_weight.data_ptr()
         self.problem = p
+        self.compacted = False
+        if allow_compact and SKIP_IGNORED and not self.split:
+            self._compact()
+
+    def _compact(self):
+        """Stable-partition the rows (targets that are not ignore_index first) and point the problem at the result."""
+        n, dev = self.n_rows, self.device
+        xc = torch.empty((n, self.x.shape[1]), dtype=self.x.dtype, device=dev)
+        tc = torch.empty_like(self.target)
+        self.perm = torch.empty(n, dtype=torch.int32, device=dev)
+        self.active = torch.empty(1, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            check(lib.flce_b200_compact_rows(C.byref(self.problem), _ptr(xc), _ptr(tc), _ptr(self.perm), _ptr(self.active),
+                                             _stream(dev)))
+        self.x, self.target = xc, tc
+        p = self.problem
+        p.x, p.ld_x, p.target = xc.data_ptr(), xc.stride(0), tc.data_ptr()
+        p.active_rows = self.active.data_ptr()
+        self.compacted = True
+
+    def to_token_order(self, t: torch.Tensor, fill=0) -> torch.Tensor:
+        """Per-row values in compact order -> token order (rows of ignored tokens are already what they should be)."""
+        if not self.compacted:
+            return t
+        out = torch.full_like(t, fill)
+        out[self.perm.long()] = t
+        return out
+
+    def to_compact_order(self, t: torch.Tensor) -> torch.Tensor:
+        return t[self.perm.long()] if self.compacted else t
+
+    def rows_to_token_order(self, m: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """A compact [n_rows, cols] matrix (grad_input) -> token order, zeros on ignored rows."""
+        if m is None or not self.compacted:
+            return m
+        out = torch.empty_like(m)
+        with torch.cuda.device(self.device):
+            check(lib.flce_b200_scatter_rows(_ptr(m), m.shape[1] * m.element_size(), _ptr(self.perm), _ptr(self.active),
+                                             m.shape[0], _ptr(out), _stream(self.device)))
+        return out
 
     def workspace(self, phase: int, budget: int = 0) -> torch.Tensor:
         nbytes = lib.flce_b200_workspace_bytes(C.byref(self.problem), phase, budget)
@@ -298,8 +342,14 @@ def fused_linear_cross_entropy_forward(
     assert isinstance(return_token_accuracy, bool), f"return_token_accuracy must be True or False. Got: {return_token_accuracy}"
     assert isinstance(return_predicted_tokens, bool), f"return_predicted_tokens must be True or False. Got: {return_predicted_tokens}"
     prep = _Prepared(_input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction,
-                     softcap, use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)
+                     softcap, use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens,
+                     allow_compact=True)
     out, norm, _rowstats = flce_forward_device(prep)
+    if prep.compacted:  # per-row results back to token order (lse / target_prob stay compact: backward works there)
+        saved_lse, saved_prob = out["lse"], out["target_prob"]
+        out = dict(out, loss_rows=prep.to_token_order(out["loss_rows"]), z_loss_rows=prep.to_token_order(out["z_loss_rows"]),
+                   correct_rows=prep.to_token_order(out["correct_rows"]),
+                   predicted_tokens=prep.to_token_order(out["predicted_tokens"], fill=-1), lse=saved_lse, target_prob=saved_prob)
     if CHECK_TARGETS:
         _raise_on_bad_targets(norm, prep.vocab)
     if reduction == "none":
@@ -320,7 +370,10 @@ def fused_linear_cross_entropy_backward(grad_output, saved, need_input=True, nee
     gradient (scalar, or per token for ``reduction="none"``) is folded into the logit gradient before the
     two projections, so no separate scaling pass exists."""
     prep, lse, target_prob, norm = saved
+    if prep.compacted and grad_output is not None and grad_output.numel() == prep.n_rows and prep.reduction == "none":
+        grad_output = prep.to_compact_order(grad_output.reshape(-1))
     gx, gw, gb = flce_backward_device(prep, lse, target_prob, norm, grad_output, need_input, need_weight, need_bias)
+    gx = prep.rows_to_token_order(gx)
     h = prep.hidden
     if gx is not None and gx.shape[1] != h:
         gx = gx[:, :h].contiguous()
