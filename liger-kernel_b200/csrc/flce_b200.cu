@@ -198,8 +198,7 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   if (units > tiles) units = tiles;
   auto kernel = gemm_tcgen05_kernel<kCtas, kAMajor, kBMajor, Epi>;
   FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(units * kCtas), 1, 1);
   cfg.blockDim = dim3(kNumThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
@@ -877,7 +876,7 @@ int flce_b200_count(const flce_problem_t* p, float* norm, void* stream) {
   int rc = check_problem(p);
   if (rc != FLCE_OK) return rc;
   if (norm == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "norm is NULL");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   count_kernel<<<1, kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -893,7 +892,7 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
   int rc = check_problem(p);
   if (rc != FLCE_OK) return rc;
   if (rowstats == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "rowstats is NULL");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -951,7 +950,7 @@ int flce_b200_forward_stats_static(const flce_problem_t* p, float* rowstats, voi
   int rc = check_problem(p);
   if (rc != FLCE_OK) return rc;
   if (rowstats == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "rowstats is NULL");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1062,7 +1061,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
     return fail(FLCE_ERR_INVALID_ARGUMENT, "token scaling needs target_prob from the forward pass");
   if (args->grad_dtype != p->dtype && args->grad_dtype != FLCE_FP32)
     return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1238,7 +1237,7 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
                                       "reduction 'none' needs the two-sweep path");
   if (args->grad_dtype != p->dtype && args->grad_dtype != FLCE_FP32)
     return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1388,7 +1387,7 @@ int flce_b200_ce_forward(const flce_ce_problem_t* p, float* norm, float* rowstat
   if (norm == nullptr || rowstats == nullptr || out == nullptr)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "norm, rowstats and out must not be NULL");
   if (out->scalars != nullptr && out->loss_rows == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "scalars requires loss_rows");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1425,7 +1424,7 @@ int flce_b200_ce_backward(const flce_ce_problem_t* p, const float* lse, const fl
   if (lse == nullptr || norm == nullptr || grad_logits == nullptr || coef_scratch == nullptr)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "lse, norm, grad_logits and coef_scratch must not be NULL");
   if (ld_grad < p->vocab) return fail(FLCE_ERR_INVALID_ARGUMENT, "ld_grad smaller than vocab");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1476,7 +1475,7 @@ int flce_b200_compact_rows(const flce_problem_t* p, void* x_compact, int64_t* ta
     return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL output");
   if ((reinterpret_cast<uintptr_t>(x_compact) & 15) != 0 || (reinterpret_cast<uintptr_t>(p->x) & 15) != 0)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "x and x_compact must be 16-byte aligned");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1498,7 +1497,7 @@ int flce_b200_scatter_rows(const void* src, int64_t row_bytes, const int32_t* pe
     return fail(FLCE_ERR_INVALID_ARGUMENT, "bad scatter_rows arguments");
   if (row_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (reinterpret_cast<uintptr_t>(dst) & 15) != 0)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "rows must be 16-byte multiples and 16-byte aligned");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   int rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   scatter_rows_kernel<<<static_cast<unsigned>(n_rows), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
@@ -1511,7 +1510,7 @@ int flce_b200_scatter_rows(const void* src, int64_t row_bytes, const int32_t* pe
 int flce_b200_scale_gradient(void* data, int64_t n, int32_t dtype, const float* scale, void* stream_) {
   if (data == nullptr || scale == nullptr || n <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "bad scale_gradient arguments");
   if (dtype < FLCE_BF16 || dtype > FLCE_FP32) return fail(FLCE_ERR_INVALID_ARGUMENT, "bad dtype");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   int rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   const int fmt = dtype == FLCE_FP32 ? kOutFp32 : (dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
@@ -1538,7 +1537,7 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
   if (ab_dtype != FLCE_BF16 && ab_dtype != FLCE_FP16) return fail(FLCE_ERR_UNSUPPORTED, "A/B must be bf16 or fp16");
   if (d_dtype != FLCE_FP32 && d_dtype != ab_dtype) return fail(FLCE_ERR_UNSUPPORTED, "D must be fp32 or the input dtype");
   if (n % 8 != 0 || ld_d % 8 != 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "n and ld_d must be multiples of 8");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   int rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1600,7 +1599,7 @@ int flce_b200_debug_clock_trace(unsigned long long* out, int n_words) {
 #endif
 
 int flce_b200_check_device_status(void* stream) {
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   int rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   FLCE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
