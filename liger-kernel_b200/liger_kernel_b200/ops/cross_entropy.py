@@ -17,7 +17,8 @@ import torch
 
 from .. import _lib
 from .._lib import CeProblem, check, lib
-from .fused_linear_cross_entropy import _DTYPES, _REDUCTIONS, _as_forward_out, _ptr, _stream
+from . import fused_linear_cross_entropy as _fl
+from .fused_linear_cross_entropy import _DTYPES, _REDUCTIONS, _as_forward_out, _ptr
 
 # write the logit gradient over the logits' own storage in backward (as the reference does, to avoid a second
 # [BT, V] buffer); set to False to get a fresh tensor and keep the logits intact
@@ -26,8 +27,7 @@ INPLACE_GRADIENT = True
 
 class _CePrepared:
     def __init__(self, _input, target, weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap):
-        if _input.device.type != "cuda":
-            raise RuntimeError("liger_kernel_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+        _fl._require_cuda(_input)
         if _input.dim() != 2:
             raise ValueError(f"expected logits [BT, V], got {tuple(_input.shape)}")
         if target.dim() != 1 or target.shape[0] != _input.shape[0]:
@@ -73,8 +73,8 @@ def cross_entropy_forward(_input, target, weight, ignore_index, lse_square_scale
     norm = torch.empty(4, **f32)
     rowstats = torch.empty((_lib.ROWSTAT_PLANES, n), **f32)
     fo = _as_forward_out(out)
-    with torch.cuda.device(dev):
-        check(lib.flce_b200_ce_forward(C.byref(prep.problem), _ptr(norm), _ptr(rowstats), C.byref(fo), _stream(dev)))
+    with _fl._device_guard(dev):
+        check(lib.flce_b200_ce_forward(C.byref(prep.problem), _ptr(norm), _ptr(rowstats), C.byref(fo), _fl._stream(dev)))
     if reduction == "none":
         loss = out["loss_rows"].to(prep.dtype)
         z_loss = out["z_loss_rows"].to(prep.dtype) if return_z_loss else None
@@ -98,9 +98,9 @@ def cross_entropy_backward(saved, grad_output, inplace: Optional[bool] = None):
         raise ValueError(f"grad_output must have 1 or {prep.n_rows} elements, got {go.numel()}")
     per_row = int(go.numel() == prep.n_rows and prep.reduction == "none")
     scratch = torch.empty(3 * prep.n_rows, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _fl._device_guard(dev):
         check(lib.flce_b200_ce_backward(C.byref(prep.problem), _ptr(lse), _ptr(norm), _ptr(go), per_row, _ptr(grad),
-                                        grad.stride(0), _ptr(scratch), _stream(dev)))
+                                        grad.stride(0), _ptr(scratch), _fl._stream(dev)))
     return grad
 
 

@@ -59,6 +59,16 @@ def _stream(device):
     return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def _device_guard(device):
+    """Make `device` current for the calls inside (the library works on the current device)."""
+    return torch.cuda.device(device)
+
+
+def _require_cuda(t: torch.Tensor):
+    if t.device.type != "cuda":
+        raise RuntimeError("liger_kernel_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+
+
 def _pad_hidden(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
     """Rows must be 16-byte multiples for the TMA engine; zero-pad the hidden dimension if needed."""
     h = t.shape[1]
@@ -83,7 +93,7 @@ def _split_fp32(t: torch.Tensor, pattern, block_cols: int) -> torch.Tensor:
     rows, cols = t.shape
     out = torch.empty((rows, len(pattern) * block_cols), dtype=torch.bfloat16, device=t.device)
     pat = (C.c_int32 * len(pattern))(*pattern)
-    with torch.cuda.device(t.device):
+    with _device_guard(t.device):
         for r0 in range(0, rows, 65535):
             n = min(65535, rows - r0)
             check(lib.flce_b200_split_fp32(_ptr(t[r0:r0 + n]), n, cols, t.stride(0), _ptr(out[r0:r0 + n]), out.stride(0),
@@ -97,8 +107,7 @@ class _Prepared:
     def __init__(self, _input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing,
                  reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=True,
                  allow_compact=False):
-        if _input.device.type != "cuda":
-            raise RuntimeError("liger_kernel_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+        _require_cuda(_input)
         if _input.dim() != 2 or weight.dim() != 2 or _input.shape[1] != weight.shape[1]:
             raise ValueError(f"expected _input [BT, H] and weight [V, H], got {tuple(_input.shape)} and {tuple(weight.shape)}")
         if target.dim() != 1 or target.shape[0] != _input.shape[0]:
@@ -162,7 +171,7 @@ class _Prepared:
         tc = torch.empty_like(self.target)
         self.perm = torch.empty(n, dtype=torch.int32, device=dev)
         self.active = torch.empty(1, dtype=torch.int32, device=dev)
-        with torch.cuda.device(dev):
+        with _device_guard(dev):
             check(lib.flce_b200_compact_rows(C.byref(self.problem), _ptr(xc), _ptr(tc), _ptr(self.perm), _ptr(self.active),
                                              _stream(dev)))
         self.x, self.target = xc, tc
@@ -187,7 +196,7 @@ class _Prepared:
         if m is None or not self.compacted:
             return m
         out = torch.empty_like(m)
-        with torch.cuda.device(self.device):
+        with _device_guard(self.device):
             check(lib.flce_b200_scatter_rows(_ptr(m), m.shape[1] * m.element_size(), _ptr(self.perm), _ptr(self.active),
                                              m.shape[0], _ptr(out), _stream(self.device)))
         return out
@@ -218,7 +227,7 @@ def _as_forward_out(o) -> ForwardOut:
 
 def flce_forward_device(prep: _Prepared):
     """Run count + sweep 1 + finalize.  Returns (outputs dict, norm[4], rowstats[6, N])."""
-    with torch.cuda.device(prep.device):
+    with _device_guard(prep.device):
         norm = torch.empty(4, dtype=torch.float32, device=prep.device)
         rowstats = torch.empty((_lib.ROWSTAT_PLANES, prep.n_rows), dtype=torch.float32, device=prep.device)
         out = _forward_outputs(prep)
@@ -242,7 +251,7 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
     if prep.split:
         gd = torch.float32
         hp = prep.proj_x.shape[1]
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         gx = torch.empty((prep.n_rows, hp), dtype=gd, device=dev) if need_input else None
         gw = torch.empty((prep.vocab, hp), dtype=gd, device=dev) if need_weight else None
         gb = torch.empty(prep.vocab, dtype=torch.float32, device=dev) if need_bias else None
@@ -289,7 +298,7 @@ def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True,
     gd = prep.dtype if grad_dtype is None else grad_dtype
     budget = CHUNK_BUDGET_BYTES if chunk_budget is None else int(chunk_budget)
     hp = prep.x.shape[1]
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         norm = torch.empty(4, dtype=torch.float32, device=dev)
         out = _forward_outputs(prep)
         fo = _as_forward_out(out)
@@ -312,7 +321,7 @@ def scale_gradient_(t: Optional[torch.Tensor], scale: torch.Tensor):
     """In-place ``t *= scale`` with a device-resident fp32 scalar; a no-op on the device when the scalar is 1."""
     if t is None:
         return None
-    with torch.cuda.device(t.device):
+    with _device_guard(t.device):
         check(lib.flce_b200_scale_gradient(_ptr(t), t.numel(), _DTYPES[t.dtype], _ptr(scale), _stream(t.device)))
     return t
 

@@ -42,13 +42,13 @@ class CudaBackend:
 
     def count(self, prep):
         norm = torch.empty(4, dtype=torch.float32, device=prep.device)
-        with torch.cuda.device(prep.device):
+        with _op._device_guard(prep.device):
             check(lib.flce_b200_count(C.byref(prep.problem), _op._ptr(norm), _op._stream(prep.device)))
         return norm
 
     def forward_stats(self, prep):
         rowstats = torch.empty((_lib.ROWSTAT_PLANES, prep.n_rows), dtype=torch.float32, device=prep.device)
-        with torch.cuda.device(prep.device):
+        with _op._device_guard(prep.device):
             ws = prep.workspace(_lib.PHASE_FORWARD)
             check(lib.flce_b200_forward_stats(C.byref(prep.problem), _op._ptr(rowstats), _op._ptr(ws), ws.numel(),
                                               _op._stream(prep.device)))
@@ -57,7 +57,7 @@ class CudaBackend:
     def finalize(self, prep, rowstats, norm):
         out = _op._forward_outputs(prep)
         fo = _op._as_forward_out(out)
-        with torch.cuda.device(prep.device):
+        with _op._device_guard(prep.device):
             check(lib.flce_b200_forward_finalize(C.byref(prep.problem), _op._ptr(rowstats), _op._ptr(norm), C.byref(fo),
                                                  _op._stream(prep.device)))
         return out
