@@ -139,6 +139,8 @@ class CpuReference:
     fed with rows of the workload's shape at the full H and V.  The weight is built once, outside any timing."""
 
     def __init__(self, spec, seed=99):
+        # torchrun pins OMP_NUM_THREADS=1 for its workers: take all host cores back for the CPU arm
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
         self.g = torch.Generator().manual_seed(seed)
         self.H, self.V = spec["H"], spec["V"]
         self.w = torch.randn(self.V, self.H, generator=self.g) * 0.02
