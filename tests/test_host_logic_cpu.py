@@ -170,3 +170,25 @@ def test_sharded_operators_single_process_path(monkeypatch):
         assert (prob.vocab, prob.vocab_total, prob.vocab_offset, prob.flags) == (20, 50, 10, 1)
         loss.backward()
         assert fake.structs["flce_b200_backward"][-1].grad_dtype == 2 and w_shard.grad.shape == (20, 32)
+
+
+def test_cross_entropy_switch_routes_hf_loss_through_the_operator(monkeypatch):
+    """apply_liger_kernel_to_llama(cross_entropy=True) keeps the logits and sends Hugging Face's loss helper to
+    liger_cross_entropy (the reference rebinds nn.functional.cross_entropy the same way, monkey_patch.py:191-194)."""
+    transformers = pytest.importorskip("transformers")
+    import liger_kernel_b200 as lk
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    monkeypatch.setattr(torch.nn.functional, "cross_entropy", torch.nn.functional.cross_entropy)   # restored at teardown
+    with fake_lib.installed(monkeypatch) as fake:
+        torch.manual_seed(0)
+        model = LlamaForCausalLM(LlamaConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+                                             num_key_value_heads=2, vocab_size=97, max_position_embeddings=64))
+        lk.apply_liger_kernel_to_llama(rope=False, cross_entropy=True, fused_linear_cross_entropy=False, rms_norm=False,
+                                       swiglu=False, model=model)
+        assert torch.nn.functional.cross_entropy is lk.liger_cross_entropy
+        ids = torch.randint(0, 97, (2, 9))
+        out = model(input_ids=ids, labels=ids)
+        assert out.logits is not None and "flce_b200_ce_forward" in fake.calls
+        prob = fake.structs["flce_b200_ce_forward"][0]
+        assert (prob.n_rows, prob.vocab, prob.dtype, prob.reduction) == (18, 97, 2, 0)      # shifted + flattened fp32 logits
