@@ -305,9 +305,9 @@ def run_ours(args, spec, rank, world, local_rank):
             skw = {k: v for k, v in kw.items() if k != "return_z_loss"}
             loss = vocab_sharded_fused_linear_cross_entropy(xin, w, tin, vocab_lo, spec["V"], **skw)
         elif world > 1:
-            # global-batch loss; grad_weight is all-reduced slab by slab on a side stream inside backward
+            # global-batch loss; grad_weight is all-reduced over NCCL inside backward
             skw = {k: v for k, v in kw.items() if k != "return_z_loss"}
-            loss = token_sharded_fused_linear_cross_entropy(xin, w, tin, **skw)
+            loss = token_sharded_fused_linear_cross_entropy(xin, w, tin, overlap_grad_weight=args.overlap, **skw)
         else:
             out = liger_fused_linear_cross_entropy(xin, w, tin, **kw)
             loss = out if torch.is_tensor(out) else out.loss
@@ -455,6 +455,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true", dest="no_variants")
     ap.add_argument("--sharding", default="token", choices=["token", "vocab"])
+    ap.add_argument("--overlap", action="store_true", help="all-reduce grad_weight slab by slab on a side stream")
     ap.add_argument("--strong", action="store_true", help="fixed global batch split over the ranks (token sharding)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

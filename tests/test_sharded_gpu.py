@@ -52,7 +52,7 @@ def _worker(rank, world, init_file, mode, kw, result_file):
             xs, ws = x[lo:hi].clone().requires_grad_(True), w.clone().requires_grad_(True)
             import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
             mod.SLAB_BUDGET_BYTES = (hi - lo) * 2 * 1024      # several slabs: exercises the overlapped all-reduce
-            loss = sharded.token_sharded_fused_linear_cross_entropy(xs, ws, t[lo:hi], **kw)
+            loss = sharded.token_sharded_fused_linear_cross_entropy(xs, ws, t[lo:hi], overlap_grad_weight=True, **kw)
             loss.backward()
             ok = close(loss, ref, "loss", rtol=1e-5)
             ok &= close(xs.grad, xr.grad[lo:hi], "grad_input")
