@@ -5,7 +5,7 @@
 //   ce_grad_kernel  : one read + one write per element       -> logit gradient (may overwrite the logits)
 #pragma once
 
-#include "epilogues.cuh"
+#include "simt_common.cuh"
 
 namespace flce {
 

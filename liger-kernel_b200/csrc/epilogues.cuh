@@ -2,25 +2,10 @@
 // thread owns one output row of the tile and sees its 256 fp32 accumulators 32 at a time.
 #pragma once
 
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-
 #include "ptx_sm100.cuh"
+#include "simt_common.cuh"
 
 namespace flce {
-
-constexpr float kLog2e = 1.4426950408889634f;
-
-enum OutFormat : int { kOutBf16 = 0, kOutFp16 = 1, kOutFp32 = 2 };
-
-__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
-  if (fmt == kOutBf16) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // 32 fp32 values -> 32 16-bit values (64 bytes) at dst; one format branch for the whole row segment
 __device__ __forceinline__ void store32_16bit(uint4* dst, const float (&g)[32], int fmt) {
@@ -45,22 +30,6 @@ __device__ __forceinline__ void store32_16bit(uint4* dst, const float (&g)[32], 
                           *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
     }
   }
-}
-
-// tanh without branches: exp-based form away from zero, odd polynomial near zero (where the
-// exp form cancels).  Absolute error stays near 3e-7 (2e-7 from fp32 rounding of the exp form, the rest from the
-// approximate ex2 / rcp), so a soft-cap of 30 moves a logit by about 1e-5.
-__device__ __forceinline__ float tanh_accurate(float x) {
-  const float t = ex2_approx(x * (2.f * kLog2e));
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + t));
-  const float big = fmaf(-2.f, r, 1.f);
-  const float x2 = x * x;
-  float poly = fmaf(x2, 62.f / 2835.f, -17.f / 315.f);
-  poly = fmaf(x2, poly, 2.f / 15.f);
-  poly = fmaf(x2, poly, -1.f / 3.f);
-  poly = fmaf(x2 * x, poly, x);
-  return (fabsf(x) < 0.3f) ? poly : big;
 }
 
 // =====================================================================================

@@ -292,16 +292,4 @@ __device__ __forceinline__ void cluster_sync() {
   cluster_wait();
 }
 
-// ---------------------------------------------------------------- fast math used by the epilogues
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 }  // namespace flce

@@ -1,0 +1,134 @@
+"""The library's SIMT kernels run on host threads (tests/emu/): build helper, ctypes binding and a stand-in library
+object that sends the entry points made only of SIMT kernels (stand-alone cross-entropy, target counting, row
+compaction / scatter, fp32 term split, gradient scaling) to the emulation, so the Python operators can be driven on
+CPU tensors with real numerics.  Entry points that need the tensor-core sweeps stay recording stubs (fake_lib).
+
+Only the tests use this."""
+
+import contextlib
+import ctypes as C
+import os
+import subprocess
+
+import fake_lib
+from fake_lib import _addr
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SRC = os.path.join(_HERE, "emu", "emu_kernels.cpp")
+_CSRC = os.path.join(os.path.dirname(_HERE), "liger-kernel_b200", "csrc")
+_OUT = os.path.join(_HERE, "emu", "_build", "libflce_emu.so")
+_CUDA_INCLUDE = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+
+_lib = None
+
+
+def _stale():
+    if not os.path.exists(_OUT):
+        return True
+    built = os.path.getmtime(_OUT)
+    deps = [_SRC, os.path.join(_HERE, "emu", "simt_emulation.hpp")]
+    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "simt_common.cuh")]
+    return any(os.path.getmtime(d) > built for d in deps)
+
+
+def load():
+    """Compile (g++, C++20, host only) when sources changed, then load."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if _stale():
+        os.makedirs(os.path.dirname(_OUT), exist_ok=True)
+        cmd = ["g++", "-std=c++20", "-O1", "-pthread", "-fPIC", "-shared", "-I", _CUDA_INCLUDE, "-I", _CSRC, "-o", _OUT, _SRC]
+        done = subprocess.run(cmd, capture_output=True, text=True)
+        if done.returncode != 0:
+            raise RuntimeError("building the SIMT emulation failed:\n" + done.stderr[-4000:])
+    lib = C.CDLL(_OUT)
+    P, LL, I, F = C.c_void_p, C.c_longlong, C.c_int, C.c_float
+    sigs = {
+        "emu_ce_forward": [I, P, LL, LL, LL, P, P, LL, F, F, F, I, P, P, P, P, P, P, P, P, P],
+        "emu_ce_backward": [I, P, LL, LL, LL, P, P, LL, F, F, F, I, P, P, P, I, P, LL, P],
+        "emu_count": [P, LL, LL, P, LL, LL, F, P],
+        "emu_compact_rows": [P, LL, LL, LL, P, LL, P, P, P, P],
+        "emu_scatter_rows": [P, LL, P, P, LL, P],
+        "emu_split_fp32": [P, LL, LL, LL, P, LL, LL, P, I, I],
+        "emu_dz_inplace": [P, LL, LL, LL, I, P, LL, P, P, P, P, P, F],
+        "emu_colsum": [P, LL, LL, LL, I, P, I],
+        "emu_scale_inplace": [P, LL, I, P],
+        "emu_merge_partials": [LL, I, P, P, P, P, P, P],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = I
+    _lib = lib
+    return lib
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+class EmuLib(fake_lib.FakeLib):
+    """FakeLib whose SIMT-only entry points compute for real (on host memory)."""
+
+    def __init__(self):
+        super().__init__()
+        self.emu = load()
+
+    def _ce_args(self, prob):
+        return (prob.dtype, prob.logits, prob.ld, prob.n_rows, prob.vocab, prob.target, prob.ce_weight, prob.ignore_index,
+                prob.label_smoothing, prob.lse_square_scale, prob.softcap, prob.reduction)
+
+    def flce_b200_ce_forward(self, p, norm, rowstats, out, stream):
+        self.calls.append("flce_b200_ce_forward")
+        prob, fo = p._obj, out._obj
+        self.structs.setdefault("flce_b200_ce_forward", []).append(prob)
+        return self.emu.emu_ce_forward(*self._ce_args(prob), _addr(norm), _addr(rowstats), fo.lse, fo.target_prob, fo.loss_rows,
+                                       fo.z_loss_rows, fo.correct_rows, fo.predicted_tokens, fo.scalars)
+
+    def flce_b200_ce_backward(self, p, lse, norm, go, per_row, grad, ld_grad, scratch, stream):
+        self.calls.append("flce_b200_ce_backward")
+        return self.emu.emu_ce_backward(*self._ce_args(p._obj), _addr(lse), _addr(norm), _addr(go) or None, per_row, _addr(grad),
+                                        ld_grad, _addr(scratch))
+
+    def flce_b200_count(self, p, norm, stream):
+        self.calls.append("flce_b200_count")
+        prob = p._obj
+        return self.emu.emu_count(prob.target, prob.n_rows, prob.ignore_index, prob.ce_weight, prob.vocab, prob.vocab_offset,
+                                  float(prob.vocab_total), _addr(norm))
+
+    def flce_b200_compact_rows(self, p, xc, tc, perm, active, stream):
+        self.calls.append("flce_b200_compact_rows")
+        prob = p._obj
+        return self.emu.emu_compact_rows(prob.x, prob.ld_x, prob.hidden, prob.n_rows, prob.target, prob.ignore_index, _addr(xc),
+                                         _addr(tc), _addr(perm), _addr(active))
+
+    def flce_b200_scatter_rows(self, src, row_bytes, perm, active, n_rows, dst, stream):
+        self.calls.append("flce_b200_scatter_rows")
+        return self.emu.emu_scatter_rows(_addr(src), row_bytes, _addr(perm), _addr(active), n_rows, _addr(dst))
+
+    def flce_b200_split_fp32(self, src, rows, cols, ld_src, dst, ld_dst, block_cols, pattern, n_blocks, dst_dtype, stream):
+        self.calls.append("flce_b200_split_fp32")
+        pat = (C.c_int * 8)(*[int(pattern[i]) for i in range(n_blocks)])
+        return self.emu.emu_split_fp32(_addr(src), rows, cols, ld_src, _addr(dst), ld_dst, block_cols, C.addressof(pat), n_blocks,
+                                       dst_dtype)
+
+    def flce_b200_scale_gradient(self, data, n, dtype, scale, stream):
+        self.calls.append("flce_b200_scale_gradient")
+        return self.emu.emu_scale_inplace(_addr(data), n, {0: 0, 1: 1, 2: 2}[dtype], _addr(scale))
+
+
+@contextlib.contextmanager
+def installed(monkeypatch):
+    """Like fake_lib.installed, with the SIMT-only entry points computing through the emulation."""
+    import liger_kernel_b200.ops.cross_entropy as ce
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as fl
+    import liger_kernel_b200.sharded as sh
+
+    lib = EmuLib()
+    for mod in (fl, ce, sh):
+        monkeypatch.setattr(mod, "lib", lib)
+    monkeypatch.setattr(fl, "_stream", lambda device: None)
+    monkeypatch.setattr(fl, "_device_guard", lambda device: contextlib.nullcontext())
+    monkeypatch.setattr(fl, "_require_cuda", lambda t: None)
+    yield lib

@@ -3,115 +3,34 @@ reference's golden vectors.  Case grid follows test/transformers/test_cross_entr
 (shapes incl. V=128256-like wide rows and odd sizes, dtypes, reductions, label smoothing, z-loss, soft-cap,
 class weights, ignore_index, not-last-layer upstream gradients, per-row gradients for reduction "none").
 
-These kernels compile and their host logic is tested on the CPU, but they have not run on a GPU yet.  Until they
-have, this file only runs when LIGER_B200_RUN_UNVALIDATED=1 is set, so that the validated suite stays a clean signal."""
+The case bodies live in tests/ce_cases.py; tests/test_simt_emulation_cpu.py runs the same bodies on CPU tensors with
+the kernels emulated on host threads."""
 
-import os
-
-import numpy as np
 import pytest
 import torch
 
-from flce_cases import assert_close
-from golden_util import ce_golden_names, golden_grad_output, load_golden
-from oracle.flce_oracle import ce_oracle
+import ce_cases
+from golden_util import ce_golden_names
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("LIGER_B200_RUN_UNVALIDATED") != "1",
-                                 reason="stand-alone cross-entropy kernels not yet validated on a GPU")]
-
-
-def _run(logits, t, weight=None, grad_output=None, inplace=False, **kw):
-    import liger_kernel_b200.ops.cross_entropy as mod
-    from liger_kernel_b200.ops.cross_entropy import LigerCrossEntropyFunction as Fn
-
-    mod.INPLACE_GRADIENT = inplace
-    try:
-        x = logits.cuda().requires_grad_(True)
-        loss, z, acc, pred = Fn.apply(x, t.cuda(), None if weight is None else weight.cuda(), kw.get("ignore_index", -100),
-                                      kw.get("lse_square_scale", 0.0), kw.get("label_smoothing", 0.0),
-                                      kw.get("reduction", "mean"), kw.get("softcap"), True, True, True)
-        go = torch.ones_like(loss) if grad_output is None else torch.as_tensor(grad_output, dtype=loss.dtype).cuda().expand_as(loss).contiguous()
-        loss.backward(go)
-    finally:
-        mod.INPLACE_GRADIENT = True
-    return dict(loss=loss.detach().float().cpu(), z_loss=z.float().cpu(), token_accuracy=acc.cpu(), predicted=pred.cpu(),
-                grad=x.grad.float().cpu())
-
-
-def _check(res, ora, dtype):
-    low = dtype != torch.float32
-    scale = max(1.0, float(ora.loss.abs().max()))
-    assert_close(res["loss"], ora.loss.float(), (1e-2 if low else 1e-5) * scale, 1e-2 if low else 2e-5, "loss")
-    assert torch.equal(res["predicted"], ora.predicted_tokens)
-    gmax = float(ora.grad_input.abs().max())
-    assert_close(res["grad"], ora.grad_input.float(), (8e-3 if low else 2e-6) * max(gmax, 1e-30), 2e-2 if low else 2e-4, "grad")
-
-
-FEATURES = [dict(), dict(label_smoothing=0.1), dict(lse_square_scale=1e-3), dict(softcap=30.0),
-            dict(label_smoothing=0.1, ignore_index=42, lse_square_scale=1e-4, softcap=30.0)]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("N,V", [(256, 4096), (188, 123), (64, 128256), (33, 32001)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
-@pytest.mark.parametrize("feat", FEATURES)
+@pytest.mark.parametrize("feat", ce_cases.FEATURES)
 def test_ce_correctness(N, V, dtype, reduction, feat):
-    g = torch.Generator().manual_seed(N + V)
-    logits = (torch.randn(N, V, generator=g) * 2).to(dtype)
-    t = torch.randint(0, V, (N,), generator=g)
-    ii = feat.get("ignore_index", -100)
-    if ii >= 0:
-        t[t == ii] = ii + 1
-    t[torch.rand(N, generator=g) < 0.1] = ii
-    kw = dict(reduction=reduction, **feat)
-    res = _run(logits, t, **kw)
-    _check(res, ce_oracle(logits, t, **kw), dtype)
+    ce_cases.case_correctness("cuda", N, V, dtype, reduction, feat)
 
 
 def test_ce_weights_none_reduction_upstream_gradient_and_inplace():
-    g = torch.Generator().manual_seed(3)
-    logits = torch.randn(300, 1000, generator=g) * 3
-    t = torch.randint(0, 1000, (300,), generator=g)
-    t[::7] = -100
-    w = torch.rand(1000, generator=g) + 0.5
-    for kw, go in ((dict(label_smoothing=0.1), 2.0), (dict(reduction="none"), torch.rand(300) + 0.5), (dict(reduction="sum"), None)):
-        res = _run(logits, t, weight=w, grad_output=go, **kw)
-        _check(res, ce_oracle(logits, t, weight=w, grad_output=go, **kw), torch.float32)
-    # in-place mode: the gradient lands in the logits' own storage, and a second backward is refused
-    import liger_kernel_b200.ops.cross_entropy as mod
-    from liger_kernel_b200.ops.cross_entropy import LigerCrossEntropyFunction as Fn
-
-    base = logits.cuda()
-    x = base.clone().requires_grad_(True)
-    holder = x * 1.0                       # a non-leaf, as the output of an lm_head would be
-    loss = Fn.apply(holder, t.cuda(), None)[0]
-    loss.backward(retain_graph=True)
-    assert_close(x.grad.float().cpu(), ce_oracle(logits, t).grad_input.float(), 1e-7, 2e-4, "in-place grad")
-    assert holder.data_ptr() != base.data_ptr() and not torch.equal(holder.detach(), base)   # overwritten by the gradient
-    with pytest.raises(RuntimeError, match="overwritten"):
-        loss.backward()
-    assert mod.INPLACE_GRADIENT is True
+    ce_cases.case_weights_none_reduction_upstream_gradient_and_inplace("cuda")
 
 
 def test_ce_all_ignored_is_exact_zero():
-    logits = torch.randn(64, 500).bfloat16()
-    t = torch.full((64,), -100)
-    res = _run(logits, t)
-    assert float(res["loss"]) == 0.0 and float(res["grad"].abs().max()) == 0.0 and torch.all(res["predicted"] == -1)
+    ce_cases.case_all_ignored_is_exact_zero("cuda")
 
 
 @pytest.mark.parametrize("name", ce_golden_names())
 def test_ce_against_reference_golden(name):
-    rec, meta = load_golden(name)
-    dtype = getattr(torch, meta.get("dtype", "float32"))
-    logits, t = torch.from_numpy(rec["logits"]).to(dtype), torch.from_numpy(rec["target"])
-    w = None if "weight" not in rec else torch.from_numpy(rec["weight"])
-    kw = dict(ignore_index=meta["ignore_index"], lse_square_scale=meta.get("lse_square_scale", 0.0),
-              label_smoothing=meta.get("label_smoothing", 0.0), reduction=meta.get("reduction", "mean"), softcap=meta.get("softcap"))
-    res = _run(logits, t, weight=w, grad_output=golden_grad_output(rec, meta), **kw)
-    low = dtype != torch.float32
-    want = torch.from_numpy(rec["ref_grad_logits"])
-    assert_close(res["grad"], want, (8e-3 if low else 5e-6) * float(want.abs().max()), 2e-2 if low else 1e-3, "grad vs reference")
-    assert_close(res["loss"], torch.from_numpy(rec["ref_loss"]), 0.0 if low else 2e-5 * max(1.0, float(np.abs(rec["ref_loss"]).max())),
-                 1e-2 if low else 2e-4, "loss vs reference")
+    ce_cases.case_reference_golden("cuda", name)
