@@ -14,9 +14,8 @@ from .transformers.functional import liger_fused_linear_cross_entropy  # noqa: F
 from .transformers.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyLoss  # noqa: F401
 from .transformers.model.loss_utils import LigerForCausalLMLoss  # noqa: F401
 from .transformers.monkey_patch import _apply_liger_kernel_to_instance  # noqa: F401
-from .transformers.monkey_patch import apply_liger_kernel_to_gemma2  # noqa: F401
-from .transformers.monkey_patch import apply_liger_kernel_to_llama  # noqa: F401
-from .transformers.monkey_patch import apply_liger_kernel_to_qwen2  # noqa: F401
+from .transformers.monkey_patch import MODEL_TYPE_TO_APPLY_LIGER_FN  # noqa: F401
+from .transformers.monkey_patch import *  # noqa: F401,F403  (apply_liger_kernel_to_<family>, one per family in monkey_patch._FAMILIES)
 from .transformers.monkey_patch import install  # noqa: F401
 
 __version__ = "0.1.0"

@@ -1,25 +1,31 @@
-"""Switch Hugging Face llama / qwen2 / gemma2 causal-LM heads to the fused operator.
+"""Switch Hugging Face causal-LM heads to the fused operator.
 
-Signatures follow ``apply_liger_kernel_to_llama`` / ``_qwen2`` / ``_gemma2`` and
-``_apply_liger_kernel_to_instance`` of the reference
-(``src/liger_kernel/transformers/monkey_patch.py:221-285, 990-1060, 1598-1660, 3588-3650``).
+Signatures follow the ``apply_liger_kernel_to_<family>`` functions and ``_apply_liger_kernel_to_instance`` of the
+reference (``src/liger_kernel/transformers/monkey_patch.py``: llama ``:221-285``, qwen2 ``:990-1060``, gemma2
+``:1598-1660``, the model-type table ``:3534-3585``, instance patching ``:3588-3650``).  Covered: the text decoders whose
+head is ``hidden_states -> lm_head -> cross-entropy`` (dense, soft-capped and mixture-of-experts); vision-language
+wrappers and hybrid state-space models are not.
+
 The ``fused_linear_cross_entropy`` switch and the ``cross_entropy`` switch (logits kept, loss through the
 stand-alone cross-entropy operator) are implemented by this package; the other flags (rope, rms_norm,
-swiglu / geglu) belong to kernels outside this package and are accepted so existing call sites keep
-working: when set they are reported once and otherwise ignored.
+swiglu / geglu, layer_norm, relu_squared) belong to kernels outside this package and are accepted so existing
+call sites keep working: when set they are reported once and otherwise ignored.
 
 ``install()`` additionally rebinds the operator symbol inside an installed ``liger_kernel`` so that
 code which imports Liger directly (e.g. ``Trainer(use_liger_kernel=True)``) reaches this
 implementation.
 """
 
+import importlib
 import inspect
 import logging
 
+from dataclasses import dataclass
 from types import MethodType
+from typing import Callable, Optional, Tuple
 
 from ..ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction
-from .model.causal_lm import gemma2_lce_forward, llama_lce_forward, qwen2_lce_forward
+from .model.causal_lm import dense_lce_forward, moe_lce_forward, softcap_lce_forward
 
 logger = logging.getLogger(__name__)
 _reported = set()
@@ -43,59 +49,120 @@ def _patch_cross_entropy():
 
 
 def _patch_forward(modeling_module, class_name, forward_fn, model):
-    if model is not None:
-        model.forward = MethodType(forward_fn, model)
-    else:
+    if model is None:
         getattr(modeling_module, class_name).forward = forward_fn
+        return
+    target = model
+    cls = getattr(modeling_module, class_name)
+    if not isinstance(model, cls):
+        # a wrapper around the text decoder (e.g. a multimodal model holding it as language_model)
+        inner = getattr(model, "language_model", None)
+        if not isinstance(inner, cls):
+            raise TypeError(f"expected an instance of {class_name}, got {type(model).__name__}")
+        target = inner
+    target.forward = MethodType(forward_fn, target)
 
 
-def apply_liger_kernel_to_llama(rope: bool = True, cross_entropy: bool = False, fused_linear_cross_entropy: bool = True,
-                                rms_norm: bool = True, swiglu: bool = True, model=None) -> None:
-    assert not (cross_entropy and fused_linear_cross_entropy), (
-        "cross_entropy and fused_linear_cross_entropy cannot both be True."
-    )
-    from transformers.models.llama import modeling_llama
+@dataclass(frozen=True)
+class _Family:
+    """One ``apply_liger_kernel_to_<name>``: where the causal-LM class lives, which forward it gets, and the
+    reference's keyword defaults (flags of kernels outside this package included)."""
 
-    _report_unhandled(rope=rope, rms_norm=rms_norm, swiglu=swiglu)
-    if cross_entropy:
-        _patch_cross_entropy()
-    if fused_linear_cross_entropy:
-        _patch_forward(modeling_llama, "LlamaForCausalLM", llama_lce_forward, model)
-
-
-def apply_liger_kernel_to_qwen2(rope: bool = True, cross_entropy: bool = False, fused_linear_cross_entropy: bool = True,
-                                rms_norm: bool = True, swiglu: bool = True, model=None) -> None:
-    assert not (cross_entropy and fused_linear_cross_entropy), (
-        "cross_entropy and fused_linear_cross_entropy cannot both be True."
-    )
-    from transformers.models.qwen2 import modeling_qwen2
-
-    _report_unhandled(rope=rope, rms_norm=rms_norm, swiglu=swiglu)
-    if cross_entropy:
-        _patch_cross_entropy()
-    if fused_linear_cross_entropy:
-        _patch_forward(modeling_qwen2, "Qwen2ForCausalLM", qwen2_lce_forward, model)
+    name: str
+    module: str
+    class_name: str
+    forward: Optional[Callable]
+    other_flags: Tuple[Tuple[str, bool], ...] = (("rope", True), ("rms_norm", True), ("swiglu", True))
+    cross_entropy: bool = False
+    fused_linear_cross_entropy: bool = True
+    extra_kwargs: bool = False        # the reference's function also swallows **kwargs
+    model_types: Tuple[str, ...] = ()
 
 
-def apply_liger_kernel_to_gemma2(rope: bool = True, cross_entropy: bool = False, fused_linear_cross_entropy: bool = True,
-                                 rms_norm: bool = True, geglu: bool = True, model=None) -> None:
-    assert not (cross_entropy and fused_linear_cross_entropy), (
-        "cross_entropy and fused_linear_cross_entropy cannot both be True."
-    )
-    from transformers.models.gemma2 import modeling_gemma2
+_GEGLU = (("rope", True), ("rms_norm", True), ("geglu", True))
 
-    _report_unhandled(rope=rope, rms_norm=rms_norm, geglu=geglu)
-    if cross_entropy:
-        _patch_cross_entropy()
-    if fused_linear_cross_entropy:
-        _patch_forward(modeling_gemma2, "Gemma2ForCausalLM", gemma2_lce_forward, model)
+_FAMILIES = (
+    _Family("llama", "transformers.models.llama.modeling_llama", "LlamaForCausalLM", dense_lce_forward),
+    _Family("mistral", "transformers.models.mistral.modeling_mistral", "MistralForCausalLM", dense_lce_forward),
+    _Family("ministral", "transformers.models.ministral.modeling_ministral", "MinistralForCausalLM", dense_lce_forward),
+    _Family("mixtral", "transformers.models.mixtral.modeling_mixtral", "MixtralForCausalLM", moe_lce_forward),
+    _Family("gemma", "transformers.models.gemma.modeling_gemma", "GemmaForCausalLM", dense_lce_forward, _GEGLU),
+    _Family("gemma2", "transformers.models.gemma2.modeling_gemma2", "Gemma2ForCausalLM", softcap_lce_forward, _GEGLU),
+    _Family("gemma3_text", "transformers.models.gemma3.modeling_gemma3", "Gemma3ForCausalLM", softcap_lce_forward, _GEGLU),
+    _Family("qwen2", "transformers.models.qwen2.modeling_qwen2", "Qwen2ForCausalLM", dense_lce_forward),
+    _Family("qwen3", "transformers.models.qwen3.modeling_qwen3", "Qwen3ForCausalLM", dense_lce_forward),
+    _Family("qwen3_moe", "transformers.models.qwen3_moe.modeling_qwen3_moe", "Qwen3MoeForCausalLM", moe_lce_forward),
+    _Family("phi3", "transformers.models.phi3.modeling_phi3", "Phi3ForCausalLM", dense_lce_forward),
+    _Family("olmo2", "transformers.models.olmo2.modeling_olmo2", "Olmo2ForCausalLM", dense_lce_forward),
+    _Family("olmo3", "transformers.models.olmo3.modeling_olmo3", "Olmo3ForCausalLM", dense_lce_forward),
+    _Family("glm4", "transformers.models.glm4.modeling_glm4", "Glm4ForCausalLM", dense_lce_forward,
+            (("rope", False), ("rms_norm", True), ("swiglu", True))),
+    _Family("smollm3", "transformers.models.smollm3.modeling_smollm3", "SmolLM3ForCausalLM", dense_lce_forward),
+    _Family("nemotron", "transformers.models.nemotron.modeling_nemotron", "NemotronForCausalLM", dense_lce_forward,
+            (("relu_squared", True),), extra_kwargs=True),
+    _Family("exaone4", "transformers.models.exaone4.modeling_exaone4", "Exaone4ForCausalLM", dense_lce_forward),
+    _Family("hunyuan_v1_dense", "transformers.models.hunyuan_v1_dense.modeling_hunyuan_v1_dense", "HunYuanDenseV1ForCausalLM",
+            dense_lce_forward),
+    _Family("hunyuan_v1_moe", "transformers.models.hunyuan_v1_moe.modeling_hunyuan_v1_moe", "HunYuanMoEV1ForCausalLM",
+            dense_lce_forward),
+    _Family("gpt_oss", "transformers.models.gpt_oss.modeling_gpt_oss", "GptOssForCausalLM", moe_lce_forward,
+            (("rope", True), ("rms_norm", True), ("swiglu", False))),
+    _Family("llama4", "transformers.models.llama4.modeling_llama4", "Llama4ForCausalLM", dense_lce_forward,
+            (("rope", True), ("rms_norm", True), ("swiglu", True), ("layer_norm", True)), model_types=("llama4_text", "llama4")),
+    # the reference offers only the cross-entropy switch for granite (its logits are divided by config.logits_scaling)
+    _Family("granite", "transformers.models.granite.modeling_granite", "GraniteForCausalLM", None,
+            cross_entropy=True, fused_linear_cross_entropy=False),
+)
 
 
-MODEL_TYPE_TO_APPLY_LIGER_FN = {
-    "llama": apply_liger_kernel_to_llama,
-    "qwen2": apply_liger_kernel_to_qwen2,
-    "gemma2": apply_liger_kernel_to_gemma2,
-}
+def _make_apply(family: _Family):
+    P = inspect.Parameter
+    params = [P(name, P.POSITIONAL_OR_KEYWORD, default=default, annotation=bool) for name, default in family.other_flags]
+    # the reference's order: other flags first except that cross_entropy / fused_linear_cross_entropy follow the first one
+    head, tail = params[:1], params[1:]
+    params = head + [P("cross_entropy", P.POSITIONAL_OR_KEYWORD, default=family.cross_entropy, annotation=bool),
+                     P("fused_linear_cross_entropy", P.POSITIONAL_OR_KEYWORD, default=family.fused_linear_cross_entropy,
+                       annotation=bool)] + tail
+    if family.name == "llama4":   # (..., swiglu, model, layer_norm) in the reference
+        params = [q for q in params if q.name != "layer_norm"]
+        params += [P("model", P.POSITIONAL_OR_KEYWORD, default=None), P("layer_norm", P.POSITIONAL_OR_KEYWORD, default=True)]
+    else:
+        params.append(P("model", P.POSITIONAL_OR_KEYWORD, default=None))
+    if family.extra_kwargs:
+        params.append(P("kwargs", P.VAR_KEYWORD))
+    signature = inspect.Signature(params, return_annotation=None)
+
+    def apply(*args, **kwargs) -> None:
+        bound = signature.bind(*args, **kwargs)
+        bound.apply_defaults()
+        a = bound.arguments
+        assert not (a["cross_entropy"] and a["fused_linear_cross_entropy"]), (
+            "cross_entropy and fused_linear_cross_entropy cannot both be True."
+        )
+        if a["fused_linear_cross_entropy"] and family.forward is None:
+            raise NotImplementedError(f"LigerFusedLinearCrossEntropy is not available for {family.name.capitalize()} models.")
+        modeling = importlib.import_module(family.module)
+        _report_unhandled(**{name: a[name] for name, _ in family.other_flags})
+        if a["cross_entropy"]:
+            _patch_cross_entropy()
+        if a["fused_linear_cross_entropy"]:
+            _patch_forward(modeling, family.class_name, family.forward, a["model"])
+
+    apply.__signature__ = signature
+    apply.__name__ = apply.__qualname__ = f"apply_liger_kernel_to_{family.name}"
+    apply.__doc__ = (f"Route the training loss of ``{family.class_name}`` through the fused operator (class-wide, or one "
+                     f"instance when ``model`` is given); keyword defaults are the reference's.")
+    return apply
+
+
+MODEL_TYPE_TO_APPLY_LIGER_FN = {}
+for _family in _FAMILIES:
+    _fn = _make_apply(_family)
+    globals()[_fn.__name__] = _fn
+    for _model_type in (_family.model_types or (_family.name,)):
+        MODEL_TYPE_TO_APPLY_LIGER_FN[_model_type] = _fn
+__all__ = sorted({fn.__name__ for fn in MODEL_TYPE_TO_APPLY_LIGER_FN.values()}) + [
+    "MODEL_TYPE_TO_APPLY_LIGER_FN", "_apply_liger_kernel", "_apply_liger_kernel_to_instance", "install"]
 
 
 def _apply_liger_kernel(model_type: str, **kwargs) -> None:
