@@ -1,8 +1,9 @@
-"""Generate the golden FLCE vectors in this directory from the reference itself.
+"""Generate the golden vectors in this directory from the reference itself: fused linear cross-entropy (no prefix),
+stand-alone cross-entropy (``xent_*``), fused linear JSD (``jsd_*``) and fused linear scaled cross-entropy (``sce_*``).
 
 Run once, in a container that has the reference checkout and no GPU:
 
-    REFERENCE_SRC=<reference checkout>/src python tests/golden/make_golden.py
+    REFERENCE_SRC=<reference checkout>/src python tests/golden/make_golden.py [all|flce|ce|jsd|sce]
 
 For every case below the script
   1. builds seeded inputs,
@@ -254,10 +255,105 @@ def run_ce_case(name, spec):
     print(f"{name}: loss={np.asarray(rec['ref_loss']).reshape(-1)[:1]}")
 
 
+# ---- fused linear JSD: the reference's fused_linear_jsd_forward / _backward (Triton _jsd_kernel under the interpreter) ---
+JSD_CASES = {
+    "jsd_default": dict(N=48, Hs=32, Ht=64, V=131),
+    "jsd_labels_beta01_t2": dict(N=48, Hs=32, Ht=64, V=131, labels=0.25, beta=0.1, temperature=2.0),
+    "jsd_forward_kl": dict(N=40, Hs=24, Ht=24, V=203, labels=0.1, beta=0.0),
+    "jsd_reverse_kl": dict(N=40, Hs=24, Ht=24, V=203, labels=0.1, beta=1.0, temperature=0.5),
+    "jsd_bf16_grad_output": dict(N=64, Hs=32, Ht=64, V=256, labels=0.1, beta=0.5, dtype="bfloat16", grad_output=2.5),
+    "jsd_ignore_index_7": dict(N=40, Hs=24, Ht=48, V=97, labels=0.3, beta=0.7, ignore_index=7, temperature=1.5),
+}
+
+
+def run_jsd_case(name, spec):
+    from liger_kernel.ops.fused_linear_jsd import fused_linear_jsd_backward, fused_linear_jsd_forward
+
+    seed = 3000 + sorted(JSD_CASES).index(name)
+    g = torch.Generator().manual_seed(seed)
+    N, Hs, Ht, V = spec["N"], spec["Hs"], spec["Ht"], spec["V"]
+    dtype = getattr(torch, spec.get("dtype", "float32"))
+    xs = torch.randn(N, Hs, generator=g).to(dtype)
+    ws = (torch.randn(V, Hs, generator=g) * 0.3).to(dtype)
+    xt = torch.randn(N, Ht, generator=g).to(dtype)
+    wt = (torch.randn(V, Ht, generator=g) * 0.3).to(dtype)
+    ignore_index = spec.get("ignore_index", -100)
+    labels = None
+    if "labels" in spec:
+        labels = torch.randint(0, V, (N,), generator=g)
+        if ignore_index >= 0:
+            labels[labels == ignore_index] = (ignore_index + 1) % V
+        labels[torch.rand(N, generator=g) < spec["labels"]] = ignore_index
+    xr, wr = xs.clone().requires_grad_(True), ws.clone().requires_grad_(True)
+    with torch.no_grad():
+        loss, gx, gw = fused_linear_jsd_forward(xr, wr, xt, wt, labels, spec.get("beta", 0.5), ignore_index, labels is not None,
+                                                spec.get("temperature", 1.0))
+        if spec.get("grad_output") is not None:
+            gx, gw = fused_linear_jsd_backward(torch.tensor(spec["grad_output"]), gx, gw)
+    rec = dict(student_input=xs.float().numpy(), student_weight=ws.float().numpy(), teacher_input=xt.float().numpy(),
+               teacher_weight=wt.float().numpy(), ref_loss=loss.float().numpy(), ref_grad_input=gx.float().numpy(),
+               ref_grad_weight=gw.float().numpy())
+    if labels is not None:
+        rec["labels"] = labels.numpy()
+    meta = dict(spec)
+    meta["ignore_index"] = ignore_index
+    rec["meta"] = np.array(repr(meta))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+    print(f"{name}: loss={np.asarray(rec['ref_loss']).reshape(-1)[:1]}")
+
+
+# ---- fused linear scaled cross-entropy: the reference's device-independent implementation, run on CPU tensors -------------
+SCE_CASES = {
+    "sce_fp32_ragged_both": dict(N=37, H=31, V=257, temperature=1.5, ign=0.2, grads="both"),
+    "sce_nll_only": dict(N=40, H=32, V=131, temperature=1.0, ign=0.1, grads="nll"),
+    "sce_entropy_only": dict(N=40, H=32, V=131, temperature=0.7, ign=0.1, grads="entropy"),
+    "sce_bf16_both": dict(N=64, H=64, V=256, temperature=2.0, ign=0.1, grads="both", dtype="bfloat16"),
+    "sce_multichunk": dict(N=600, H=16, V=67, temperature=1.25, ign=0.05, grads="both"),      # spans two 512-token chunks
+}
+
+
+def run_sce_case(name, spec):
+    from liger_kernel.ops.fused_linear_scaled_cross_entropy import LigerFusedLinearScaledCrossEntropyFunction
+
+    seed = 4000 + sorted(SCE_CASES).index(name)
+    g = torch.Generator().manual_seed(seed)
+    N, H, V = spec["N"], spec["H"], spec["V"]
+    dtype = getattr(torch, spec.get("dtype", "float32"))
+    x = (torch.randn(N, H, generator=g) * 0.5).to(dtype)
+    w = (torch.randn(V, H, generator=g) / H ** 0.5 * 2).to(dtype)
+    t = torch.randint(0, V, (N,), generator=g)
+    t[torch.rand(N, generator=g) < spec["ign"]] = -100
+    g_nll = torch.randn(N, generator=g)
+    g_ent = torch.randn(N, generator=g)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    nll, entropy = LigerFusedLinearScaledCrossEntropyFunction.apply(xr, wr, t, spec["temperature"], -100, 1, True)
+    total = 0
+    if spec["grads"] in ("both", "nll"):
+        total = total + (nll * g_nll).sum()
+    if spec["grads"] in ("both", "entropy"):
+        total = total + (entropy.float() * g_ent).sum()
+    total.backward()
+    rec = dict(x=x.float().numpy(), w=w.float().numpy(), target=t.numpy(), grad_nll=g_nll.numpy(), grad_entropy=g_ent.numpy(),
+               ref_nll=nll.detach().float().numpy(), ref_entropy=entropy.detach().float().numpy(),
+               ref_grad_input=xr.grad.float().numpy(), ref_grad_weight=wr.grad.float().numpy())
+    meta = dict(spec)
+    meta["ignore_index"] = -100
+    rec["meta"] = np.array(repr(meta))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+    print(f"{name}: nll[:2]={rec['ref_nll'][:2]} entropy[:2]={rec['ref_entropy'][:2]}")
+
+
 if __name__ == "__main__":
-    only_ce = len(sys.argv) > 1 and sys.argv[1] == "ce"
-    if not only_ce:
+    which = sys.argv[1] if len(sys.argv) > 1 else "all"       # all | flce | ce | jsd | sce
+    if which in ("all", "flce"):
         for case_name in sorted(CASES):
             run_case(case_name, CASES[case_name])
-    for case_name in sorted(CE_CASES):
-        run_ce_case(case_name, CE_CASES[case_name])
+    if which in ("all", "ce"):
+        for case_name in sorted(CE_CASES):
+            run_ce_case(case_name, CE_CASES[case_name])
+    if which in ("all", "jsd"):
+        for case_name in sorted(JSD_CASES):
+            run_jsd_case(case_name, JSD_CASES[case_name])
+    if which in ("all", "sce"):
+        for case_name in sorted(SCE_CASES):
+            run_sce_case(case_name, SCE_CASES[case_name])

@@ -14,9 +14,22 @@ def _all_names():
     return sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
 
 
+_PREFIXES = ("xent_", "jsd_", "sce_")
+
+
 def golden_names():
     """Fused linear cross-entropy cases."""
-    return [n for n in _all_names() if not n.startswith("xent_")]
+    return [n for n in _all_names() if not n.startswith(_PREFIXES)]
+
+
+def jsd_golden_names():
+    """Fused linear JSD cases."""
+    return [n for n in _all_names() if n.startswith("jsd_")]
+
+
+def sce_golden_names():
+    """Fused linear scaled cross-entropy cases."""
+    return [n for n in _all_names() if n.startswith("sce_")]
 
 
 def ce_golden_names():

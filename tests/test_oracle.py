@@ -8,7 +8,8 @@ import numpy as np
 import pytest
 import torch
 
-from golden_util import golden_grad_output, golden_kwargs, golden_names, load_golden
+from golden_util import golden_grad_output, golden_kwargs, golden_names, jsd_golden_names, load_golden, sce_golden_names
+from oracle.distill_oracle import fused_linear_jsd_oracle, fused_linear_scaled_ce_oracle
 from oracle.flce_oracle import flce_oracle, torch_linear_ce_reference
 
 
@@ -115,3 +116,89 @@ def test_ce_oracle_matches_reference_golden(name):
         _close(res.token_accuracy, rec["ref_token_accuracy"], 1e-6, 0, "token_accuracy")
     if "ref_predicted_tokens" in rec:
         assert np.array_equal(res.predicted_tokens.numpy(), rec["ref_predicted_tokens"])
+
+
+# ---------------------------------------------------------------- fused linear JSD / scaled cross-entropy oracles
+def _jsd_inputs(rec, meta):
+    t = {k: torch.from_numpy(rec[k]) for k in ("student_input", "student_weight", "teacher_input", "teacher_weight")}
+    labels = torch.from_numpy(rec["labels"]) if "labels" in rec else None
+    kw = dict(jsd_beta=meta.get("beta", 0.5), ignore_index=meta["ignore_index"], temperature=meta.get("temperature", 1.0))
+    return t, labels, kw
+
+
+@pytest.mark.parametrize("name", jsd_golden_names())
+def test_jsd_oracle_matches_reference_golden(name):
+    """fp64 closed form vs the reference's fused_linear_jsd_forward (/ _backward) run on CPU by Triton's interpreter."""
+    rec, meta = load_golden(name)
+    bf16 = meta.get("dtype") == "bfloat16"
+    t, labels, kw = _jsd_inputs(rec, meta)
+    low = torch.bfloat16 if bf16 else None
+    res = fused_linear_jsd_oracle(t["student_input"], t["student_weight"], t["teacher_input"], t["teacher_weight"], labels,
+                                  grad_output=meta.get("grad_output", 1.0), round_logits_to=low, round_dlogits_to=low, **kw)
+    _close(res.loss, rec["ref_loss"], 1e-2 if bf16 else 1e-6, 1e-2 if bf16 else 2e-5, "loss")
+    for key, got in (("ref_grad_input", res.grad_input), ("ref_grad_weight", res.grad_weight)):
+        gmax = float(np.abs(rec[key]).max())
+        _close(got, rec[key], (1e-2 if bf16 else 2e-6) * gmax, 2e-2 if bf16 else 2e-4, key)
+    if "labels" in rec:
+        ignored = rec["labels"] == meta["ignore_index"]
+        assert float(np.abs(res.grad_input.numpy()[ignored]).max(initial=0.0)) == 0.0
+
+
+@pytest.mark.parametrize("name", sce_golden_names())
+def test_scaled_ce_oracle_matches_reference_golden(name):
+    """fp64 closed form vs the reference's LigerFusedLinearScaledCrossEntropyFunction on CPU tensors."""
+    rec, meta = load_golden(name)
+    bf16 = meta.get("dtype") == "bfloat16"
+    x, w, t = torch.from_numpy(rec["x"]), torch.from_numpy(rec["w"]), torch.from_numpy(rec["target"])
+    g_nll = torch.from_numpy(rec["grad_nll"]) if meta["grads"] in ("both", "nll") else None
+    g_ent = torch.from_numpy(rec["grad_entropy"]) if meta["grads"] in ("both", "entropy") else None
+    low = torch.bfloat16 if bf16 else None
+    res = fused_linear_scaled_ce_oracle(x, w, t, meta["temperature"], -100, g_nll, g_ent, round_logits_to=low, round_dlogits_to=low)
+    _close(res.nll, rec["ref_nll"], 4e-2 if bf16 else 2e-5, 1e-2 if bf16 else 2e-5, "nll")
+    _close(res.entropy, rec["ref_entropy"], 4e-2 if bf16 else 2e-5, 1e-2 if bf16 else 2e-5, "entropy")
+    for key, got in (("ref_grad_input", res.grad_input), ("ref_grad_weight", res.grad_weight)):
+        gmax = float(np.abs(rec[key]).max())
+        _close(got, rec[key], (2e-2 if bf16 else 5e-6) * gmax, 2e-2 if bf16 else 5e-4, key)
+    ignored = rec["target"] == -100
+    assert float(np.abs(res.nll.numpy()[ignored]).max(initial=0.0)) == 0.0
+
+
+def test_distill_oracles_equal_autograd_fp64():
+    """Both closed forms against torch autograd in fp64 (independent of the reference's hand-written gradients)."""
+    g = torch.Generator().manual_seed(11)
+    N, H, V = 13, 9, 29
+    xs = torch.randn(N, H, generator=g, dtype=torch.float64).requires_grad_(True)
+    ws = torch.randn(V, H, generator=g, dtype=torch.float64).requires_grad_(True)
+    xt, wt = torch.randn(N, 2 * H, generator=g, dtype=torch.float64), torch.randn(V, 2 * H, generator=g, dtype=torch.float64)
+    labels = torch.randint(0, V, (N,), generator=g)
+    labels[::4] = -100
+    for beta in (0.0, 0.3, 1.0):
+        X = torch.log_softmax(xs @ ws.T / 1.7, -1)
+        Y = torch.log_softmax(xt @ wt.T / 1.7, -1)
+        P, Q = Y.exp(), X.exp()
+        if beta == 0.0:
+            rows = (P * (Y - X)).sum(-1)
+        elif beta == 1.0:
+            rows = (Q * (X - Y)).sum(-1)
+        else:
+            M = beta * P + (1 - beta) * Q
+            rows = beta * (P * (Y - M.log())).sum(-1) + (1 - beta) * (Q * (X - M.log())).sum(-1)
+        live = labels != -100
+        loss = (rows * live).sum() / live.sum()
+        gx, gw = torch.autograd.grad(loss, (xs, ws))
+        res = fused_linear_jsd_oracle(xs.detach(), ws.detach(), xt, wt, labels, jsd_beta=beta, temperature=1.7)
+        _close(res.loss, loss.detach(), 1e-12, 1e-10, "jsd loss")
+        _close(res.grad_input, gx, 1e-12, 1e-9, "jsd grad_input")
+        _close(res.grad_weight, gw, 1e-12, 1e-9, "jsd grad_weight")
+    s = xs @ ws.T / 0.8
+    logp = torch.log_softmax(s, -1)
+    nll = -logp.gather(-1, labels.clamp_min(0)[:, None])[:, 0]
+    ent = -(logp.exp() * logp).sum(-1)
+    g_nll, g_ent = torch.randn(N, generator=g, dtype=torch.float64), torch.randn(N, generator=g, dtype=torch.float64)
+    live = (labels != -100).double()
+    gx, gw = torch.autograd.grad(((nll * g_nll + ent * g_ent) * live).sum(), (xs, ws))
+    res = fused_linear_scaled_ce_oracle(xs.detach(), ws.detach(), labels, 0.8, -100, g_nll, g_ent)
+    _close(res.nll, (nll * live).detach(), 1e-12, 1e-10, "nll")
+    _close(res.entropy, (ent * live).detach(), 1e-12, 1e-10, "entropy")
+    _close(res.grad_input, gx, 1e-12, 1e-9, "sce grad_input")
+    _close(res.grad_weight, gw, 1e-12, 1e-9, "sce grad_weight")
