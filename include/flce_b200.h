@@ -258,6 +258,44 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
                    int64_t ld_b, int64_t ld_d, int32_t ab_dtype, int32_t d_dtype, int32_t a_mn_major,
                    int32_t b_mn_major, int32_t cta_pair, void* stream);
 
+/* flce_b200_gemm with an fp32 accumulator: v = A . B^T (+ acc when acc != NULL); v is written to acc (fp32, in/out,
+ * [m, ld_acc]) when acc != NULL and to out ([m, ld_out] in out_dtype: fp32 or the A/B dtype) when out != NULL.  n need
+ * not be a multiple of 8 as long as ld_acc / ld_out, rounded to 8 elements, cover it: stores go in 16-byte groups and
+ * may touch the padding of a row.  Used by the chunked losses below for grad_weight += dZ^T . X across token chunks
+ * (the reference's grad_weight.add_ / torch.addmm, src/liger_kernel/ops/fused_linear_jsd.py:127-150). */
+int flce_b200_gemm_accumulate(const void* a, const void* b, float* acc, void* out, int64_t m, int64_t n, int64_t k,
+                              int64_t ld_a, int64_t ld_b, int64_t ld_acc, int64_t ld_out, int32_t ab_dtype,
+                              int32_t out_dtype, int32_t a_mn_major, int32_t b_mn_major, int32_t cta_pair, void* stream);
+
+/* ---- Fused linear scaled cross-entropy and fused linear JSD: row kernels over a token chunk's logits ----------------
+ *
+ * Both losses run as a loop over token chunks on the host (as in the reference): logits of the chunk by flce_b200_gemm
+ * into a slab [rows, ld] of the operands' dtype, one of the row kernels below over the slab, then the two projections
+ * (flce_b200_gemm / flce_b200_gemm_accumulate) from the slab, which by then holds the gradient with respect to the
+ * logits.  dtype is the slab's flce_dtype_t; all row arrays are fp32 on the device.
+ *
+ * Scaled cross-entropy (src/liger_kernel/ops/fused_linear_scaled_cross_entropy.py:50-93), s = z / temperature:
+ *   rows: nll[i] = lse(s_i) - s_i[target_i], entropy[i] = lse(s_i) - sum_j p_ij s_ij, both 0 when target_i ==
+ *         ignore_index; lse[i] for every row.
+ *   grad: logits[i][j] <- (g_nll[i] (p_ij - [j == target_i]) - g_ent[i] p_ij (log p_ij + entropy[i])) / temperature,
+ *         zeros on ignored rows; grad_nll / grad_entropy may be NULL (treated as zeros). */
+int flce_b200_scaled_ce_rows(const void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab,
+                             const int64_t* target, int64_t ignore_index, float temperature, float* nll, float* entropy,
+                             float* lse, void* stream);
+int flce_b200_scaled_ce_grad(void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab, const int64_t* target,
+                             int64_t ignore_index, float temperature, const float* lse, const float* entropy,
+                             const float* grad_nll, const float* grad_entropy, void* stream);
+
+/* Generalised Jensen-Shannon divergence between the student's and the teacher's distribution of every token
+ * (src/liger_kernel/ops/jsd.py:12-93 and the chain rule of src/liger_kernel/ops/fused_linear_jsd.py:118-122):
+ * loss_rows[i] = the token's loss / count; student[i][:] <- d loss / d (student logits), zeros when labels[i] ==
+ * ignore_index (labels may be NULL: every token counts).  count: device pointer to the number of tokens that matter
+ * (norm[0] of flce_b200_count), or NULL to use fixed_count; no host synchronisation either way (the reference reads the
+ * count back with .item(), ops/fused_linear_jsd.py:55).  beta 0 = forward KL, 1 = reverse KL. */
+int flce_b200_jsd_rows(void* student, int64_t ld_student, const void* teacher, int64_t ld_teacher, int32_t dtype,
+                       int64_t n_rows, int64_t vocab, const int64_t* labels, int64_t ignore_index, float beta,
+                       float temperature, const float* count, float fixed_count, float* loss_rows, void* stream);
+
 /* Synchronises `stream`, then reports whether any kernel of this library abandoned a bounded wait
  * since the last call (FLCE_ERR_DEVICE_TIMEOUT) and clears the record.  For tests and debugging. */
 int flce_b200_check_device_status(void* stream);

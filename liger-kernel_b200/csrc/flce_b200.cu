@@ -11,6 +11,7 @@
 #include "ce_kernels.cuh"
 #include "epilogues.cuh"
 #include "gemm_sm100.cuh"
+#include "head_loss_kernels.cuh"
 #include "row_kernels.cuh"
 
 namespace flce {
@@ -408,6 +409,53 @@ static void launch_ce_grad(const flce_ce_problem_t* p, void* grad, long long ld_
     ce_grad_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(x, p->ld, static_cast<T*>(grad), ld_grad,
                                                              static_cast<int>(p->n_rows), static_cast<int>(p->vocab), tgt,
                                                              p->ce_weight, p->softcap, inv, lse, c1, c2, c3);
+}
+
+// ---- launchers of the chunked sibling losses' row kernels (head_loss_kernels.cuh)
+template <typename T>
+static void launch_scaled_ce_rows(const void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab,
+                                  const long long* target, long long ignore_index, float inv_t, float* nll, float* entropy,
+                                  float* lse, cudaStream_t stream) {
+  const T* x = static_cast<const T*>(logits);
+  const unsigned grid = static_cast<unsigned>(n_rows);
+  if (ce_rows_vectorisable(logits, ld, dtype))
+    scaled_ce_rows_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab),
+                                                                   target, ignore_index, inv_t, nll, entropy, lse);
+  else
+    scaled_ce_rows_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab),
+                                                                    target, ignore_index, inv_t, nll, entropy, lse);
+}
+
+template <typename T>
+static void launch_scaled_ce_grad(void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab, const long long* target,
+                                  long long ignore_index, float inv_t, const float* lse, const float* entropy,
+                                  const float* grad_nll, const float* grad_entropy, cudaStream_t stream) {
+  const bool vec = ce_rows_vectorisable(logits, ld, dtype);
+  const long long per_thread = vec ? CeElem<T>::kVec : 1;
+  dim3 grid(static_cast<unsigned>(n_rows), static_cast<unsigned>(ceil_div(ceil_div(vocab, per_thread), kCeThreads)), 1);
+  T* x = static_cast<T*>(logits);
+  if (vec)
+    scaled_ce_grad_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab), target,
+                                                                   ignore_index, inv_t, lse, entropy, grad_nll, grad_entropy);
+  else
+    scaled_ce_grad_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab), target,
+                                                                    ignore_index, inv_t, lse, entropy, grad_nll, grad_entropy);
+}
+
+template <typename T>
+static void launch_jsd_rows(void* student, int64_t ld_s, const void* teacher, int64_t ld_t, int32_t dtype, int64_t n_rows,
+                            int64_t vocab, const long long* labels, long long ignore_index, float beta, float inv_t,
+                            const float* count, float fixed_count, float* loss_rows, cudaStream_t stream) {
+  const bool vec = ce_rows_vectorisable(student, ld_s, dtype) && ce_rows_vectorisable(teacher, ld_t, dtype);
+  const unsigned grid = static_cast<unsigned>(n_rows);
+  T* xs = static_cast<T*>(student);
+  const T* xt = static_cast<const T*>(teacher);
+  if (vec)
+    jsd_rows_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
+                                                             labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
+  else
+    jsd_rows_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
+                                                              labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
 }
 
 }  // namespace flce
@@ -1162,6 +1210,129 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
   if (!a_mn_major && b_mn_major)
     return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
   return fail(FLCE_ERR_UNSUPPORTED, "A MN-major with B K-major is not instantiated");
+}
+
+int flce_b200_gemm_accumulate(const void* a, const void* b, float* acc, void* out, int64_t m, int64_t n, int64_t k,
+                              int64_t ld_a, int64_t ld_b, int64_t ld_acc, int64_t ld_out, int32_t ab_dtype,
+                              int32_t out_dtype, int32_t a_mn_major, int32_t b_mn_major, int32_t cta_pair, void* stream_) {
+  if (a == nullptr || b == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL matrix");
+  if (acc == nullptr && out == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "acc and out are both NULL");
+  if (ab_dtype != FLCE_BF16 && ab_dtype != FLCE_FP16) return fail(FLCE_ERR_UNSUPPORTED, "A/B must be bf16 or fp16");
+  const long long n8 = ceil_div(n, 8) * 8;
+  if (out != nullptr) {
+    if (out_dtype != FLCE_FP32 && out_dtype != ab_dtype) return fail(FLCE_ERR_UNSUPPORTED, "out must be fp32 or the input dtype");
+    if (ld_out % 8 != 0 || ld_out < n8) return fail(FLCE_ERR_INVALID_ARGUMENT, "ld_out must be a multiple of 8 covering n");
+    if ((reinterpret_cast<uintptr_t>(out) & 15) != 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "out must be 16-byte aligned");
+  }
+  if (acc != nullptr) {
+    if (ld_acc % 4 != 0 || ld_acc < ceil_div(n, 4) * 4)
+      return fail(FLCE_ERR_INVALID_ARGUMENT, "ld_acc must be a multiple of 4 covering n");
+    if ((reinterpret_cast<uintptr_t>(acc) & 15) != 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "acc must be 16-byte aligned");
+  }
+  DeviceState* dev = nullptr;
+  int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  StoreEpilogue::Params ep;
+  ep.m_rows = static_cast<int>(m);
+  ep.n_cols = static_cast<int>(n);
+  ep.acc_in = acc;
+  ep.acc_out = acc;
+  ep.ld_acc = ld_acc;
+  ep.out = out;
+  ep.ld_out = ld_out;
+  ep.out_fmt = out_dtype == FLCE_FP32 ? kOutFp32 : (out_dtype == FLCE_BF16 ? kOutBf16 : kOutFp16);
+  Operand oa{a, m, k, ld_a, a_mn_major != 0};
+  Operand ob{b, n, k, ld_b, b_mn_major != 0};
+  const bool pair = cta_pair != 0;
+  const long long row_bytes = static_cast<long long>(kBlockM) * k * 2;
+  if (!a_mn_major && !b_mn_major)
+    return launch_gemm<kMajorK, kMajorK, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, false, ep, stream);
+  if (a_mn_major && b_mn_major)
+    return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
+  if (!a_mn_major && b_mn_major)
+    return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
+  return fail(FLCE_ERR_UNSUPPORTED, "A MN-major with B K-major is not instantiated");
+}
+
+// ------------------------------------------------------------------ chunked sibling losses: row kernels
+static int check_slab(const void* slab, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab, const char* what) {
+  if (slab == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "%s is NULL", what);
+  if (n_rows <= 0 || vocab <= 0 || ld < vocab)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad %s shape (n_rows=%lld vocab=%lld ld=%lld)", what, (long long)n_rows,
+                (long long)vocab, (long long)ld);
+  if (n_rows > 0x7fffffffll || vocab > 0x7fffffffll) return fail(FLCE_ERR_INVALID_ARGUMENT, "shapes must fit 32 bits");
+  if (dtype < FLCE_BF16 || dtype > FLCE_FP32) return fail(FLCE_ERR_UNSUPPORTED, "%s must be bf16, fp16 or fp32", what);
+  return FLCE_OK;
+}
+
+int flce_b200_scaled_ce_rows(const void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab,
+                             const int64_t* target_, int64_t ignore_index, float temperature, float* nll, float* entropy,
+                             float* lse, void* stream_) {
+  int rc = check_slab(logits, ld, dtype, n_rows, vocab, "logits");
+  if (rc != FLCE_OK) return rc;
+  if (target_ == nullptr || nll == nullptr || entropy == nullptr || lse == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "target, nll, entropy and lse must not be NULL");
+  if (!(temperature > 0.f) || !isfinite(temperature)) return fail(FLCE_ERR_INVALID_ARGUMENT, "temperature must be finite and > 0");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long* target = reinterpret_cast<const long long*>(target_);
+  const float inv_t = 1.f / temperature;
+  if (dtype == FLCE_FP32) launch_scaled_ce_rows<float>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, nll, entropy, lse, stream);
+  else if (dtype == FLCE_BF16) launch_scaled_ce_rows<__nv_bfloat16>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, nll, entropy, lse, stream);
+  else launch_scaled_ce_rows<__half>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, nll, entropy, lse, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_scaled_ce_grad(void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab, const int64_t* target_,
+                             int64_t ignore_index, float temperature, const float* lse, const float* entropy,
+                             const float* grad_nll, const float* grad_entropy, void* stream_) {
+  int rc = check_slab(logits, ld, dtype, n_rows, vocab, "logits");
+  if (rc != FLCE_OK) return rc;
+  if (target_ == nullptr || lse == nullptr || entropy == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "target, lse and entropy must not be NULL");
+  if (!(temperature > 0.f) || !isfinite(temperature)) return fail(FLCE_ERR_INVALID_ARGUMENT, "temperature must be finite and > 0");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long* target = reinterpret_cast<const long long*>(target_);
+  const float inv_t = 1.f / temperature;
+  if (dtype == FLCE_FP32) launch_scaled_ce_grad<float>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, lse, entropy, grad_nll, grad_entropy, stream);
+  else if (dtype == FLCE_BF16) launch_scaled_ce_grad<__nv_bfloat16>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, lse, entropy, grad_nll, grad_entropy, stream);
+  else launch_scaled_ce_grad<__half>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, lse, entropy, grad_nll, grad_entropy, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_jsd_rows(void* student, int64_t ld_student, const void* teacher, int64_t ld_teacher, int32_t dtype,
+                       int64_t n_rows, int64_t vocab, const int64_t* labels_, int64_t ignore_index, float beta,
+                       float temperature, const float* count, float fixed_count, float* loss_rows, void* stream_) {
+  int rc = check_slab(student, ld_student, dtype, n_rows, vocab, "student logits");
+  if (rc != FLCE_OK) return rc;
+  rc = check_slab(teacher, ld_teacher, dtype, n_rows, vocab, "teacher logits");
+  if (rc != FLCE_OK) return rc;
+  if (loss_rows == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "loss_rows must not be NULL");
+  if (!(beta >= 0.f && beta <= 1.f)) return fail(FLCE_ERR_INVALID_ARGUMENT, "beta must be in [0, 1]");
+  if (temperature == 0.f || !isfinite(temperature)) return fail(FLCE_ERR_INVALID_ARGUMENT, "temperature must be finite and not 0");
+  if (count == nullptr && !(fixed_count > 0.f)) return fail(FLCE_ERR_INVALID_ARGUMENT, "fixed_count must be positive when count is NULL");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long* labels = reinterpret_cast<const long long*>(labels_);
+  const float inv_t = 1.f / temperature;
+  if (dtype == FLCE_FP32) launch_jsd_rows<float>(student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
+  else if (dtype == FLCE_BF16) launch_jsd_rows<__nv_bfloat16>(student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
+  else launch_jsd_rows<__half>(student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
 }
 
 int flce_b200_profile_enable(int on) {

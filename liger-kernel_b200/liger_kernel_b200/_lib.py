@@ -32,6 +32,10 @@ EXPORTS = (
     "flce_b200_ce_forward",
     "flce_b200_ce_backward",
     "flce_b200_gemm",
+    "flce_b200_gemm_accumulate",
+    "flce_b200_scaled_ce_rows",
+    "flce_b200_scaled_ce_grad",
+    "flce_b200_jsd_rows",
     "flce_b200_check_device_status",
     "flce_b200_profile_enable",
     "flce_b200_profile_read",
@@ -129,6 +133,15 @@ def _load():
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]
+    f32 = C.c_float
+    lib.flce_b200_gemm_accumulate.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]
+    lib.flce_b200_gemm_accumulate.restype = C.c_int
+    lib.flce_b200_scaled_ce_rows.argtypes = [vp, i64, i32, i64, i64, vp, i64, f32, vp, vp, vp, vp]
+    lib.flce_b200_scaled_ce_rows.restype = C.c_int
+    lib.flce_b200_scaled_ce_grad.argtypes = [vp, i64, i32, i64, i64, vp, i64, f32, vp, vp, vp, vp, vp]
+    lib.flce_b200_scaled_ce_grad.restype = C.c_int
+    lib.flce_b200_jsd_rows.argtypes = [vp, i64, vp, i64, i32, i64, i64, vp, i64, f32, f32, vp, f32, vp, vp]
+    lib.flce_b200_jsd_rows.restype = C.c_int
     lib.flce_b200_check_device_status.argtypes = [vp]
     lib.flce_b200_set_option.argtypes = [C.c_char_p, i64]
     lib.flce_b200_profile_enable.argtypes = [C.c_int]

@@ -1,4 +1,4 @@
-// The library's SIMT kernels (csrc/row_kernels.cuh, csrc/ce_kernels.cuh) compiled for the host and run on host threads
+// The library's SIMT kernels (csrc/row_kernels.cuh, csrc/ce_kernels.cuh, csrc/head_loss_kernels.cuh) compiled for the host and run on host threads
 // through simt_emulation.hpp, behind a small C interface for the CPU tests.  Every wrapper repeats the launch geometry
 // and kernel order of the library entry point it is named after (csrc/flce_b200.cu), so the tests exercise the same
 // index arithmetic a GPU launch would.  ex2.approx / rcp.approx are replaced by libm (FLCE_HOST_EMULATION), so results
@@ -9,6 +9,7 @@
 #include "simt_emulation.hpp"
 
 #include "ce_kernels.cuh"
+#include "head_loss_kernels.cuh"
 #include "row_kernels.cuh"
 
 using namespace flce;
@@ -98,6 +99,56 @@ CeProblem make_problem(int dtype, const void* logits, long long ld, long long n_
   p.softcap = softcap;
   p.reduction = reduction;
   return p;
+}
+
+template <typename T>
+void run_scaled_ce_rows(const void* logits, long long ld, int dtype, long long n_rows, long long vocab, const long long* target,
+                        long long ignore_index, float inv_t, float* nll, float* entropy, float* lse) {
+  const T* x = static_cast<const T*>(logits);
+  const bool vec = vectorisable(logits, ld, dtype);
+  emu::launch(emu::Dim3(static_cast<unsigned>(n_rows)), emu::Dim3(kCeThreads), [&]() {
+    if (vec)
+      scaled_ce_rows_kernel<T, true>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab), target, ignore_index, inv_t, nll,
+                                     entropy, lse);
+    else
+      scaled_ce_rows_kernel<T, false>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab), target, ignore_index, inv_t, nll,
+                                      entropy, lse);
+  });
+}
+
+template <typename T>
+void run_scaled_ce_grad(void* logits, long long ld, int dtype, long long n_rows, long long vocab, const long long* target,
+                        long long ignore_index, float inv_t, const float* lse, const float* entropy, const float* g_nll,
+                        const float* g_ent) {
+  const bool vec = vectorisable(logits, ld, dtype);
+  const long long per_thread = vec ? CeElem<T>::kVec : 1;
+  const emu::Dim3 grid(static_cast<unsigned>(n_rows), static_cast<unsigned>(ceil_div(ceil_div(vocab, per_thread), kCeThreads)), 1);
+  T* x = static_cast<T*>(logits);
+  emu::launch_serial(grid, emu::Dim3(kCeThreads), [&]() {
+    if (vec)
+      scaled_ce_grad_kernel<T, true>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab), target, ignore_index, inv_t, lse,
+                                     entropy, g_nll, g_ent);
+    else
+      scaled_ce_grad_kernel<T, false>(x, ld, static_cast<int>(n_rows), static_cast<int>(vocab), target, ignore_index, inv_t, lse,
+                                      entropy, g_nll, g_ent);
+  });
+}
+
+template <typename T>
+void run_jsd_rows(void* student, long long ld_s, const void* teacher, long long ld_t, int dtype, long long n_rows, long long vocab,
+                  const long long* labels, long long ignore_index, float beta, float inv_t, const float* count,
+                  float fixed_count, float* loss_rows) {
+  const bool vec = vectorisable(student, ld_s, dtype) && vectorisable(teacher, ld_t, dtype);
+  T* xs = static_cast<T*>(student);
+  const T* xt = static_cast<const T*>(teacher);
+  emu::launch(emu::Dim3(static_cast<unsigned>(n_rows)), emu::Dim3(kCeThreads), [&]() {
+    if (vec)
+      jsd_rows_kernel<T, true>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab), labels, ignore_index, beta,
+                               inv_t, count, fixed_count, loss_rows);
+    else
+      jsd_rows_kernel<T, false>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab), labels, ignore_index, beta,
+                                inv_t, count, fixed_count, loss_rows);
+  });
 }
 
 }  // namespace
@@ -226,6 +277,36 @@ int emu_merge_partials(long long n_rows, int n_tiles, const float* pmax, const f
   emu::launch_serial(static_cast<unsigned>(ceil_div(n_rows, threads)), threads, [&]() {
     merge_partials_kernel(static_cast<int>(n_rows), n_tiles, pmax, psum, plogit_sum, pamax_val, pamax_idx, rowstats);
   });
+  return 0;
+}
+
+// flce_b200_scaled_ce_rows / _grad / flce_b200_jsd_rows
+int emu_scaled_ce_rows(const void* logits, long long ld, int dtype, long long n_rows, long long vocab, const long long* target,
+                       long long ignore_index, float temperature, float* nll, float* entropy, float* lse) {
+  const float inv_t = 1.f / temperature;
+  if (dtype == 2) run_scaled_ce_rows<float>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, nll, entropy, lse);
+  else if (dtype == 0) run_scaled_ce_rows<__nv_bfloat16>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, nll, entropy, lse);
+  else run_scaled_ce_rows<__half>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, nll, entropy, lse);
+  return 0;
+}
+
+int emu_scaled_ce_grad(void* logits, long long ld, int dtype, long long n_rows, long long vocab, const long long* target,
+                       long long ignore_index, float temperature, const float* lse, const float* entropy, const float* g_nll,
+                       const float* g_ent) {
+  const float inv_t = 1.f / temperature;
+  if (dtype == 2) run_scaled_ce_grad<float>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, lse, entropy, g_nll, g_ent);
+  else if (dtype == 0) run_scaled_ce_grad<__nv_bfloat16>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, lse, entropy, g_nll, g_ent);
+  else run_scaled_ce_grad<__half>(logits, ld, dtype, n_rows, vocab, target, ignore_index, inv_t, lse, entropy, g_nll, g_ent);
+  return 0;
+}
+
+int emu_jsd_rows(void* student, long long ld_s, const void* teacher, long long ld_t, int dtype, long long n_rows, long long vocab,
+                 const long long* labels, long long ignore_index, float beta, float temperature, const float* count,
+                 float fixed_count, float* loss_rows) {
+  const float inv_t = 1.f / temperature;
+  if (dtype == 2) run_jsd_rows<float>(student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
+  else if (dtype == 0) run_jsd_rows<__nv_bfloat16>(student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
+  else run_jsd_rows<__half>(student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
   return 0;
 }
 

@@ -1,12 +1,13 @@
 // A small SIMT emulation for CPU tests: runs a CUDA kernel body that uses only threadIdx / blockIdx / blockDim /
-// gridDim, __shared__ arrays, __syncthreads() and full-warp shuffles on host threads, one block at a time.
+// gridDim, __shared__ arrays, __syncthreads() and full-warp shuffles on the host, one block at a time.
 //
-//   * every CUDA thread of a block is one std::thread; __syncthreads() is a std::barrier over the block's threads
-//     (a thread that returns from the kernel leaves the barrier, like an exited CUDA thread);
+//   * every CUDA thread of a block is a fiber (ucontext) on the calling OS thread, scheduled round-robin; a barrier is a
+//     generation counter that a fiber polls, yielding to the next fiber until everyone has arrived (a fiber that returns
+//     from the kernel leaves the barriers, like an exited CUDA thread).  Deterministic, and no OS synchronisation;
 //   * __shared__ becomes `static`: blocks run one after another, so the static storage of a kernel is the shared
 //     memory of the block that is running (kernels must write it before they read it, as on the GPU);
 //   * __shfl_xor_sync / __shfl_up_sync exchange through a per-block slot array and a per-warp barrier, so they need
-//     all 32 lanes of the calling warp to take part (the kernels here call them in warp-uniform control flow only);
+//     all live lanes of the calling warp to take part (the kernels here call them in warp-uniform control flow only);
 //   * kernels that neither synchronise nor shuffle can use launch_serial(), which runs the threads of a block in a
 //     plain loop.
 //
@@ -18,13 +19,14 @@
 #include <vector_functions.h>
 #include <vector_types.h>
 
+#include <ucontext.h>
+
 #include <algorithm>
-#include <barrier>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <memory>
-#include <thread>
 #include <vector>
 
 #undef __shared__
@@ -48,50 +50,115 @@ struct Dim3 {
   Dim3(unsigned x_, unsigned y_ = 1, unsigned z_ = 1) : x(x_), y(y_), z(z_) {}
 };
 
-struct BlockCtx {
-  explicit BlockCtx(unsigned n_threads)
-      : block_bar(static_cast<std::ptrdiff_t>(n_threads)), slots(n_threads, 0) {
-    for (unsigned w = 0; w < (n_threads + 31) / 32; ++w) {
-      const unsigned lanes = std::min(32u, n_threads - w * 32);
-      warp_bar.emplace_back(std::make_unique<std::barrier<>>(static_cast<std::ptrdiff_t>(lanes)));
-    }
-  }
-  std::barrier<> block_bar;
-  std::vector<std::unique_ptr<std::barrier<>>> warp_bar;
-  std::vector<uint64_t> slots;
+struct Barrier {
+  unsigned expected = 0, arrived = 0, generation = 0;
 };
 
-inline thread_local Dim3 t_thread_idx, t_block_idx;
-inline thread_local BlockCtx* t_ctx = nullptr;
+struct Fiber {
+  ucontext_t ctx;
+  std::vector<char> stack;
+  bool done = false;
+  Dim3 thread_idx;
+};
+
+struct BlockCtx {
+  Barrier block_bar;
+  std::vector<Barrier> warp_bar;
+  std::vector<uint64_t> slots;
+  std::vector<Fiber> fibers;
+  ucontext_t scheduler;
+  unsigned current = 0;
+  std::function<void()> body;
+};
+
+// one OS thread: plain globals, set by the scheduler before it resumes a fiber
+inline Dim3 t_thread_idx, t_block_idx;
+inline BlockCtx* t_ctx = nullptr;
 inline Dim3 g_block_dim, g_grid_dim;
 
 inline unsigned linear_tid() {
   return t_thread_idx.x + g_block_dim.x * (t_thread_idx.y + g_block_dim.y * t_thread_idx.z);
 }
 
-// one std::thread per CUDA thread, blocks one after another
+inline void yield() {
+  BlockCtx& ctx = *t_ctx;
+  swapcontext(&ctx.fibers[ctx.current].ctx, &ctx.scheduler);
+}
+
+inline void barrier_release_if_complete(Barrier& b) {
+  if (b.expected > 0 && b.arrived == b.expected) {
+    b.arrived = 0;
+    ++b.generation;
+  }
+}
+
+inline void barrier_wait(Barrier& b) {
+  const unsigned gen = b.generation;
+  ++b.arrived;
+  barrier_release_if_complete(b);
+  while (b.generation == gen) yield();
+}
+
+// an exiting fiber no longer takes part: waiting fibers may now be complete
+inline void barrier_drop(Barrier& b) {
+  --b.expected;
+  barrier_release_if_complete(b);
+}
+
+inline void fiber_entry() {
+  BlockCtx& ctx = *t_ctx;
+  const unsigned me = ctx.current;
+  ctx.body();
+  ctx.fibers[me].done = true;
+  barrier_drop(ctx.block_bar);
+  barrier_drop(ctx.warp_bar[me >> 5]);
+  swapcontext(&ctx.fibers[me].ctx, &ctx.scheduler);      // never resumed
+}
+
+constexpr size_t kFiberStackBytes = 256 * 1024;
+
+// the threads of a block as fibers, blocks one after another
 template <typename Body>
 void launch(Dim3 grid, Dim3 block, Body body) {
   g_grid_dim = grid;
   g_block_dim = block;
   const unsigned n_threads = block.x * block.y * block.z;
+  BlockCtx ctx;
+  ctx.body = body;
+  ctx.fibers.resize(n_threads);
+  for (auto& f : ctx.fibers) f.stack.resize(kFiberStackBytes);
+  ctx.slots.assign(n_threads, 0);
+  t_ctx = &ctx;
   for (unsigned bz = 0; bz < grid.z; ++bz)
     for (unsigned by = 0; by < grid.y; ++by)
       for (unsigned bx = 0; bx < grid.x; ++bx) {
-        BlockCtx ctx(n_threads);
-        std::vector<std::thread> threads;
-        threads.reserve(n_threads);
+        t_block_idx = Dim3(bx, by, bz);
+        ctx.block_bar = Barrier{n_threads, 0, 0};
+        ctx.warp_bar.assign((n_threads + 31) / 32, Barrier{});
+        for (unsigned w = 0; w < ctx.warp_bar.size(); ++w) ctx.warp_bar[w].expected = std::min(32u, n_threads - w * 32);
         for (unsigned t = 0; t < n_threads; ++t) {
-          threads.emplace_back([&, t]() {
-            t_ctx = &ctx;
-            t_block_idx = Dim3(bx, by, bz);
-            t_thread_idx = Dim3(t % block.x, (t / block.x) % block.y, t / (block.x * block.y));
-            body();
-            ctx.block_bar.arrive_and_drop();
-          });
+          Fiber& f = ctx.fibers[t];
+          f.done = false;
+          f.thread_idx = Dim3(t % block.x, (t / block.x) % block.y, t / (block.x * block.y));
+          getcontext(&f.ctx);
+          f.ctx.uc_stack.ss_sp = f.stack.data();
+          f.ctx.uc_stack.ss_size = f.stack.size();
+          f.ctx.uc_link = &ctx.scheduler;
+          makecontext(&f.ctx, reinterpret_cast<void (*)()>(fiber_entry), 0);
         }
-        for (auto& th : threads) th.join();
+        unsigned live = n_threads;
+        while (live > 0) {
+          live = 0;
+          for (unsigned t = 0; t < n_threads; ++t) {
+            if (ctx.fibers[t].done) continue;
+            ctx.current = t;
+            t_thread_idx = ctx.fibers[t].thread_idx;
+            swapcontext(&ctx.scheduler, &ctx.fibers[t].ctx);
+            if (!ctx.fibers[t].done) ++live;
+          }
+        }
       }
+  t_ctx = nullptr;
 }
 
 // for kernels without __syncthreads() and shuffles
@@ -120,9 +187,9 @@ T shuffle_from(T v, unsigned src_lane) {
   uint64_t bits = 0;
   std::memcpy(&bits, &v, sizeof(T));
   ctx.slots[tid] = bits;
-  ctx.warp_bar[warp]->arrive_and_wait();
+  barrier_wait(ctx.warp_bar[warp]);
   const uint64_t got = ctx.slots[warp * 32 + src_lane];
-  ctx.warp_bar[warp]->arrive_and_wait();
+  barrier_wait(ctx.warp_bar[warp]);
   T out;
   std::memcpy(&out, &got, sizeof(T));
   return out;
@@ -135,7 +202,7 @@ T shuffle_from(T v, unsigned src_lane) {
 #define blockDim (emu::g_block_dim)
 #define gridDim (emu::g_grid_dim)
 
-inline void __syncthreads() { emu::t_ctx->block_bar.arrive_and_wait(); }
+inline void __syncthreads() { emu::barrier_wait(emu::t_ctx->block_bar); }
 
 template <typename T>
 T __shfl_xor_sync(unsigned, T v, int lane_mask) {

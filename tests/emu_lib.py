@@ -1,7 +1,8 @@
 """The library's SIMT kernels run on host threads (tests/emu/): build helper, ctypes binding and a stand-in library
 object that sends the entry points made only of SIMT kernels (stand-alone cross-entropy, target counting, row
-compaction / scatter, fp32 term split, gradient scaling) to the emulation, so the Python operators can be driven on
-CPU tensors with real numerics.  Entry points that need the tensor-core sweeps stay recording stubs (fake_lib).
+compaction / scatter, fp32 term split, gradient scaling, the row kernels of the chunked head losses) to the emulation,
+so the Python operators can be driven on CPU tensors with real numerics.  The plain tensor-core GEMM entry point is
+replaced by torch arithmetic on the same host memory; the fused sweeps stay recording stubs (fake_lib).
 
 Only the tests use this."""
 
@@ -9,6 +10,8 @@ import contextlib
 import ctypes as C
 import os
 import subprocess
+
+import torch
 
 import fake_lib
 from fake_lib import _addr
@@ -27,7 +30,7 @@ def _stale():
         return True
     built = os.path.getmtime(_OUT)
     deps = [_SRC, os.path.join(_HERE, "emu", "simt_emulation.hpp")]
-    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "simt_common.cuh")]
+    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "head_loss_kernels.cuh", "simt_common.cuh")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
@@ -38,7 +41,7 @@ def load():
         return _lib
     if _stale():
         os.makedirs(os.path.dirname(_OUT), exist_ok=True)
-        cmd = ["g++", "-std=c++20", "-O1", "-pthread", "-fPIC", "-shared", "-I", _CUDA_INCLUDE, "-I", _CSRC, "-o", _OUT, _SRC]
+        cmd = ["g++", "-std=c++20", "-O1", "-fPIC", "-shared", "-I", _CUDA_INCLUDE, "-I", _CSRC, "-o", _OUT, _SRC]
         done = subprocess.run(cmd, capture_output=True, text=True)
         if done.returncode != 0:
             raise RuntimeError("building the SIMT emulation failed:\n" + done.stderr[-4000:])
@@ -55,6 +58,9 @@ def load():
         "emu_colsum": [P, LL, LL, LL, I, P, I],
         "emu_scale_inplace": [P, LL, I, P],
         "emu_merge_partials": [LL, I, P, P, P, P, P, P],
+        "emu_scaled_ce_rows": [P, LL, I, LL, LL, P, LL, F, P, P, P],
+        "emu_scaled_ce_grad": [P, LL, I, LL, LL, P, LL, F, P, P, P, P],
+        "emu_jsd_rows": [P, LL, P, LL, I, LL, LL, P, LL, F, F, P, F, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -116,6 +122,49 @@ class EmuLib(fake_lib.FakeLib):
     def flce_b200_scale_gradient(self, data, n, dtype, scale, stream):
         self.calls.append("flce_b200_scale_gradient")
         return self.emu.emu_scale_inplace(_addr(data), n, {0: 0, 1: 1, 2: 2}[dtype], _addr(scale))
+
+
+    def flce_b200_scaled_ce_rows(self, logits, ld, dtype, n_rows, vocab, target, ignore_index, temperature, nll, entropy, lse, stream):
+        self.calls.append("flce_b200_scaled_ce_rows")
+        return self.emu.emu_scaled_ce_rows(_addr(logits), ld, dtype, n_rows, vocab, _addr(target), ignore_index, temperature, _addr(nll),
+                                           _addr(entropy), _addr(lse))
+
+    def flce_b200_scaled_ce_grad(self, logits, ld, dtype, n_rows, vocab, target, ignore_index, temperature, lse, entropy, g_nll, g_ent,
+                                 stream):
+        self.calls.append("flce_b200_scaled_ce_grad")
+        return self.emu.emu_scaled_ce_grad(_addr(logits), ld, dtype, n_rows, vocab, _addr(target), ignore_index, temperature, _addr(lse),
+                                           _addr(entropy), _addr(g_nll) or None, _addr(g_ent) or None)
+
+    def flce_b200_jsd_rows(self, student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, temperature, count,
+                           fixed_count, loss_rows, stream):
+        self.calls.append("flce_b200_jsd_rows")
+        return self.emu.emu_jsd_rows(_addr(student), ld_s, _addr(teacher), ld_t, dtype, n_rows, vocab, _addr(labels) or None, ignore_index,
+                                     beta, temperature, _addr(count) or None, fixed_count, _addr(loss_rows))
+
+    def flce_b200_gemm_accumulate(self, a, b, acc, out, m, n, k, ld_a, ld_b, ld_acc, ld_out, ab_dtype, out_dtype, a_mn_major,
+                                  b_mn_major, cta_pair, stream):
+        """The tensor-core GEMM replaced by torch on host memory: 16-bit operands, fp32 accumulation, the library's
+        layouts (K-major [rows, k] or MN-major [k, rows]) and its two outputs."""
+        self.calls.append("flce_b200_gemm_accumulate")
+        tdt = {0: torch.bfloat16, 1: torch.float16}[ab_dtype]
+
+        def matrix(addr, rows, cols, ld, dt):       # [rows, cols] view with row pitch ld
+            n_el = (rows - 1) * ld + cols
+            buf = (C.c_char * (n_el * dt.itemsize)).from_address(addr)
+            flat = torch.frombuffer(buf, dtype=dt, count=n_el)
+            return torch.as_strided(flat, (rows, cols), (ld, 1))
+
+        A = matrix(_addr(a), k, m, ld_a, tdt).T if a_mn_major else matrix(_addr(a), m, k, ld_a, tdt)
+        B = matrix(_addr(b), k, n, ld_b, tdt).T if b_mn_major else matrix(_addr(b), n, k, ld_b, tdt)
+        v = A.float() @ B.float().T
+        if _addr(acc):
+            ACC = matrix(_addr(acc), m, n, ld_acc, torch.float32)
+            v = v + ACC
+            ACC.copy_(v)
+        if _addr(out):
+            odt = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}[out_dtype]
+            matrix(_addr(out), m, n, ld_out, odt).copy_(v.to(odt))
+        return 0
 
 
 @contextlib.contextmanager

@@ -1,0 +1,89 @@
+"""Fused linear JSD and fused linear scaled cross-entropy end to end on CPU tensors: the Python operators and their chunk
+loops run unchanged, the row kernels (csrc/head_loss_kernels.cuh) and the fp32 term split run on host threads
+(tests/emu/), and the tensor-core GEMM entry point is replaced by torch arithmetic on the same memory
+(tests/emu_lib.py).  The case bodies are the GPU test's own (tests/head_loss_cases.py), at sizes the emulation handles
+in seconds."""
+
+import pytest
+import torch
+
+import emu_lib
+import head_loss_cases as cases
+from golden_util import jsd_golden_names, sce_golden_names
+
+JSD_GRID = [
+    # N, Hs, Ht, V, dtype, beta, temperature, label fraction, ignore_index
+    (33, 24, 40, 131, torch.float32, 0.5, 1.0, None, -100),
+    (33, 24, 40, 131, torch.bfloat16, 0.5, 1.0, None, -100),
+    (33, 24, 40, 131, torch.float16, 0.1, 2.0, 0.3, -100),
+    (40, 16, 16, 256, torch.bfloat16, 0.0, 1.0, 0.2, -100),
+    (40, 16, 16, 256, torch.float32, 0.0, 0.5, 0.2, 2),
+    (40, 31, 17, 203, torch.bfloat16, 1.0, 1.0, 0.2, -100),
+    (40, 31, 17, 203, torch.float32, 1.0, 1.5, None, -100),
+    (21, 8, 8, 1000, torch.float32, 0.9, 4.0, 0.5, -100),
+]
+
+
+@pytest.mark.parametrize("N,Hs,Ht,V,dtype,beta,temperature,labels,ignore_index", JSD_GRID)
+def test_jsd_correctness(monkeypatch, N, Hs, Ht, V, dtype, beta, temperature, labels, ignore_index):
+    with emu_lib.installed(monkeypatch):
+        cases.case_jsd_correctness("cpu", N, Hs, Ht, V, dtype, beta, temperature, labels, ignore_index)
+
+
+def test_jsd_functional_and_upstream_gradient(monkeypatch):
+    with emu_lib.installed(monkeypatch):
+        cases.case_jsd_correctness("cpu", 24, 16, 32, 97, torch.bfloat16, 0.5, 1.0, 0.1, grad_output=2.5, functional=True)
+        cases.case_jsd_correctness("cpu", 24, 16, 32, 97, torch.float32, 0.3, 1.0, 0.1, grad_output=0.5)
+
+
+@pytest.mark.parametrize("name", jsd_golden_names())
+def test_jsd_against_reference_golden(monkeypatch, name):
+    with emu_lib.installed(monkeypatch):
+        cases.case_jsd_golden("cpu", name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_jsd_multichunk(monkeypatch, dtype):
+    with emu_lib.installed(monkeypatch) as lib:
+        cases.case_jsd_multichunk_equals_single_chunk("cpu", dtype)
+        assert lib.calls.count("flce_b200_jsd_rows") == 1 + 3        # one chunk, then 530 rows in chunks of 256
+
+
+def test_jsd_weight_without_grad_and_second_backward(monkeypatch):
+    with emu_lib.installed(monkeypatch) as lib:
+        cases.case_jsd_weight_without_grad_and_second_backward("cpu")
+        # no student-weight gradient requested: logits x2 and grad_input only
+        assert lib.calls.count("flce_b200_gemm_accumulate") == 3
+
+
+SCE_GRID = [
+    (17, 31, 257, torch.float32, 1.5, "both"),
+    (40, 32, 131, torch.bfloat16, 1.0, "both"),
+    (40, 32, 131, torch.float16, 0.7, "nll"),
+    (40, 32, 131, torch.bfloat16, 2.0, "entropy"),
+    (25, 16, 1000, torch.float32, 0.5, "entropy"),
+    (25, 16, 1000, torch.bfloat16, 1.0, "both"),
+]
+
+
+@pytest.mark.parametrize("N,H,V,dtype,temperature,grads", SCE_GRID)
+def test_scaled_ce_correctness(monkeypatch, N, H, V, dtype, temperature, grads):
+    with emu_lib.installed(monkeypatch):
+        cases.case_sce_correctness("cpu", N, H, V, dtype, temperature, grads)
+
+
+@pytest.mark.parametrize("name", sce_golden_names())
+def test_scaled_ce_against_reference_golden(monkeypatch, name):
+    with emu_lib.installed(monkeypatch):
+        cases.case_sce_golden("cpu", name)
+
+
+def test_scaled_ce_multichunk_single_output_and_errors(monkeypatch):
+    import liger_kernel_b200.ops._chunked as ck
+
+    with emu_lib.installed(monkeypatch) as lib:
+        monkeypatch.setattr(ck, "SLAB_BUDGET_BYTES", 256 * ck.slab_pitch(67) * 2)          # 256 rows per chunk
+        cases.case_sce_correctness("cpu", 530, 16, 67, torch.bfloat16, 1.25, "both")
+        assert lib.calls.count("flce_b200_scaled_ce_rows") == 3 and lib.calls.count("flce_b200_scaled_ce_grad") == 3
+        cases.case_sce_nll_only_output_and_no_grad("cpu")
+        cases.case_sce_argument_errors("cpu")
