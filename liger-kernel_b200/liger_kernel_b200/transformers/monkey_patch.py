@@ -190,17 +190,40 @@ def _apply_liger_kernel_to_instance(model, **kwargs) -> None:
     fn(model=model, **{k: v for k, v in kwargs.items() if k in accepted})
 
 
-def install() -> bool:
+# operator symbol -> modules of an installed liger_kernel that bind it at import time
+_INSTALL_SITES = {
+    "LigerFusedLinearCrossEntropyFunction": (
+        "liger_kernel.ops", "liger_kernel.transformers.functional", "liger_kernel.transformers.fused_linear_cross_entropy"),
+    "LigerCrossEntropyFunction": (
+        "liger_kernel.ops", "liger_kernel.transformers.functional", "liger_kernel.transformers.cross_entropy"),
+    "LigerFusedLinearJSDFunction": (
+        "liger_kernel.ops", "liger_kernel.transformers.functional", "liger_kernel.transformers.fused_linear_jsd"),
+    "LigerFusedLinearScaledCrossEntropyFunction": ("liger_kernel.ops",),
+}
+
+
+def install(cross_entropy: bool = False, fused_linear_jsd: bool = False, fused_linear_scaled_cross_entropy: bool = False) -> bool:
     """Rebind ``LigerFusedLinearCrossEntropyFunction`` inside an importable ``liger_kernel`` package
     at the three places that bind it at import time (``liger_kernel.ops``,
-    ``liger_kernel.transformers.functional``, ``liger_kernel.transformers.fused_linear_cross_entropy``).
+    ``liger_kernel.transformers.functional``, ``liger_kernel.transformers.fused_linear_cross_entropy``), and on request
+    the stand-alone cross-entropy, fused linear JSD and fused linear scaled cross-entropy operators at theirs.
     Returns False when no ``liger_kernel`` is installed."""
+    from ..ops.cross_entropy import LigerCrossEntropyFunction
+    from ..ops.fused_linear_jsd import LigerFusedLinearJSDFunction
+    from ..ops.fused_linear_scaled_cross_entropy import LigerFusedLinearScaledCrossEntropyFunction
+
+    wanted = {"LigerFusedLinearCrossEntropyFunction": LigerFusedLinearCrossEntropyFunction}
+    if cross_entropy:
+        wanted["LigerCrossEntropyFunction"] = LigerCrossEntropyFunction
+    if fused_linear_jsd:
+        wanted["LigerFusedLinearJSDFunction"] = LigerFusedLinearJSDFunction
+    if fused_linear_scaled_cross_entropy:
+        wanted["LigerFusedLinearScaledCrossEntropyFunction"] = LigerFusedLinearScaledCrossEntropyFunction
     try:
-        import liger_kernel.ops as lk_ops
-        import liger_kernel.transformers.functional as lk_functional
-        import liger_kernel.transformers.fused_linear_cross_entropy as lk_module
+        modules = {name: importlib.import_module(name) for symbol in wanted for name in _INSTALL_SITES[symbol]}
     except ImportError:
         return False
-    for mod in (lk_ops, lk_functional, lk_module):
-        setattr(mod, "LigerFusedLinearCrossEntropyFunction", LigerFusedLinearCrossEntropyFunction)
+    for symbol, fn in wanted.items():
+        for name in _INSTALL_SITES[symbol]:
+            setattr(modules[name], symbol, fn)
     return True

@@ -34,6 +34,24 @@ def test_install_rebinds_the_three_import_sites(monkeypatch):
         assert mods[n].LigerFusedLinearCrossEntropyFunction is not sentinel
 
 
+def test_install_on_request_rebinds_the_sibling_operators(monkeypatch):
+    import liger_kernel_b200 as lk
+
+    mods, sentinel = _fake_liger(monkeypatch)
+    for n in ("liger_kernel.transformers.cross_entropy", "liger_kernel.transformers.fused_linear_jsd"):
+        mods[n] = types.ModuleType(n)
+        setattr(mods["liger_kernel.transformers"], n.rsplit(".", 1)[1], mods[n])
+        monkeypatch.setitem(sys.modules, n, mods[n])
+    assert lk.install(cross_entropy=True, fused_linear_jsd=True, fused_linear_scaled_cross_entropy=True) is True
+    assert mods["liger_kernel.transformers.cross_entropy"].LigerCrossEntropyFunction is lk.LigerCrossEntropyFunction
+    assert mods["liger_kernel.transformers.fused_linear_jsd"].LigerFusedLinearJSDFunction is lk.LigerFusedLinearJSDFunction
+    assert mods["liger_kernel.ops"].LigerFusedLinearScaledCrossEntropyFunction is lk.LigerFusedLinearScaledCrossEntropyFunction
+    assert mods["liger_kernel.transformers.functional"].LigerFusedLinearJSDFunction is lk.LigerFusedLinearJSDFunction
+    # the default install leaves them alone
+    mods2, _ = _fake_liger(monkeypatch)
+    assert lk.install() is True and not hasattr(mods2["liger_kernel.ops"], "LigerCrossEntropyFunction")
+
+
 def test_install_without_liger_returns_false(monkeypatch):
     import liger_kernel_b200 as lk
 
