@@ -52,11 +52,14 @@ def _worker(rank, world, init_file, mode, kw, result_file):
             xs, ws = x[lo:hi].clone().requires_grad_(True), w.clone().requires_grad_(True)
             import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
             mod.SLAB_BUDGET_BYTES = (hi - lo) * 2 * 1024      # several slabs: exercises the overlapped all-reduce
-            loss = sharded.token_sharded_fused_linear_cross_entropy(xs, ws, t[lo:hi], overlap_grad_weight=True, **kw)
-            loss.backward()
-            ok = close(loss, ref, "loss", rtol=1e-5)
-            ok &= close(xs.grad, xr.grad[lo:hi], "grad_input")
-            ok &= close(ws.grad, wr.grad, "grad_weight")
+            ok = True
+            for overlap in (True, False):           # slab-by-slab all-reduce on a side stream / one all-reduce at the end (default)
+                xs.grad = ws.grad = None
+                loss = sharded.token_sharded_fused_linear_cross_entropy(xs, ws, t[lo:hi], overlap_grad_weight=overlap, **kw)
+                loss.backward()
+                ok &= close(loss, ref, f"loss overlap={overlap}", rtol=1e-5)
+                ok &= close(xs.grad, xr.grad[lo:hi], f"grad_input overlap={overlap}")
+                ok &= close(ws.grad, wr.grad, f"grad_weight overlap={overlap}")
         else:
             per = (V + world - 1) // world
             lo, hi = rank * per, min(V, (rank + 1) * per)
