@@ -276,8 +276,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if constexpr (kCtas == 1) umma_commit(smem_u32(&tmem_full_bar[acc]));
-        else umma_commit_pair(smem_u32(&tmem_full_bar[acc]), 0x3);
+        if (shape.k_blocks == 0) {
+          // no MMA was issued for this tile (no active rows): release the epilogue warps with plain arrivals rather
+          // than a commit that has nothing to track
+          if constexpr (kCtas == 1) {
+            mbar_arrive(smem_u32(&tmem_full_bar[acc]));
+          } else {
+            mbar_arrive_cluster(smem_u32(&tmem_full_bar[acc]), 0);
+            mbar_arrive_cluster(smem_u32(&tmem_full_bar[acc]), 1);
+          }
+        } else if constexpr (kCtas == 1) {
+          umma_commit(smem_u32(&tmem_full_bar[acc]));
+        } else {
+          umma_commit_pair(smem_u32(&tmem_full_bar[acc]), 0x3);
+        }
       }
       FLCE_TRACE_STORE(0, wait_full);
       FLCE_TRACE_STORE(1, wait_tmem_empty);
