@@ -21,6 +21,7 @@
 #pragma once
 
 #include "ptx_sm100.cuh"
+#include "tile_schedule.cuh"
 
 namespace flce {
 
@@ -41,9 +42,6 @@ __device__ unsigned long long g_clock_trace[1024 * 8];
 #define FLCE_TRACE_STORE(slot, v)
 #endif
 
-constexpr int kBlockM = 128;      // rows per CTA
-constexpr int kBlockN = 256;      // columns per tile
-constexpr int kBlockK = 64;       // two-byte elements per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kNumThreads = 192;  // 6 warps
 constexpr int kNumEpilogueWarps = 4;
@@ -60,41 +58,6 @@ struct StageCfg {
   static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
 };
 
-struct GemmShape {
-  int M, N, K;         // logical extents
-  int m_tiles;         // ceil(M / (128 * kCtas))
-  int n_tiles;         // ceil(N / 256)
-  int k_blocks;        // ceil(K / 64)
-  int group;           // raster: tiles are walked in groups of `group` rows (or columns) of tiles
-  int group_along_m;   // 1: a group is `group` m-tiles x all n-tiles, m fastest; 0: the transpose
-  int hint_a, hint_b;  // L2 eviction priority of the A / B loads: 0 default, 1 evict first, 2 evict last
-  int poll_sleep_ns;   // back-off of the epilogue warps while they wait for an accumulator
-  // Optional device-resident row count (rows that matter come first, e.g. after ignored tokens were moved to the end):
-  // role 1 limits the m-tiles to those that contain such rows, role 2 limits the k-blocks (when K runs over rows).
-  const int* active_rows;
-  int active_role;
-};
-
-__device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& mt, int& nt) {
-  if (s.group_along_m) {
-    const int per_group = s.group * s.n_tiles;
-    const int g = tile / per_group;
-    const int r = tile - g * per_group;
-    const int first = g * s.group;
-    const int rows = min(s.group, s.m_tiles - first);
-    nt = r / rows;
-    mt = first + (r - nt * rows);
-  } else {
-    const int per_group = s.group * s.m_tiles;
-    const int g = tile / per_group;
-    const int r = tile - g * per_group;
-    const int first = g * s.group;
-    const int cols = min(s.group, s.n_tiles - first);
-    mt = r / cols;
-    nt = first + (r - mt * cols);
-  }
-}
-
 // Epilogue concept:
 //   struct Epi {
 //     struct Params {...};                                  // trivially copyable, passed by value
@@ -108,11 +71,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const GemmShape shape_arg, const int ab_format, const typename Epi::Params ep, int* status) {
   using Cfg = StageCfg<kCtas>;
   GemmShape shape = shape_arg;
-  if (shape.active_rows != nullptr) {   // uniform across the grid: every CTA reads the same word
-    const int rows = max(0, *shape.active_rows);
-    if (shape.active_role == 1) shape.m_tiles = min(shape.m_tiles, (rows + kBlockM * kCtas - 1) / (kBlockM * kCtas));
-    else if (shape.active_role == 2) shape.k_blocks = min(shape.k_blocks, (rows + kBlockK - 1) / kBlockK);
-  }
+  if (shape.active_rows != nullptr) limit_to_active_rows(shape, *shape.active_rows, kCtas);   // uniform across the grid
   constexpr int kStages = Cfg::kStages;
 
   extern __shared__ uint8_t smem_raw[];

@@ -8,7 +8,7 @@
 //
 // One CTA per row for the reductions (fixed-order trees: run-to-run identical), 16-byte accesses when the slab allows.
 // The slab of a chunk is sized to stay far below L2 x SM count, so the second and third sweeps of a row hit L2.
-// SIMT only: this header also compiles for the host-thread emulation the CPU tests use.
+// SIMT only: this header also compiles for the host emulation the CPU tests use.
 #pragma once
 
 #include "ce_kernels.cuh"

@@ -1,7 +1,7 @@
 // The SIMT kernels around the tensor-core sweeps: target counting, merging of per-tile softmax partials, per-row loss
 // and gradient coefficients, ordered reductions, the in-place logit gradient of the single-sweep mode, column sums,
 // row compaction for ignored tokens and the fp32 -> 16-bit term split.  All HBM- or latency-bound; none touches
-// tensor memory, so this header also compiles for the host-thread emulation the CPU tests use.
+// tensor memory, so this header also compiles for the host emulation the CPU tests use.
 #pragma once
 
 #include "simt_common.cuh"

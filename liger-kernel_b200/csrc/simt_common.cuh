@@ -2,7 +2,7 @@
 // approximate exp2 / tanh the softmax math is built on.
 //
 // With FLCE_HOST_EMULATION defined the two PTX instructions are replaced by libm calls, so that the SIMT kernels
-// (row_kernels.cuh, ce_kernels.cuh) can be compiled by a host compiler and run on host threads by the CPU tests.
+// (row_kernels.cuh, ce_kernels.cuh) can be compiled by a host compiler and run on the host by the CPU tests.
 // The library itself is never built that way.
 #pragma once
 

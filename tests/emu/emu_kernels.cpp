@@ -1,4 +1,4 @@
-// The library's SIMT kernels (csrc/row_kernels.cuh, csrc/ce_kernels.cuh, csrc/head_loss_kernels.cuh) compiled for the host and run on host threads
+// The library's SIMT kernels (csrc/row_kernels.cuh, csrc/ce_kernels.cuh, csrc/head_loss_kernels.cuh) compiled for the host and run on the host
 // through simt_emulation.hpp, behind a small C interface for the CPU tests.  Every wrapper repeats the launch geometry
 // and kernel order of the library entry point it is named after (csrc/flce_b200.cu), so the tests exercise the same
 // index arithmetic a GPU launch would.  ex2.approx / rcp.approx are replaced by libm (FLCE_HOST_EMULATION), so results
@@ -11,6 +11,7 @@
 #include "ce_kernels.cuh"
 #include "head_loss_kernels.cuh"
 #include "row_kernels.cuh"
+#include "tile_schedule.cuh"
 
 using namespace flce;
 
@@ -307,6 +308,39 @@ int emu_jsd_rows(void* student, long long ld_s, const void* teacher, long long l
   if (dtype == 2) run_jsd_rows<float>(student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
   else if (dtype == 0) run_jsd_rows<__nv_bfloat16>(student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
   else run_jsd_rows<__half>(student, ld_s, teacher, ld_t, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
+  return 0;
+}
+
+// The persistent kernel's walk over the tile space: unit u visits tiles u, u + num_units, ... (gemm_sm100.cuh); visits[mt *
+// n_tiles + nt] counts how often a tile is reached, order[] lists the tile ids in the order unit 0 sees them.
+int emu_tile_schedule(int m_tiles, int n_tiles, int group, int group_along_m, int num_units, int* visits, int* order_unit0) {
+  GemmShape shape{};
+  shape.m_tiles = m_tiles;
+  shape.n_tiles = n_tiles;
+  shape.group = group;
+  shape.group_along_m = group_along_m;
+  const int num_tiles = m_tiles * n_tiles;
+  int n0 = 0;
+  for (int unit = 0; unit < num_units; ++unit)
+    for (int tile = unit; tile < num_tiles; tile += num_units) {
+      int mt = -1, nt = -1;
+      decode_tile(shape, tile, mt, nt);
+      if (mt < 0 || mt >= m_tiles || nt < 0 || nt >= n_tiles) return 1;
+      ++visits[mt * n_tiles + nt];
+      if (unit == 0) order_unit0[n0++] = mt * n_tiles + nt;
+    }
+  return 0;
+}
+
+// limit_to_active_rows: out[0] = m_tiles, out[1] = k_blocks after the adjustment
+int emu_limit_to_active_rows(int m_tiles, int k_blocks, int role, int active_rows, int ctas_per_tile, int* out) {
+  GemmShape shape{};
+  shape.m_tiles = m_tiles;
+  shape.k_blocks = k_blocks;
+  shape.active_role = role;
+  limit_to_active_rows(shape, active_rows, ctas_per_tile);
+  out[0] = shape.m_tiles;
+  out[1] = shape.k_blocks;
   return 0;
 }
 

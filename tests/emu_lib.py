@@ -1,4 +1,4 @@
-"""The library's SIMT kernels run on host threads (tests/emu/): build helper, ctypes binding and a stand-in library
+"""The library's SIMT kernels run on the host (tests/emu/): build helper, ctypes binding and a stand-in library
 object that sends the entry points made only of SIMT kernels (stand-alone cross-entropy, target counting, row
 compaction / scatter, fp32 term split, gradient scaling, the row kernels of the chunked head losses) to the emulation,
 so the Python operators can be driven on CPU tensors with real numerics.  The plain tensor-core GEMM entry point is
@@ -30,7 +30,7 @@ def _stale():
         return True
     built = os.path.getmtime(_OUT)
     deps = [_SRC, os.path.join(_HERE, "emu", "simt_emulation.hpp")]
-    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "head_loss_kernels.cuh", "simt_common.cuh")]
+    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "head_loss_kernels.cuh", "simt_common.cuh", "tile_schedule.cuh")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
@@ -61,6 +61,8 @@ def load():
         "emu_scaled_ce_rows": [P, LL, I, LL, LL, P, LL, F, P, P, P],
         "emu_scaled_ce_grad": [P, LL, I, LL, LL, P, LL, F, P, P, P, P],
         "emu_jsd_rows": [P, LL, P, LL, I, LL, LL, P, LL, F, F, P, F, P],
+        "emu_tile_schedule": [I, I, I, I, I, P, P],
+        "emu_limit_to_active_rows": [I, I, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)

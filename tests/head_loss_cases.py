@@ -1,5 +1,5 @@
 """Shared bodies of the fused linear JSD and fused linear scaled cross-entropy tests: the same cases run on a B200
-(tests/test_y_head_losses_gpu.py) and, with the library's SIMT kernels emulated on host threads and the tensor-core
+(tests/test_y_head_losses_gpu.py) and, with the library's SIMT kernels emulated on the host and the tensor-core
 GEMM entry point replaced by torch arithmetic, on CPU tensors (tests/test_head_losses_emulation_cpu.py).
 
 Tolerances follow the reference's tests (test/transformers/test_fused_linear_jsd.py: fp32 atol 1e-5 / rtol 5e-4, bf16

@@ -1,5 +1,5 @@
 """Fused linear JSD and fused linear scaled cross-entropy end to end on CPU tensors: the Python operators and their chunk
-loops run unchanged, the row kernels (csrc/head_loss_kernels.cuh) and the fp32 term split run on host threads
+loops run unchanged, the row kernels (csrc/head_loss_kernels.cuh) and the fp32 term split run on the host
 (tests/emu/), and the tensor-core GEMM entry point is replaced by torch arithmetic on the same memory
 (tests/emu_lib.py).  The case bodies are the GPU test's own (tests/head_loss_cases.py), at sizes the emulation handles
 in seconds."""

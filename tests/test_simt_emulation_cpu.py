@@ -1,4 +1,4 @@
-"""The library's SIMT kernels (everything outside the tensor-core sweeps) compiled for the host and run on host threads
+"""The library's SIMT kernels (everything outside the tensor-core sweeps) compiled for the host and run on the host
 (tests/emu/): real numerics on CPU for the stand-alone cross-entropy operator, target counting, row compaction and
 scatter, the fp32 term split, the single-sweep mode's in-place logit gradient, column sums and gradient scaling.
 
@@ -231,3 +231,42 @@ def test_colsum_and_scale_and_merge(emu):
     np.testing.assert_allclose(rowstats[3].numpy(), pls.sum(0).numpy(), rtol=1e-5, atol=1e-6)
     best = pav.argmax(0)
     assert torch.equal(rowstats[5].view(torch.int32), pai.gather(0, best[None])[0])
+
+
+# ---------------------------------------------------------------- tile schedule of the tensor-core main loop
+@pytest.mark.parametrize("m_tiles,n_tiles", [(1, 1), (3, 7), (128, 501), (501, 16), (64, 4), (37, 37)])
+@pytest.mark.parametrize("num_units", [74, 148, 5])
+def test_tile_schedule_visits_every_tile_once(emu, m_tiles, n_tiles, num_units):
+    """The producer, the MMA issuer and the epilogue warps of a persistent CTA derive their tiles from the same arithmetic
+    (csrc/tile_schedule.cuh); here: for every raster group shape the walk over all units reaches each tile exactly once, and
+    consecutive tiles of a group share the operand panel the raster is meant to keep in L2."""
+    for along_m in (0, 1):
+        extent = m_tiles if along_m else n_tiles
+        for group in sorted({1, 2, 3, 8, extent, max(1, extent - 1), extent + 5}):
+            visits = np.zeros(m_tiles * n_tiles, np.int32)
+            order = np.full(m_tiles * n_tiles, -1, np.int32)
+            rc = emu.emu_tile_schedule(m_tiles, n_tiles, group, along_m, num_units, visits.ctypes.data, order.ctypes.data)
+            assert rc == 0 and (visits == 1).all(), (m_tiles, n_tiles, group, along_m)
+    # walk order inside the first group (one unit sees every tile): group of g m-tiles x all n-tiles, m fastest
+    g = min(3, m_tiles)
+    visits = np.zeros(m_tiles * n_tiles, np.int32)
+    order = np.full(m_tiles * n_tiles, -1, np.int32)
+    emu.emu_tile_schedule(m_tiles, n_tiles, g, 1, 1, visits.ctypes.data, order.ctypes.data)
+    first = [(int(t) // n_tiles, int(t) % n_tiles) for t in order[:g * n_tiles]]
+    assert first == [(m, n) for n in range(n_tiles) for m in range(g)]
+
+
+def test_active_rows_shrink_m_tiles_or_k_blocks(emu):
+    out = np.zeros(2, np.int32)
+
+    def limit(m_tiles, k_blocks, role, rows, ctas):
+        emu.emu_limit_to_active_rows(m_tiles, k_blocks, role, rows, ctas, out.ctypes.data)
+        return int(out[0]), int(out[1])
+
+    assert limit(100, 50, 0, 10, 1) == (100, 50)                       # no role: untouched
+    assert limit(100, 50, 1, 0, 1) == (0, 50) and limit(100, 50, 2, 0, 2) == (100, 0)
+    assert limit(100, 50, 1, 1, 1) == (1, 50) and limit(100, 50, 1, 128, 1) == (1, 50) and limit(100, 50, 1, 129, 1) == (2, 50)
+    assert limit(100, 50, 1, 256, 2) == (1, 50) and limit(100, 50, 1, 257, 2) == (2, 50)      # a CTA pair owns 256 rows
+    assert limit(100, 50, 2, 64, 1) == (100, 1) and limit(100, 50, 2, 65, 2) == (100, 2)
+    assert limit(100, 50, 1, 10 ** 9, 1) == (100, 50) and limit(100, 50, 2, 10 ** 9, 1) == (100, 50)   # never grows
+    assert limit(100, 50, 1, -5, 1) == (0, 50)                         # a negative count reads as zero

@@ -4,7 +4,7 @@ reference's golden vectors.  Case grid follows test/transformers/test_cross_entr
 class weights, ignore_index, not-last-layer upstream gradients, per-row gradients for reduction "none").
 
 The case bodies live in tests/ce_cases.py; tests/test_simt_emulation_cpu.py runs the same bodies on CPU tensors with
-the kernels emulated on host threads."""
+the kernels emulated on the host."""
 
 import pytest
 import torch

@@ -4,7 +4,7 @@ the reference (shapes with odd sizes and a 128 k-wide vocabulary, dtypes, beta 0
 with ignore_index, upstream gradients, single-output backward).
 
 The case bodies live in tests/head_loss_cases.py; tests/test_head_losses_emulation_cpu.py runs the same bodies on CPU
-tensors with the row kernels emulated on host threads."""
+tensors with the row kernels emulated on the host."""
 
 import pytest
 import torch
