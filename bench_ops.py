@@ -1,0 +1,177 @@
+#!/usr/bin/env python
+"""Forward + backward time of the operators beside the fused linear cross-entropy path, one GPU:
+
+    python bench_ops.py --op ce|jsd|scaled_ce [--impl ours|liger] [--rows N --hidden H --vocab V] [--steps K --warmup W]
+
+  ce         stand-alone cross-entropy on materialised logits [N, V]            (HBM-bound: 3 N V b bytes per step)
+  jsd        fused linear JSD, student head H/2 and teacher head H               (tensor-bound)
+  scaled_ce  fused linear scaled cross-entropy (nll + entropy, both upstream gradients per token)   (tensor-bound)
+
+Shapes default to the reference's benchmark scripts (benchmark/scripts/benchmark_cross_entropy.py,
+benchmark_fused_linear_jsd.py: B*T = 4096 ... 8192 rows, H = 4096, V = 128256); inputs are seeded random tensors, bf16.
+`--impl liger` times the unmodified reference from baseline/_ref (its Triton cross-entropy and JSD kernels; for the
+scaled cross-entropy the device-independent implementation the reference itself selects on this GPU) on the same
+inputs.  One JSON line per run.  `bench.py` stays the benchmark of the headline path; this file measures the rows
+that were widened into after it.
+"""
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "liger-kernel_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+DEFAULTS = {"ce": dict(rows=8192, hidden=0, vocab=128256), "jsd": dict(rows=4096, hidden=4096, vocab=128256),
+            "scaled_ce": dict(rows=8192, hidden=4096, vocab=128256)}
+
+
+def make_case(op, rows, hidden, vocab, dtype, device, seed=1234):
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def rand(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+
+    target = torch.randint(0, vocab, (rows,), generator=g, device=device)
+    target = torch.where(torch.rand(rows, generator=g, device=device) < 0.05, torch.full_like(target, -100), target)
+    if op == "ce":
+        return dict(logits=rand(rows, vocab, scale=2.0), target=target)
+    if op == "jsd":
+        return dict(xs=rand(rows, hidden // 2), ws=rand(vocab, hidden // 2, scale=0.02), xt=rand(rows, hidden),
+                    wt=rand(vocab, hidden, scale=0.02), target=target)
+    return dict(x=rand(rows, hidden), w=rand(vocab, hidden, scale=0.02), target=target,
+                g_nll=torch.randn(rows, generator=g, device=device), g_ent=torch.randn(rows, generator=g, device=device))
+
+
+def make_step(op, impl, case, n_calls):
+    """Returns a callable running one forward + backward; gradients are dropped between steps.  Both cross-entropy
+    implementations write the gradient over the logits they are given, so that operator gets a fresh copy per call,
+    made before the clock starts."""
+    if impl == "ours":
+        import liger_kernel_b200 as lk
+
+        ce, jsd, sce = lk.liger_cross_entropy, lk.LigerFusedLinearJSD(), lk.LigerFusedLinearScaledCrossEntropyFunction.apply
+    else:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        from liger_kernel.ops.fused_linear_scaled_cross_entropy import LigerFusedLinearScaledCrossEntropyFunction
+        from liger_kernel.transformers.functional import liger_cross_entropy as ce
+        from liger_kernel.transformers.fused_linear_jsd import LigerFusedLinearJSD
+
+        jsd, sce = LigerFusedLinearJSD(), LigerFusedLinearScaledCrossEntropyFunction.apply
+    if op == "ce":
+        pool = [case["logits"].clone().requires_grad_(True) for _ in range(n_calls)]
+
+        def step():
+            logits = pool.pop()
+            loss = ce(logits, case["target"])
+            loss.backward()
+            return loss
+    elif op == "jsd":
+        xs, ws = case["xs"].requires_grad_(True), case["ws"].requires_grad_(True)
+
+        def step():
+            xs.grad = ws.grad = None
+            loss = jsd(xs, ws, case["xt"], case["wt"], case["target"])
+            loss.backward()
+            return loss
+    else:
+        x, w = case["x"].requires_grad_(True), case["w"].requires_grad_(True)
+
+        def step():
+            x.grad = w.grad = None
+            nll, entropy = sce(x, w, case["target"], 1.0, -100, 1, True)
+            loss = (nll * case["g_nll"]).sum() + (entropy.float() * case["g_ent"]).sum()
+            loss.backward()
+            return loss
+    return step
+
+
+def work_per_step(op, rows, hidden, vocab, element_size):
+    """(bound, algorithmic units per step): HBM bytes for ce, tensor FLOPs for the two fused heads."""
+    if op == "ce":
+        return "hbm", 3.0 * rows * vocab * element_size                    # read for the statistics, read + write for the gradient
+    if op == "jsd":
+        return "tensor", 2.0 * rows * vocab * (hidden // 2 + hidden) + 4.0 * rows * vocab * (hidden // 2)
+    return "tensor", 8.0 * rows * hidden * vocab                           # logits twice (recomputed in backward) + two projections
+
+
+def time_steps(step, steps, warmup, device):
+    for _ in range(warmup):
+        step()
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            last = step()
+        stop.record()
+        torch.cuda.synchronize(device)
+        return start.elapsed_time(stop) / steps, float(last.detach())
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        last = step()
+    return (time.perf_counter() - t0) * 1e3 / steps, float(last.detach())
+
+
+def run(op, impl, rows, hidden, vocab, dtype, steps, warmup, device):
+    from bench import ClockSampler, load_peaks
+
+    case = make_case(op, rows, hidden, vocab, dtype, device)
+    step = make_step(op, impl, case, steps + warmup)
+    launches_before = 0
+    if impl == "ours":
+        from liger_kernel_b200._lib import lib
+        launches_before = lib.flce_b200_kernel_launches()
+    if device.type == "cuda":
+        with ClockSampler(device.index or 0) as sampler:
+            ms, loss = time_steps(step, steps, warmup, device)
+        clocks = sampler.summary()
+    else:
+        ms, loss = time_steps(step, steps, warmup, device)
+        clocks = None
+    launches = None
+    if impl == "ours":
+        launches = (lib.flce_b200_kernel_launches() - launches_before) * steps // (steps + warmup)
+    bound, units = work_per_step(op, rows, hidden, vocab, torch.empty((), dtype=dtype).element_size())
+    peaks = load_peaks()
+    achieved = units / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+    peak = peaks["hbm"] if bound == "hbm" else peaks["sustained"]
+    return {
+        "op": op, "impl": impl, "metric": f"{op}_fwd_bwd_tokens_per_s", "value": rows / (ms * 1e-3), "unit": "tokens/s",
+        "ms_per_step": ms, "steps": steps, "warmup": warmup, "n_gpus": 1, "higher_is_better": True,
+        "dtype": str(dtype).replace("torch.", ""), "data": "synthetic (seeded random tensors, 5 % ignored targets)",
+        "config": {"workload": f"{op}: rows={rows} hidden={hidden} vocab={vocab}", "inputs_larger_than_l2": True},
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"]},
+        "gpu_launches": launches, "clocks": clocks, "last_loss": loss,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=sorted(DEFAULTS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "liger"])
+    ap.add_argument("--rows", type=int, default=None)
+    ap.add_argument("--hidden", type=int, default=None)
+    ap.add_argument("--vocab", type=int, default=None)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    d = DEFAULTS[args.op]
+    if not torch.cuda.is_available():
+        raise SystemExit("bench_ops.py needs a CUDA device (sm_100a); there is no CPU path")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    out = run(args.op, args.impl, args.rows or d["rows"], args.hidden if args.hidden is not None else d["hidden"],
+              args.vocab or d["vocab"], getattr(torch, args.dtype), args.steps, args.warmup, device)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
