@@ -34,7 +34,7 @@ WORKLOADS = {
     "profile": dict(N=8192, H=4096, V=32768, ign=0.05, kw=dict()),  # small case for ncu captures (W = 268 MB > L2)
     "c2": dict(N=32768, H=4096, V=128256, ign=0.05, kw=dict()),
     "c3": dict(N=32768, H=3584, V=152064, ign=0.20, kw=dict(label_smoothing=0.1, lse_square_scale=1e-4, return_z_loss=True)),
-    "c4": dict(N=16384, H=3584, V=256000, ign=0.05, kw=dict(softcap=30.0, reduction="sum")),
+    "c4": dict(N=16384, H=3584, V=256000, ign=0.05, zipf=1.1, kw=dict(softcap=30.0, reduction="sum")),
     "c5": dict(N=65536, H=8192, V=128256, ign=0.05, kw=dict()),
 }
 NAMES = {
@@ -42,7 +42,7 @@ NAMES = {
     "profile": "FLCE profiling case N=8192 H=4096 V=32768 bf16 (one vocabulary slab)",
     "c2": "Llama-3-8B LM head FLCE bf16: N=32768 (B=8,T=4096) H=4096 V=128256, 5% ignored, mean, fwd+bwd",
     "c3": "Qwen2.5-7B-style head FLCE bf16: N=32768 H=3584 V=152064, label_smoothing 0.1, z-loss 1e-4, 20% ignored",
-    "c4": "Gemma-2-9B-style head FLCE bf16: N=16384 H=3584 V=256000, softcap 30, sum, 5% ignored",
+    "c4": "Gemma-2-9B-style head FLCE bf16: N=16384 H=3584 V=256000, softcap 30, sum, Zipf(1.1) targets, 5% ignored",
     "c5": "Llama-3-70B LM head FLCE bf16: N=65536 H=8192 V=128256, 5% ignored, mean",
 }
 
@@ -69,7 +69,13 @@ def make_inputs(spec, device, seed):
     N, H, V = spec["N"], spec["H"], spec["V"]
     x = torch.randn(N, H, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
     w = (torch.randn(V, H, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-    t = torch.randint(0, V, (N,), generator=g, device=device)
+    if spec.get("zipf"):
+        # class frequencies of natural text: rank r drawn with probability proportional to r^-s (inverse-CDF sampling)
+        cdf = torch.cumsum(torch.arange(1, V + 1, device=device, dtype=torch.float64).pow(-float(spec["zipf"])), 0)
+        u = torch.rand(N, generator=g, device=device, dtype=torch.float64) * cdf[-1]
+        t = torch.searchsorted(cdf, u).clamp_(max=V - 1)
+    else:
+        t = torch.randint(0, V, (N,), generator=g, device=device)
     drop = torch.rand(N, generator=g, device=device) < spec["ign"]
     t = torch.where(drop, torch.full_like(t, -100), t)
     return x, w, t
@@ -333,13 +339,16 @@ def run_ours(args, spec, rank, world, local_rank):
     _lib.profile_enable(True)
     barrier()
     with ClockSampler(local_rank) as clocks:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        marks[0].record()
+        for i in range(args.steps):
             step(x, t)
-        e1.record()
+            marks[i + 1].record()
+        e0, e1 = marks[0], marks[-1]
         barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))      # this rank's steps
+    step_quantiles = {f"p{q}": per_step[min(len(per_step) - 1, int(q / 100 * len(per_step)))] for q in (20, 50, 80)}
     prof = _lib.profile_read(reset=True)
     _lib.profile_enable(False)
     launches = _lib.lib.flce_b200_kernel_launches() - launches0
@@ -405,6 +414,7 @@ def run_ours(args, spec, rank, world, local_rank):
         "global_tokens_per_step": tokens,
         "gpu_launches": int(launches),
         "peak_mem_gb": peak_mem / 1e9,
+        "ms_per_step_quantiles": step_quantiles,
         "clocks": {"sm_mhz": clock_info["sm_mhz"], "sm_max_mhz": clock_info["sm_max_mhz"], "reasons": clock_info["reasons"],
                    "samples": clock_info["samples"]},
     }

@@ -29,3 +29,21 @@ def test_bench_ops_record(monkeypatch, op, rows, hidden, vocab):
     else:
         assert units == 8 * rows * hidden * vocab
     assert rec["last_loss"] == rec["last_loss"]          # finite / not NaN
+
+
+def test_bench_inputs_zipf_targets_for_the_gemma_style_workload():
+    """bench.py's config C4 draws targets from a Zipf(1.1) law over the class ranks; the other workloads stay uniform."""
+    import bench
+
+    assert bench.WORKLOADS["c4"]["zipf"] == 1.1 and "zipf" not in bench.WORKLOADS["c2"]
+    spec = dict(N=40000, H=8, V=1000, ign=0.05, zipf=1.1, kw={})
+    x, w, t = bench.make_inputs(spec, torch.device("cpu"), 1)
+    assert x.shape == (40000, 8) and x.dtype == torch.bfloat16 and w.shape == (1000, 8)
+    live = t[t >= 0]
+    counts = torch.bincount(live, minlength=1000).double()
+    assert 1.9 < float(counts[0] / counts[1]) < 2.4                       # 2^1.1 = 2.14
+    assert 10.0 < float(counts[0] / counts[9]) < 16.0                     # 10^1.1 = 12.6
+    assert int(live.max()) <= 999 and 0.04 < float((t == -100).float().mean()) < 0.06
+    uniform = bench.make_inputs(dict(N=40000, H=8, V=1000, ign=0.05, kw={}), torch.device("cpu"), 1)[2]
+    u = torch.bincount(uniform[uniform >= 0], minlength=1000).double()
+    assert float(u.max() / u.min()) < 6.0 and float(counts.max() / max(1.0, float(counts[500:].mean()))) > 100.0
