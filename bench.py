@@ -201,21 +201,34 @@ def run_reference(args, spec, rank, world):
 def run_liger(args, spec, rank, world, local_rank):
     """The reference's own GPU operator (installed unmodified under baseline/_ref) on the same workload and
     timing, for the side-by-side number.  `--impl liger_triton`: its default Triton path; `--impl liger_cutedsl`:
-    its CuTe-DSL sm_100 path (LIGER_KERNEL_IMPL=cutedsl), which needs a newer nvidia-cutlass-dsl than some images have."""
+    its CuTe-DSL sm_100 path (LIGER_KERNEL_IMPL=cutedsl), which needs a newer nvidia-cutlass-dsl than some images have;
+    `--impl torch_gpu`: plain torch Linear + cross-entropy on the GPU with materialised fp32 logits."""
     if rank != 0:
         return
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "liger_kernel")):
-        print(json.dumps({"impl": args.impl, "unavailable": "baseline/_ref/liger_kernel is not installed"}))
-        return
-    if args.impl == "liger_cutedsl":
-        os.environ["LIGER_KERNEL_IMPL"] = "cutedsl"
-    sys.path.insert(0, ref_dir)
-    try:
-        from liger_kernel.transformers.functional import liger_fused_linear_cross_entropy as ref_flce
-    except Exception as e:  # noqa: BLE001
-        print(json.dumps({"impl": args.impl, "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}))
-        return
+    if args.impl == "torch_gpu":
+        def ref_flce(xin, w, t, softcap=None, lse_square_scale=0.0, return_z_loss=False, accum_dtype=None, **ce_kw):
+            # the plain path the fused operator replaces: fp32 logits [N, V] materialised, torch cross-entropy
+            logits = (xin @ w.t()).float()
+            if softcap is not None:
+                logits = softcap * torch.tanh(logits / softcap)
+            loss = torch.nn.functional.cross_entropy(logits, t, ignore_index=-100, **ce_kw)
+            if lse_square_scale:
+                lse = torch.logsumexp(logits, dim=-1)
+                loss = loss + lse_square_scale * (lse[t != -100] ** 2).mean()
+            return loss
+    else:
+        ref_dir = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref_dir, "liger_kernel")):
+            print(json.dumps({"impl": args.impl, "unavailable": "baseline/_ref/liger_kernel is not installed"}))
+            return
+        if args.impl == "liger_cutedsl":
+            os.environ["LIGER_KERNEL_IMPL"] = "cutedsl"
+        sys.path.insert(0, ref_dir)
+        try:
+            from liger_kernel.transformers.functional import liger_fused_linear_cross_entropy as ref_flce
+        except Exception as e:  # noqa: BLE001
+            print(json.dumps({"impl": args.impl, "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}))
+            return
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     x, w, t = make_inputs(spec, device, 1234)
@@ -456,7 +469,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "liger_triton", "liger_cutedsl"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "liger_triton", "liger_cutedsl", "torch_gpu"])
     ap.add_argument("--accum-fp32", action="store_true", dest="accum_fp32")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cta-pair", type=int, default=None, dest="cta_pair")
@@ -474,7 +487,7 @@ def main():
     spec = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, spec, rank, world)
-    elif args.impl in ("liger_triton", "liger_cutedsl"):
+    elif args.impl in ("liger_triton", "liger_cutedsl", "torch_gpu"):
         run_liger(args, spec, rank, world, local_rank)
     else:
         run_ours(args, spec, rank, world, local_rank)
