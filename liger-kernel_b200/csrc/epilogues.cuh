@@ -2,7 +2,6 @@
 // thread owns one output row of the tile and sees its 256 fp32 accumulators 32 at a time.
 #pragma once
 
-#include "ptx_sm100.cuh"
 #include "simt_common.cuh"
 
 namespace flce {

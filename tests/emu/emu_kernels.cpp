@@ -1,4 +1,5 @@
-// The library's SIMT kernels (csrc/row_kernels.cuh, csrc/ce_kernels.cuh, csrc/head_loss_kernels.cuh) compiled for the host and run on the host
+// The library's SIMT kernels (csrc/row_kernels.cuh, csrc/ce_kernels.cuh, csrc/head_loss_kernels.cuh), the register
+// epilogues of its tensor-core sweeps (csrc/epilogues.cuh) and its tile schedule (csrc/tile_schedule.cuh) compiled for the host and run on the host
 // through simt_emulation.hpp, behind a small C interface for the CPU tests.  Every wrapper repeats the launch geometry
 // and kernel order of the library entry point it is named after (csrc/flce_b200.cu), so the tests exercise the same
 // index arithmetic a GPU launch would.  ex2.approx / rcp.approx are replaced by libm (FLCE_HOST_EMULATION), so results
@@ -9,6 +10,7 @@
 #include "simt_emulation.hpp"
 
 #include "ce_kernels.cuh"
+#include "epilogues.cuh"
 #include "head_loss_kernels.cuh"
 #include "row_kernels.cuh"
 #include "tile_schedule.cuh"
@@ -150,6 +152,46 @@ void run_jsd_rows(void* student, long long ld_s, const void* teacher, long long 
       jsd_rows_kernel<T, false>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab), labels, ignore_index, beta,
                                 inv_t, count, fixed_count, loss_rows);
   });
+}
+
+// ---- the tensor-core sweeps at tile level: the main loop's accumulators are replaced by a float dot product of the 16-bit
+// operands (what the tensor cores compute up to summation order, zeros where TMA would fill out-of-range rows / columns), and
+// each epilogue instance is driven the way an epilogue thread of gemm_tcgen05_kernel drives it: begin, up to eight chunks of
+// 32 accumulators, end -- for every row of every 128 x 256 tile, including the rows of the last tile that lie beyond M.
+float load16(const void* base, long long index, int dtype) {
+  if (dtype == 0) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[index]);
+  return __half2float(static_cast<const __half*>(base)[index]);
+}
+
+template <class Epi>
+void run_tiles(const typename Epi::Params& ep, const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a,
+               long long ld_b) {
+  const int m_tiles = static_cast<int>(ceil_div(m, kBlockM)), n_tiles = static_cast<int>(ceil_div(n, kBlockN));
+  std::vector<float> arow(k);
+  for (int mt = 0; mt < m_tiles; ++mt)
+    for (int r = 0; r < kBlockM; ++r) {
+      const int row = mt * kBlockM + r;
+      const bool ok = row < m;
+      for (int kk = 0; kk < k; ++kk) arow[kk] = ok ? load16(a, static_cast<long long>(row) * ld_a + kk, dtype) : 0.f;
+      for (int nt = 0; nt < n_tiles; ++nt) {
+        const int col0 = nt * kBlockN;
+        Epi epi;
+        epi.begin(ep, row, col0, nt, ok);
+        const int n_chunks = std::min(kBlockN / 32, (n - col0 + 31) / 32);
+        for (int c = 0; c < n_chunks; ++c) {
+          uint32_t acc[32];
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + c * 32 + j;
+            float v = 0.f;
+            if (ok && col < n)
+              for (int kk = 0; kk < k; ++kk) v = fmaf(arow[kk], load16(b, static_cast<long long>(col) * ld_b + kk, dtype), v);
+            acc[j] = __float_as_uint(v);
+          }
+          epi.chunk(ep, acc, col0 + c * 32);
+        }
+        epi.end(ep);
+      }
+    }
 }
 
 }  // namespace
@@ -341,6 +383,124 @@ int emu_limit_to_active_rows(int m_tiles, int k_blocks, int role, int active_row
   limit_to_active_rows(shape, active_rows, ctas_per_tile);
   out[0] = shape.m_tiles;
   out[1] = shape.k_blocks;
+  return 0;
+}
+
+// sweep 1 (StatsEpilogue): per-(tile, row) partials, target logit, optional 16-bit copy of the soft-capped logits.
+// Plane pointers may be null as in the library; target_logit must be zeroed by the caller (the library memsets it).
+int emu_sweep_stats(const void* x, const void* w, int dtype, int m, int vocab, int k, long long ld_x, long long ld_w,
+                    const long long* target, const float* bias, const float* col_weight, float softcap, long long vocab_offset,
+                    float* pmax, float* psum, float* plogit_sum, float* pamax_val, int* pamax_idx, float* target_logit,
+                    void* logits_out, long long ld_logits, int logits_fmt) {
+  StatsEpilogue::Params ep;
+  ep.target = target;
+  ep.bias = bias;
+  ep.col_weight = col_weight;
+  ep.softcap = softcap;
+  ep.inv_softcap = softcap > 0.f ? 1.f / softcap : 0.f;
+  ep.n_cols = vocab;
+  ep.vocab_offset = vocab_offset;
+  ep.m_rows = m;
+  ep.pmax = pmax;
+  ep.psum = psum;
+  ep.plogit_sum = plogit_sum;
+  ep.pamax_val = pamax_val;
+  ep.pamax_idx = pamax_idx;
+  ep.target_logit = target_logit;
+  ep.logits_out = logits_out;
+  ep.ld_logits = ld_logits;
+  ep.logits_fmt = logits_fmt;
+  run_tiles<StatsEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w);
+  return 0;
+}
+
+// sweep 2 (DzEpilogue): the 16-bit logit-gradient slab (and the optional rounding-residual slab)
+int emu_sweep_dz(const void* x, const void* w, int dtype, int m, int vocab, int k, long long ld_x, long long ld_w,
+                 const long long* target, const float* bias, const float* col_weight, float softcap, long long vocab_offset,
+                 const float* lse, const float* c1, const float* c2, const float* c3, void* dz, void* dz_lo, long long ld_dz,
+                 int out_fmt) {
+  DzEpilogue::Params ep;
+  ep.target = target;
+  ep.bias = bias;
+  ep.col_weight = col_weight;
+  ep.softcap = softcap;
+  ep.inv_softcap = softcap > 0.f ? 1.f / softcap : 0.f;
+  ep.n_cols = vocab;
+  ep.vocab_offset = vocab_offset;
+  ep.m_rows = m;
+  ep.lse = lse;
+  ep.c1 = c1;
+  ep.c2 = c2;
+  ep.c3 = c3;
+  ep.dz = dz;
+  ep.dz_lo = dz_lo;
+  ep.ld_dz = ld_dz;
+  ep.out_fmt = out_fmt;
+  run_tiles<DzEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w);
+  return 0;
+}
+
+// StoreEpilogue: D = A . B^T (+ acc) with both operands K-major; acc (fp32, in/out) and out (out_fmt) may each be null
+int emu_gemm_store(const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a, long long ld_b, float* acc,
+                   long long ld_acc, void* out, long long ld_out, int out_fmt) {
+  StoreEpilogue::Params ep;
+  ep.m_rows = m;
+  ep.n_cols = n;
+  ep.acc_in = acc;
+  ep.acc_out = acc;
+  ep.ld_acc = ld_acc;
+  ep.out = out;
+  ep.ld_out = ld_out;
+  ep.out_fmt = out_fmt;
+  run_tiles<StoreEpilogue>(ep, a, b, dtype, m, n, k, ld_a, ld_b);
+  return 0;
+}
+
+// coefficients of the logit gradient (coef_kernel, geometry of flce_b200_backward)
+int emu_coef(long long n_rows, long long ignore_index, float alpha, float lambda, int mean, int token_scaling, long long vocab,
+             long long vocab_total, long long vocab_offset, const long long* target, const float* ce_weight, const float* lse,
+             const float* prob, const float* norm, const float* grad_output, int per_row, float* c1, float* c2, float* c3) {
+  RowMath rm;
+  rm.ignore_index = ignore_index;
+  rm.alpha = alpha;
+  rm.eps = alpha / static_cast<float>(vocab_total);
+  rm.lambda = lambda;
+  rm.mean = mean;
+  rm.token_scaling = token_scaling;
+  rm.weighted = ce_weight != nullptr;
+  rm.vocab = vocab;
+  rm.vocab_offset = vocab_offset;
+  const int threads = 256;
+  emu::launch_serial(static_cast<unsigned>(ceil_div(n_rows, threads)), threads, [&]() {
+    coef_kernel(static_cast<int>(n_rows), rm, target, ce_weight, lse, prob, norm, grad_output, per_row, c1, c2, c3);
+  });
+  return 0;
+}
+
+// per-row loss and metrics (finalize_rows_kernel + reduce_rows_kernel, geometry of flce_b200_forward_finalize)
+int emu_finalize(long long n_rows, long long ignore_index, float alpha, float lambda, int mean, int token_scaling, long long vocab,
+                 long long vocab_total, long long vocab_offset, const long long* target, const float* ce_weight,
+                 const float* rowstats, const float* norm, float* lse, float* prob, float* loss_rows, float* z_rows,
+                 float* correct_rows, long long* predicted, float* scalars) {
+  RowMath rm;
+  rm.ignore_index = ignore_index;
+  rm.alpha = alpha;
+  rm.eps = alpha / static_cast<float>(vocab_total);
+  rm.lambda = lambda;
+  rm.mean = mean;
+  rm.token_scaling = token_scaling;
+  rm.weighted = ce_weight != nullptr;
+  rm.vocab = vocab;
+  rm.vocab_offset = vocab_offset;
+  const int threads = 256;
+  emu::launch_serial(static_cast<unsigned>(ceil_div(n_rows, threads)), threads, [&]() {
+    finalize_rows_kernel(static_cast<int>(n_rows), rm, target, ce_weight, rowstats, norm, lse, prob, loss_rows, z_rows,
+                         correct_rows, predicted);
+  });
+  if (scalars != nullptr)
+    emu::launch(1, kRedThreads, [&]() {
+      reduce_rows_kernel(static_cast<int>(n_rows), loss_rows, z_rows, correct_rows, norm, scalars);
+    });
   return 0;
 }
 

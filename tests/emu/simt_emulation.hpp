@@ -215,6 +215,16 @@ T __shfl_up_sync(unsigned, T v, unsigned delta) {
 }
 template <typename T>
 T __ldg(const T* p) { return *p; }
+inline float __uint_as_float(unsigned v) {
+  float f;
+  std::memcpy(&f, &v, sizeof(f));
+  return f;
+}
+inline unsigned __float_as_uint(float f) {
+  unsigned v;
+  std::memcpy(&v, &f, sizeof(v));
+  return v;
+}
 
 using std::max;
 using std::min;

@@ -30,7 +30,7 @@ def _stale():
         return True
     built = os.path.getmtime(_OUT)
     deps = [_SRC, os.path.join(_HERE, "emu", "simt_emulation.hpp")]
-    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "head_loss_kernels.cuh", "simt_common.cuh", "tile_schedule.cuh")]
+    deps += [os.path.join(_CSRC, f) for f in ("row_kernels.cuh", "ce_kernels.cuh", "head_loss_kernels.cuh", "simt_common.cuh", "tile_schedule.cuh", "epilogues.cuh")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
@@ -62,6 +62,11 @@ def load():
         "emu_scaled_ce_grad": [P, LL, I, LL, LL, P, LL, F, P, P, P, P],
         "emu_jsd_rows": [P, LL, P, LL, I, LL, LL, P, LL, F, F, P, F, P],
         "emu_tile_schedule": [I, I, I, I, I, P, P],
+        "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I],
+        "emu_sweep_dz": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, LL, I],
+        "emu_gemm_store": [P, P, I, I, I, I, LL, LL, P, LL, P, LL, I],
+        "emu_coef": [LL, LL, F, F, I, I, LL, LL, LL, P, P, P, P, P, P, I, P, P, P],
+        "emu_finalize": [LL, LL, F, F, I, I, LL, LL, LL, P, P, P, P, P, P, P, P, P, P, P],
         "emu_limit_to_active_rows": [I, I, I, I, I, P],
     }
     for name, args in sigs.items():
