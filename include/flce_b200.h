@@ -286,6 +286,40 @@ int flce_b200_scaled_ce_grad(void* logits, int64_t ld, int32_t dtype, int64_t n_
                              int64_t ignore_index, float temperature, const float* lse, const float* entropy,
                              const float* grad_nll, const float* grad_entropy, void* stream);
 
+/* Scaled cross-entropy fused into the two tensor-core sweeps (no logits slab in forward, a bounded 16-bit slab of the logit
+ * gradient per vocabulary slab in backward): the same results as the rows / grad kernels above for 16-bit operands.
+ * This is the form the reference's sm_90 path takes (src/liger_kernel/ops/cutedsl/ops/fused_scaled_cross_entropy_sm90.py);
+ * on sm_100 the reference falls back to the chunked loop. */
+typedef struct flce_sce_problem {
+  int64_t n_rows;           /* tokens M                                                          */
+  int64_t hidden;           /* H                                                                 */
+  int64_t vocab;            /* V                                                                 */
+  int64_t ld_x;             /* row pitch of x in elements (multiple of 8)                        */
+  int64_t ld_w;             /* row pitch of w in elements (multiple of 8)                        */
+  int32_t dtype;            /* FLCE_BF16 or FLCE_FP16                                            */
+  int32_t reserved;         /* 0                                                                 */
+  int64_t ignore_index;
+  float temperature;        /* finite, > 0                                                       */
+  float reserved2;          /* 0                                                                 */
+  const void* x;            /* [n_rows, ld_x]                                                    */
+  const void* w;            /* [vocab, ld_w]                                                     */
+  const int64_t* target;    /* [n_rows]                                                          */
+} flce_sce_problem_t;
+
+/* phase: FLCE_PHASE_FORWARD or FLCE_PHASE_BACKWARD (slab_budget_bytes as in flce_b200_workspace_bytes; 0 = 1 GiB). */
+size_t flce_b200_sce_workspace_bytes(const flce_sce_problem_t* p, int phase, size_t slab_budget_bytes);
+
+/* nll, entropy (both 0 on ignored tokens) and lse, [n_rows] fp32 each. */
+int flce_b200_sce_forward(const flce_sce_problem_t* p, float* nll, float* entropy, float* lse, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/* lse / entropy from the forward call; grad_nll / grad_entropy [n_rows] fp32, either may be NULL (zeros).  grad_input
+ * [n_rows, hidden] and grad_weight [vocab, hidden] (dense, in grad_dtype: the operands' dtype or FLCE_FP32) may each be
+ * NULL.  grad_input is accumulated over vocabulary slabs in fp32 and rounded once. */
+int flce_b200_sce_backward(const flce_sce_problem_t* p, const float* lse, const float* entropy, const float* grad_nll,
+                           const float* grad_entropy, int32_t grad_dtype, void* grad_input, void* grad_weight,
+                           void* workspace, size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
+
 /* Generalised Jensen-Shannon divergence between the student's and the teacher's distribution of every token
  * (src/liger_kernel/ops/jsd.py:12-93 and the chain rule of src/liger_kernel/ops/fused_linear_jsd.py:118-122):
  * loss_rows[i] = the token's loss / count; student[i][:] <- d loss / d (student logits), zeros when labels[i] ==

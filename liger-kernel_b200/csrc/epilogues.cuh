@@ -290,6 +290,159 @@ struct DzEpilogue {
 };
 
 // =====================================================================================
+// Scaled cross-entropy (negative log-likelihood + entropy of softmax(z / T)) on the same two sweeps.
+// Sweep 1 keeps, per (row, tile), max, sum exp(s - max) and sum exp(s - max) * s with s = z * scale; the entropy is
+// lse - (sum e s) / (sum e).  Sweep 2 turns the recomputed logits into
+//   dZ[r, j] = (p[r, j] * (a_r + b_r * s[r, j]) - c_r * [j == target_r]),   p = exp(s - lse_r),
+//   a = (g_nll - g_ent * (H - lse)) * scale,  b = -g_ent * scale,  c = g_nll * scale     (zero on ignored rows),
+// which is d(nll * g_nll + entropy * g_ent) / dz.
+// =====================================================================================
+struct EntropyStatsEpilogue {
+  struct Params {
+    const long long* target;  // [M] class ids
+    float scale;              // 1 / temperature
+    int n_cols;               // valid columns
+    int m_rows;               // M
+    float* pmax;              // [n_tiles][M]
+    float* psum;              // [n_tiles][M]
+    float* pts;               // [n_tiles][M]  sum exp(s - max) * s
+    float* target_logit;      // [M] scaled logit of the target, written by the one tile that contains it
+  };
+
+  float m, d, t;
+  int row, nt, tgt_local;
+  bool row_ok;
+
+  __device__ __forceinline__ void begin(const Params& p, int row_, int /*col0*/, int n_tile, bool ok) {
+    row = row_;
+    nt = n_tile;
+    row_ok = ok;
+    m = -INFINITY;
+    d = 0.f;
+    t = 0.f;
+    tgt_local = -1;
+    if (ok) {
+      const long long y = p.target[row];
+      if (y >= 0 && y < p.n_cols) tgt_local = static_cast<int>(y);
+    }
+  }
+
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+    float s[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(acc[j]) * p.scale;
+    const bool ragged = col + 32 > p.n_cols;
+    float c0 = -INFINITY, c1 = -INFINITY, c2 = -INFINITY, c3 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      c0 = fmaxf(c0, (!ragged || col + j < p.n_cols) ? s[j] : -INFINITY);
+      c1 = fmaxf(c1, (!ragged || col + j + 1 < p.n_cols) ? s[j + 1] : -INFINITY);
+      c2 = fmaxf(c2, (!ragged || col + j + 2 < p.n_cols) ? s[j + 2] : -INFINITY);
+      c3 = fmaxf(c3, (!ragged || col + j + 3 < p.n_cols) ? s[j + 3] : -INFINITY);
+    }
+    const float m_new = fmaxf(m, fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)));
+    const float ml2 = m_new * kLog2e;
+    float p0 = 0.f, p1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const bool v0 = !ragged || col + j < p.n_cols, v1 = !ragged || col + j + 1 < p.n_cols;
+      const float e0 = v0 ? ex2_approx(fmaf(s[j], kLog2e, -ml2)) : 0.f;
+      const float e1 = v1 ? ex2_approx(fmaf(s[j + 1], kLog2e, -ml2)) : 0.f;
+      p0 += e0;
+      p1 += e1;
+      q0 = fmaf(e0, v0 ? s[j] : 0.f, q0);
+      q1 = fmaf(e1, v1 ? s[j + 1] : 0.f, q1);
+    }
+    const float keep = ex2_approx((m - m_new) * kLog2e);
+    d = fmaf(d, keep, p0 + p1);
+    t = fmaf(t, keep, q0 + q1);
+    m = m_new;
+    const unsigned rel = static_cast<unsigned>(tgt_local - col);
+    if (rel < 32u) {
+      float sy = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sy = (rel == static_cast<unsigned>(j)) ? s[j] : sy;
+      p.target_logit[row] = sy;
+    }
+  }
+
+  __device__ __forceinline__ void end(const Params& p) {
+    if (!row_ok) return;
+    const size_t o = static_cast<size_t>(nt) * p.m_rows + row;
+    p.pmax[o] = m;
+    p.psum[o] = d;
+    p.pts[o] = t;
+  }
+};
+
+struct ScaledDzEpilogue {
+  struct Params {
+    const long long* target;
+    long long ignore_index;
+    float scale;              // 1 / temperature
+    int n_cols;               // valid columns of this slab
+    long long vocab_offset;   // class id of slab column 0
+    int m_rows;
+    const float* lse;         // [M]
+    const float* entropy;     // [M]
+    const float* grad_nll;    // [M] or null
+    const float* grad_entropy;  // [M] or null
+    void* dz;                 // [M][ld_dz] 16-bit
+    long long ld_dz;
+    int out_fmt;
+  };
+
+  float l2, a, b, c;
+  int row, tgt_local;
+  bool row_ok;
+
+  __device__ __forceinline__ void begin(const Params& p, int row_, int /*col0*/, int /*n_tile*/, bool ok) {
+    row = row_;
+    row_ok = ok;
+    tgt_local = -1;
+    l2 = 0.f;
+    a = b = c = 0.f;
+    if (ok) {
+      const long long y = p.target[row];
+      const float lse = p.lse[row];
+      l2 = lse * kLog2e;
+      if (y != p.ignore_index) {
+        const long long local = y - p.vocab_offset;
+        if (local >= 0 && local < p.n_cols) tgt_local = static_cast<int>(local);
+        const float gn = p.grad_nll != nullptr ? p.grad_nll[row] : 0.f;
+        const float ge = p.grad_entropy != nullptr ? p.grad_entropy[row] : 0.f;
+        a = (gn - ge * (p.entropy[row] - lse)) * p.scale;
+        b = -ge * p.scale;
+        c = gn * p.scale;
+      }
+    }
+  }
+
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+    if (!row_ok) return;
+    float g[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float s = __uint_as_float(acc[j]) * p.scale;
+      g[j] = ex2_approx(fmaf(s, kLog2e, -l2)) * fmaf(b, s, a);
+    }
+    const unsigned rel = static_cast<unsigned>(tgt_local - col);
+    if (rel < 32u) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = (rel == static_cast<unsigned>(j)) ? g[j] - c : g[j];
+    }
+    if (col + 32 > p.n_cols) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = (col + j < p.n_cols) ? g[j] : 0.f;
+    }
+    store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.dz) + static_cast<size_t>(row) * p.ld_dz + col), g,
+                  p.out_fmt);
+  }
+
+  __device__ __forceinline__ void end(const Params&) {}
+};
+
+// =====================================================================================
 // Plain store / accumulate epilogue for the two gradient GEMMs.
 //   acc_in  != null : v += acc_in[row][col]     (fp32 partial from earlier slabs)
 //   acc_out != null : acc_out[row][col] = v     (fp32 partial for later slabs)

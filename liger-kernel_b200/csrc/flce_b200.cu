@@ -1335,6 +1335,189 @@ int flce_b200_jsd_rows(void* student, int64_t ld_student, const void* teacher, i
   return FLCE_OK;
 }
 
+// ------------------------------------------------------------------ scaled cross-entropy on the two sweeps
+static int sce_as_problem(const flce_sce_problem_t* p, flce_problem_t* q) {
+  if (p == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "problem is NULL");
+  if (!(p->temperature > 0.f) || !isfinite(p->temperature))
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "temperature must be finite and > 0");
+  memset(q, 0, sizeof(*q));
+  q->n_rows = p->n_rows;
+  q->hidden = p->hidden;
+  q->vocab = p->vocab;
+  q->vocab_total = p->vocab;
+  q->vocab_offset = 0;
+  q->ld_x = p->ld_x;
+  q->ld_w = p->ld_w;
+  q->dtype = p->dtype;
+  q->reduction = FLCE_NONE;
+  q->ignore_index = p->ignore_index;
+  q->x = p->x;
+  q->w = p->w;
+  q->target = p->target;
+  return check_problem(q);   // shapes, pitches, alignment, dtype: the same rules as the main path
+}
+
+struct ScePlan {
+  int n_tiles;
+  size_t plane;   // bytes of one [n_tiles][n_rows] fp32 plane
+  size_t target_logit_bytes;
+  size_t total;
+};
+static ScePlan sce_forward_plan(const flce_problem_t* q) {
+  ScePlan f;
+  f.n_tiles = static_cast<int>(ceil_div(q->vocab, kBlockN));
+  f.plane = align_up(static_cast<size_t>(f.n_tiles) * q->n_rows * sizeof(float), 256);
+  f.target_logit_bytes = align_up(static_cast<size_t>(q->n_rows) * sizeof(float), 256);
+  f.total = 3 * f.plane + f.target_logit_bytes;
+  return f;
+}
+
+size_t flce_b200_sce_workspace_bytes(const flce_sce_problem_t* p, int phase, size_t slab_budget_bytes) {
+  flce_problem_t q;
+  if (sce_as_problem(p, &q) != FLCE_OK) return 0;
+  if (phase == FLCE_PHASE_FORWARD) return sce_forward_plan(&q).total;
+  if (phase == FLCE_PHASE_BACKWARD) {
+    const BackwardPlan b = backward_plan(&q, slab_budget_bytes, true);
+    return b.slab_bytes + b.acc_bytes;
+  }
+  return 0;
+}
+
+int flce_b200_sce_forward(const flce_sce_problem_t* p, float* nll, float* entropy, float* lse, void* workspace,
+                          size_t workspace_bytes, void* stream_) {
+  flce_problem_t q;
+  int rc = sce_as_problem(p, &q);
+  if (rc != FLCE_OK) return rc;
+  if (nll == nullptr || entropy == nullptr || lse == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "nll, entropy and lse must not be NULL");
+  const ScePlan plan = sce_forward_plan(&q);
+  if (workspace == nullptr || workspace_bytes < plan.total)
+    return fail(FLCE_ERR_WORKSPACE, "scaled cross-entropy forward needs %zu bytes of workspace, got %zu", plan.total,
+                workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  EntropyStatsEpilogue::Params ep;
+  ep.target = reinterpret_cast<const long long*>(p->target);
+  ep.scale = 1.f / p->temperature;
+  ep.n_cols = static_cast<int>(p->vocab);
+  ep.m_rows = static_cast<int>(p->n_rows);
+  ep.pmax = reinterpret_cast<float*>(ws);
+  ep.psum = reinterpret_cast<float*>(ws + plan.plane);
+  ep.pts = reinterpret_cast<float*>(ws + 2 * plan.plane);
+  ep.target_logit = reinterpret_cast<float*>(ws + 3 * plan.plane);
+  FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(p->n_rows) * sizeof(float), stream));
+  Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
+  Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
+  rc = launch_gemm<kMajorK, kMajorK, EntropyStatsEpilogue>(*dev, kKindStats, g_cta_pair != 0, a, b, p->dtype, p->n_rows, p->vocab,
+                                                           p->hidden, static_cast<long long>(kBlockM) * p->hidden * 2, false, ep,
+                                                           stream);
+  if (rc != FLCE_OK) return rc;
+  const int threads = 256;
+  scaled_ce_merge_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+      static_cast<int>(p->n_rows), plan.n_tiles, ep.pmax, ep.psum, ep.pts, ep.target_logit,
+      reinterpret_cast<const long long*>(p->target), p->ignore_index, nll, entropy, lse);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_sce_backward(const flce_sce_problem_t* p, const float* lse, const float* entropy, const float* grad_nll,
+                           const float* grad_entropy, int32_t grad_dtype, void* grad_input, void* grad_weight,
+                           void* workspace, size_t workspace_bytes, size_t slab_budget_bytes, void* stream_) {
+  flce_problem_t q;
+  int rc = sce_as_problem(p, &q);
+  if (rc != FLCE_OK) return rc;
+  if (lse == nullptr || entropy == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "lse and entropy must not be NULL");
+  if (grad_dtype != p->dtype && grad_dtype != FLCE_FP32)
+    return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
+  if (p->hidden % 8 != 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "hidden must be a multiple of 8 (pad the operands)");
+  const bool grads_fp32 = grad_dtype == FLCE_FP32;
+  const BackwardPlan plan = backward_plan(&q, slab_budget_bytes, true);
+  const size_t needed = plan.slab_bytes + ((grad_input != nullptr && !grads_fp32) ? plan.acc_bytes : 0);
+  if (workspace == nullptr || workspace_bytes < needed)
+    return fail(FLCE_ERR_WORKSPACE, "scaled cross-entropy backward needs %zu bytes of workspace, got %zu", needed,
+                workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint16_t* dz = reinterpret_cast<uint16_t*>(ws);
+  float* dx_acc = reinterpret_cast<float*>(ws + plan.slab_bytes);   // unused with fp32 gradients
+  const bool pair = g_cta_pair != 0;
+  const int esize_out = grads_fp32 ? 4 : 2;
+  const int fmt16 = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
+  for (int s = 0; s < plan.n_slabs; ++s) {
+    const long long v0 = static_cast<long long>(s) * plan.slab_cols;
+    const long long cols = (p->vocab - v0 < plan.slab_cols) ? p->vocab - v0 : plan.slab_cols;
+    const uint16_t* w_slab = static_cast<const uint16_t*>(p->w) + v0 * p->ld_w;
+    {  // recompute the logits of this slab -> dZ
+      ScaledDzEpilogue::Params ep;
+      ep.target = reinterpret_cast<const long long*>(p->target);
+      ep.ignore_index = p->ignore_index;
+      ep.scale = 1.f / p->temperature;
+      ep.n_cols = static_cast<int>(cols);
+      ep.vocab_offset = v0;
+      ep.m_rows = static_cast<int>(p->n_rows);
+      ep.lse = lse;
+      ep.entropy = entropy;
+      ep.grad_nll = grad_nll;
+      ep.grad_entropy = grad_entropy;
+      ep.dz = dz;
+      ep.ld_dz = plan.ld_dz;
+      ep.out_fmt = fmt16;
+      Operand a{p->x, p->n_rows, p->hidden, p->ld_x, 0};
+      Operand b{w_slab, cols, p->hidden, p->ld_w, 0};
+      rc = launch_gemm<kMajorK, kMajorK, ScaledDzEpilogue>(*dev, kKindDz, pair, a, b, p->dtype, p->n_rows, cols, p->hidden,
+                                                           static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    if (grad_weight != nullptr) {  // grad_weight[slab] = dZ^T . X   (M = cols, N = hidden, K = n_rows; both MN-major)
+      StoreEpilogue::Params ep;
+      ep.m_rows = static_cast<int>(cols);
+      ep.n_cols = static_cast<int>(p->hidden);
+      ep.acc_in = nullptr;
+      ep.acc_out = nullptr;
+      ep.ld_acc = 0;
+      ep.out = static_cast<uint8_t*>(grad_weight) + static_cast<size_t>(v0) * p->hidden * esize_out;
+      ep.ld_out = p->hidden;
+      ep.out_fmt = grads_fp32 ? kOutFp32 : fmt16;
+      Operand a{dz, cols, p->n_rows, plan.ld_dz, 1};
+      Operand b{p->x, p->hidden, p->n_rows, p->ld_x, 1};
+      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, cols, p->hidden, p->n_rows, 0, true,
+                                                          ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+    if (grad_input != nullptr) {  // grad_input (+)= dZ . W[slab]   (M = n_rows, N = hidden, K = cols; B MN-major)
+      StoreEpilogue::Params ep;
+      ep.m_rows = static_cast<int>(p->n_rows);
+      ep.n_cols = static_cast<int>(p->hidden);
+      const bool first = s == 0, last = s == plan.n_slabs - 1;
+      float* acc = grads_fp32 ? static_cast<float*>(grad_input) : dx_acc;
+      ep.acc_in = first ? nullptr : acc;
+      ep.acc_out = (last && !grads_fp32) ? nullptr : acc;
+      if (plan.n_slabs == 1 && !grads_fp32) ep.acc_out = nullptr;
+      ep.ld_acc = p->hidden;
+      ep.out = (last && !grads_fp32) ? grad_input : nullptr;
+      ep.ld_out = p->hidden;
+      ep.out_fmt = fmt16;
+      Operand a{dz, p->n_rows, cols, plan.ld_dz, 0};
+      Operand b{w_slab, p->hidden, cols, p->ld_w, 1};
+      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, p->n_rows, p->hidden, cols, 0, true,
+                                                         ep, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+  }
+  return FLCE_OK;
+}
+
 int flce_b200_profile_enable(int on) {
   std::lock_guard<std::mutex> lock(g_profile_mutex);
   g_profile_on = on != 0;

@@ -180,6 +180,28 @@ scaled_ce_grad_kernel(T* logits, long long ld, int n_rows, int n_cols, const lon
   }
 }
 
+// per-(row, tile) partials of EntropyStatsEpilogue -> per-row nll, entropy (0 on ignored rows) and lse
+__global__ void scaled_ce_merge_kernel(int m_rows, int n_tiles, const float* pmax, const float* psum, const float* pts,
+                                       const float* target_logit, const long long* target, long long ignore_index, float* nll,
+                                       float* entropy, float* lse_out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= m_rows) return;
+  float m = -INFINITY;
+  for (int i = 0; i < n_tiles; ++i) m = fmaxf(m, pmax[static_cast<size_t>(i) * m_rows + row]);
+  float d = 0.f, t = 0.f;
+  for (int i = 0; i < n_tiles; ++i) {
+    const size_t o = static_cast<size_t>(i) * m_rows + row;
+    const float k = expf(pmax[o] - m);
+    d = fmaf(psum[o], k, d);
+    t = fmaf(pts[o], k, t);
+  }
+  const float lse = m + logf(d);
+  const bool live = target[row] != ignore_index;
+  nll[row] = live ? lse - target_logit[row] : 0.f;
+  entropy[row] = live ? lse - t / d : 0.f;
+  lse_out[row] = lse;
+}
+
 // ---- generalised Jensen-Shannon divergence -----------------------------------------------------------------------
 // X = log Q = s - lse_s, Y = log P = t - lse_t (both at the temperature).  Returns the element's loss term and the
 // derivative with respect to X.  beta == 0: forward KL, beta == 1: reverse KL.

@@ -36,6 +36,9 @@ EXPORTS = (
     "flce_b200_scaled_ce_rows",
     "flce_b200_scaled_ce_grad",
     "flce_b200_jsd_rows",
+    "flce_b200_sce_workspace_bytes",
+    "flce_b200_sce_forward",
+    "flce_b200_sce_backward",
     "flce_b200_check_device_status",
     "flce_b200_profile_enable",
     "flce_b200_profile_read",
@@ -87,6 +90,15 @@ class CeProblem(C.Structure):
         ("dtype", C.c_int32), ("reduction", C.c_int32), ("ignore_index", C.c_int64),
         ("label_smoothing", C.c_float), ("lse_square_scale", C.c_float), ("softcap", C.c_float), ("flags", C.c_int32),
         ("logits", C.c_void_p), ("target", C.c_void_p), ("ce_weight", C.c_void_p),
+    ]
+
+
+class SceProblem(C.Structure):
+    _fields_ = [
+        ("n_rows", C.c_int64), ("hidden", C.c_int64), ("vocab", C.c_int64), ("ld_x", C.c_int64), ("ld_w", C.c_int64),
+        ("dtype", C.c_int32), ("reserved", C.c_int32), ("ignore_index", C.c_int64),
+        ("temperature", C.c_float), ("reserved2", C.c_float),
+        ("x", C.c_void_p), ("w", C.c_void_p), ("target", C.c_void_p),
     ]
 
 
@@ -142,6 +154,13 @@ def _load():
     lib.flce_b200_scaled_ce_grad.restype = C.c_int
     lib.flce_b200_jsd_rows.argtypes = [vp, i64, vp, i64, i32, i64, i64, vp, i64, f32, f32, vp, f32, vp, vp]
     lib.flce_b200_jsd_rows.restype = C.c_int
+    SP = C.POINTER(SceProblem)
+    lib.flce_b200_sce_workspace_bytes.argtypes = [SP, C.c_int, sz]
+    lib.flce_b200_sce_workspace_bytes.restype = sz
+    lib.flce_b200_sce_forward.argtypes = [SP, vp, vp, vp, vp, sz, vp]
+    lib.flce_b200_sce_forward.restype = C.c_int
+    lib.flce_b200_sce_backward.argtypes = [SP, vp, vp, vp, vp, i32, vp, vp, vp, sz, sz, vp]
+    lib.flce_b200_sce_backward.restype = C.c_int
     lib.flce_b200_check_device_status.argtypes = [vp]
     lib.flce_b200_set_option.argtypes = [C.c_char_p, i64]
     lib.flce_b200_profile_enable.argtypes = [C.c_int]

@@ -2,7 +2,12 @@
 keeping the ``[M, V]`` logits (the policy-gradient head of RL fine-tuning), host side.
 
 Call surface of the reference's ``src/liger_kernel/ops/fused_linear_scaled_cross_entropy.py``
-(``LigerFusedLinearScaledCrossEntropyFunction.apply`` ``:163-199``; math of ``:50-93``).  Forward: per token chunk, logits
+(``LigerFusedLinearScaledCrossEntropyFunction.apply`` ``:163-199``; math of ``:50-93``).
+
+Two forms (``MODE``).  ``"fused"`` (16-bit operands, default): the two tensor-core sweeps of the main path with scaled
+cross-entropy epilogues -- sweep 1 keeps max / sum-exp / sum exp*s per (row, tile), nothing of size M x V is written;
+backward recomputes the logits per vocabulary slab, forms the logit gradient in the epilogue and projects it
+(``flce_b200_sce_forward`` / ``flce_b200_sce_backward``).  ``"chunked"`` (and fp32 operands): per token chunk, logits
 by one tcgen05 GEMM into a slab of the operands' dtype and one row kernel (online max / sum-exp / sum of p.s in a single read).
 Backward: the upstream gradients of both outputs arrive per token, so the chunk's logits are recomputed (as the
 reference's device-independent path does), turned into the logit gradient in place, and projected twice
@@ -15,14 +20,24 @@ bf16 term products (see ``_chunked.py``); ``m_tiles_per_cluster`` is accepted an
 
 from __future__ import annotations
 
+import ctypes as C
 import math
+import os
 
 import torch
 
-from .._lib import check
+from .. import _lib
+from .._lib import SceProblem, check
 from . import _chunked as ck
 from . import fused_linear_cross_entropy as _fl
 from .fused_linear_cross_entropy import _DTYPES, _ptr
+
+
+# "fused": 16-bit operands run on the two tensor-core sweeps of the main path with scaled cross-entropy epilogues (no logits
+# slab in forward, vocabulary slabs of the logit gradient in backward); "chunked": the token-chunk loop over a logits slab.
+# fp32 operands always take the chunked form.
+MODE = os.environ.get("LIGER_B200_SCE_MODE", "fused")
+SLAB_BUDGET_BYTES = 1 << 30
 
 
 def _validate_temperature(temperature):
@@ -50,6 +65,67 @@ def _validate_inputs(_input, weight, target):
         raise TypeError("target must be an int64 tensor")
 
 
+def _fused_problem(x, w, target, temperature, ignore_index):
+    p = SceProblem()
+    p.n_rows, p.hidden, p.vocab = x.shape[0], x.shape[1], w.shape[0]
+    p.ld_x, p.ld_w = x.stride(0), w.stride(0)
+    p.dtype = _DTYPES[x.dtype]
+    p.ignore_index = int(ignore_index)
+    p.temperature = float(temperature)
+    p.x, p.w, p.target = x.data_ptr(), w.data_ptr(), target.data_ptr()
+    return p
+
+
+def _workspace(n_bytes, device):
+    return torch.empty(max(int(n_bytes), 256), dtype=torch.uint8, device=device)
+
+
+def _fused_forward(ctx, hidden_states, vocab_weights, input_ids, temperature, ignore_index, return_entropy):
+    dev, dtype = hidden_states.device, hidden_states.dtype
+    lib = ck._lib_handle()
+    x, w = _fl._pad_hidden(hidden_states.detach()), _fl._pad_hidden(vocab_weights.detach())
+    target = input_ids.detach().contiguous()
+    prob = _fused_problem(x, w, target, temperature, ignore_index)
+    n_rows = x.shape[0]
+    nll = torch.empty(n_rows, dtype=torch.float32, device=dev)
+    entropy = torch.empty(n_rows, dtype=torch.float32, device=dev)
+    lse = torch.empty(n_rows, dtype=torch.float32, device=dev)
+    with _fl._device_guard(dev):
+        ws = _workspace(lib.flce_b200_sce_workspace_bytes(C.byref(prob), _lib.PHASE_FORWARD, 0), dev)
+        check(lib.flce_b200_sce_forward(C.byref(prob), _ptr(nll), _ptr(entropy), _ptr(lse), _ptr(ws), ws.numel(), _fl._stream(dev)))
+    ctx.sce = ("fused", x, w, target, lse, entropy, float(temperature), int(ignore_index), hidden_states.shape[1])
+    if return_entropy:
+        return nll, entropy.to(dtype)
+    return nll
+
+
+def _fused_backward(ctx, grad_nll, grad_entropy):
+    _, x, w, target, lse, entropy, temperature, ignore_index, hidden = ctx.sce
+    need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+    dev, dtype = x.device, x.dtype
+    lib = ck._lib_handle()
+    n_rows, h8 = x.shape
+    vocab = w.shape[0]
+    g_nll = None if grad_nll is None else grad_nll.detach().to(device=dev, dtype=torch.float32).contiguous()
+    g_ent = None if grad_entropy is None else grad_entropy.detach().to(device=dev, dtype=torch.float32).contiguous()
+    grad_x = torch.empty((n_rows, h8), dtype=dtype, device=dev) if need_x else None
+    grad_w = torch.empty((vocab, h8), dtype=dtype, device=dev) if need_w else None
+    if (need_x or need_w) and not (g_nll is None and g_ent is None):
+        prob = _fused_problem(x, w, target, temperature, ignore_index)
+        with _fl._device_guard(dev):
+            ws = _workspace(lib.flce_b200_sce_workspace_bytes(C.byref(prob), _lib.PHASE_BACKWARD, SLAB_BUDGET_BYTES), dev)
+            check(lib.flce_b200_sce_backward(C.byref(prob), _ptr(lse), _ptr(entropy), _ptr(g_nll), _ptr(g_ent), _DTYPES[dtype],
+                                             _ptr(grad_x), _ptr(grad_w), _ptr(ws), ws.numel(), SLAB_BUDGET_BYTES, _fl._stream(dev)))
+    else:
+        for g in (grad_x, grad_w):
+            if g is not None:
+                g.zero_()
+    if h8 != hidden:
+        grad_x = None if grad_x is None else grad_x[:, :hidden].contiguous()
+        grad_w = None if grad_w is None else grad_w[:, :hidden].contiguous()
+    return grad_x, grad_w, None, None, None, None
+
+
 class _ScaledCrossEntropy(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden_states, vocab_weights, input_ids, temperature, ignore_index, return_entropy):
@@ -57,6 +133,8 @@ class _ScaledCrossEntropy(torch.autograd.Function):
         _validate_inputs(hidden_states, vocab_weights, input_ids)
         _validate_temperature(temperature)
         _fl._require_cuda(hidden_states)
+        if MODE == "fused" and hidden_states.dtype in (torch.bfloat16, torch.float16):
+            return _fused_forward(ctx, hidden_states, vocab_weights, input_ids, temperature, ignore_index, return_entropy)
         dev, dtype = hidden_states.device, hidden_states.dtype
         lib = ck._lib_handle()
         need_grads = any(ctx.needs_input_grad[:2])
@@ -84,6 +162,8 @@ class _ScaledCrossEntropy(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_nll, grad_entropy=None):
+        if ctx.sce[0] == "fused":
+            return _fused_backward(ctx, grad_nll, grad_entropy)
         head, target, lse, entropy, temperature, ignore_index, chunk_rows = ctx.sce
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         dev, dtype = head.device, head.dtype

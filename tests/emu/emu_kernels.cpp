@@ -504,4 +504,50 @@ int emu_finalize(long long n_rows, long long ignore_index, float alpha, float la
   return 0;
 }
 
+// scaled cross-entropy on the two sweeps: EntropyStatsEpilogue + scaled_ce_merge_kernel (flce_b200_sce_forward) ...
+int emu_sce_forward(const void* x, const void* w, int dtype, int m, int vocab, int k, long long ld_x, long long ld_w,
+                    const long long* target, long long ignore_index, float temperature, float* planes, float* target_logit,
+                    float* nll, float* entropy, float* lse) {
+  const int n_tiles = static_cast<int>(ceil_div(vocab, kBlockN));
+  const size_t plane = static_cast<size_t>(n_tiles) * m;
+  EntropyStatsEpilogue::Params ep;
+  ep.target = target;
+  ep.scale = 1.f / temperature;
+  ep.n_cols = vocab;
+  ep.m_rows = m;
+  ep.pmax = planes;
+  ep.psum = planes + plane;
+  ep.pts = planes + 2 * plane;
+  ep.target_logit = target_logit;
+  run_tiles<EntropyStatsEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w);
+  const int threads = 256;
+  emu::launch_serial(static_cast<unsigned>(ceil_div(m, threads)), threads, [&]() {
+    scaled_ce_merge_kernel(m, n_tiles, ep.pmax, ep.psum, ep.pts, target_logit, target, ignore_index, nll, entropy, lse);
+  });
+  return 0;
+}
+
+// ... and ScaledDzEpilogue over one vocabulary slab (the logit-gradient step of flce_b200_sce_backward); w points at the
+// slab's first row, vocab_offset is that row's class id
+int emu_sce_sweep_dz(const void* x, const void* w, int dtype, int m, int cols, int k, long long ld_x, long long ld_w,
+                     const long long* target, long long ignore_index, float temperature, long long vocab_offset, const float* lse,
+                     const float* entropy, const float* g_nll, const float* g_ent, void* dz, long long ld_dz, int out_fmt) {
+  ScaledDzEpilogue::Params ep;
+  ep.target = target;
+  ep.ignore_index = ignore_index;
+  ep.scale = 1.f / temperature;
+  ep.n_cols = cols;
+  ep.vocab_offset = vocab_offset;
+  ep.m_rows = m;
+  ep.lse = lse;
+  ep.entropy = entropy;
+  ep.grad_nll = g_nll;
+  ep.grad_entropy = g_ent;
+  ep.dz = dz;
+  ep.ld_dz = ld_dz;
+  ep.out_fmt = out_fmt;
+  run_tiles<ScaledDzEpilogue>(ep, x, w, dtype, m, cols, k, ld_x, ld_w);
+  return 0;
+}
+
 }  // extern "C"

@@ -62,6 +62,8 @@ def load():
         "emu_scaled_ce_grad": [P, LL, I, LL, LL, P, LL, F, P, P, P, P],
         "emu_jsd_rows": [P, LL, P, LL, I, LL, LL, P, LL, F, F, P, F, P],
         "emu_tile_schedule": [I, I, I, I, I, P, P],
+        "emu_sce_forward": [P, P, I, I, I, I, LL, LL, P, LL, F, P, P, P, P, P],
+        "emu_sce_sweep_dz": [P, P, I, I, I, I, LL, LL, P, LL, F, LL, P, P, P, P, P, LL, I],
         "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I],
         "emu_sweep_dz": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, LL, I],
         "emu_gemm_store": [P, P, I, I, I, I, LL, LL, P, LL, P, LL, I],
@@ -147,6 +149,55 @@ class EmuLib(fake_lib.FakeLib):
         self.calls.append("flce_b200_jsd_rows")
         return self.emu.emu_jsd_rows(_addr(student), ld_s, _addr(teacher), ld_t, dtype, n_rows, vocab, _addr(labels) or None, ignore_index,
                                      beta, temperature, _addr(count) or None, fixed_count, _addr(loss_rows))
+
+    # ---- scaled cross-entropy on the two sweeps: the library's epilogues tile by tile, its slab loop restated here
+    SCE_SLAB_COLS = 256          # small slabs so that the slab offsets are exercised
+
+    def flce_b200_sce_workspace_bytes(self, p, phase, budget):
+        self.calls.append("flce_b200_sce_workspace_bytes")
+        prob = p._obj
+        n_tiles = (prob.vocab + 255) // 256
+        return 4 * (3 * n_tiles * prob.n_rows + prob.n_rows) + 1024
+
+    def flce_b200_sce_forward(self, p, nll, entropy, lse, ws, ws_bytes, stream):
+        self.calls.append("flce_b200_sce_forward")
+        prob = p._obj
+        n_tiles = (prob.vocab + 255) // 256
+        planes = torch.zeros(3 * n_tiles * prob.n_rows)
+        target_logit = torch.zeros(prob.n_rows)
+        return self.emu.emu_sce_forward(prob.x, prob.w, prob.dtype, prob.n_rows, prob.vocab, prob.hidden, prob.ld_x, prob.ld_w,
+                                        prob.target, prob.ignore_index, prob.temperature, planes.data_ptr(), target_logit.data_ptr(),
+                                        _addr(nll), _addr(entropy), _addr(lse))
+
+    def flce_b200_sce_backward(self, p, lse, entropy, g_nll, g_ent, grad_dtype, grad_input, grad_weight, ws, ws_bytes, budget, stream):
+        self.calls.append("flce_b200_sce_backward")
+        prob = p._obj
+        tdt = {0: torch.bfloat16, 1: torch.float16}[prob.dtype]
+        gdt = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}[grad_dtype]
+        m, h, v = prob.n_rows, prob.hidden, prob.vocab
+
+        def matrix(addr, rows, cols, ld, dt):
+            n_el = (rows - 1) * ld + cols
+            buf = (C.c_char * (n_el * dt.itemsize)).from_address(addr)
+            return torch.as_strided(torch.frombuffer(buf, dtype=dt, count=n_el), (rows, cols), (ld, 1))
+
+        x = matrix(prob.x, m, h, prob.ld_x, tdt).float()
+        w = matrix(prob.w, v, h, prob.ld_w, tdt)
+        gx = torch.zeros(m, h)
+        for v0 in range(0, v, self.SCE_SLAB_COLS):
+            cols = min(self.SCE_SLAB_COLS, v - v0)
+            dz = torch.zeros((m, self.SCE_SLAB_COLS), dtype=tdt)
+            w_slab = w[v0:v0 + cols]
+            self.emu.emu_sce_sweep_dz(prob.x, w_slab.data_ptr(), prob.dtype, m, cols, h, prob.ld_x, prob.ld_w, prob.target,
+                                      prob.ignore_index, prob.temperature, v0, _addr(lse), _addr(entropy), _addr(g_nll) or None,
+                                      _addr(g_ent) or None, dz.data_ptr(), self.SCE_SLAB_COLS, prob.dtype)
+            dzf = dz[:, :cols].float()
+            if _addr(grad_weight):
+                matrix(_addr(grad_weight), v, h, h, gdt)[v0:v0 + cols] = (dzf.T @ x).to(gdt)
+            gx += dzf @ w_slab.float()
+        if _addr(grad_input):
+            matrix(_addr(grad_input), m, h, h, gdt).copy_(gx.to(gdt))
+        return 0
 
     def flce_b200_gemm_accumulate(self, a, b, acc, out, m, n, k, ld_a, ld_b, ld_acc, ld_out, ab_dtype, out_dtype, a_mn_major,
                                   b_mn_major, cta_pair, stream):

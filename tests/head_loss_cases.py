@@ -6,6 +6,8 @@ Tolerances follow the reference's tests (test/transformers/test_fused_linear_jsd
 atol 5e-3 / rtol 5e-2 ... ; test_fused_linear_scaled_cross_entropy.py: fp32 6e-5 / 6e-5, bf16 8e-2 / 5e-2), tightened
 where the fp64 oracle on the same rounded inputs allows it."""
 
+import contextlib
+
 import numpy as np
 import torch
 
@@ -128,6 +130,19 @@ def case_jsd_weight_without_grad_and_second_backward(device):
 
 
 # ---------------------------------------------------------------- fused linear scaled cross-entropy
+@contextlib.contextmanager
+def sce_mode(mode):
+    """Run the operator in its "fused" (epilogues on the two sweeps) or "chunked" (token chunks over a logits slab) form."""
+    import liger_kernel_b200.ops.fused_linear_scaled_cross_entropy as mod
+
+    before = mod.MODE
+    mod.MODE = mode
+    try:
+        yield
+    finally:
+        mod.MODE = before
+
+
 def run_sce(device, x, w, t, temperature, g_nll=None, g_ent=None, ignore_index=-100, return_entropy=True):
     import liger_kernel_b200 as lk
 
@@ -170,11 +185,12 @@ def sce_inputs(N, H, V, dtype, ignored=0.1, seed=0):
     return x, w, t, torch.randn(N, generator=g), torch.randn(N, generator=g)
 
 
-def case_sce_correctness(device, N, H, V, dtype, temperature, grads="both"):
+def case_sce_correctness(device, N, H, V, dtype, temperature, grads="both", mode="fused"):
     x, w, t, g_nll, g_ent = sce_inputs(N, H, V, dtype, seed=N + V)
     g_nll = g_nll if grads in ("both", "nll") else None
     g_ent = g_ent if grads in ("both", "entropy") else None
-    res = run_sce(device, x, w, t, temperature, g_nll, g_ent)
+    with sce_mode(mode):
+        res = run_sce(device, x, w, t, temperature, g_nll, g_ent)
     low = None if dtype == torch.float32 else dtype
     ora = fused_linear_scaled_ce_oracle(x, w, t, temperature, -100, g_nll, g_ent, round_logits_to=low, round_dlogits_to=low)
     check_sce(res, ora, dtype)
@@ -184,13 +200,14 @@ def case_sce_correctness(device, N, H, V, dtype, temperature, grads="both"):
         assert float(res["grad_input"][ignored].abs().max()) == 0.0
 
 
-def case_sce_golden(device, name):
+def case_sce_golden(device, name, mode="fused"):
     rec, meta = load_golden(name)
     dtype = getattr(torch, meta.get("dtype", "float32"))
     x, w, t = torch.from_numpy(rec["x"]).to(dtype), torch.from_numpy(rec["w"]).to(dtype), torch.from_numpy(rec["target"])
     g_nll = torch.from_numpy(rec["grad_nll"]) if meta["grads"] in ("both", "nll") else None
     g_ent = torch.from_numpy(rec["grad_entropy"]) if meta["grads"] in ("both", "entropy") else None
-    res = run_sce(device, x, w, t, meta["temperature"], g_nll, g_ent)
+    with sce_mode(mode):
+        res = run_sce(device, x, w, t, meta["temperature"], g_nll, g_ent)
     l_atol, l_rtol, g_atol, g_rtol = _tols(dtype)
     low = dtype != torch.float32
     assert_close(res["nll"], torch.from_numpy(rec["ref_nll"]), 4e-2 if low else 8e-5, l_rtol, "nll vs reference")

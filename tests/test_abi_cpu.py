@@ -34,6 +34,7 @@ def test_struct_sizes_match_header_layout():
     # 7 int64 + 2 int32 + int64 + 3 float + 2 int32 (+pad) + 5 pointers
     assert C.sizeof(_lib.Problem) == 7 * 8 + 8 + 8 + 12 + 8 + 4 + 6 * 8
     assert C.sizeof(_lib.ForwardOut) == 7 * 8
+    assert C.sizeof(_lib.SceProblem) == 5 * 8 + 8 + 8 + 8 + 3 * 8
     assert C.sizeof(_lib.BackwardArgs) == 4 * 8 + 8 + 3 * 8 + 8 + 6 * 8 + 8 + 2 * 8
 
 

@@ -66,16 +66,30 @@ SCE_GRID = [
 ]
 
 
+@pytest.mark.parametrize("mode", ["fused", "chunked"])
 @pytest.mark.parametrize("N,H,V,dtype,temperature,grads", SCE_GRID)
-def test_scaled_ce_correctness(monkeypatch, N, H, V, dtype, temperature, grads):
-    with emu_lib.installed(monkeypatch):
-        cases.case_sce_correctness("cpu", N, H, V, dtype, temperature, grads)
+def test_scaled_ce_correctness(monkeypatch, N, H, V, dtype, temperature, grads, mode):
+    if mode == "fused" and dtype == torch.float32:
+        pytest.skip("fp32 operands always take the chunked form")
+    with emu_lib.installed(monkeypatch) as lib:
+        cases.case_sce_correctness("cpu", N, H, V, dtype, temperature, grads, mode=mode)
+        assert ("flce_b200_sce_forward" in lib.calls) == (mode == "fused")
+        assert ("flce_b200_scaled_ce_rows" in lib.calls) == (mode == "chunked")
 
 
+@pytest.mark.parametrize("mode", ["fused", "chunked"])
 @pytest.mark.parametrize("name", sce_golden_names())
-def test_scaled_ce_against_reference_golden(monkeypatch, name):
+def test_scaled_ce_against_reference_golden(monkeypatch, name, mode):
     with emu_lib.installed(monkeypatch):
-        cases.case_sce_golden("cpu", name)
+        cases.case_sce_golden("cpu", name, mode=mode)
+
+
+def test_scaled_ce_fused_slabs_and_hidden_padding(monkeypatch):
+    """Fused form with a vocabulary that spans several gradient slabs (the stand-in library cuts slabs of 256 classes) and a
+    hidden size that needs zero-padding to a multiple of 8; targets in the first, a middle and the last slab."""
+    with emu_lib.installed(monkeypatch) as lib:
+        cases.case_sce_correctness("cpu", 37, 31, 700, torch.bfloat16, 1.3, "both", mode="fused")
+        assert lib.calls.count("flce_b200_sce_backward") == 1
 
 
 def test_scaled_ce_multichunk_single_output_and_errors(monkeypatch):
@@ -83,7 +97,7 @@ def test_scaled_ce_multichunk_single_output_and_errors(monkeypatch):
 
     with emu_lib.installed(monkeypatch) as lib:
         monkeypatch.setattr(ck, "SLAB_BUDGET_BYTES", 256 * ck.slab_pitch(67) * 2)          # 256 rows per chunk
-        cases.case_sce_correctness("cpu", 530, 16, 67, torch.bfloat16, 1.25, "both")
+        cases.case_sce_correctness("cpu", 530, 16, 67, torch.bfloat16, 1.25, "both", mode="chunked")
         assert lib.calls.count("flce_b200_scaled_ce_rows") == 3 and lib.calls.count("flce_b200_scaled_ce_grad") == 3
         cases.case_sce_nll_only_output_and_no_grad("cpu")
         cases.case_sce_argument_errors("cpu")

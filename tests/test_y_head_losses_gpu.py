@@ -46,19 +46,31 @@ def test_jsd_weight_without_grad_and_second_backward():
 @pytest.mark.parametrize("N,H,V,dtype", [(17, 31, 257, torch.float32), (1025, 64, 131072, torch.bfloat16), (512, 256, 4096, torch.float16),
                                          (300, 128, 32001, torch.float32)])
 @pytest.mark.parametrize("temperature,grads", [(1.0, "both"), (1.5, "nll"), (0.7, "entropy")])
-def test_scaled_ce_correctness(N, H, V, dtype, temperature, grads):
-    cases.case_sce_correctness("cuda", N, H, V, dtype, temperature, grads)
+@pytest.mark.parametrize("mode", ["fused", "chunked"])
+def test_scaled_ce_correctness(N, H, V, dtype, temperature, grads, mode):
+    if mode == "fused" and dtype == torch.float32:
+        pytest.skip("fp32 operands always take the chunked form")
+    cases.case_sce_correctness("cuda", N, H, V, dtype, temperature, grads, mode=mode)
 
 
+@pytest.mark.parametrize("mode", ["fused", "chunked"])
 @pytest.mark.parametrize("name", sce_golden_names())
-def test_scaled_ce_against_reference_golden(name):
-    cases.case_sce_golden("cuda", name)
+def test_scaled_ce_against_reference_golden(name, mode):
+    cases.case_sce_golden("cuda", name, mode=mode)
+
+
+def test_scaled_ce_fused_several_gradient_slabs(monkeypatch):
+    """A slab budget that cuts the vocabulary into several logit-gradient slabs (fp32 accumulation of grad_input across them)."""
+    import liger_kernel_b200.ops.fused_linear_scaled_cross_entropy as mod
+
+    monkeypatch.setattr(mod, "SLAB_BUDGET_BYTES", 300 * 512 * 2)            # 512 classes per slab for 300 rows
+    cases.case_sce_correctness("cuda", 300, 72, 2000, torch.bfloat16, 1.3, "both", mode="fused")
 
 
 def test_scaled_ce_multichunk_single_output_and_errors(monkeypatch):
     import liger_kernel_b200.ops._chunked as ck
 
     monkeypatch.setattr(ck, "SLAB_BUDGET_BYTES", 256 * ck.slab_pitch(67) * 2)          # 256 rows per chunk
-    cases.case_sce_correctness("cuda", 600, 16, 67, torch.bfloat16, 1.25, "both")
+    cases.case_sce_correctness("cuda", 600, 16, 67, torch.bfloat16, 1.25, "both", mode="chunked")
     cases.case_sce_nll_only_output_and_no_grad("cuda")
     cases.case_sce_argument_errors("cuda")
