@@ -165,8 +165,10 @@ float load16(const void* base, long long index, int dtype) {
 
 template <class Epi>
 void run_tiles(const typename Epi::Params& ep, const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a,
-               long long ld_b) {
-  const int m_tiles = static_cast<int>(ceil_div(m, kBlockM)), n_tiles = static_cast<int>(ceil_div(n, kBlockN));
+               long long ld_b, int m_tile_limit = -1) {
+  int m_tiles = static_cast<int>(ceil_div(m, kBlockM));
+  if (m_tile_limit >= 0) m_tiles = std::min(m_tiles, m_tile_limit);   // tiles a device-resident active-row count leaves
+  const int n_tiles = static_cast<int>(ceil_div(n, kBlockN));
   std::vector<float> arow(k);
   for (int mt = 0; mt < m_tiles; ++mt)
     for (int r = 0; r < kBlockM; ++r) {
@@ -391,7 +393,7 @@ int emu_limit_to_active_rows(int m_tiles, int k_blocks, int role, int active_row
 int emu_sweep_stats(const void* x, const void* w, int dtype, int m, int vocab, int k, long long ld_x, long long ld_w,
                     const long long* target, const float* bias, const float* col_weight, float softcap, long long vocab_offset,
                     float* pmax, float* psum, float* plogit_sum, float* pamax_val, int* pamax_idx, float* target_logit,
-                    void* logits_out, long long ld_logits, int logits_fmt) {
+                    void* logits_out, long long ld_logits, int logits_fmt, int m_tile_limit) {
   StatsEpilogue::Params ep;
   ep.target = target;
   ep.bias = bias;
@@ -410,7 +412,7 @@ int emu_sweep_stats(const void* x, const void* w, int dtype, int m, int vocab, i
   ep.logits_out = logits_out;
   ep.ld_logits = ld_logits;
   ep.logits_fmt = logits_fmt;
-  run_tiles<StatsEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w);
+  run_tiles<StatsEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w, m_tile_limit);
   return 0;
 }
 
@@ -418,7 +420,7 @@ int emu_sweep_stats(const void* x, const void* w, int dtype, int m, int vocab, i
 int emu_sweep_dz(const void* x, const void* w, int dtype, int m, int vocab, int k, long long ld_x, long long ld_w,
                  const long long* target, const float* bias, const float* col_weight, float softcap, long long vocab_offset,
                  const float* lse, const float* c1, const float* c2, const float* c3, void* dz, void* dz_lo, long long ld_dz,
-                 int out_fmt) {
+                 int out_fmt, int m_tile_limit) {
   DzEpilogue::Params ep;
   ep.target = target;
   ep.bias = bias;
@@ -436,7 +438,7 @@ int emu_sweep_dz(const void* x, const void* w, int dtype, int m, int vocab, int 
   ep.dz_lo = dz_lo;
   ep.ld_dz = ld_dz;
   ep.out_fmt = out_fmt;
-  run_tiles<DzEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w);
+  run_tiles<DzEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w, m_tile_limit);
   return 0;
 }
 

@@ -64,8 +64,8 @@ def load():
         "emu_tile_schedule": [I, I, I, I, I, P, P],
         "emu_sce_forward": [P, P, I, I, I, I, LL, LL, P, LL, F, P, P, P, P, P],
         "emu_sce_sweep_dz": [P, P, I, I, I, I, LL, LL, P, LL, F, LL, P, P, P, P, P, LL, I],
-        "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I],
-        "emu_sweep_dz": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, LL, I],
+        "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I, I],
+        "emu_sweep_dz": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, LL, I, I],
         "emu_gemm_store": [P, P, I, I, I, I, LL, LL, P, LL, P, LL, I],
         "emu_coef": [LL, LL, F, F, I, I, LL, LL, LL, P, P, P, P, P, P, I, P, P, P],
         "emu_finalize": [LL, LL, F, F, I, I, LL, LL, LL, P, P, P, P, P, P, P, P, P, P, P],
@@ -149,6 +149,124 @@ class EmuLib(fake_lib.FakeLib):
         self.calls.append("flce_b200_jsd_rows")
         return self.emu.emu_jsd_rows(_addr(student), ld_s, _addr(teacher), ld_t, dtype, n_rows, vocab, _addr(labels) or None, ignore_index,
                                      beta, temperature, _addr(count) or None, fixed_count, _addr(loss_rows))
+
+    # ---- the fused linear cross-entropy entry points: the library's epilogues and row kernels, its host sequence restated
+    PAIR_ROWS = 256              # rows a CTA pair owns: granularity of the active-row limit on m-tiles
+
+    @staticmethod
+    def _matrix(addr, rows, cols, ld, dt):
+        n_el = (rows - 1) * ld + cols
+        buf = (C.c_char * (n_el * dt.itemsize)).from_address(addr)
+        return torch.as_strided(torch.frombuffer(buf, dtype=dt, count=n_el), (rows, cols), (ld, 1))
+
+    def _m_tile_limit(self, prob):
+        if not prob.active_rows:
+            return -1, prob.n_rows
+        active = int(fake_lib._array(prob.active_rows, C.c_int32, 1)[0])
+        pairs = (max(active, 0) + self.PAIR_ROWS - 1) // self.PAIR_ROWS
+        return pairs * (self.PAIR_ROWS // 128), min(prob.n_rows, pairs * self.PAIR_ROWS)
+
+    def flce_b200_forward_stats(self, p, rowstats, ws, ws_bytes, stream):
+        self.calls.append("flce_b200_forward_stats")
+        prob = p._obj
+        self.structs.setdefault("flce_b200_forward_stats", []).append(prob)
+        n, v = prob.n_rows, prob.vocab
+        n_tiles = (v + 255) // 256
+        nan = float("nan")                      # what the sweeps do not write stays poisoned, like real scratch memory
+        planes = [torch.full((n_tiles, n), nan) for _ in range(4)]
+        pidx = torch.zeros((n_tiles, n), dtype=torch.int32)
+        fake_lib.float_array(_addr(rowstats) + 2 * n * 4, n)[:] = 0.0            # target-logit plane: the library memsets it
+        limit, _ = self._m_tile_limit(prob)
+        cap = float(prob.softcap)
+        rc = self.emu.emu_sweep_stats(prob.x, prob.w, prob.dtype, n, v, prob.hidden, prob.ld_x, prob.ld_w, prob.target, prob.bias,
+                                      prob.ce_weight, cap, prob.vocab_offset, planes[0].data_ptr(), planes[1].data_ptr(),
+                                      planes[2].data_ptr(), planes[3].data_ptr(), pidx.data_ptr(), _addr(rowstats) + 2 * n * 4,
+                                      None, 0, 0, limit)
+        self.emu.emu_merge_partials(n, n_tiles, planes[0].data_ptr(), planes[1].data_ptr(), planes[2].data_ptr(),
+                                    planes[3].data_ptr(), pidx.data_ptr(), _addr(rowstats))
+        return rc
+
+    def flce_b200_forward_finalize(self, p, rowstats, norm, out, stream):
+        self.calls.append("flce_b200_forward_finalize")
+        prob, fo = p._obj, out._obj
+        return self.emu.emu_finalize(prob.n_rows, prob.ignore_index, prob.label_smoothing, prob.lse_square_scale,
+                                     int(prob.reduction == 0), prob.use_token_scaling, prob.vocab, prob.vocab_total, prob.vocab_offset,
+                                     prob.target, prob.ce_weight, _addr(rowstats), _addr(norm), fo.lse, fo.target_prob, fo.loss_rows,
+                                     fo.z_loss_rows, fo.correct_rows, fo.predicted_tokens, fo.scalars)
+
+    def flce_b200_forward(self, p, norm, rowstats, out, ws, ws_bytes, stream):
+        rc = self.flce_b200_count(p, norm, stream) or self.flce_b200_forward_stats(p, rowstats, ws, ws_bytes, stream) \
+            or self.flce_b200_forward_finalize(p, rowstats, norm, out, stream)
+        del self.calls[-3:]
+        self.calls.append("flce_b200_forward")
+        self.structs.setdefault("flce_b200_forward", []).append(p._obj)
+        return rc
+
+    def _backward_slabs(self, prob, budget):
+        budget = budget or (1 << 30)
+        max_cols = max(256, budget // (prob.n_rows * 2) // 256 * 256)
+        n_slabs = (prob.vocab + max_cols - 1) // max_cols
+        slab_cols = ((prob.vocab + n_slabs - 1) // n_slabs + 255) // 256 * 256
+        return (prob.vocab + slab_cols - 1) // slab_cols, slab_cols
+
+    def flce_b200_backward_plan(self, p, budget, n_slabs, slab_cols):
+        self.calls.append("flce_b200_backward_plan")
+        n_slabs._obj.value, slab_cols._obj.value = self._backward_slabs(p._obj, budget)
+        return 0
+
+    def flce_b200_backward(self, p, args, ws, ws_bytes, budget, stream):
+        self.calls.append("flce_b200_backward")
+        prob, a = p._obj, args._obj
+        self.structs.setdefault("flce_b200_backward", []).append(a)
+        tdt = {0: torch.bfloat16, 1: torch.float16}[prob.dtype]
+        gdt = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}[a.grad_dtype]
+        n, h, v = prob.n_rows, prob.hidden, prob.vocab
+        px, px_cols, ld_px = (a.proj_x, a.proj_x_cols, a.ld_proj_x) if a.proj_x else (prob.x, h, prob.ld_x)
+        pw, pw_cols, ld_pw = (a.proj_w, a.proj_w_cols, a.ld_proj_w) if a.proj_w else (prob.w, h, prob.ld_w)
+        split = bool(a.split_logit_grad)
+        PX = self._matrix(px, n, px_cols, ld_px, tdt).float()
+        PW = self._matrix(pw, v, pw_cols, ld_pw, tdt).float()
+        c = torch.zeros(3, n)
+        self.emu.emu_coef(n, prob.ignore_index, prob.label_smoothing, prob.lse_square_scale, int(prob.reduction == 0),
+                          prob.use_token_scaling, v, prob.vocab_total, prob.vocab_offset, prob.target, prob.ce_weight, a.lse,
+                          a.target_prob, a.norm, a.grad_output, a.grad_output_per_row, c[0].data_ptr(), c[1].data_ptr(),
+                          c[2].data_ptr())
+        n_slabs, slab_cols = self._backward_slabs(prob, budget)
+        first, last = (a.slab_begin, a.slab_end) if (a.slab_begin or a.slab_end) else (0, n_slabs)
+        limit, row_limit = self._m_tile_limit(prob)
+        k_rows = n
+        if prob.active_rows:
+            active = int(fake_lib._array(prob.active_rows, C.c_int32, 1)[0])
+            k_rows = min(n, (max(active, 0) + 63) // 64 * 64)
+        acc = self.__dict__.setdefault("_dx_acc", {})
+        for s_i in range(first, last):
+            v0 = s_i * slab_cols
+            cols = min(slab_cols, v - v0)
+            dz = torch.full((n, slab_cols), float("nan")).to(tdt)      # rows no tile covers stay poisoned
+            dz_lo = torch.full((n, slab_cols), float("nan")).to(tdt) if split else None
+            self.emu.emu_sweep_dz(prob.x, prob.w + v0 * prob.ld_w * 2, prob.dtype, n, cols, h, prob.ld_x, prob.ld_w, prob.target,
+                                  prob.bias + v0 * 4 if prob.bias else None, prob.ce_weight + v0 * 4 if prob.ce_weight else None,
+                                  float(prob.softcap), prob.vocab_offset + v0, a.lse, c[0].data_ptr(), c[1].data_ptr(),
+                                  c[2].data_ptr(), dz.data_ptr(), None if dz_lo is None else dz_lo.data_ptr(), slab_cols, prob.dtype,
+                                  limit)
+            dzf = dz[:, :cols].float()
+            lof = None if dz_lo is None else dz_lo[:, :cols].float()
+            if a.grad_weight:
+                gw = dzf[:k_rows].T @ PX[:k_rows]
+                if split:
+                    gw[:, :a.lo_cols_x] += lof[:k_rows].T @ PX[:k_rows, :a.lo_cols_x]
+                self._matrix(a.grad_weight, v, px_cols, px_cols, gdt)[v0:v0 + cols] = gw.to(gdt)
+            if a.grad_input:
+                part = dzf[:row_limit] @ PW[v0:v0 + cols]
+                if split:
+                    part[:, :a.lo_cols_w] += lof[:row_limit] @ PW[v0:v0 + cols, :a.lo_cols_w]
+                acc[a.grad_input] = part if s_i == 0 else acc[a.grad_input] + part
+                if s_i == n_slabs - 1:
+                    self._matrix(a.grad_input, n, pw_cols, pw_cols, gdt)[:row_limit] = acc.pop(a.grad_input).to(gdt)
+            if a.grad_bias:
+                gb = dzf[:k_rows].sum(0) + (0 if lof is None else lof[:k_rows].sum(0))
+                fake_lib.float_array(a.grad_bias + v0 * 4, cols)[:] = gb.numpy()
+        return 0
 
     # ---- scaled cross-entropy on the two sweeps: the library's epilogues tile by tile, its slab loop restated here
     SCE_SLAB_COLS = 256          # small slabs so that the slab offsets are exercised

@@ -19,16 +19,22 @@ def make_inputs(N, H, V, dtype, seed=0, ignore_frac=0.1, ignore_index=-100, wsca
     return x, w, t, b, cw
 
 
+# Where run_cuda puts its tensors.  The CPU suite switches this to "cpu" while the library handle is replaced by the
+# kernel emulation (tests/emu_lib.py), so that the same test bodies run without a GPU.
+DEVICE = "cuda"
+
+
 def run_cuda(x, w, t, bias=None, ce_weight=None, grad_output=None, want_grads=True, **kw):
     """Public-API call on the GPU; returns a dict of CPU tensors."""
     from liger_kernel_b200.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Fn
 
-    xd = x.cuda().requires_grad_(want_grads)
-    wd = w.cuda().requires_grad_(want_grads)
-    bd = None if bias is None else bias.cuda().requires_grad_(want_grads)
-    cwd = None if ce_weight is None else ce_weight.cuda()
+    dev = DEVICE
+    xd = x.to(dev).clone().requires_grad_(want_grads)
+    wd = w.to(dev).clone().requires_grad_(want_grads)
+    bd = None if bias is None else bias.to(dev).clone().requires_grad_(want_grads)
+    cwd = None if ce_weight is None else ce_weight.to(dev)
     loss, z, acc, pred = Fn.apply(
-        xd, wd, t.cuda(), bd, cwd, kw.get("ignore_index", -100), kw.get("lse_square_scale", 0.0),
+        xd, wd, t.to(dev), bd, cwd, kw.get("ignore_index", -100), kw.get("lse_square_scale", 0.0),
         kw.get("label_smoothing", 0.0), kw.get("reduction", "mean"), kw.get("softcap"), True, None,
         kw.get("use_token_scaling", False), True, True,
     )
@@ -38,7 +44,7 @@ def run_cuda(x, w, t, bias=None, ce_weight=None, grad_output=None, want_grads=Tr
         if grad_output is None:
             go = torch.ones_like(loss)
         else:
-            go = torch.as_tensor(grad_output, dtype=loss.dtype).cuda().expand_as(loss).contiguous()
+            go = torch.as_tensor(grad_output, dtype=loss.dtype).to(dev).expand_as(loss).contiguous()
         loss.backward(go)
         out["grad_input"] = xd.grad.cpu()
         out["grad_weight"] = wd.grad.cpu()

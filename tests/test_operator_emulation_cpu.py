@@ -1,0 +1,111 @@
+"""The fused linear cross-entropy operator end to end on CPU tensors: the Python host layer runs unchanged (argument
+checks, hidden-size padding, fp32 term splits, dtype conventions, autograd wiring, row compaction for ignored tokens,
+the sharded operators' single-process path), and behind the C ABI the library's own epilogues and row kernels run on the
+host with the tcgen05 main loop replaced by a float dot product (tests/emu_lib.py).  Several bodies are the GPU tests'
+own (tests/test_flce_gpu.py), called here with tests/flce_cases.DEVICE switched to "cpu"."""
+
+import numpy as np
+import pytest
+import torch
+
+import emu_lib
+import flce_cases
+import test_flce_gpu as gpu_tests
+from flce_cases import assert_close, make_inputs, oracle_for, run_cuda
+from golden_util import golden_names
+
+
+@pytest.fixture
+def emulated(monkeypatch):
+    monkeypatch.setattr(flce_cases, "DEVICE", "cpu")
+    with emu_lib.installed(monkeypatch) as lib:
+        yield lib
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("feat", range(len(gpu_tests.FEATURES)))
+def test_correctness_16bit(emulated, dtype, reduction, bias, feat):
+    gpu_tests.test_correctness(4, 47, 31, 123, dtype, reduction, bias, gpu_tests.FEATURES[feat])
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("feat", range(len(gpu_tests.FEATURES)))
+def test_correctness_fp32_term_splits(emulated, reduction, feat):
+    gpu_tests.test_correctness_fp32(4, 47, 31, 123, reduction, True, gpu_tests.FEATURES[feat])
+    assert emulated.calls.count("flce_b200_split_fp32") >= 4
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_against_reference_golden(emulated, name):
+    gpu_tests.test_against_reference_golden(name)
+
+
+@pytest.mark.parametrize("name", ["mean_default", "all_features", "none_reduction", "ce_weight", "ragged_odd", "softcap", "z_loss"])
+def test_golden_fp32_inputs_against_reference_outputs(emulated, name):
+    """fp32 inputs exactly as the reference saw them, through the term-split path: agreement with the reference's own
+    outputs to fp32 accuracy."""
+    gpu_tests.test_golden_fp32_inputs_against_reference_outputs(name)
+
+
+def test_upstream_gradients_weights_scaling_and_edges(emulated):
+    gpu_tests.test_grad_output_scalar(2.0)
+    gpu_tests.test_reduction_none_per_token_grad()
+    gpu_tests.test_token_scaling_and_class_weights()
+    gpu_tests.test_all_rows_ignored_exact_zero()
+    gpu_tests.test_ignored_rows_have_exact_zero_gradient()
+    gpu_tests.test_targets_at_vocab_edges()
+
+
+def test_multi_slab_backward_equals_single_slab(emulated, monkeypatch):
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+
+    x, w, t, b, _ = make_inputs(150, 32, 1100, torch.bfloat16, seed=2, bias=True)
+    one = run_cuda(x, w, t, bias=b, label_smoothing=0.1)
+    monkeypatch.setattr(mod, "SLAB_BUDGET_BYTES", 150 * 2 * 256)              # 256 classes per slab -> 5 slabs
+    many = run_cuda(x, w, t, bias=b, label_smoothing=0.1)
+    assert torch.equal(one["grad_weight"], many["grad_weight"]) and torch.equal(one["grad_bias"], many["grad_bias"])
+    gmax = float(one["grad_input"].float().abs().max())
+    assert_close(many["grad_input"].float(), one["grad_input"].float(), 8e-3 * gmax, 1e-2, "grad_input across slabs")
+
+
+@pytest.mark.parametrize("ignored", [0.0, 0.3, 0.97, 1.0])
+@pytest.mark.parametrize("reduction", ["mean", "none"])
+def test_skipping_ignored_tokens_changes_nothing(emulated, monkeypatch, ignored, reduction):
+    """LIGER_B200_FLCE_SKIP_IGNORED: rows are compacted on the device, the sweeps stop at the tiles / k-blocks that still hold
+    live rows (scratch beyond them is poisoned with NaN here), and every result comes back in token order."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+
+    x, w, t, _, _ = make_inputs(600, 32, 300, torch.bfloat16, seed=7, ignore_frac=ignored)
+    if ignored == 1.0:
+        t[:] = -100
+    go = (torch.rand(600) + 0.5) if reduction == "none" else None
+    kw = dict(reduction=reduction, label_smoothing=0.1, lse_square_scale=1e-3)
+    plain = run_cuda(x, w, t, grad_output=go, **kw)
+    monkeypatch.setattr(mod, "SKIP_IGNORED", True)
+    skipped = run_cuda(x, w, t, grad_output=go, **kw)
+    assert "flce_b200_compact_rows" in emulated.calls
+    for key in ("loss", "z_loss", "token_accuracy", "predicted_tokens", "grad_input"):
+        a, b = plain[key].float(), skipped[key].float()
+        assert torch.equal(torch.nan_to_num(a), torch.nan_to_num(b)), key
+    gmax = max(float(plain["grad_weight"].float().abs().max()), 1e-30)
+    assert_close(skipped["grad_weight"].float(), plain["grad_weight"].float(), 8e-3 * gmax, 1e-2, "grad_weight")   # row order of the sum
+    assert bool(torch.isfinite(skipped["grad_weight"].float()).all()) and bool(torch.isfinite(skipped["grad_input"].float()).all())
+    gpu_tests._check(skipped, oracle_for(x, w, t, grad_output=go, **kw), torch.bfloat16, reduction, 600)
+
+
+def test_sharded_operators_single_process_numerics(emulated):
+    """The token- and vocabulary-sharded operators without a process group: count / statistics / finalize / backward through
+    the C ABI one by one (the path every rank runs), equal to the plain operator."""
+    from liger_kernel_b200 import sharded
+
+    x, w, t, _, _ = make_inputs(130, 32, 300, torch.bfloat16, seed=11)
+    ora = oracle_for(x, w, t, label_smoothing=0.1)
+    for fn, extra in ((sharded.token_sharded_fused_linear_cross_entropy, ()), (sharded.vocab_sharded_fused_linear_cross_entropy, (0, 300))):
+        xd, wd = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        loss = fn(xd, wd, t, *extra, label_smoothing=0.1)
+        loss.backward()
+        np.testing.assert_allclose(float(loss.detach()), float(ora.loss), rtol=1e-5)
+        for got, want in ((xd.grad, ora.grad_input), (wd.grad, ora.grad_weight)):
+            assert_close(got.float(), want.float(), 8e-3 * float(want.abs().max()), 5e-2, "gradient")

@@ -47,7 +47,7 @@ def flce_on_emulated_tiles(emu, x, w, t, bias=None, ce_weight=None, ignore_index
     pidx = torch.zeros(n_tiles, N, dtype=torch.int32)
     rowstats = torch.zeros(6, N)
     emu.emu_sweep_stats(_p(x), _p(w), FMT[dtype], N, V, H, x.stride(0), w.stride(0), _p(t), _p(bias32), _p(cw), cap, vocab_offset,
-                        _p(planes[0]), _p(planes[1]), _p(planes[2]), _p(planes[3]), _p(pidx), rowstats[2].data_ptr(), None, 0, 0)
+                        _p(planes[0]), _p(planes[1]), _p(planes[2]), _p(planes[3]), _p(pidx), rowstats[2].data_ptr(), None, 0, 0, -1)
     emu.emu_merge_partials(N, n_tiles, _p(planes[0]), _p(planes[1]), _p(planes[2]), _p(planes[3]), _p(pidx), _p(rowstats))
     f = lambda: torch.zeros(N)                                                    # noqa: E731
     lse, prob, loss_rows, z_rows, correct = f(), f(), f(), f(), f()
@@ -68,7 +68,7 @@ def flce_on_emulated_tiles(emu, x, w, t, bias=None, ce_weight=None, ignore_index
     ld = (V + 63) // 64 * 64
     dz = torch.full((N, ld), 7.0).to(dtype)                                      # the padding must never be read back
     emu.emu_sweep_dz(_p(x), _p(w), FMT[dtype], N, V, H, x.stride(0), w.stride(0), _p(t), _p(bias32), _p(cw), cap, vocab_offset,
-                     _p(lse), _p(c1), _p(c2), _p(c3), _p(dz), None, ld, FMT[dtype])
+                     _p(lse), _p(c1), _p(c2), _p(c3), _p(dz), None, ld, FMT[dtype], -1)
     dzf = dz[:, :V].double()
     if reduction == "none":
         loss, z = loss_rows, z_rows
