@@ -47,3 +47,21 @@ def test_bench_inputs_zipf_targets_for_the_gemma_style_workload():
     uniform = bench.make_inputs(dict(N=40000, H=8, V=1000, ign=0.05, kw={}), torch.device("cpu"), 1)[2]
     u = torch.bincount(uniform[uniform >= 0], minlength=1000).double()
     assert float(u.max() / u.min()) < 6.0 and float(counts.max() / max(1.0, float(counts[500:].mean()))) > 100.0
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` (the CPU arm of the headline benchmark) needs no GPU: one JSON line with the contract's keys."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    done = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "small", "--steps", "1",
+                           "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert done.returncode == 0, done.stderr[-2000:]
+    rec = json.loads(done.stdout.strip().splitlines()[-1])
+    assert rec["impl"] == "reference" and rec["metric"] == "flce_fwd_bwd_tokens_per_s" and rec["unit"] == "tokens/s"
+    assert rec["value"] > 0 and rec["higher_is_better"] is True and rec["n_gpus"] == 1 and rec["steps"] == 1
+    assert rec["cpu_baseline"]["kind"] == "port" and rec["cpu_baseline"]["cores"] >= 1 and rec["cpu_baseline"]["value"] == rec["value"]
+    assert rec["e2e"] == {"value": rec["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in rec["config"] and "sample" in rec["config"]
