@@ -217,8 +217,8 @@ __device__ __forceinline__ void jsd_terms(float X, float Y, float beta, float& l
   } else {
     const float bP = beta * P, bQ = (1.f - beta) * Q;
     const float M = bP + bQ;
-    if (M > 0.f) {
-      const float log_m = logf(M);
+    if (M >= 1.17549435e-38f) {   // below the smallest normal the term is worth less than 1e-36 (and lg2.approx reads a subnormal as 0)
+      const float log_m = ln_approx(M);   // M in [2^-126, 1]: the approximate logarithm is good to about 2e-7 absolute here
       loss = (bP > 0.f ? bP * Y : 0.f) + (bQ > 0.f ? bQ * X : 0.f) - M * log_m;
       dX = (bQ > 0.f) ? bQ * (X - log_m) : 0.f;
     } else {

@@ -40,6 +40,17 @@ __device__ __forceinline__ float ex2_approx(float x) {
 #endif
 }
 
+// natural logarithm through lg2.approx (absolute error of the base-2 logarithm about 2^-22 for normal inputs)
+__device__ __forceinline__ float ln_approx(float x) {
+#ifdef FLCE_HOST_EMULATION
+  return std::log(x);
+#else
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y * 0.6931471805599453f;
+#endif
+}
+
 __device__ __forceinline__ float rcp_approx(float x) {
 #ifdef FLCE_HOST_EMULATION
   return 1.f / x;
