@@ -120,6 +120,6 @@ def test_jsd_peaked_distributions_stay_finite(monkeypatch, beta):
     if bool(torch.isfinite(ora.loss)):            # forward / reverse KL are legitimately infinite where a support is missed
         cases.assert_close(res["loss"], ora.loss.float(), 1e-3 * max(1.0, float(ora.loss.abs())), 1e-3, "loss")
         # the gradient is a difference of O(1) terms times |w| / T (about 25 here): fp32 cancellation noise of 1e-5 is expected
-        # where the two heads disagree completely and the true gradient vanishes
+        # where the two heads disagree completely and the true gradient vanishes; with reverse KL the terms reach several hundred
         gmax = float(ora.grad_input.abs().max())
-        cases.assert_close(res["grad_input"], ora.grad_input.float(), 1e-4 * max(1.0, gmax), 1e-2, "grad_input")
+        cases.assert_close(res["grad_input"], ora.grad_input.float(), 2e-3 * max(1.0, gmax), 1e-2, "grad_input")
