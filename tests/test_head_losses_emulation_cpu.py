@@ -123,3 +123,27 @@ def test_jsd_peaked_distributions_stay_finite(monkeypatch, beta):
         # where the two heads disagree completely and the true gradient vanishes; with reverse KL the terms reach several hundred
         gmax = float(ora.grad_input.abs().max())
         cases.assert_close(res["grad_input"], ora.grad_input.float(), 2e-3 * max(1.0, gmax), 1e-2, "grad_input")
+
+
+@pytest.mark.parametrize("mode", ["fused", "chunked"])
+def test_scaled_ce_peaked_distributions(monkeypatch, mode):
+    """Logit gaps of several hundred at a low temperature: entropy near zero, nll in the hundreds, everything finite and equal
+    to the fp64 closed form."""
+    from oracle.distill_oracle import fused_linear_scaled_ce_oracle
+
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(20, 16, generator=g).bfloat16()
+    w = (torch.randn(300, 16, generator=g) * 6).bfloat16()
+    t = torch.randint(0, 300, (20,), generator=g)
+    t[3] = -100
+    g_nll, g_ent = torch.randn(20, generator=g), torch.randn(20, generator=g)
+    with emu_lib.installed(monkeypatch), cases.sce_mode(mode):
+        res = cases.run_sce("cpu", x, w, t, 0.25, g_nll, g_ent)
+    low = torch.bfloat16 if mode == "chunked" else None        # the chunked form rounds its logits slab to the operands' dtype
+    ora = fused_linear_scaled_ce_oracle(x, w, t, 0.25, -100, g_nll, g_ent, round_logits_to=low, round_dlogits_to=torch.bfloat16)
+    for key in ("nll", "entropy", "grad_input", "grad_weight"):
+        assert bool(torch.isfinite(res[key]).all()), key
+    cases.assert_close(res["nll"], ora.nll.float(), 1e-3 * float(ora.nll.abs().max()), 1e-3 if low is None else 2e-2, "nll")
+    cases.assert_close(res["entropy"], ora.entropy.float(), 2e-2, 2e-2, "entropy")
+    gmax = float(ora.grad_input.abs().max())
+    cases.assert_close(res["grad_input"], ora.grad_input.float(), 2e-2 * gmax, 5e-2, "grad_input")
