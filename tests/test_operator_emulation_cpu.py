@@ -109,3 +109,20 @@ def test_sharded_operators_single_process_numerics(emulated):
         np.testing.assert_allclose(float(loss.detach()), float(ora.loss), rtol=1e-5)
         for got, want in ((xd.grad, ora.grad_input), (wd.grad, ora.grad_weight)):
             assert_close(got.float(), want.float(), 8e-3 * float(want.abs().max()), 5e-2, "gradient")
+
+
+def test_logit_gaps_of_several_hundred_stay_finite(emulated):
+    """Peaked rows (logits in the hundreds): the online softmax never forms exp of a positive number, the loss is the exact
+    gap for confidently wrong rows and 0 for confidently right ones."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(70, 32, generator=g).bfloat16()
+    w = (torch.randn(300, 32, generator=g) * 8).bfloat16()
+    t = torch.randint(0, 300, (70,), generator=g)
+    logits = x.double() @ w.double().T
+    t[:35] = logits[:35].argmax(1)                                   # half of the rows predict their target with certainty
+    for kw in (dict(), dict(label_smoothing=0.1, lse_square_scale=1e-4)):
+        res = run_cuda(x, w, t, **kw)
+        ora = oracle_for(x, w, t, **kw)
+        assert bool(torch.isfinite(res["loss"])) and bool(torch.isfinite(res["grad_input"].float()).all())
+        assert bool(torch.isfinite(res["grad_weight"].float()).all())
+        gpu_tests._check(res, ora, torch.bfloat16, "mean", 70)
