@@ -7,7 +7,8 @@
 //                           student slab is overwritten by the gradient with respect to the student's logits
 //
 // One CTA per row for the reductions (fixed-order trees: run-to-run identical), 16-byte accesses when the slab allows.
-// The slab of a chunk is sized to stay far below L2 x SM count, so the second and third sweeps of a row hit L2.
+// Whether the second and third sweeps of a row hit L2 depends on how many rows are resident at once (a row of a 128 k
+// vocabulary is 256 KB per head).
 // SIMT only: this header also compiles for the host emulation the CPU tests use.
 #pragma once
 
