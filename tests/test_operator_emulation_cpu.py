@@ -126,3 +126,32 @@ def test_logit_gaps_of_several_hundred_stay_finite(emulated):
         assert bool(torch.isfinite(res["loss"])) and bool(torch.isfinite(res["grad_input"].float()).all())
         assert bool(torch.isfinite(res["grad_weight"].float()).all())
         gpu_tests._check(res, ora, torch.bfloat16, "mean", 70)
+
+
+@pytest.mark.parametrize("ignore_frac", [0.0, 0.5, 0.97])
+def test_skip_ignored_gpu_bodies(emulated, monkeypatch, ignore_frac):
+    """The bodies of tests/test_y_skip_ignored_gpu.py at a size the emulation handles."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+    import test_y_skip_ignored_gpu as skip_tests
+
+    monkeypatch.setattr(mod, "SKIP_IGNORED", True)
+    skip_tests.test_skip_ignored_matches_oracle_and_plain_path(mod, monkeypatch, 300, 31, 123, ignore_frac)
+    if ignore_frac == 0.5:
+        monkeypatch.setattr(mod, "SKIP_IGNORED", True)
+        skip_tests.test_skip_ignored_all_rows_ignored_and_per_token_gradient(mod)
+
+
+def test_extras_gpu_bodies(emulated, monkeypatch):
+    """The bodies of tests/test_x_extras_gpu.py: out-of-range targets, the full-size property checks at a reduced size, and
+    automatic mixed precision (the CUDA autocast state is simulated: this box has no GPU for torch.autocast to act on)."""
+    import test_x_extras_gpu as extras
+
+    extras.test_out_of_range_targets_are_counted_and_optionally_raised(monkeypatch)
+    monkeypatch.setattr(extras, "FULL_SIZE", {"small_qwen_style": (300, 32, 1300, 0.2, dict(label_smoothing=0.1, lse_square_scale=1e-4)),
+                                              "small_gemma_style": (200, 24, 900, 0.05, dict(softcap=30.0, reduction="sum"))})
+    for name in extras.FULL_SIZE:
+        extras.test_full_size_configs_sampled_against_fp64(name)
+    for amp_dtype in (torch.bfloat16, torch.float16):
+        monkeypatch.setattr(torch, "is_autocast_enabled", lambda device_type=None: True)
+        monkeypatch.setattr(torch, "get_autocast_dtype", lambda device_type=None, d=amp_dtype: d)
+        extras.test_amp_autocast_with_fp32_parameters(amp_dtype)

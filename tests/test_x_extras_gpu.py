@@ -4,6 +4,7 @@ automatic mixed precision (fp32 parameters and inputs under torch.autocast) and 
 import pytest
 import torch
 
+import flce_cases
 from flce_cases import make_inputs, oracle_for
 from test_flce_gpu import _check
 
@@ -16,12 +17,13 @@ def test_amp_autocast_with_fp32_parameters(amp_dtype):
     in fp32 (reference: test/transformers/test_fused_linear_cross_entropy.py:558-604)."""
     from liger_kernel_b200 import LigerFusedLinearCrossEntropyLoss
 
+    dev = flce_cases.DEVICE
     x, w, t, b, _ = make_inputs(256, 128, 1000, torch.float32, seed=31, bias=True)
-    xd = x.cuda().requires_grad_(True)
-    wd = w.cuda().requires_grad_(True)
-    bd = b.cuda().requires_grad_(True)
+    xd = x.to(dev).clone().requires_grad_(True)
+    wd = w.to(dev).clone().requires_grad_(True)
+    bd = b.to(dev).clone().requires_grad_(True)
     with torch.autocast(device_type="cuda", dtype=amp_dtype):
-        loss = LigerFusedLinearCrossEntropyLoss()(wd, xd, t.cuda(), bd)
+        loss = LigerFusedLinearCrossEntropyLoss()(wd, xd, t.to(dev), bd)
     loss.backward()
     assert loss.dtype == torch.float32 and xd.grad.dtype == torch.float32 and wd.grad.dtype == torch.float32
     assert bd.grad.dtype == torch.float32
@@ -36,16 +38,17 @@ def test_out_of_range_targets_are_counted_and_optionally_raised(monkeypatch):
     can ask for the reference's assertion (ops/cross_entropy.py:389-392) at the price of a host synchronisation."""
     import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
 
+    dev = flce_cases.DEVICE
     x, w, t, _, _ = make_inputs(200, 64, 300, torch.bfloat16, seed=41)
     t[5], t[9] = 303, -7
-    prep = mod._Prepared(x.cuda(), w.cuda(), t.cuda(), None, None, -100, 0.0, 0.0, "mean", None, False)
+    prep = mod._Prepared(x.to(dev), w.to(dev), t.to(dev), None, None, -100, 0.0, 0.0, "mean", None, False)
     out, norm, _ = mod.flce_forward_device(prep)
     assert int(norm[3].item()) == 2 and bool(torch.isfinite(out["scalars"][0]))
     monkeypatch.setattr(mod, "CHECK_TARGETS", True)
     with pytest.raises(AssertionError, match="out of bounds"):
-        mod.LigerFusedLinearCrossEntropyFunction.apply(x.cuda(), w.cuda(), t.cuda())
+        mod.LigerFusedLinearCrossEntropyFunction.apply(x.to(dev), w.to(dev), t.to(dev))
     t[5], t[9] = 1, 2
-    mod.LigerFusedLinearCrossEntropyFunction.apply(x.cuda(), w.cuda(), t.cuda())
+    mod.LigerFusedLinearCrossEntropyFunction.apply(x.to(dev), w.to(dev), t.to(dev))
 
 
 FULL_SIZE = {
@@ -64,13 +67,14 @@ def test_full_size_configs_sampled_against_fp64(name):
     from flce_cases import sampled_fp64_check
 
     N, H, V, ign, kw = FULL_SIZE[name]
-    if torch.cuda.get_device_properties(0).total_memory < 60e9:
+    dev = flce_cases.DEVICE
+    if dev == "cuda" and torch.cuda.get_device_properties(0).total_memory < 60e9:
         pytest.skip("needs ~25 GB of device memory")
-    g = torch.Generator(device="cuda").manual_seed(77)
-    x = torch.randn(N, H, generator=g, device="cuda").bfloat16()
-    w = (torch.randn(V, H, generator=g, device="cuda") * 0.02).bfloat16()
-    t = torch.randint(0, V, (N,), generator=g, device="cuda")
-    t[torch.rand(N, generator=g, device="cuda") < ign] = -100
+    g = torch.Generator(device=dev).manual_seed(77)
+    x = torch.randn(N, H, generator=g, device=dev).bfloat16()
+    w = (torch.randn(V, H, generator=g, device=dev) * 0.02).bfloat16()
+    t = torch.randint(0, V, (N,), generator=g, device=dev)
+    t[torch.rand(N, generator=g, device=dev) < ign] = -100
     red = kw.get("reduction", "mean")
     xd, wd = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
     loss = mod.LigerFusedLinearCrossEntropyFunction.apply(

@@ -52,5 +52,5 @@ def test_skip_ignored_all_rows_ignored_and_per_token_gradient(skipping):
     res = run_cuda(x, w, t, reduction="none", grad_output=go)
     ora = oracle_for(x, w, t, reduction="none", grad_output=go)
     assert_close(res["loss"], ora.loss.float(), 1e-4, 1e-4, "loss rows")
-    assert_close(res["grad_input"].float(), ora.grad_input.float(), 1e-2, 5e-2, "grad_input")
-    assert_close(res["grad_weight"].float(), ora.grad_weight.float(), 1e-2, 5e-2, "grad_weight")
+    for key, want in (("grad_input", ora.grad_input), ("grad_weight", ora.grad_weight)):      # un-normalised rows: scale-aware bound
+        assert_close(res[key].float(), want.float(), 8e-3 * float(want.abs().max()), 5e-2, key)
