@@ -151,7 +151,11 @@ def test_extras_gpu_bodies(emulated, monkeypatch):
                                               "small_gemma_style": (200, 24, 900, 0.05, dict(softcap=30.0, reduction="sum"))})
     for name in extras.FULL_SIZE:
         extras.test_full_size_configs_sampled_against_fp64(name)
-    for amp_dtype in (torch.bfloat16, torch.float16):
-        monkeypatch.setattr(torch, "is_autocast_enabled", lambda device_type=None: True)
-        monkeypatch.setattr(torch, "get_autocast_dtype", lambda device_type=None, d=amp_dtype: d)
-        extras.test_amp_autocast_with_fp32_parameters(amp_dtype)
+    try:
+        for amp_dtype in (torch.bfloat16, torch.float16):
+            monkeypatch.setattr(torch, "is_autocast_enabled", lambda device_type=None: True)
+            monkeypatch.setattr(torch, "get_autocast_dtype", lambda device_type=None, d=amp_dtype: d)
+            extras.test_amp_autocast_with_fp32_parameters(amp_dtype)
+    finally:
+        # torch.autocast saved the simulated "enabled" answer on entry and wrote it back on exit: clear the real state
+        torch.set_autocast_enabled("cuda", False)
