@@ -81,3 +81,18 @@ def test_module_argument_checks_follow_the_reference():
         LigerFusedLinearCrossEntropyLoss(reduction="median")
     with pytest.raises(AssertionError, match="softcap must greater than"):
         LigerFusedLinearCrossEntropyLoss(softcap=0.0)
+
+
+def test_public_header_is_plain_c(tmp_path):
+    """include/flce_b200.h must be usable from C (the boundary is a C ABI): compile a translation unit with gcc -std=c99."""
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "flce_b200.h"\nint main(void) { flce_problem_t p; flce_sce_problem_t q; (void)p; (void)q; return 0; }\n')
+    include = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    done = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I", include, str(src)],
+                          capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
