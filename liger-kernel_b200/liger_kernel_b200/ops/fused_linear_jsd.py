@@ -27,9 +27,11 @@ from .fused_linear_cross_entropy import _DTYPES, _ptr, scale_gradient_
 
 
 def fused_linear_jsd_forward(student_input, student_weight, teacher_input, teacher_weight, shift_labels, jsd_beta,
-                             ignore_index, has_label, temperature, accum_dtype=None, weight_requires_grad=None):
+                             ignore_index, has_label, temperature, accum_dtype=None, weight_requires_grad=None,
+                             input_requires_grad=True):
     """Returns ``(loss, grad_input, grad_weight)``; ``grad_weight`` is None when the student head needs no gradient
-    (``weight_requires_grad``, by default ``student_weight.requires_grad`` as in the reference)."""
+    (``weight_requires_grad``, by default ``student_weight.requires_grad`` as in the reference) and ``grad_input`` is None
+    when ``input_requires_grad`` is False (an evaluation pass then costs the two logits GEMMs and the row kernel only)."""
     for t in (student_input, student_weight, teacher_input, teacher_weight):
         _fl._require_cuda(t)
     if student_input.dim() != 2 or teacher_input.dim() != 2 or student_weight.dim() != 2 or teacher_weight.dim() != 2:
@@ -59,7 +61,8 @@ def fused_linear_jsd_forward(student_input, student_weight, teacher_input, teach
         count = (labels != ignore_index).sum().to(torch.float32).reshape(1)      # stays on the device
     chunk_rows, n_chunks = ck.plan_chunks(n_rows, student.slab_bytes_per_row() + teacher.slab_bytes_per_row())
     slab_s, slab_t = student.new_slab(chunk_rows), teacher.new_slab(chunk_rows)
-    grad_input = student.new_grad_input()
+    need_input = bool(input_requires_grad)
+    grad_input = student.new_grad_input() if need_input else None
     grad_weight32 = student.new_grad_weight() if need_weight else None
     loss_rows = torch.empty(n_rows, dtype=torch.float32, device=dev)
     with _fl._device_guard(dev):
@@ -72,14 +75,18 @@ def fused_linear_jsd_forward(student_input, student_weight, teacher_input, teach
                 _ptr(slab_s), slab_s.stride(0), _ptr(slab_t), slab_t.stride(0), _DTYPES[dtype], rows, vocab,
                 None if labels is None else _ptr(labels[r0:r0 + rows]), int(ignore_index), float(jsd_beta), float(temperature),
                 _ptr(count), float(n_rows), _ptr(loss_rows[r0:r0 + rows]), _fl._stream(dev)))
-            student.project(slab_s, r0, rows, grad_input[r0:r0 + rows], grad_weight32)
+            if need_input or need_weight:
+                student.project(slab_s, r0, rows, grad_input[r0:r0 + rows] if need_input else None, grad_weight32)
     loss = loss_rows.sum()
     return loss, student.finish_grad_input(grad_input), student.finish_grad_weight(grad_weight32)
 
 
 def fused_linear_jsd_backward(grad_output, grad_input, grad_weight):
     """``grad *= grad_output`` unless the upstream gradient is exactly 1 (tested on the device)."""
-    go = grad_output.detach().to(device=grad_input.device, dtype=torch.float32).reshape(1)
+    present = grad_input if grad_input is not None else grad_weight
+    if present is None:
+        return None, None
+    go = grad_output.detach().to(device=present.device, dtype=torch.float32).reshape(1)
     grad_input = scale_gradient_(grad_input, go)
     grad_weight = scale_gradient_(grad_weight, go)
     return grad_input, grad_weight
@@ -106,19 +113,21 @@ class LigerFusedLinearJSDFunction(torch.autograd.Function):
             teacher_input, teacher_weight = teacher_input.to(dt), teacher_weight.to(dt)
         loss, grad_input, grad_weight = fused_linear_jsd_forward(
             student_input, student_weight, teacher_input, teacher_weight, shift_labels, jsd_beta, ignore_index, has_label,
-            temperature, accum_dtype, weight_requires_grad=ctx.needs_input_grad[1])
+            temperature, accum_dtype, weight_requires_grad=ctx.needs_input_grad[1], input_requires_grad=ctx.needs_input_grad[0])
         ctx.jsd_grads = (grad_input, grad_weight)
+        ctx.jsd_handed_off = False
         ctx.jsd_in_dtypes = in_dtypes
         return loss
 
     @staticmethod
     def backward(ctx, grad_output):
         grad_input, grad_weight = ctx.jsd_grads
-        if grad_input is None:
+        if ctx.jsd_handed_off:
             raise RuntimeError("the gradients of this fused linear JSD call were already handed off by an earlier backward")
+        ctx.jsd_handed_off = True
         ctx.jsd_grads = (None, None)
         grad_input, grad_weight = fused_linear_jsd_backward(grad_output, grad_input, grad_weight)
         dx, dw = ctx.jsd_in_dtypes
-        grad_input = grad_input.to(dx)
+        grad_input = None if grad_input is None else grad_input.to(dx)
         grad_weight = None if grad_weight is None else grad_weight.to(dw)
         return (grad_input, grad_weight) + (None,) * 7

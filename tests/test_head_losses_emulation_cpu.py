@@ -147,3 +147,18 @@ def test_scaled_ce_peaked_distributions(monkeypatch, mode):
     cases.assert_close(res["entropy"], ora.entropy.float(), 2e-2, 2e-2, "entropy")
     gmax = float(ora.grad_input.abs().max())
     cases.assert_close(res["grad_input"], ora.grad_input.float(), 2e-2 * gmax, 5e-2, "grad_input")
+
+
+def test_jsd_evaluation_pass_skips_the_projections(monkeypatch):
+    """Without a gradient to produce (torch.no_grad, or only the head trainable) the chunk loop drops the GEMMs it does not need."""
+    import liger_kernel_b200 as lk
+
+    xs, ws, xt, wt, _ = cases.jsd_inputs(40, 16, 16, 67, torch.bfloat16, seed=9)
+    with emu_lib.installed(monkeypatch) as lib:
+        with torch.no_grad():
+            loss = lk.LigerFusedLinearJSD()(xs, ws, xt, wt, None)
+        assert lib.calls.count("flce_b200_gemm_accumulate") == 2 and bool(torch.isfinite(loss))
+        del lib.calls[:]
+        w_train = ws.clone().requires_grad_(True)
+        lk.LigerFusedLinearJSD()(xs, w_train, xt, wt, None).backward()
+        assert lib.calls.count("flce_b200_gemm_accumulate") == 3 and w_train.grad.shape == (67, 16)      # logits x2 + grad_weight
