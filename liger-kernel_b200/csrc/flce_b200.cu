@@ -443,18 +443,18 @@ static void launch_scaled_ce_grad(void* logits, int64_t ld, int32_t dtype, int64
 }
 
 template <typename T>
-static void launch_jsd_rows(void* student, int64_t ld_s, const void* teacher, int64_t ld_t, int32_t dtype, int64_t n_rows,
-                            int64_t vocab, const long long* labels, long long ignore_index, float beta, float inv_t,
+static void launch_jsd_rows(int sm_count, void* student, int64_t ld_s, const void* teacher, int64_t ld_t, int32_t dtype,
+                            int64_t n_rows, int64_t vocab, const long long* labels, long long ignore_index, float beta, float inv_t,
                             const float* count, float fixed_count, float* loss_rows, cudaStream_t stream) {
   const bool vec = ce_rows_vectorisable(student, ld_s, dtype) && ce_rows_vectorisable(teacher, ld_t, dtype);
-  const unsigned grid = static_cast<unsigned>(n_rows);
+  const unsigned grid = static_cast<unsigned>(n_rows < sm_count ? n_rows : sm_count);   // one CTA per SM walks over the rows
   T* xs = static_cast<T*>(student);
   const T* xt = static_cast<const T*>(teacher);
   if (vec)
-    jsd_rows_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
+    jsd_rows_kernel<T, true><<<grid, kJsdThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
                                                              labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
   else
-    jsd_rows_kernel<T, false><<<grid, kCeThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
+    jsd_rows_kernel<T, false><<<grid, kJsdThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
                                                               labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
 }
 
@@ -1327,9 +1327,9 @@ int flce_b200_jsd_rows(void* student, int64_t ld_student, const void* teacher, i
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const long long* labels = reinterpret_cast<const long long*>(labels_);
   const float inv_t = 1.f / temperature;
-  if (dtype == FLCE_FP32) launch_jsd_rows<float>(student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
-  else if (dtype == FLCE_BF16) launch_jsd_rows<__nv_bfloat16>(student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
-  else launch_jsd_rows<__half>(student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
+  if (dtype == FLCE_FP32) launch_jsd_rows<float>(dev->sm_count, student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
+  else if (dtype == FLCE_BF16) launch_jsd_rows<__nv_bfloat16>(dev->sm_count, student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
+  else launch_jsd_rows<__half>(dev->sm_count, student, ld_student, teacher, ld_teacher, dtype, n_rows, vocab, labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows, stream);
   FLCE_CUDA(cudaGetLastError());
   ++g_kernel_launches;
   return FLCE_OK;

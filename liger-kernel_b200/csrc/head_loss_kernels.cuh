@@ -7,8 +7,7 @@
 //                           student slab is overwritten by the gradient with respect to the student's logits
 //
 // One CTA per row for the reductions (fixed-order trees: run-to-run identical), 16-byte accesses when the slab allows.
-// Whether the second and third sweeps of a row hit L2 depends on how many rows are resident at once (a row of a 128 k
-// vocabulary is 256 KB per head).
+// The JSD kernel keeps the rows in flight within L2 (see there).
 // SIMT only: this header also compiles for the host emulation the CPU tests use.
 #pragma once
 
@@ -46,6 +45,7 @@ __device__ __forceinline__ void ent_merge(EntropyState& a, const EntropyState& b
   a.m = m_new;
 }
 
+template <int kThreads = kCeThreads>
 __device__ __forceinline__ EntropyState ent_block_reduce(EntropyState st, EntropyState* warp_state) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -61,7 +61,7 @@ __device__ __forceinline__ EntropyState ent_block_reduce(EntropyState st, Entrop
   __syncthreads();
   EntropyState acc;
   ent_init(acc);
-  if (lane < kCeThreads / 32) acc = warp_state[lane];
+  if (lane < kThreads / 32) acc = warp_state[lane];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     EntropyState other;
@@ -74,6 +74,7 @@ __device__ __forceinline__ EntropyState ent_block_reduce(EntropyState st, Entrop
 }
 
 // sum of two floats per thread over the block, fixed order; result valid in every thread
+template <int kThreads = kCeThreads>
 __device__ __forceinline__ float2 block_sum2(float a, float b, float2* warp_part) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -85,7 +86,7 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float2* warp_part
   if (lane == 0) warp_part[warp] = make_float2(a, b);
   __syncthreads();
   float2 r = make_float2(0.f, 0.f);
-  if (lane < kCeThreads / 32) r = warp_part[lane];
+  if (lane < kThreads / 32) r = warp_part[lane];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     r.x += __shfl_xor_sync(0xffffffffu, r.x, o);
@@ -95,21 +96,21 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float2* warp_part
 }
 
 // visit every element of a row once: f(value, column); 16-byte loads over the aligned body
-template <typename T, bool kVectorised, typename F>
+template <typename T, bool kVectorised, int kThreads = kCeThreads, typename F>
 __device__ __forceinline__ void for_each_in_row(const T* x, int n_cols, F&& f) {
   constexpr int kVec = CeElem<T>::kVec;
   int tail_begin = 0;
   if constexpr (kVectorised) {
     const int n_vec = n_cols / kVec;
     tail_begin = n_vec * kVec;
-    for (int i = threadIdx.x; i < n_vec; i += kCeThreads) {
+    for (int i = threadIdx.x; i < n_vec; i += kThreads) {
       float v[kVec];
       ce_load_vec<T>(x + i * kVec, v);
 #pragma unroll
       for (int j = 0; j < kVec; ++j) f(v[j], i * kVec + j);
     }
   }
-  for (int col = tail_begin + threadIdx.x; col < n_cols; col += kCeThreads) f(CeElem<T>::load(x + col), col);
+  for (int col = tail_begin + threadIdx.x; col < n_cols; col += kThreads) f(CeElem<T>::load(x + col), col);
 }
 
 // ---- scaled cross-entropy ------------------------------------------------------------------------------------------
@@ -229,40 +230,49 @@ __device__ __forceinline__ void jsd_terms(float X, float Y, float beta, float& l
   }
 }
 
-// One CTA per token.  `count` (device, may be null) holds the number of tokens that matter; with null, `fixed_count` is
-// used.  loss_rows[row] receives the token's share of the loss (already divided by the count); the student's row is
-// overwritten with d loss / d (student logits), zeros when the token's label is ignore_index.
+// A CTA of kJsdThreads threads per SM walks over the tokens (row = blockIdx.x, += gridDim.x): one student row and one teacher
+// row of a 128 k vocabulary are 513 KB in 16-bit, so 148 rows in flight fit the 126 MB L2 and the second and third sweep of a
+// row are served from it; with one small CTA per row several times as many rows would be resident and every sweep would go to
+// HBM.  `count` (device, may be null) holds the number of tokens that matter; with null, `fixed_count` is used.
+// loss_rows[row] receives the token's share of the loss (already divided by the count); the student's row is overwritten with
+// d loss / d (student logits), zeros when the token's label is ignore_index.
+#ifndef FLCE_JSD_THREADS
+#define FLCE_JSD_THREADS 1024   // the host emulation of the CPU tests builds this kernel with fewer threads to stay fast
+#endif
+constexpr int kJsdThreads = FLCE_JSD_THREADS;
+
 template <typename T, bool kVectorised>
-__global__ void __launch_bounds__(kCeThreads)
+__global__ void __launch_bounds__(kJsdThreads, 1)
 jsd_rows_kernel(T* student, long long ld_s, const T* teacher, long long ld_t, int n_rows, int n_cols, const long long* labels,
                 long long ignore_index, float beta, float inv_temperature, const float* count, float fixed_count,
                 float* loss_rows) {
-  __shared__ EntropyState warp_state[kCeThreads / 32];
-  __shared__ float2 warp_part[kCeThreads / 32];
-  const int row = blockIdx.x;
-  if (row >= n_rows) return;
-  T* xs = student + static_cast<size_t>(row) * ld_s;
-  const T* xt = teacher + static_cast<size_t>(row) * ld_t;
+  __shared__ EntropyState warp_state[kJsdThreads / 32];
+  __shared__ float2 warp_part[kJsdThreads / 32];
   constexpr int kVec = CeElem<T>::kVec;
-  if (labels != nullptr && labels[row] == ignore_index) {
-    for (int col = threadIdx.x; col < n_cols; col += kCeThreads) CeElem<T>::store(xs + col, 0.f);
-    if (threadIdx.x == 0) loss_rows[row] = 0.f;
-    return;
-  }
-  // sweep 1: both log-normalisers
-  EntropyState a, b;
-  ent_init(a);
-  ent_init(b);
-  for_each_in_row<T, kVectorised>(xs, n_cols, [&](float z, int) { ent_push(a, z * inv_temperature); });
-  for_each_in_row<T, kVectorised>(xt, n_cols, [&](float z, int) { ent_push(b, z * inv_temperature); });
-  a = ent_block_reduce(a, warp_state);
-  b = ent_block_reduce(b, warp_state);
-  const float lse_s = a.m + logf(a.d), lse_t = b.m + logf(b.d);
-  // sweep 2: the token's loss and sum_k dX_k
-  float loss_acc = 0.f, dx_acc = 0.f;
-  {
+  const float n_live = count != nullptr ? *count : fixed_count;
+  const float scale = n_live > 0.f ? 1.f / n_live : 0.f;
+  const float out_scale = scale * inv_temperature;
+  for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {   // uniform per CTA: the barriers below are reached by all threads
+    T* xs = student + static_cast<size_t>(row) * ld_s;
+    const T* xt = teacher + static_cast<size_t>(row) * ld_t;
+    if (labels != nullptr && labels[row] == ignore_index) {
+      for (int col = threadIdx.x; col < n_cols; col += kJsdThreads) CeElem<T>::store(xs + col, 0.f);
+      if (threadIdx.x == 0) loss_rows[row] = 0.f;
+      continue;
+    }
+    // sweep 1: both log-normalisers
+    EntropyState a, b;
+    ent_init(a);
+    ent_init(b);
+    for_each_in_row<T, kVectorised, kJsdThreads>(xs, n_cols, [&](float z, int) { ent_push(a, z * inv_temperature); });
+    for_each_in_row<T, kVectorised, kJsdThreads>(xt, n_cols, [&](float z, int) { ent_push(b, z * inv_temperature); });
+    a = ent_block_reduce<kJsdThreads>(a, warp_state);
+    b = ent_block_reduce<kJsdThreads>(b, warp_state);
+    const float lse_s = a.m + logf(a.d), lse_t = b.m + logf(b.d);
+    // sweep 2: the token's loss and sum_k dX_k
+    float loss_acc = 0.f, dx_acc = 0.f;
     const int n_vec = kVectorised ? n_cols / kVec : 0;
-    for (int i = threadIdx.x; i < n_vec; i += kCeThreads) {
+    for (int i = threadIdx.x; i < n_vec; i += kJsdThreads) {
       float vs[kVec], vt[kVec];
       ce_load_vec<T>(xs + i * kVec, vs);
       ce_load_vec<T>(xt + i * kVec, vt);
@@ -274,23 +284,17 @@ jsd_rows_kernel(T* student, long long ld_s, const T* teacher, long long ld_t, in
         dx_acc += dx;
       }
     }
-    for (int col = n_vec * kVec + threadIdx.x; col < n_cols; col += kCeThreads) {
+    for (int col = n_vec * kVec + threadIdx.x; col < n_cols; col += kJsdThreads) {
       float l, dx, q;
       jsd_terms(CeElem<T>::load(xs + col) * inv_temperature - lse_s, CeElem<T>::load(xt + col) * inv_temperature - lse_t, beta, l,
                 dx, q);
       loss_acc += l;
       dx_acc += dx;
     }
-  }
-  const float2 tot = block_sum2(loss_acc, dx_acc, warp_part);
-  const float n_live = count != nullptr ? *count : fixed_count;
-  const float scale = n_live > 0.f ? 1.f / n_live : 0.f;
-  if (threadIdx.x == 0) loss_rows[row] = tot.x * scale;
-  // sweep 3: d logits = (dX - Q * sum dX) * scale / T, over the student's row
-  const float out_scale = scale * inv_temperature;
-  {
-    const int n_vec = kVectorised ? n_cols / kVec : 0;
-    for (int i = threadIdx.x; i < n_vec; i += kCeThreads) {
+    const float2 tot = block_sum2<kJsdThreads>(loss_acc, dx_acc, warp_part);
+    if (threadIdx.x == 0) loss_rows[row] = tot.x * scale;
+    // sweep 3: d logits = (dX - Q * sum dX) * scale / T, over the student's row
+    for (int i = threadIdx.x; i < n_vec; i += kJsdThreads) {
       float vs[kVec], vt[kVec];
       ce_load_vec<T>(xs + i * kVec, vs);
       ce_load_vec<T>(xt + i * kVec, vt);
@@ -302,7 +306,7 @@ jsd_rows_kernel(T* student, long long ld_s, const T* teacher, long long ld_t, in
       }
       ce_store_vec<T>(xs + i * kVec, vs);
     }
-    for (int col = n_vec * kVec + threadIdx.x; col < n_cols; col += kCeThreads) {
+    for (int col = n_vec * kVec + threadIdx.x; col < n_cols; col += kJsdThreads) {
       float l, dx, q;
       jsd_terms(CeElem<T>::load(xs + col) * inv_temperature - lse_s, CeElem<T>::load(xt + col) * inv_temperature - lse_t, beta, l,
                 dx, q);

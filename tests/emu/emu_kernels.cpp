@@ -7,6 +7,7 @@
 //
 // Test infrastructure only.
 #define FLCE_HOST_EMULATION 1
+#define FLCE_JSD_THREADS 256   // 1024 on the GPU; fewer fibers keep the emulated barriers cheap, the code is the same
 #include "simt_emulation.hpp"
 
 #include "ce_kernels.cuh"
@@ -144,7 +145,8 @@ void run_jsd_rows(void* student, long long ld_s, const void* teacher, long long 
   const bool vec = vectorisable(student, ld_s, dtype) && vectorisable(teacher, ld_t, dtype);
   T* xs = static_cast<T*>(student);
   const T* xt = static_cast<const T*>(teacher);
-  emu::launch(emu::Dim3(static_cast<unsigned>(n_rows)), emu::Dim3(kCeThreads), [&]() {
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(n_rows, 148));   // one CTA per SM walks over the rows
+  emu::launch(emu::Dim3(grid), emu::Dim3(kJsdThreads), [&]() {
     if (vec)
       jsd_rows_kernel<T, true>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab), labels, ignore_index, beta,
                                inv_t, count, fixed_count, loss_rows);
