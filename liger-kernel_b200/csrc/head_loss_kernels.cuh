@@ -264,14 +264,26 @@ jsd_rows_kernel(T* student, long long ld_s, const T* teacher, long long ld_t, in
     EntropyState a, b;
     ent_init(a);
     ent_init(b);
-    for_each_in_row<T, kVectorised, kJsdThreads>(xs, n_cols, [&](float z, int) { ent_push(a, z * inv_temperature); });
-    for_each_in_row<T, kVectorised, kJsdThreads>(xt, n_cols, [&](float z, int) { ent_push(b, z * inv_temperature); });
+    const int n_vec = kVectorised ? n_cols / kVec : 0;
+    for (int i = threadIdx.x; i < n_vec; i += kJsdThreads) {   // both rows in one loop: two independent loads in flight
+      float vs[kVec], vt[kVec];
+      ce_load_vec<T>(xs + i * kVec, vs);
+      ce_load_vec<T>(xt + i * kVec, vt);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        ent_push(a, vs[j] * inv_temperature);
+        ent_push(b, vt[j] * inv_temperature);
+      }
+    }
+    for (int col = n_vec * kVec + threadIdx.x; col < n_cols; col += kJsdThreads) {
+      ent_push(a, CeElem<T>::load(xs + col) * inv_temperature);
+      ent_push(b, CeElem<T>::load(xt + col) * inv_temperature);
+    }
     a = ent_block_reduce<kJsdThreads>(a, warp_state);
     b = ent_block_reduce<kJsdThreads>(b, warp_state);
     const float lse_s = a.m + logf(a.d), lse_t = b.m + logf(b.d);
     // sweep 2: the token's loss and sum_k dX_k
     float loss_acc = 0.f, dx_acc = 0.f;
-    const int n_vec = kVectorised ? n_cols / kVec : 0;
     for (int i = threadIdx.x; i < n_vec; i += kJsdThreads) {
       float vs[kVec], vt[kVec];
       ce_load_vec<T>(xs + i * kVec, vs);
