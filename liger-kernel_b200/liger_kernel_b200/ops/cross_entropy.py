@@ -5,7 +5,8 @@ Call surface of the reference's ``src/liger_kernel/ops/cross_entropy.py`` (``cro
 ``libflce_b200.so``.  Differences a caller can observe: forward leaves the logits untouched (the reference
 overwrites them with the gradient there); backward writes the gradient, with the upstream gradient already
 folded in, over the logits buffer by default (``INPLACE_GRADIENT``), which keeps the reference's memory footprint;
-there is no host synchronisation, so out-of-range targets are not reported (they simply match no class).
+there is no host synchronisation, so out-of-range targets are not reported (they simply match no class) unless
+``LIGER_B200_CHECK_TARGETS=1`` asks for the reference's assertion.
 """
 
 from __future__ import annotations
@@ -75,6 +76,8 @@ def cross_entropy_forward(_input, target, weight, ignore_index, lse_square_scale
     fo = _as_forward_out(out)
     with _fl._device_guard(dev):
         check(lib.flce_b200_ce_forward(C.byref(prep.problem), _ptr(norm), _ptr(rowstats), C.byref(fo), _fl._stream(dev)))
+    if _fl.CHECK_TARGETS:      # the reference's assertion (ops/cross_entropy.py:389-392), at the price of a host synchronisation
+        _fl._raise_on_bad_targets(norm, prep.vocab)
     if reduction == "none":
         loss = out["loss_rows"].to(prep.dtype)
         z_loss = out["z_loss_rows"].to(prep.dtype) if return_z_loss else None

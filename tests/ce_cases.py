@@ -106,3 +106,57 @@ def case_reference_golden(device, name):
     assert_close(res["grad"], want, (8e-3 if low else 5e-6) * float(want.abs().max()), 2e-2 if low else 1e-3, "grad vs reference")
     assert_close(res["loss"], torch.from_numpy(rec["ref_loss"]), 0.0 if low else 2e-5 * max(1.0, float(np.abs(rec["ref_loss"]).max())),
                  1e-2 if low else 2e-4, "loss vs reference")
+
+
+def case_true_class_gradient_confident_predictions(device, dtype, label_smoothing, reduction):
+    """The reference's test of the same name (test/transformers/test_cross_entropy.py:1282-1324): once the model is confident,
+    dx_y = (softmax(x_y) - (1 - label_smoothing)) / N is a small difference of large terms and must be formed before rounding to
+    the logits' dtype.  Required: no less accurate than torch's own low-precision backward (within a factor of 4)."""
+    import liger_kernel_b200 as lk
+
+    torch.manual_seed(0)
+    n, v = 96, 4096
+    logits = torch.randn(n, v)
+    target = torch.randint(0, v, (n,))
+    logits[torch.arange(n), target] = logits.max(dim=-1).values + 10.0
+    low = logits.to(dtype)
+    ours = low.to(device).clone().requires_grad_(True)
+    theirs = low.clone().requires_grad_(True)
+    exact = low.clone().float().requires_grad_(True)
+    torch_ce = torch.nn.CrossEntropyLoss(reduction=reduction, label_smoothing=label_smoothing)
+    torch_ce(theirs, target).backward()
+    torch_ce(exact, target).backward()
+    lk.LigerCrossEntropyLoss(reduction=reduction, label_smoothing=label_smoothing)(ours, target.to(device)).backward()
+    rows = torch.arange(n)
+    ref = exact.grad[rows, target].double()
+    torch_err = float((theirs.grad[rows, target].double() - ref).abs().max())
+    our_err = float((ours.grad.cpu()[rows, target].double() - ref).abs().max())
+    assert our_err <= max(4 * torch_err, torch.finfo(dtype).tiny), (our_err, torch_err)
+
+
+def case_forward_only_structured_output_and_target_check(device):
+    """No-grad forward (test_correctness_with_forward_only), the CrossEntropyOutput convention of the module
+    (test_liger_cross_entropy_structured_output) and the optional out-of-range-target assertion
+    (test_correctness_with_out_of_bounds_target_once)."""
+    import liger_kernel_b200 as lk
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as fl
+
+    logits, t = random_case(50, 300, torch.bfloat16, dict())
+    with torch.no_grad():
+        loss = lk.LigerCrossEntropyLoss()(logits.to(device), t.to(device))
+    assert torch.is_tensor(loss) and loss.shape == () and not loss.requires_grad
+    assert_close(loss.float().cpu(), ce_oracle(logits, t).loss.float(), 1e-2, 1e-2, "loss")
+    out = lk.LigerCrossEntropyLoss(lse_square_scale=1e-3, return_z_loss=True, return_token_accuracy=True,
+                                   return_predicted_tokens=True)(logits.to(device), t.to(device))
+    assert isinstance(out, lk.CrossEntropyOutput)
+    assert out.z_loss is not None and out.token_accuracy is not None and out.predicted_tokens.shape == (50,)
+    bad = t.clone()
+    bad[3] = 300
+    before = fl.CHECK_TARGETS
+    fl.CHECK_TARGETS = True
+    try:
+        with pytest.raises(AssertionError, match="out of bounds"):
+            lk.LigerCrossEntropyLoss()(logits.to(device), bad.to(device))
+        lk.LigerCrossEntropyLoss()(logits.to(device), t.to(device))
+    finally:
+        fl.CHECK_TARGETS = before

@@ -116,6 +116,14 @@ def case_jsd_multichunk_equals_single_chunk(device, dtype=torch.bfloat16):
     assert_close(many["grad_weight"], one["grad_weight"], (1e-2 if dtype != torch.float32 else 1e-6) * gmax, 1e-2, "grad_weight")
 
 
+def case_jsd_all_ignored(device):
+    """Every label ignored (the reference's test_correctness_all_ignored): zero loss, zero gradients, nothing undefined."""
+    xs, ws, xt, wt, _ = jsd_inputs(48, 16, 32, 131, torch.bfloat16, seed=4)
+    labels = torch.full((48,), 2)
+    res = run_jsd(device, xs, ws, xt, wt, labels, jsd_beta=0.1, ignore_index=2, temperature=2.0)
+    assert float(res["loss"]) == 0.0 and float(res["grad_input"].abs().max()) == 0.0 and float(res["grad_weight"].abs().max()) == 0.0
+
+
 def case_jsd_weight_without_grad_and_second_backward(device):
     import liger_kernel_b200 as lk
     import pytest

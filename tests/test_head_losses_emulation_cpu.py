@@ -49,6 +49,11 @@ def test_jsd_multichunk(monkeypatch, dtype):
         assert lib.calls.count("flce_b200_jsd_rows") == 1 + 3        # one chunk, then 530 rows in chunks of 256
 
 
+def test_jsd_all_ignored(monkeypatch):
+    with emu_lib.installed(monkeypatch):
+        cases.case_jsd_all_ignored("cpu")
+
+
 def test_jsd_weight_without_grad_and_second_backward(monkeypatch):
     with emu_lib.installed(monkeypatch) as lib:
         cases.case_jsd_weight_without_grad_and_second_backward("cpu")

@@ -52,6 +52,18 @@ def test_ce_against_reference_golden(monkeypatch, name):
         ce_cases.case_reference_golden("cpu", name)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("label_smoothing,reduction", [(0.0, "mean"), (0.1, "sum")])
+def test_ce_true_class_gradient_confident_predictions(monkeypatch, dtype, label_smoothing, reduction):
+    with emu_lib.installed(monkeypatch):
+        ce_cases.case_true_class_gradient_confident_predictions("cpu", dtype, label_smoothing, reduction)
+
+
+def test_ce_forward_only_structured_output_and_target_check(monkeypatch):
+    with emu_lib.installed(monkeypatch):
+        ce_cases.case_forward_only_structured_output_and_target_check("cpu")
+
+
 def test_ce_rows_with_minus_inf_and_unaligned_views(monkeypatch):
     """-inf logits (masked classes) keep the statistics finite; a column-sliced view (row pitch not a multiple of 16
     bytes, base not 16-byte aligned) takes the scalar kernels and gives the same answer as the vectorised ones."""

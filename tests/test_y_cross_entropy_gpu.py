@@ -34,3 +34,14 @@ def test_ce_all_ignored_is_exact_zero():
 @pytest.mark.parametrize("name", ce_golden_names())
 def test_ce_against_reference_golden(name):
     ce_cases.case_reference_golden("cuda", name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("label_smoothing", [0.0, 0.1])
+@pytest.mark.parametrize("reduction", ["sum", "mean"])
+def test_ce_true_class_gradient_confident_predictions(dtype, label_smoothing, reduction):
+    ce_cases.case_true_class_gradient_confident_predictions("cuda", dtype, label_smoothing, reduction)
+
+
+def test_ce_forward_only_structured_output_and_target_check():
+    ce_cases.case_forward_only_structured_output_and_target_check("cuda")

@@ -39,6 +39,10 @@ def test_jsd_multichunk(dtype):
     cases.case_jsd_multichunk_equals_single_chunk("cuda", dtype)
 
 
+def test_jsd_all_ignored():
+    cases.case_jsd_all_ignored("cuda")
+
+
 def test_jsd_weight_without_grad_and_second_backward():
     cases.case_jsd_weight_without_grad_and_second_backward("cuda")
 
