@@ -159,3 +159,26 @@ def test_extras_gpu_bodies(emulated, monkeypatch):
     finally:
         # torch.autocast saved the simulated "enabled" answer on entry and wrote it back on exit: clear the real state
         torch.set_autocast_enabled("cuda", False)
+
+
+def test_module_forward_only_structured_output_and_metrics(emulated):
+    """After the reference's test_correctness_with_forward_only, test_liger_fused_linear_cross_entropy_structured_output,
+    test_correctness_with_token_accuracy and test_correctness_with_predicted_tokens."""
+    import liger_kernel_b200 as lk
+
+    x, w, t, b, _ = make_inputs(90, 32, 300, torch.bfloat16, seed=13, bias=True)
+    ora = oracle_for(x, w, t, bias=b, lse_square_scale=1e-3)
+    with torch.no_grad():
+        loss = lk.LigerFusedLinearCrossEntropyLoss()(w, x, t, b)
+    assert torch.is_tensor(loss) and not loss.requires_grad and emulated.calls.count("flce_b200_backward") == 0
+    assert_close(loss, oracle_for(x, w, t, bias=b).loss.float(), 1e-4, 1e-4, "forward-only loss")
+    out = lk.LigerFusedLinearCrossEntropyLoss(lse_square_scale=1e-3, return_z_loss=True, return_token_accuracy=True,
+                                              return_predicted_tokens=True)(w, x, t, b)
+    assert isinstance(out, lk.CrossEntropyOutput)
+    assert_close(out.loss, ora.loss.float(), 1e-4, 1e-4, "loss")
+    assert out.z_loss.dtype == torch.bfloat16                                    # z-loss comes back in the operands' dtype
+    assert_close(out.z_loss.float(), ora.z_loss.float(), 1e-2 * float(ora.z_loss), 1e-2, "z_loss")
+    assert torch.equal(out.predicted_tokens, ora.predicted_tokens)
+    np.testing.assert_allclose(float(out.token_accuracy), float(ora.token_accuracy), rtol=1e-6)
+    only_loss = lk.liger_fused_linear_cross_entropy(x, w, t, b)
+    assert torch.is_tensor(only_loss)
