@@ -182,3 +182,38 @@ def test_module_forward_only_structured_output_and_metrics(emulated):
     np.testing.assert_allclose(float(out.token_accuracy), float(ora.token_accuracy), rtol=1e-6)
     only_loss = lk.liger_fused_linear_cross_entropy(x, w, t, b)
     assert torch.is_tensor(only_loss)
+
+
+def test_tiny_llama_trains_the_same_with_the_patched_head(emulated):
+    """Convergence in miniature (the reference's test/convergence idea): a 2-layer llama takes five optimiser steps with the
+    Hugging Face loss and five with the patched forward (fused operator through the emulation); the loss curves coincide."""
+    transformers = pytest.importorskip("transformers")
+    import copy
+
+    import liger_kernel_b200 as lk
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=97, max_position_embeddings=64)
+    plain = transformers.LlamaForCausalLM(cfg)
+    patched = copy.deepcopy(plain)
+    lk.apply_liger_kernel_to_llama(rope=False, rms_norm=False, swiglu=False, model=patched)
+    g = torch.Generator().manual_seed(1)
+    batches = [torch.randint(1, 97, (2, 12), generator=g) for _ in range(5)]
+    curves = []
+    for model in (plain, patched):
+        model.train()
+        opt = torch.optim.SGD(model.parameters(), lr=0.05)
+        losses = []
+        for ids in batches:
+            labels = ids.clone()
+            labels[:, :3] = -100
+            out = model(input_ids=ids, labels=labels)
+            opt.zero_grad()
+            out.loss.backward()
+            opt.step()
+            losses.append(float(out.loss.detach()))
+        curves.append(losses)
+    assert emulated.calls.count("flce_b200_forward") == 5 and emulated.calls.count("flce_b200_backward") == 5
+    np.testing.assert_allclose(curves[1], curves[0], rtol=2e-4, atol=2e-4)
+    assert curves[0][-1] < curves[0][0]                                          # and it does learn
