@@ -175,3 +175,26 @@ def test_loss_utils_shift_and_unpack():
     assert unpack_cross_entropy_result((t, 2)) == (t, 2, None, None)
     o = CrossEntropyOutput(loss=t, token_accuracy=torch.tensor(0.5))
     assert unpack_cross_entropy_result(o)[2] == torch.tensor(0.5)
+
+
+def test_class_level_patch_for_every_family():
+    """Without a model instance the switch rebinds the causal-LM class's forward (and nothing else); restored afterwards."""
+    import importlib
+
+    import liger_kernel_b200 as lk
+    from liger_kernel_b200.transformers import monkey_patch as mp
+
+    for family in mp._FAMILIES:
+        if family.forward is None:
+            continue
+        try:
+            module = importlib.import_module(family.module)
+        except ImportError:
+            continue
+        cls = getattr(module, family.class_name)
+        original = cls.forward
+        try:
+            getattr(lk, f"apply_liger_kernel_to_{family.name}")(**{name: False for name, _ in family.other_flags})
+            assert cls.forward is family.forward, family.name
+        finally:
+            cls.forward = original
