@@ -251,16 +251,20 @@ def run_liger(args, spec, rank, world, local_rank):
             step()
         torch.cuda.synchronize()
         torch.cuda.reset_peak_memory_stats()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+        with ClockSampler(local_rank) as clocks:
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+            marks[0].record()
+            for i in range(args.steps):
+                step()
+                marks[i + 1].record()
+            torch.cuda.synchronize()
     except Exception as e:  # noqa: BLE001
         print(json.dumps({"impl": args.impl, "unavailable": f"run failed: {type(e).__name__}: {e}"[:300]}))
         return
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = marks[0].elapsed_time(marks[-1]) / args.steps
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
+    quantiles = {f"p{q}": per_step[min(len(per_step) - 1, int(q / 100 * len(per_step)))] for q in (20, 50, 80)}
+    clock_info = clocks.summary()
     peaks = load_peaks()
     tflops = 8.0 * N * H * V / (ms * 1e-3) / 1e12
     print(json.dumps({
@@ -269,7 +273,51 @@ def run_liger(args, spec, rank, world, local_rank):
         "data": "synthetic", "config": {"workload": NAMES[args.workload], "accum_dtype": "fp32" if args.accum_fp32 else None},
         "tflops_credited_8NHV": tflops, "frac_of_burst": tflops / peaks["burst"],
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+        "ms_per_step_quantiles": quantiles,
+        "clocks": {"sm_mhz": clock_info["sm_mhz"], "sm_max_mhz": clock_info["sm_max_mhz"], "reasons": clock_info["reasons"]},
     }))
+
+
+COMPARATORS = [
+    # name in the bench line, extra command-line arguments
+    ("liger_triton", ["--impl", "liger_triton"]),
+    ("liger_triton_accum_fp32", ["--impl", "liger_triton", "--accum-fp32"]),
+    ("liger_cutedsl", ["--impl", "liger_cutedsl"]),
+    ("torch_gpu", ["--impl", "torch_gpu"]),
+]
+
+
+def run_comparators(args, timeout_s):
+    """The reference's own GPU operators and plain torch on the same box, same inputs (same seed), same steps and the same
+    CUDA-event timing, each in a child process of its own (a fresh CUDA context, nothing of this library loaded)."""
+    out = {}
+    for name, extra in COMPARATORS:
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", args.workload, "--steps", str(args.steps),
+               "--warmup", str(args.warmup)] + extra
+        t0 = time.perf_counter()
+        try:
+            proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, stdin=subprocess.DEVNULL)
+        except subprocess.TimeoutExpired:
+            out[name] = {"unavailable": f"no result within {timeout_s} s"}
+            continue
+        rec = None
+        for line in reversed(proc.stdout.strip().splitlines()):
+            if line.startswith("{"):
+                try:
+                    rec = json.loads(line)
+                    break
+                except ValueError:
+                    continue
+        if rec is None:
+            tail = (proc.stderr or proc.stdout or "").strip().splitlines()[-1:] or [""]
+            out[name] = {"unavailable": f"exit code {proc.returncode}: {tail[0][:200]}"}
+        elif "unavailable" in rec:
+            out[name] = {"unavailable": rec["unavailable"]}
+        else:
+            out[name] = {"ms_per_step": rec["ms_per_step"], "tokens_per_s": rec["value"], "peak_mem_gb": rec.get("peak_mem_gb"),
+                         "ms_per_step_quantiles": rec.get("ms_per_step_quantiles"), "clocks": rec.get("clocks"),
+                         "wall_s": round(time.perf_counter() - t0, 1)}
+    return out
 
 
 def run_ours(args, spec, rank, world, local_rank):
@@ -437,6 +485,7 @@ def run_ours(args, spec, rank, world, local_rank):
         for _ in range(args.warmup):
             step(x, t)
         torch.cuda.reset_peak_memory_stats()
+        _lib.profile_enable(True)
         barrier()
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s0.record()
@@ -445,12 +494,15 @@ def run_ours(args, spec, rank, world, local_rank):
         s1.record()
         barrier()
         ms_ss = s0.elapsed_time(s1) / args.steps
+        prof_ss = _lib.profile_read(reset=True)
+        _lib.profile_enable(False)
         flce_op.MODE = "recompute"
         result["single_sweep"] = {
             "ms_per_step": ms_ss, "value": tokens / (ms_ss * 1e-3), "unit": "tokens/s",
             "tflops_executed_6NHV": 6.0 * N * H * V / (ms_ss * 1e-3) / 1e12,
             "tflops_credited_8NHV": 8.0 * N * H * V / (ms_ss * 1e-3) / 1e12,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            "kernels_ms_per_step": {k: prof_ss[k][0] / args.steps for k in prof_ss},
             "note": "opt-in mode LIGER_B200_FLCE_MODE=single_sweep; the headline value above is the recompute mode",
         }
     if world == 1 and not args.no_cpu_baseline:
@@ -459,6 +511,12 @@ def run_ours(args, spec, rank, world, local_rank):
             "value": rate, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"first {rows} rows with the full H and V, fp32 torch Linear+CrossEntropy with autograd, {secs:.1f} s",
         }
+    if world == 1 and not args.no_comparators:
+        comps = run_comparators(args, args.comparator_timeout)
+        result["comparators"] = comps
+        liger_ms = [c["ms_per_step"] for n, c in comps.items() if n.startswith("liger") and "ms_per_step" in c]
+        # below 1 means this library's step is shorter than the fastest of the reference's own GPU paths on this box
+        result["vs_liger_best"] = (ms_step / min(liger_ms)) if liger_ms else None
     print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
@@ -477,6 +535,9 @@ def main():
     ap.add_argument("--mode", default=None, choices=["recompute", "single_sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true", dest="no_variants")
+    ap.add_argument("--no-comparators", action="store_true", dest="no_comparators",
+                    help="skip the reference's GPU operators and plain torch (timed after the main measurement at --gpus 1)")
+    ap.add_argument("--comparator-timeout", type=int, default=180, dest="comparator_timeout", help="seconds per comparator")
     ap.add_argument("--sharding", default="token", choices=["token", "vocab"])
     ap.add_argument("--overlap", action="store_true", help="all-reduce grad_weight slab by slab on a side stream")
     ap.add_argument("--strong", action="store_true", help="fixed global batch split over the ranks (token sharding)")

@@ -84,7 +84,8 @@ def _pad_hidden(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
 
 _X_TERMS = (0, 0, 0, 1, 1, 2)   # paired with _W_TERMS: x0w0 + x0w1 + x0w2 + x1w0 + x1w1 + x2w0 = x.w to ~2^-24
 _W_TERMS = (0, 1, 2, 0, 1, 0)
-_PROJ_TERMS = (0, 1)            # projections use the two leading terms (2^-16)
+_PROJ_TERMS = (0, 1)            # projections use the two leading terms: each product good to about 2^-16, so a
+                                # gradient element is good to a few 1e-4 of the largest entry at V = 128k, not to fp32 ulp
 
 
 def _split_fp32(t: torch.Tensor, pattern, block_cols: int) -> torch.Tensor:

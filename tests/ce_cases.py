@@ -1,4 +1,4 @@
-"""Shared bodies of the stand-alone cross-entropy tests: the same cases run on a B200 (tests/test_y_cross_entropy_gpu.py)
+"""Shared bodies of the stand-alone cross-entropy tests: the same cases run on a B200 (tests/test_cross_entropy_gpu.py)
 and, with the library's SIMT kernels emulated on the host, on CPU tensors (tests/test_simt_emulation_cpu.py)."""
 
 import numpy as np

@@ -1,11 +1,6 @@
 """LIGER_B200_FLCE_SKIP_IGNORED: rows whose target is ignore_index are moved to the end on the device and the sweeps
 skip the token tiles that hold only such rows.  Results must equal the plain path (loss to rounding of the summation
-order, gradients to a 16-bit ulp) and the oracle, for any ignored fraction including none and all.
-
-The compaction kernels and the dynamic tile counts compile and are wired in, but have not run on a GPU yet; until they
-have, this file only runs when LIGER_B200_RUN_UNVALIDATED=1 is set."""
-
-import os
+order, gradients to a 16-bit ulp) and the oracle, for any ignored fraction including none and all."""
 
 import pytest
 import torch
@@ -13,9 +8,7 @@ import torch
 from flce_cases import assert_close, make_inputs, oracle_for, run_cuda
 from test_flce_gpu import _check
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("LIGER_B200_RUN_UNVALIDATED") != "1",
-                                 reason="row compaction not yet validated on a GPU")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture

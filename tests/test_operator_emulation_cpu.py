@@ -130,9 +130,9 @@ def test_logit_gaps_of_several_hundred_stay_finite(emulated):
 
 @pytest.mark.parametrize("ignore_frac", [0.0, 0.5, 0.97])
 def test_skip_ignored_gpu_bodies(emulated, monkeypatch, ignore_frac):
-    """The bodies of tests/test_y_skip_ignored_gpu.py at a size the emulation handles."""
+    """The bodies of tests/test_flce_skip_ignored_gpu.py at a size the emulation handles."""
     import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
-    import test_y_skip_ignored_gpu as skip_tests
+    import test_flce_skip_ignored_gpu as skip_tests
 
     monkeypatch.setattr(mod, "SKIP_IGNORED", True)
     skip_tests.test_skip_ignored_matches_oracle_and_plain_path(mod, monkeypatch, 300, 31, 123, ignore_frac)
@@ -142,9 +142,9 @@ def test_skip_ignored_gpu_bodies(emulated, monkeypatch, ignore_frac):
 
 
 def test_extras_gpu_bodies(emulated, monkeypatch):
-    """The bodies of tests/test_x_extras_gpu.py: out-of-range targets, the full-size property checks at a reduced size, and
+    """The bodies of tests/test_flce_full_size_gpu.py: out-of-range targets, the full-size property checks at a reduced size, and
     automatic mixed precision (the CUDA autocast state is simulated: this box has no GPU for torch.autocast to act on)."""
-    import test_x_extras_gpu as extras
+    import test_flce_full_size_gpu as extras
 
     extras.test_out_of_range_targets_are_counted_and_optionally_raised(monkeypatch)
     monkeypatch.setattr(extras, "FULL_SIZE", {"small_qwen_style": (300, 32, 1300, 0.2, dict(label_smoothing=0.1, lse_square_scale=1e-4)),
