@@ -338,6 +338,10 @@ def run_ours(args, spec, rank, world, local_rank):
     import liger_kernel_b200.ops.fused_linear_cross_entropy as flce_op
     if args.mode is not None:
         flce_op.MODE = args.mode
+    if args.store is not None:
+        flce_op.STORE_MODE = args.store
+    if args.wide_tiles is not None:
+        _lib.set_option("wide_tiles", args.wide_tiles)
     peaks = load_peaks()
     from liger_kernel_b200.sharded import vocab_sharded_fused_linear_cross_entropy
 
@@ -442,15 +446,22 @@ def run_ours(args, spec, rank, world, local_rank):
     strong = world > 1 and (args.strong or args.sharding == "vocab")
     tokens = N if strong else N * world
     value = tokens / (ms_step * 1e-3)
-    flops_step = 8.0 * N * H * V / (world if strong else 1)  # per rank
+    flops_step = 8.0 * N * H * V / (world if strong else 1)  # per rank, as the metric credits them
     tflops = flops_step / (ms_step * 1e-3) / 1e12
-    kind_flops = 2.0 * N * H * V * args.steps / (world if strong else 1)  # algorithmic flops of each kernel kind, per rank
-    dom = max(("stats", "dz", "dw", "dx"), key=lambda k: prof[k][0])
+    # Each tensor-core kernel kind multiplies this rank's live rows (targets that are not ignore_index: the others are
+    # moved out of the way and skipped) by H x V (its share of the vocabulary) once: 2 * rows * H * V executed FLOPs.
+    rows_here = x.shape[0]
+    live_here = int((t != -100).sum().item()) if flce_op.SKIP_IGNORED else rows_here
+    kind_flops = 2.0 * live_here * H * w.shape[0] * args.steps
+    kinds = [k for k in ("stats", "dz", "dw", "dx") if prof[k][0] > 0]
+    dom = max(kinds, key=lambda k: prof[k][0])
     dom_ms, dom_launches = prof[dom]
     achieved = kind_flops / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
     per_kind = {k: {"ms_per_step": prof[k][0] / args.steps, "launches_per_step": prof[k][1] / args.steps,
-                    "tflops": (kind_flops / (prof[k][0] * 1e-3) / 1e12) if prof[k][0] > 0 else None}
+                    "tflops_executed": (kind_flops / (prof[k][0] * 1e-3) / 1e12) if prof[k][0] > 0 else None}
                 for k in ("stats", "dz", "dw", "dx")}
+    per_kind["row_passes"] = {"ms_per_step": prof["gemm"][0] / args.steps, "launches_per_step": prof["gemm"][1] / args.steps}
+    executed_step = sum(2.0 * live_here * H * w.shape[0] for k in kinds)
     result = {
         "metric": "flce_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -460,14 +471,21 @@ def run_ours(args, spec, rank, world, local_rank):
                        f"vocab-sharded x{world}: all-gather of row statistics, all-reduce of grad_input" if args.sharding == "vocab"
                        else f"token-sharded x{world}, NCCL all-reduce of grad_weight"),
                    "l2_policy": "inputs larger than L2 (weight alone is %.2f GB)" % (V * H * 2 / 1e9),
-                   "cta_pair": args.cta_pair, "raster_mb": args.raster_mb, "mode": flce_op.MODE},
+                   "cta_pair": args.cta_pair, "raster_mb": args.raster_mb, "mode": flce_op.MODE,
+                   "store": flce_op.STORE_MODE, "skip_ignored_rows": flce_op.SKIP_IGNORED},
         "tflops_per_gpu": tflops,
+        "tflops_per_gpu_executed": executed_step / (ms_step * 1e-3) / 1e12,
+        "flops_note": "tflops_per_gpu credits 8.N.H.V per step as the metric defines it; executed = 2.rows.H.V per tensor-core "
+                      "sweep actually run (3 sweeps when gradients are formed in forward, 4 with recompute), rows = targets "
+                      "that are not ignore_index",
+        "live_rows_per_gpu": live_here,
         "frac_of_bf16_peak": {"burst": tflops / peaks["burst"], "sustained": tflops / peaks["sustained"], "peaks": peaks["source"]},
         "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["sustained"], "frac_of_burst": achieved / peaks["burst"],
                      "launches": dom_launches, "avg_launch_ms": dom_ms / max(1, dom_launches),
                      "peak_kind": f"sustained bf16 GEMM, {peaks['source']}",
-                     "traffic": NCU_DRAM_BYTES_PER_UNIT[dom] * N * V / (world if strong else 1) * args.steps / max(1, dom_launches),
+                     "flops_basis": "executed: 2 x live rows x H x V per step for this kernel kind",
+                     "traffic": NCU_DRAM_BYTES_PER_UNIT[dom] * live_here * w.shape[0] * args.steps / max(1, dom_launches),
                      "traffic_note": "ncu capture of the N=8192,V=32768 case scaled by rows x columns per launch"},
         "kernels": per_kind,
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
@@ -480,8 +498,9 @@ def run_ours(args, spec, rank, world, local_rank):
                    "samples": clock_info["samples"]},
     }
     if world == 1 and args.mode is None and not args.no_variants:
-        # the same workload with gradients formed in forward from a bounded 16-bit logits copy (6.N.H.V executed FLOPs)
-        flce_op.MODE = "single_sweep"
+        # the same workload on the two-sweep path (logits recomputed in backward: 8.N.H.V executed, least memory)
+        default_mode = flce_op.MODE
+        flce_op.MODE = "recompute"
         for _ in range(args.warmup):
             step(x, t)
         torch.cuda.reset_peak_memory_stats()
@@ -496,14 +515,14 @@ def run_ours(args, spec, rank, world, local_rank):
         ms_ss = s0.elapsed_time(s1) / args.steps
         prof_ss = _lib.profile_read(reset=True)
         _lib.profile_enable(False)
-        flce_op.MODE = "recompute"
-        result["single_sweep"] = {
+        flce_op.MODE = default_mode
+        result["recompute_mode"] = {
             "ms_per_step": ms_ss, "value": tokens / (ms_ss * 1e-3), "unit": "tokens/s",
-            "tflops_executed_6NHV": 6.0 * N * H * V / (ms_ss * 1e-3) / 1e12,
             "tflops_credited_8NHV": 8.0 * N * H * V / (ms_ss * 1e-3) / 1e12,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
             "kernels_ms_per_step": {k: prof_ss[k][0] / args.steps for k in prof_ss},
-            "note": "opt-in mode LIGER_B200_FLCE_MODE=single_sweep; the headline value above is the recompute mode",
+            "note": "LIGER_B200_FLCE_MODE=recompute: forward keeps nothing of size N x V, backward recomputes the logit tiles; "
+                    "the headline value above is the default mode (gradients formed in forward from a bounded 16-bit copy)",
         }
     if world == 1 and not args.no_cpu_baseline:
         rate, rows, secs = cpu_reference_rate(spec, seconds_budget=12.0)
@@ -532,7 +551,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cta-pair", type=int, default=None, dest="cta_pair")
     ap.add_argument("--raster-mb", type=int, default=None, dest="raster_mb")
-    ap.add_argument("--mode", default=None, choices=["recompute", "single_sweep"])
+    ap.add_argument("--mode", default=None, choices=["recompute", "single_sweep", "auto"])
+    ap.add_argument("--store", default=None, choices=["auto", "logits", "exp"], help="what the single-sweep mode keeps of a chunk")
+    ap.add_argument("--wide-tiles", type=int, default=None, dest="wide_tiles")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true", dest="no_variants")
     ap.add_argument("--no-comparators", action="store_true", dest="no_comparators",

@@ -117,7 +117,19 @@ typedef struct flce_fused_args {
   void* grad_input;              /* [n_rows, hidden] dense, or NULL                                           */
   void* grad_weight;             /* [vocab, hidden] dense, or NULL                                            */
   float* grad_bias;              /* [vocab] fp32, or NULL                                                     */
+  int32_t norm_given;            /* 1: norm is an input (already counted, e.g. all-reduced over token shards)  */
+  int32_t store_mode;            /* flce_store_mode_t: what the bounded 16-bit copy of a chunk holds          */
 } flce_fused_args_t;
+
+/* The single-sweep mode keeps a bounded 16-bit copy of each token chunk's logits.  FLCE_STORE_LOGITS keeps the
+ * soft-capped logits and turns them into the logit gradient in place with one more pass once the chunk's
+ * log-sum-exp is known (the reference's structure).  FLCE_STORE_EXP keeps E = exp(logit - shift) instead, with a
+ * per-row reference point computed up front from the target logit: the gradient GEMMs consume E as it is (the
+ * per-row factor exp(shift - lse) moves into their epilogue or other operand, the uniform label-smoothing term
+ * becomes a rank-1 correction), so the extra pass disappears and every stored value is good to one 16-bit ulp
+ * whatever the logit's size.  It needs bf16 operands (the stored values span e^-87 .. e^60) and does not cover label
+ * smoothing combined with a soft-cap, nor grad_bias; FLCE_STORE_AUTO picks it wherever it applies. */
+typedef enum { FLCE_STORE_AUTO = 0, FLCE_STORE_LOGITS = 1, FLCE_STORE_EXP = 2 } flce_store_mode_t;
 
 enum { FLCE_PHASE_FORWARD = 0, FLCE_PHASE_BACKWARD = 1, FLCE_PHASE_FUSED = 2, FLCE_PHASE_BACKWARD_SPLIT = 3 };
 

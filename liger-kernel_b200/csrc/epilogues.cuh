@@ -31,6 +31,14 @@ __device__ __forceinline__ void store32_16bit(uint4* dst, const float (&g)[32], 
   }
 }
 
+// Largest exponent (natural log units) the exp-store form of sweep 1 writes: exp(60) times a vocabulary-long sum stays far
+// inside fp32, and with the reference point 40 above the target logit a row would need a loss of 100 nats to reach it.
+constexpr float kExpStoreClamp = 60.f;
+constexpr float kExpStoreOffset = 40.f;
+// lse - shift above this (a loss above 90 nats with the offset of 40) sends the chunk through sweep 1 once more with
+// shift = lse, where every stored value is a probability
+constexpr float kExpStoreRedoLimit = 50.f;
+
 // =====================================================================================
 // Sweep 1: logits tile -> per-(row, tile) softmax statistics.  Nothing of size N x V is stored.
 // Feature tests are hoisted out of the per-element loops: each optional stage is one uniform
@@ -54,11 +62,18 @@ struct StatsEpilogue {
     void* logits_out;         // optional [M][ld_logits] 16-bit copy of the soft-capped logits (single-sweep mode) or null
     long long ld_logits;
     int logits_fmt;           // kOutBf16 / kOutFp16
+    // With `shift` ([M], a per-row reference point near the row's log-sum-exp) the copy holds, instead of the logits s,
+    //   E = exp(min(s - shift, kExpStoreClamp)) * (1 - (s / softcap)^2)      (zeros on rows whose target is ignore_index),
+    // i.e. the softmax numerator up to a per-row factor, with the soft-cap chain factor folded in: the gradient GEMMs
+    // take it as an operand as it is and the per-row factor exp(shift - lse) moves into their epilogue / other operand.
+    // Unlike rounded logits, E keeps a relative accuracy of one 16-bit ulp whatever the logit's magnitude.
+    const float* shift;
+    long long ignore_index;
   };
 
-  float m, d, ssum, best;
+  float m, d, ssum, best, shift2;
   int best_idx, row, nt, tgt_local;
-  bool row_ok;
+  bool row_ok, row_live;
 
   __device__ __forceinline__ void begin(const Params& p, int row_, int /*col0*/, int n_tile, bool ok) {
     row = row_;
@@ -70,9 +85,16 @@ struct StatsEpilogue {
     best = -INFINITY;
     best_idx = 0;
     tgt_local = -1;
+    shift2 = 0.f;
+    row_live = false;
     if (ok) {
-      const long long t = p.target[row] - p.vocab_offset;
+      const long long y = p.target[row];
+      const long long t = y - p.vocab_offset;
       if (t >= 0 && t < p.n_cols) tgt_local = static_cast<int>(t);
+      if (p.shift != nullptr) {
+        shift2 = p.shift[row] * kLog2e;
+        row_live = y != p.ignore_index;
+      }
     }
   }
 
@@ -89,9 +111,33 @@ struct StatsEpilogue {
 #pragma unroll
       for (int j = 0; j < 32; ++j) s[j] = p.softcap * tanh_accurate(s[j] * p.inv_softcap);
     }
-    if (p.logits_out != nullptr && row_ok)
+    if (p.logits_out != nullptr && p.shift == nullptr && row_ok)
       store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.logits_out) + static_cast<size_t>(row) * p.ld_logits + col),
                     s, p.logits_fmt);
+    if (p.logits_out != nullptr && p.shift != nullptr && row_ok) {
+      float e[32];
+      if (row_live) {
+        const float lim = kExpStoreClamp * kLog2e;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) e[j] = ex2_approx(fminf(fmaf(s[j], kLog2e, -shift2), lim));
+        if (p.softcap > 0.f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float th = s[j] * p.inv_softcap;
+            e[j] *= fmaf(-th, th, 1.f);
+          }
+        }
+        if (ragged) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) e[j] = (col + j < p.n_cols) ? e[j] : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) e[j] = 0.f;
+      }
+      store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.logits_out) + static_cast<size_t>(row) * p.ld_logits + col),
+                    e, p.logits_fmt);
+    }
     if (ragged) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) s[j] = (col + j < p.n_cols) ? s[j] : -INFINITY;
@@ -448,6 +494,10 @@ struct ScaledDzEpilogue {
 //   acc_out != null : acc_out[row][col] = v     (fp32 partial for later slabs)
 //   out     != null : out[row][col] = cast(v)   (final result, out_fmt)
 // n_cols must be a multiple of 8 and ld_* keep rows 16-byte aligned.
+// Optional, applied to the accumulator before anything else (the exp-store form of the single-sweep mode):
+//   row_scale != null : v *= row_scale[row]                       (per-row softmax factor of grad_input)
+//   r1_col    != null : v -= r1_row[row] * r1_col[col]            (r1_row null = 1; the uniform label-smoothing term,
+//                                                                  a rank-1 matrix, never formed)
 // =====================================================================================
 struct StoreEpilogue {
   struct Params {
@@ -458,14 +508,24 @@ struct StoreEpilogue {
     void* out;
     long long ld_out;
     int out_fmt;
+    const float* row_scale;
+    const float* r1_row;
+    const float* r1_col;
   };
 
   int row;
   bool row_ok;
+  float scale, r1;
 
-  __device__ __forceinline__ void begin(const Params&, int row_, int, int, bool ok) {
+  __device__ __forceinline__ void begin(const Params& p, int row_, int, int, bool ok) {
     row = row_;
     row_ok = ok;
+    scale = 1.f;
+    r1 = 0.f;
+    if (ok) {
+      if (p.row_scale != nullptr) scale = p.row_scale[row];
+      if (p.r1_col != nullptr) r1 = p.r1_row != nullptr ? p.r1_row[row] : 1.f;
+    }
   }
 
   __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
@@ -473,6 +533,14 @@ struct StoreEpilogue {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+    if (p.row_scale != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= scale;
+    }
+    if (p.r1_col != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaf(-r1, __ldg(p.r1_col + min(col + j, p.n_cols - 1)), v[j]);
+    }
     if (p.acc_in != nullptr) {
       const float4* src = reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(row) * p.ld_acc + col);
 #pragma unroll

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "ce_kernels.cuh"
 #include "epilogues.cuh"
@@ -39,6 +40,7 @@ static int g_cta_pair = 1;                      // use CTA pairs (cta_group::2) 
 static int g_poll_sleep_ns = 0;                 // epilogue back-off while waiting for an accumulator
 static int g_l2_hints = 0;                      // 1: mark streamed operands evict-first and re-read ones evict-last
 static int g_n_group = 0;                       // n-fastest raster: n-tiles per group (0 = all)
+static int g_wide_tiles = 1;                    // 256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
 
 // ------------------------------------------------------------------ optional per-kernel timing
 // When enabled, every tensor-core launch is bracketed by a pair of CUDA events on the caller's stream;
@@ -158,11 +160,12 @@ static int operand_map(CUtensorMap* map, const Operand& op, int dtype, int tile_
 static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-template <int kCtas, int kAMajor, int kBMajor, class Epi>
+template <int kCtas, int kAMajor, int kBMajor, class Epi, int kNSub = 1>
 static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, const Operand& b, int dtype, long long M,
                             long long N, long long K, long long raster_row_bytes, bool n_fastest,
-                            const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows, int active_role) {
-  using Cfg = StageCfg<kCtas>;
+                            const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows, int active_role,
+                            int active_base, const int* gate) {
+  using Cfg = StageCfg<kCtas, kNSub>;
   CUtensorMap map_a, map_b;
   int rc = operand_map(&map_a, a, dtype, kBlockM);
   if (rc != FLCE_OK) return rc;
@@ -173,11 +176,13 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   shape.N = static_cast<int>(N);
   shape.K = static_cast<int>(K);
   shape.m_tiles = static_cast<int>(ceil_div(M, kBlockM * kCtas));
-  shape.n_tiles = static_cast<int>(ceil_div(N, kBlockN));
+  shape.n_tiles = static_cast<int>(ceil_div(N, kBlockN * kNSub));
   shape.k_blocks = static_cast<int>(ceil_div(K, kBlockK));
   shape.poll_sleep_ns = g_poll_sleep_ns;
   shape.active_rows = active_rows;
   shape.active_role = active_rows != nullptr ? active_role : 0;
+  shape.active_base = active_base;
+  shape.gate = gate;
   shape.hint_a = 0;
   shape.hint_b = 0;
   if (g_l2_hints) {
@@ -198,7 +203,7 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   const long long tiles = static_cast<long long>(shape.m_tiles) * shape.n_tiles;
   long long units = dev.sm_count / kCtas;
   if (units > tiles) units = tiles;
-  auto kernel = gemm_tcgen05_kernel<kCtas, kAMajor, kBMajor, Epi>;
+  auto kernel = gemm_tcgen05_kernel<kCtas, kAMajor, kBMajor, Epi, kNSub>;
   FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(units * kCtas), 1, 1);
@@ -225,15 +230,21 @@ template <int kAMajor, int kBMajor, class Epi>
 static int launch_gemm(const DeviceState& dev, int kind, bool pair, const Operand& a, const Operand& b, int dtype, long long M,
                        long long N, long long K, long long raster_row_bytes, bool n_fastest,
                        const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows = nullptr,
-                       int active_role = 0) {
+                       int active_role = 0, int active_base = 0, const int* gate = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "empty GEMM %lld x %lld x %lld", M, N, K);
   if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "GEMM extent does not fit 32 bits");
+  if constexpr (std::is_same<Epi, StoreEpilogue>::value) {
+    // long K, light epilogue, enough columns to fill 512-wide tiles: the wide form moves a quarter less data per product
+    if (pair && g_wide_tiles && K >= 2048 && N >= 1024)
+      return launch_gemm_impl<2, kAMajor, kBMajor, Epi, 2>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep,
+                                                           stream, active_rows, active_role, active_base, gate);
+  }
   if (pair)
     return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream,
-                                                      active_rows, active_role);
+                                                      active_rows, active_role, active_base, gate);
   return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream,
-                                                    active_rows, active_role);
+                                                    active_rows, active_role, active_base, gate);
 }
 
 // (the small SIMT kernels live in row_kernels.cuh)
@@ -321,6 +332,8 @@ struct FusedPlan {
   long long chunk_rows, ld_slab;
   int n_chunks, n_tiles;
   size_t plane, rowstats_bytes, coef_bytes, slab_bytes, acc_bytes, total;
+  // exp-store form: per-row reference points (all rows), per-chunk alpha and scaled copy of x, label-smoothing vectors
+  size_t shift_bytes, alpha_bytes, xs_bytes, vec_bytes, colsum_scratch_bytes, flag_bytes, exp_bytes;
 };
 static FusedPlan fused_plan(const flce_problem_t* p, size_t budget, bool need_acc) {
   FusedPlan f;
@@ -339,7 +352,14 @@ static FusedPlan fused_plan(const flce_problem_t* p, size_t budget, bool need_ac
   f.coef_bytes = align_up(static_cast<size_t>(f.chunk_rows) * 3 * sizeof(float), 256);
   f.slab_bytes = align_up(static_cast<size_t>(f.chunk_rows) * f.ld_slab * 2, 256);
   f.acc_bytes = (need_acc && f.n_chunks > 1) ? align_up(static_cast<size_t>(p->vocab) * p->hidden * sizeof(float), 256) : 0;
-  f.total = 5 * f.plane + f.rowstats_bytes + f.coef_bytes + f.slab_bytes + f.acc_bytes;
+  f.shift_bytes = align_up(static_cast<size_t>(p->n_rows) * sizeof(float), 256);
+  f.alpha_bytes = align_up(static_cast<size_t>(f.chunk_rows) * sizeof(float), 256);
+  f.xs_bytes = align_up(static_cast<size_t>(f.chunk_rows) * p->hidden * 2, 256);
+  f.vec_bytes = align_up(static_cast<size_t>(p->hidden) * sizeof(float), 256);          // one of: sum_j w_j W_j, sum_r c2_r x_r
+  f.colsum_scratch_bytes = align_up(static_cast<size_t>(kColsumSplits) * p->hidden * sizeof(float), 256);
+  f.flag_bytes = align_up(static_cast<size_t>(f.n_chunks) * sizeof(int), 256);
+  f.exp_bytes = f.shift_bytes + f.alpha_bytes + f.xs_bytes + 2 * f.vec_bytes + f.colsum_scratch_bytes + f.flag_bytes;
+  f.total = 5 * f.plane + f.rowstats_bytes + f.coef_bytes + f.slab_bytes + f.exp_bytes + f.acc_bytes;
   return f;
 }
 
@@ -500,6 +520,10 @@ int flce_b200_set_option(const char* name, int64_t value) {
     g_l2_hints = value != 0;
     return FLCE_OK;
   }
+  if (strcmp(name, "wide_tiles") == 0) {
+    g_wide_tiles = value != 0;
+    return FLCE_OK;
+  }
   if (strcmp(name, "raster_n_group") == 0) {
     if (value < 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "raster_n_group must be >= 0");
     g_n_group = static_cast<int>(value);
@@ -552,7 +576,7 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
     return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   const bool need_sum = p->label_smoothing > 0.f;
-  StatsEpilogue::Params ep;
+  StatsEpilogue::Params ep{};
   ep.target = reinterpret_cast<const long long*>(p->target);
   ep.bias = p->bias;
   ep.col_weight = p->ce_weight;
@@ -632,7 +656,7 @@ int flce_b200_forward_stats_static(const flce_problem_t* p, float* rowstats, voi
   // Every (row, tile) entry that the merge below reads is written by the sweep first, so nothing in the shared
   // array has to start at zero; only the caller's target-logit plane does.
   size_t next = 0;
-  StatsEpilogue::Params ep;
+  StatsEpilogue::Params ep{};
   ep.target = reinterpret_cast<const long long*>(p->target);
   ep.bias = p->bias;
   ep.col_weight = p->ce_weight;
@@ -793,7 +817,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
     }
     // ---- grad_weight[slab] = dZ^T . X        (M = cols, N = hidden, K = n_rows; both operands MN-major)
     if (args->grad_weight != nullptr) {
-      StoreEpilogue::Params ep;
+      StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(cols);
       ep.n_cols = static_cast<int>(px_cols);
       ep.acc_in = nullptr;
@@ -823,7 +847,7 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
     }
     // ---- grad_input (+)= dZ . W[slab]        (M = n_rows, N = hidden, K = cols; B is MN-major)
     if (args->grad_input != nullptr) {
-      StoreEpilogue::Params ep;
+      StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(p->n_rows);
       ep.n_cols = static_cast<int>(pw_cols);
       const bool first = s == 0, last = s == plan.n_slabs - 1;
@@ -856,18 +880,32 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
     if (args->grad_bias != nullptr) {
       colsum_kernel<<<static_cast<unsigned>(ceil_div(cols, 64)), 1024, 0, stream>>>(
           dz, plan.ld_dz, static_cast<int>(p->n_rows), static_cast<int>(cols), p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16,
-          args->grad_bias + v0);
+          args->grad_bias + v0, p->active_rows);
       FLCE_CUDA(cudaGetLastError());
       ++g_kernel_launches;
       if (split) {
         colsum_accumulate_kernel<<<static_cast<unsigned>(ceil_div(cols, 64)), 1024, 0, stream>>>(
             dz_lo, plan.ld_dz, static_cast<int>(p->n_rows), static_cast<int>(cols),
-            p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16, args->grad_bias + v0, 1);
+            p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16, args->grad_bias + v0, 1, p->active_rows);
         FLCE_CUDA(cudaGetLastError());
         ++g_kernel_launches;
       }
     }
   }
+  return FLCE_OK;
+}
+
+// out[c] (+)= sum_r scale[r] * mat[r, c] in two ordered stages (row_kernels.cuh)
+static int launch_scaled_colsum(const void* mat, long long ld, long long n_rows, long long n_cols, int fmt, const float* scale,
+                                float* scratch, float* out, bool accumulate, cudaStream_t stream) {
+  dim3 grid(static_cast<unsigned>(ceil_div(n_cols, 64)), kColsumSplits, 1);
+  scaled_colsum_stage1_kernel<<<grid, 1024, 0, stream>>>(static_cast<const uint16_t*>(mat), ld, static_cast<int>(n_rows),
+                                                         static_cast<int>(n_cols), fmt, scale, scratch);
+  FLCE_CUDA(cudaGetLastError());
+  scaled_colsum_stage2_kernel<<<static_cast<unsigned>(ceil_div(n_cols, 256)), 256, 0, stream>>>(
+      scratch, static_cast<int>(n_cols), out, accumulate ? 1 : 0);
+  FLCE_CUDA(cudaGetLastError());
+  g_kernel_launches += 2;
   return FLCE_OK;
 }
 
@@ -880,17 +918,31 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
   const flce_forward_out_t* out = args->out;
   if (out->lse == nullptr || out->loss_rows == nullptr || out->target_prob == nullptr)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "single-sweep mode needs out->lse, out->target_prob and out->loss_rows");
-  if (p->active_rows != nullptr) return fail(FLCE_ERR_UNSUPPORTED, "active_rows is not supported in single-sweep mode");
   if (p->reduction == FLCE_NONE)
     return fail(FLCE_ERR_UNSUPPORTED, "single-sweep mode forms gradients before the upstream gradient is known; "
                                       "reduction 'none' needs the two-sweep path");
+  if (p->vocab != p->vocab_total || p->vocab_offset != 0)
+    return fail(FLCE_ERR_UNSUPPORTED, "single-sweep mode needs the whole vocabulary (a vocabulary shard does not know the "
+                                      "row's log-sum-exp before the cross-rank merge): use the two-sweep path");
   if (args->grad_dtype != p->dtype && args->grad_dtype != FLCE_FP32)
     return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
+  if (args->store_mode < FLCE_STORE_AUTO || args->store_mode > FLCE_STORE_EXP)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad store_mode %d", args->store_mode);
   DeviceState* dev = nullptr;
   rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const bool grads_fp32 = args->grad_dtype == FLCE_FP32;
+  const bool smoothing = p->label_smoothing > 0.f;
+  // The exp-store form covers everything whose logit gradient is (per-row factor) x (stored value) plus rank-1 terms:
+  // not the uniform smoothing term under a soft-cap (its chain factor varies per element), and not the bias gradient
+  // (a column sum of the scaled gradient, which this form never materialises).  It needs bf16's exponent range:
+  // exp(s - shift) spans e^-87 .. e^60 here, fp16 holds e^-16 .. e^11.
+  const bool exp_ok = !(smoothing && p->softcap > 0.f) && args->grad_bias == nullptr && p->dtype == FLCE_BF16;
+  if (args->store_mode == FLCE_STORE_EXP && !exp_ok)
+    return fail(FLCE_ERR_UNSUPPORTED, "the exp-store form needs bf16 operands and does not cover label smoothing together "
+                                      "with a soft-cap, nor grad_bias");
+  const bool exp_store = args->store_mode == FLCE_STORE_LOGITS ? false : exp_ok;
   const FusedPlan plan = fused_plan(p, slab_budget_bytes, true);
   const bool use_acc = args->grad_weight != nullptr && !grads_fp32 && plan.n_chunks > 1;
   const size_t needed = plan.total - (use_acc ? 0 : plan.acc_bytes);
@@ -899,37 +951,66 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  float* planes = reinterpret_cast<float*>(ws);
-  float* chunk_stats = reinterpret_cast<float*>(ws + 5 * plan.plane);
-  float* c1 = reinterpret_cast<float*>(ws + 5 * plan.plane + plan.rowstats_bytes);
-  uint16_t* slab = reinterpret_cast<uint16_t*>(ws + 5 * plan.plane + plan.rowstats_bytes + plan.coef_bytes);
-  float* dw_acc = reinterpret_cast<float*>(ws + 5 * plan.plane + plan.rowstats_bytes + plan.coef_bytes + plan.slab_bytes);
+  size_t at = 0;
+  auto carve = [&](size_t bytes) { uint8_t* ptr = ws + at; at += bytes; return ptr; };
+  float* planes = reinterpret_cast<float*>(carve(5 * plan.plane));
+  float* chunk_stats = reinterpret_cast<float*>(carve(plan.rowstats_bytes));
+  float* c1 = reinterpret_cast<float*>(carve(plan.coef_bytes));
+  uint16_t* slab = reinterpret_cast<uint16_t*>(carve(plan.slab_bytes));
+  float* shift = reinterpret_cast<float*>(carve(plan.shift_bytes));
+  float* alpha = reinterpret_cast<float*>(carve(plan.alpha_bytes));
+  uint16_t* xs = reinterpret_cast<uint16_t*>(carve(plan.xs_bytes));
+  float* w_sum = reinterpret_cast<float*>(carve(plan.vec_bytes));     // sum_j w_j W[j, :]
+  float* x_sum = reinterpret_cast<float*>(carve(plan.vec_bytes));     // sum_r c2_r x[r, :]
+  float* colsum_scratch = reinterpret_cast<float*>(carve(plan.colsum_scratch_bytes));
+  int* redo_flags = reinterpret_cast<int*>(carve(plan.flag_bytes));     // one per chunk: sweep 1 again with shift = lse
+  float* dw_acc = reinterpret_cast<float*>(carve(0));                  // last: present only when use_acc
 
-  rc = flce_b200_count(p, args->norm, stream_);
-  if (rc != FLCE_OK) return rc;
+  if (!args->norm_given) {
+    rc = flce_b200_count(p, args->norm, stream_);
+    if (rc != FLCE_OK) return rc;
+  }
   const bool pair = g_cta_pair != 0;
-  const bool need_sum = p->label_smoothing > 0.f;
+  const bool need_sum = smoothing;
   const bool need_argmax = (p->flags & FLCE_FLAG_ARGMAX) != 0;
   const int fmt16 = p->dtype == FLCE_BF16 ? kOutBf16 : kOutFp16;
   const int esize_out = grads_fp32 ? 4 : 2;
   const RowMath rm = row_math(p);
   const int threads = 256;
   const size_t plane_floats = plan.plane / sizeof(float);
+  const float inv_softcap = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+  const long long* target_all = reinterpret_cast<const long long*>(p->target);
+  if (exp_store) {
+    FLCE_CUDA(cudaMemsetAsync(redo_flags, 0, plan.flag_bytes, stream));
+    const int warps = 8;
+    target_shift_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, warps)), warps * 32, 0, stream>>>(
+        static_cast<const uint16_t*>(p->x), p->ld_x, static_cast<const uint16_t*>(p->w), p->ld_w, fmt16,
+        static_cast<int>(p->n_rows), static_cast<int>(p->hidden), target_all, p->ignore_index, p->vocab, p->bias, p->softcap,
+        inv_softcap, kExpStoreOffset, shift);
+    FLCE_CUDA(cudaGetLastError());
+    ++g_kernel_launches;
+    if (smoothing && args->grad_input != nullptr) {
+      rc = launch_scaled_colsum(p->w, p->ld_w, p->vocab, p->hidden, fmt16, p->ce_weight, colsum_scratch, w_sum, false, stream);
+      if (rc != FLCE_OK) return rc;
+    }
+  }
   for (int c = 0; c < plan.n_chunks; ++c) {
     const long long r0 = static_cast<long long>(c) * plan.chunk_rows;
     const long long rows = (p->n_rows - r0 < plan.chunk_rows) ? p->n_rows - r0 : plan.chunk_rows;
     const uint16_t* x_chunk = static_cast<const uint16_t*>(p->x) + r0 * p->ld_x;
-    const long long* tgt = reinterpret_cast<const long long*>(p->target) + r0;
+    const long long* tgt = target_all + r0;
+    const int base = static_cast<int>(r0);
     float* c2 = c1 + rows;
     float* c3 = c2 + rows;
-    // ---- logits of the chunk: statistics + 16-bit copy
-    {
-      StatsEpilogue::Params ep;
+    const bool first = c == 0, last = c == plan.n_chunks - 1;
+    // ---- logits of the chunk: statistics + 16-bit copy (the logits themselves, or their exponentials)
+    auto sweep1 = [&](const int* gate) -> int {
+      StatsEpilogue::Params ep{};
       ep.target = tgt;
       ep.bias = p->bias;
       ep.col_weight = p->ce_weight;
       ep.softcap = p->softcap;
-      ep.inv_softcap = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+      ep.inv_softcap = inv_softcap;
       ep.n_cols = static_cast<int>(p->vocab);
       ep.vocab_offset = p->vocab_offset;
       ep.m_rows = static_cast<int>(rows);
@@ -942,17 +1023,26 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       ep.logits_out = slab;
       ep.ld_logits = plan.ld_slab;
       ep.logits_fmt = fmt16;
-      FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(rows) * sizeof(float), stream));
+      ep.shift = exp_store ? shift + r0 : nullptr;
+      ep.ignore_index = p->ignore_index;
+      if (gate == nullptr)   // (the gated repeat writes the same target logits again)
+        FLCE_CUDA(cudaMemsetAsync(ep.target_logit, 0, static_cast<size_t>(rows) * sizeof(float), stream));
       Operand a{x_chunk, rows, p->hidden, p->ld_x, 0};
       Operand b{p->w, p->vocab, p->hidden, p->ld_w, 0};
-      rc = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, kKindStats, pair, a, b, p->dtype, rows, p->vocab, p->hidden,
-                                                        static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream);
-      if (rc != FLCE_OK) return rc;
-      merge_partials_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
-          static_cast<int>(rows), plan.n_tiles, ep.pmax, ep.psum, ep.plogit_sum, ep.pamax_val, ep.pamax_idx, chunk_stats);
-      FLCE_CUDA(cudaGetLastError());
-      ++g_kernel_launches;
-    }
+      int rc1 = launch_gemm<kMajorK, kMajorK, StatsEpilogue>(*dev, kKindStats, pair, a, b, p->dtype, rows, p->vocab, p->hidden,
+                                                             static_cast<long long>(kBlockM) * p->hidden * 2, false, ep, stream,
+                                                             p->active_rows, 1, base, gate);
+      if (rc1 != FLCE_OK) return rc1;
+      if (gate == nullptr) {
+        merge_partials_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
+            static_cast<int>(rows), plan.n_tiles, ep.pmax, ep.psum, ep.plogit_sum, ep.pamax_val, ep.pamax_idx, chunk_stats);
+        FLCE_CUDA(cudaGetLastError());
+        ++g_kernel_launches;
+      }
+      return FLCE_OK;
+    };
+    rc = sweep1(nullptr);
+    if (rc != FLCE_OK) return rc;
     // ---- per-row losses, then the gradient coefficients (upstream gradient = 1)
     finalize_rows_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
         static_cast<int>(rows), rm, tgt, p->ce_weight, chunk_stats, args->norm, out->lse + r0, out->target_prob + r0,
@@ -965,41 +1055,69 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
         static_cast<int>(rows), rm, tgt, p->ce_weight, out->lse + r0, out->target_prob + r0, args->norm, nullptr, 0, c1, c2, c3);
     FLCE_CUDA(cudaGetLastError());
     ++g_kernel_launches;
-    // ---- logits -> logit gradient, in place
-    {
-      const int tpb = 256;
-      dim3 grid(static_cast<unsigned>(ceil_div(ceil_div(p->vocab, 8), tpb)), static_cast<unsigned>(rows), 1);
+    if (exp_store) {
+      // ---- a row further from its reference point than the stored form can express sends the chunk through sweep 1 again
+      exp_store_check_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
+          static_cast<int>(rows), tgt, p->ignore_index, out->lse + r0, shift + r0, kExpStoreRedoLimit,
+          redo_flags + c);
+      FLCE_CUDA(cudaGetLastError());
+      exp_store_reshift_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
+          static_cast<int>(rows), out->lse + r0, redo_flags + c, shift + r0);
+      FLCE_CUDA(cudaGetLastError());
+      g_kernel_launches += 2;
+      rc = sweep1(redo_flags + c);
+      if (rc != FLCE_OK) return rc;
+      // ---- per-row factor, scaled copy of x, true-class entries of E
       ProfileSlot* slot = profile_begin(kKindOther, stream);
-      dz_inplace_kernel<<<grid, tpb, 0, stream>>>(slab, plan.ld_slab, static_cast<int>(rows), static_cast<int>(p->vocab), fmt16,
-                                                  tgt, p->vocab_offset, out->lse + r0, c1, c2, c3, p->ce_weight,
-                                                  p->softcap > 0.f ? 1.f / p->softcap : 0.f);
+      exp_store_fixup_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
+          x_chunk, p->ld_x, static_cast<int>(p->hidden), fmt16, static_cast<int>(rows), tgt, p->ignore_index, p->vocab,
+          out->lse + r0, shift + r0, chunk_stats + 2 * static_cast<size_t>(rows), c1, c3, inv_softcap, kExpStoreClamp, slab,
+          plan.ld_slab, alpha, xs, p->hidden);
+      profile_end(slot, stream);
+      FLCE_CUDA(cudaGetLastError());
+      ++g_kernel_launches;
+      if (smoothing && args->grad_weight != nullptr) {
+        rc = launch_scaled_colsum(x_chunk, p->ld_x, rows, p->hidden, fmt16, c2, colsum_scratch, x_sum, !first, stream);
+        if (rc != FLCE_OK) return rc;
+      }
+    } else {
+      // ---- logits -> logit gradient, in place
+      dim3 grid(static_cast<unsigned>(ceil_div(p->vocab, kDzInplaceCols)), static_cast<unsigned>(rows), 1);
+      ProfileSlot* slot = profile_begin(kKindOther, stream);
+      dz_inplace_kernel<<<grid, kDzInplaceThreads, 0, stream>>>(slab, plan.ld_slab, static_cast<int>(rows),
+                                                                static_cast<int>(p->vocab), fmt16, tgt, p->vocab_offset,
+                                                                out->lse + r0, c1, c2, c3, p->ce_weight, inv_softcap,
+                                                                p->active_rows, base);
       profile_end(slot, stream);
       FLCE_CUDA(cudaGetLastError());
       ++g_kernel_launches;
     }
     // ---- grad_input[chunk] = dZ . W          (M = rows, N = hidden, K = vocab; B is MN-major)
     if (args->grad_input != nullptr) {
-      StoreEpilogue::Params ep;
+      StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(rows);
       ep.n_cols = static_cast<int>(p->hidden);
-      ep.acc_in = nullptr;
-      ep.acc_out = nullptr;
-      ep.ld_acc = 0;
       ep.out = static_cast<uint8_t*>(args->grad_input) + static_cast<size_t>(r0) * p->hidden * esize_out;
       ep.ld_out = p->hidden;
       ep.out_fmt = grads_fp32 ? kOutFp32 : fmt16;
+      if (exp_store) {
+        ep.row_scale = alpha;
+        if (smoothing) {
+          ep.r1_row = c2;
+          ep.r1_col = w_sum;
+        }
+      }
       Operand a{slab, rows, p->vocab, plan.ld_slab, 0};
       Operand b{p->w, p->hidden, p->vocab, p->ld_w, 1};
       rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, rows, p->hidden, p->vocab, 0, true,
-                                                         ep, stream);
+                                                         ep, stream, p->active_rows, 1, base);
       if (rc != FLCE_OK) return rc;
     }
     // ---- grad_weight (+)= dZ^T . X[chunk]    (M = vocab, N = hidden, K = rows; both operands MN-major)
     if (args->grad_weight != nullptr) {
-      StoreEpilogue::Params ep;
+      StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(p->vocab);
       ep.n_cols = static_cast<int>(p->hidden);
-      const bool first = c == 0, last = c == plan.n_chunks - 1;
       float* acc = grads_fp32 ? static_cast<float*>(args->grad_weight) : dw_acc;
       ep.acc_in = first ? nullptr : acc;
       ep.acc_out = (grads_fp32 || !last) ? acc : nullptr;
@@ -1007,15 +1125,21 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       ep.out = (!grads_fp32 && last) ? args->grad_weight : nullptr;
       ep.ld_out = p->hidden;
       ep.out_fmt = fmt16;
+      if (exp_store && smoothing && last) {   // the uniform term of every chunk at once: - w_j * sum_r c2_r x_r
+        ep.r1_row = p->ce_weight;
+        ep.r1_col = x_sum;
+      }
       Operand a{slab, p->vocab, rows, plan.ld_slab, 1};
-      Operand b{x_chunk, p->hidden, rows, p->ld_x, 1};
+      Operand b{exp_store ? static_cast<const void*>(xs) : static_cast<const void*>(x_chunk), p->hidden, rows,
+                exp_store ? p->hidden : p->ld_x, 1};
       rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0, true,
-                                                          ep, stream);
+                                                          ep, stream, p->active_rows, 2, base);
       if (rc != FLCE_OK) return rc;
     }
     if (args->grad_bias != nullptr) {
       colsum_accumulate_kernel<<<static_cast<unsigned>(ceil_div(p->vocab, 64)), 1024, 0, stream>>>(
-          slab, plan.ld_slab, static_cast<int>(rows), static_cast<int>(p->vocab), fmt16, args->grad_bias, c != 0);
+          slab, plan.ld_slab, static_cast<int>(rows), static_cast<int>(p->vocab), fmt16, args->grad_bias, c != 0,
+          p->active_rows, base);
       FLCE_CUDA(cudaGetLastError());
       ++g_kernel_launches;
     }
@@ -1190,7 +1314,7 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
   int rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  StoreEpilogue::Params ep;
+  StoreEpilogue::Params ep{};
   ep.m_rows = static_cast<int>(m);
   ep.n_cols = static_cast<int>(n);
   ep.acc_in = nullptr;
@@ -1233,7 +1357,7 @@ int flce_b200_gemm_accumulate(const void* a, const void* b, float* acc, void* ou
   int rc = device_state(&dev);
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  StoreEpilogue::Params ep;
+  StoreEpilogue::Params ep{};
   ep.m_rows = static_cast<int>(m);
   ep.n_cols = static_cast<int>(n);
   ep.acc_in = acc;
@@ -1401,7 +1525,7 @@ int flce_b200_sce_forward(const flce_sce_problem_t* p, float* nll, float* entrop
   if (rc != FLCE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  EntropyStatsEpilogue::Params ep;
+  EntropyStatsEpilogue::Params ep{};
   ep.target = reinterpret_cast<const long long*>(p->target);
   ep.scale = 1.f / p->temperature;
   ep.n_cols = static_cast<int>(p->vocab);
@@ -1480,7 +1604,7 @@ int flce_b200_sce_backward(const flce_sce_problem_t* p, const float* lse, const 
       if (rc != FLCE_OK) return rc;
     }
     if (grad_weight != nullptr) {  // grad_weight[slab] = dZ^T . X   (M = cols, N = hidden, K = n_rows; both MN-major)
-      StoreEpilogue::Params ep;
+      StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(cols);
       ep.n_cols = static_cast<int>(p->hidden);
       ep.acc_in = nullptr;
@@ -1496,7 +1620,7 @@ int flce_b200_sce_backward(const flce_sce_problem_t* p, const float* lse, const 
       if (rc != FLCE_OK) return rc;
     }
     if (grad_input != nullptr) {  // grad_input (+)= dZ . W[slab]   (M = n_rows, N = hidden, K = cols; B MN-major)
-      StoreEpilogue::Params ep;
+      StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(p->n_rows);
       ep.n_cols = static_cast<int>(p->hidden);
       const bool first = s == 0, last = s == plan.n_slabs - 1;

@@ -11,6 +11,11 @@
 // * warps 2..5 drain finished accumulators with tcgen05.ld, 32 columns at a time, one output row
 //   per thread, and feed them to the epilogue functor.  Two accumulators (2 x 256 columns)
 //   let the epilogue of tile i overlap the main loop of tile i+1.
+// * kNSub = 2 (CTA pairs only) widens the tile to 256 x 512: both 256-column accumulators belong to one tile and
+//   every K slice of A feeds two MMAs.  A pair then pulls (256 + 512) x 64 elements from L2 per 256 x 512 x 64
+//   products instead of (256 + 256) x 64 per 256 x 256 x 64: 48 instead of 64 bytes per clock and SM at full tensor
+//   rate, under what the L2 -> SM path delivers without cluster multicast.  The epilogue no longer overlaps the next
+//   tile's main loop, so this form is for long K and light epilogues (the two gradient GEMMs).
 //
 // Either operand may be K-major (K contiguous in global memory) or MN-major (M or N
 // contiguous); the latter is what the weight-gradient GEMM (dZ^T X) and the B side of the
@@ -47,12 +52,15 @@ constexpr int kNumThreads = 192;  // 6 warps
 constexpr int kNumEpilogueWarps = 4;
 constexpr int kTmemCols = 512;    // two 256-column accumulators
 
-template <int kCtas>
+template <int kCtas, int kNSub = 1>
 struct StageCfg {
+  static_assert(kNSub == 1 || (kNSub == 2 && kCtas == 2), "the 512-column tile exists for CTA pairs only");
   static constexpr int kABytes = kBlockM * kBlockK * 2;
-  static constexpr int kBBytes = (kBlockN / kCtas) * kBlockK * 2;
+  static constexpr int kBRows = kNSub * kBlockN / kCtas;             // rows of B this CTA stages per K slice
+  static constexpr int kBBytes = kBRows * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (kCtas == 1) ? 4 : 6;
+  static constexpr int kStages = (kNSub == 2) ? 4 : ((kCtas == 1) ? 4 : 6);
+  static constexpr int kAccStages = (kNSub == 2) ? 1 : 2;            // accumulators in flight (tensor memory: 512 columns)
   static constexpr int kRingBytes = kStages * kStageBytes;
   // ring + barriers + bookkeeping, plus 1 KiB so the ring can be aligned to the swizzle atom
   static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
@@ -65,13 +73,16 @@ struct StageCfg {
 //     __device__ void chunk(const Params&, const uint32_t (&acc)[32], int col);   // fp32 bit patterns
 //     __device__ void end(const Params&);
 //   };
-template <int kCtas, int kAMajor, int kBMajor, class Epi>
+template <int kCtas, int kAMajor, int kBMajor, class Epi, int kNSub = 1>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmShape shape_arg, const int ab_format, const typename Epi::Params ep, int* status) {
-  using Cfg = StageCfg<kCtas>;
+  using Cfg = StageCfg<kCtas, kNSub>;
+  constexpr int kTileN = kBlockN * kNSub;          // output columns per tile
+  constexpr int kAccStages = Cfg::kAccStages;
   GemmShape shape = shape_arg;
-  if (shape.active_rows != nullptr) limit_to_active_rows(shape, *shape.active_rows, kCtas);   // uniform across the grid
+  if (shape.gate != nullptr && *shape.gate == 0) return;   // uniform across the grid; nothing has been set up yet
+  if (shape.active_rows != nullptr) limit_to_active_rows(shape, *shape.active_rows - shape.active_base, kCtas);   // uniform across the grid
   constexpr int kStages = Cfg::kStages;
 
   extern __shared__ uint8_t smem_raw[];
@@ -135,7 +146,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int mt, nt;
         decode_tile(shape, tile, mt, nt);
         const int m0 = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM;
-        const int n0 = nt * kBlockN + static_cast<int>(cta_rank) * (kBlockN / kCtas);
+        // this CTA's share of sub-tile j of B: rows n0 + j * 256 + [0, 256 / kCtas)
+        const int n0 = nt * kTileN + static_cast<int>(cta_rank) * (kBlockN / kCtas);
         for (int kb = 0; kb < shape.k_blocks; ++kb) {
           FLCE_TRACE_BEGIN(t_w);
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, status, kDevTimeoutEmptyBarrier);
@@ -169,12 +181,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int i = 0; i < kBlockM / 64; ++i)                 // boxes: 64 m x 64 k
               load(dst_a + i * (64 * kBlockK * 2), &map_a, m0 + i * 64, k0);
           }
-          if constexpr (kBMajor == kMajorK) {
-            load(dst_b, &map_b, k0, n0);                          // box: 64 k x (256 / kCtas) rows
-          } else {
+          constexpr int kSubRows = kBlockN / kCtas;               // rows of one sub-tile held by this CTA
 #pragma unroll
-            for (int i = 0; i < (kBlockN / kCtas) / 64; ++i)       // boxes: 64 n x 64 k
-              load(dst_b + i * (64 * kBlockK * 2), &map_b, n0 + i * 64, k0);
+          for (int j = 0; j < kNSub; ++j) {
+            const uint32_t dst_bj = dst_b + j * (kSubRows * kBlockK * 2);
+            if constexpr (kBMajor == kMajorK) {
+              load(dst_bj, &map_b, k0, n0 + j * kBlockN);         // box: 64 k x (256 / kCtas) rows
+            } else {
+#pragma unroll
+              for (int i = 0; i < kSubRows / 64; ++i)              // boxes: 64 n x 64 k
+                load(dst_bj + i * (64 * kBlockK * 2), &map_b, n0 + j * kBlockN + i * 64, k0);
+            }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -209,7 +226,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       FLCE_TRACE_DECL(wait_full);
       FLCE_TRACE_DECL(wait_tmem_empty);
       for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
-        const int acc = local_tile & 1;
+        const int acc = (kAccStages == 2) ? (local_tile & 1) : 0;
         FLCE_TRACE_BEGIN(t_e);
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase[acc] ^ 1u, abort_flag, status, kDevTimeoutTmemEmpty);
         FLCE_TRACE_ADD(wait_tmem_empty, t_e);
@@ -225,10 +242,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tcgen05_fence_after();
           const uint64_t desc_a = make_smem_desc(smem_u32(ring_a + stage * Cfg::kABytes), kLboA, kSbo);
           const uint64_t desc_b = make_smem_desc(smem_u32(ring_b + stage * Cfg::kBBytes), kLboB, kSbo);
+          constexpr uint32_t kSubStepB = ((kBlockN / kCtas) * kBlockK * 2) / 16;   // next sub-tile of B, in 16-byte units
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            umma_f16<kCtas>(tmem_d, desc_a + static_cast<uint64_t>(k * kStepA),
-                            desc_b + static_cast<uint64_t>(k * kStepB), idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int j = 0; j < kNSub; ++j)
+              umma_f16<kCtas>(tmem_d + static_cast<uint32_t>(j * kBlockN), desc_a + static_cast<uint64_t>(k * kStepA),
+                              desc_b + static_cast<uint64_t>(k * kStepB + j * kSubStepB), idesc, (kb | k) != 0 ? 1u : 0u);
           }
           if constexpr (kCtas == 1) umma_commit(smem_u32(&empty_bar[stage]));
           else umma_commit_pair(smem_u32(&empty_bar[stage]), 0x3);
@@ -266,9 +286,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
       int mt, nt;
       decode_tile(shape, tile, mt, nt);
-      const int acc = local_tile & 1;
+      const int acc = (kAccStages == 2) ? (local_tile & 1) : 0;
       const int row = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM + row_in_tile;
-      const int col0 = nt * kBlockN;
+      const int col0 = nt * kTileN;
       FLCE_TRACE_BEGIN(t_w);
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase[acc], abort_flag, status, kDevTimeoutTmemFull,
                      static_cast<uint32_t>(shape.poll_sleep_ns));
@@ -281,7 +301,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       epi.begin(ep, row, col0, nt, row < shape.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kBlockN);
       // two register buffers: the load of the next 32 columns is in flight while the current ones are consumed
-      const int n_chunks = min(kBlockN / 32, (shape.N - col0 + 31) / 32);   // uniform across the CTA
+      const int n_chunks = min(kTileN / 32, (shape.N - col0 + 31) / 32);   // uniform across the CTA
       uint32_t va[32], vb[32];
       tmem_ld_32x32(taddr, va);
 #pragma unroll 1

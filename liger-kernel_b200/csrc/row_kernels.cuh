@@ -199,45 +199,216 @@ __global__ void coef_kernel(int m_rows, RowMath rm, const long long* target, con
 
 // Single-sweep mode: turn the stored 16-bit soft-capped logits of a token chunk into the logit gradient, in place.
 //   dZ = (exp(s - lse) * c1 - c2 * colw - c3 * [j == target]) * (1 - (s/softcap)^2)
-// One block per (row, segment of 8 * blockDim columns); HBM-bound (reads and writes each element once).
-__global__ void dz_inplace_kernel(uint16_t* slab, long long ld, int n_rows, int n_cols, int fmt, const long long* target,
-                                  long long vocab_offset, const float* lse, const float* c1, const float* c2,
-                                  const float* c3, const float* col_weight, float inv_softcap) {
+// One block per (row, segment of kDzInplaceCols columns); every thread issues its four 16-byte loads before it touches
+// any of them, so that enough bytes are in flight to fill HBM (reads and writes each element once).  With active_rows
+// given, only the first *active_rows - active_base rows matter; the weight-gradient GEMM still reads whole 64-row K
+// slices, so the rows up to the next multiple of 64 are turned into gradients too (zeros: their coefficients are
+// zero and the sweep wrote their logits), and the rest, which nothing reads, is skipped.
+constexpr int kDzInplaceThreads = 256;
+constexpr int kDzInplaceVecs = 4;
+constexpr int kDzInplaceCols = kDzInplaceThreads * kDzInplaceVecs * 8;
+__global__ void __launch_bounds__(kDzInplaceThreads)
+dz_inplace_kernel(uint16_t* slab, long long ld, int n_rows, int n_cols, int fmt, const long long* target,
+                  long long vocab_offset, const float* lse, const float* c1, const float* c2, const float* c3,
+                  const float* col_weight, float inv_softcap, const int* active_rows = nullptr, int active_base = 0) {
   const int row = blockIdx.y;
-  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (row >= n_rows || col >= n_cols) return;
+  if (row >= n_rows) return;
+  if (active_rows != nullptr && row >= (max(0, *active_rows - active_base) + 63) / 64 * 64) return;
   const float l2 = lse[row] * kLog2e, a = c1[row], b = c2[row], c = c3[row];
   const long long t = target[row] - vocab_offset;
-  uint4* ptr = reinterpret_cast<uint4*>(slab + static_cast<size_t>(row) * ld + col);
-  const uint4 raw = *ptr;
-  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-  float g[8];
+  uint16_t* row_ptr = slab + static_cast<size_t>(row) * ld;
+  const int col0 = blockIdx.x * kDzInplaceCols + threadIdx.x * 8;
+  uint4 raw[kDzInplaceVecs];
+#pragma unroll
+  for (int v = 0; v < kDzInplaceVecs; ++v) {
+    const int col = col0 + v * kDzInplaceThreads * 8;
+    if (col < n_cols) raw[v] = *reinterpret_cast<const uint4*>(row_ptr + col);
+  }
+#pragma unroll
+  for (int v = 0; v < kDzInplaceVecs; ++v) {
+    const int col = col0 + v * kDzInplaceThreads * 8;
+    if (col >= n_cols) continue;
+    const uint32_t words[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+    float g[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float2 f;
+      if (fmt == kOutBf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[q]));
+      else f = __half22float2(*reinterpret_cast<const __half2*>(&words[q]));
+      g[2 * q] = f.x;
+      g[2 * q + 1] = f.y;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = g[j];
+      const float wj = (col_weight != nullptr && col + j < n_cols) ? col_weight[col + j] : 1.f;
+      float val = fmaf(ex2_approx(fmaf(s, kLog2e, -l2)), a, -b * wj);
+      if (static_cast<long long>(col + j) == t) val -= c;
+      if (inv_softcap > 0.f) {
+        const float th = s * inv_softcap;
+        val *= fmaf(-th, th, 1.f);
+      }
+      g[j] = (col + j < n_cols) ? val : 0.f;
+    }
+    uint4 o;
+    o.x = pack2(g[0], g[1], fmt);
+    o.y = pack2(g[2], g[3], fmt);
+    o.z = pack2(g[4], g[5], fmt);
+    o.w = pack2(g[6], g[7], fmt);
+    *reinterpret_cast<uint4*>(row_ptr + col) = o;
+  }
+}
+
+// ---- the exp-store form of the single-sweep mode ----------------------------------------------------------------
+// Sweep 1 stores E = exp(s - shift) (epilogues.cuh) instead of the logits.  The three kernels below produce the per-row
+// reference point before the sweep, and, once the chunk's log-sum-exp is known, everything the two gradient GEMMs
+// need so that they can consume E as it is:  dZ[r, j] = alpha_r * E[r, j]  with  alpha_r = c1_r * exp(shift_r - lse_r).
+
+__device__ __forceinline__ float dot8_16bit(const uint4& a, const uint4& b, int fmt) {
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  float acc = 0.f;
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
-    float2 f;
-    if (fmt == kOutBf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[q]));
-    else f = __half22float2(*reinterpret_cast<const __half2*>(&words[q]));
-    g[2 * q] = f.x;
-    g[2 * q + 1] = f.y;
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float s = g[j];
-    const float wj = (col_weight != nullptr && col + j < n_cols) ? col_weight[col + j] : 1.f;
-    float v = fmaf(ex2_approx(fmaf(s, kLog2e, -l2)), a, -b * wj);
-    if (static_cast<long long>(col + j) == t) v -= c;
-    if (inv_softcap > 0.f) {
-      const float th = s * inv_softcap;
-      v *= fmaf(-th, th, 1.f);
+    float2 fa, fb;
+    if (fmt == kOutBf16) {
+      fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[q]));
+      fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[q]));
+    } else {
+      fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[q]));
+      fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[q]));
     }
-    g[j] = (col + j < n_cols) ? v : 0.f;
+    acc = fmaf(fa.x, fb.x, acc);
+    acc = fmaf(fa.y, fb.y, acc);
   }
-  uint4 o;
-  o.x = pack2(g[0], g[1], fmt);
-  o.y = pack2(g[2], g[3], fmt);
-  o.z = pack2(g[4], g[5], fmt);
-  o.w = pack2(g[6], g[7], fmt);
-  *ptr = o;
+  return acc;
+}
+
+// shift[r] = soft-capped logit of row r's target class + offset: x_r . W[y_r] (+ bias), one warp per row.
+// The log-sum-exp of a row is at least its target logit and exceeds it by the row's loss, so this point is within
+// [offset - loss, offset] of it without a pass over the vocabulary.  Rows without a usable target get the offset alone.
+__global__ void target_shift_kernel(const uint16_t* x, long long ld_x, const uint16_t* w, long long ld_w, int fmt, int n_rows,
+                                    int hidden, const long long* target, long long ignore_index, long long vocab,
+                                    const float* bias, float softcap, float inv_softcap, float offset, float* shift) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const long long y = target[row];
+  float z = 0.f;
+  if (y != ignore_index && y >= 0 && y < vocab) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ld_x);
+    const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<size_t>(y) * ld_w);
+    float acc = 0.f;
+    for (int v = lane; v < hidden / 8; v += 32) acc += dot8_16bit(xr[v], wr[v], fmt);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    z = acc + (bias != nullptr ? bias[y] : 0.f);
+    if (softcap > 0.f) z = softcap * tanh_accurate(z * inv_softcap);
+  }
+  if (lane == 0) shift[row] = z + offset;
+}
+
+// The stored exponentials are exact only while exp(s - shift) stays inside the clamp and the per-row factor inside fp32:
+// a row whose log-sum-exp lies more than `limit` above shift - offset (a loss of that many nats) breaks that.  The
+// first kernel raises *flag when the chunk holds such a row, the second then moves every reference point of the chunk
+// onto the now known log-sum-exp; sweep 1 is enqueued once more for the chunk, gated on the same flag.
+__global__ void exp_store_check_kernel(int n_rows, const long long* target, long long ignore_index, const float* lse,
+                                       const float* shift, float limit, int* flag) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n_rows || target[row] == ignore_index) return;
+  if (!(lse[row] - shift[row] <= limit)) *flag = 1;   // also true for NaN: take the exact path
+}
+__global__ void exp_store_reshift_kernel(int n_rows, const float* lse, const int* flag, float* shift) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n_rows || *flag == 0) return;
+  shift[row] = lse[row];
+}
+
+// One block per row of the chunk, after the chunk's coefficients are known:
+//   alpha[r] = c1_r * exp(shift_r - lse_r)                          (0 on rows whose target is ignore_index)
+//   xs[r, :] = 16-bit(alpha_r * x[r, :])                            (the weight-gradient GEMM's second operand)
+//   E[r, y_r] = (exp(s_y - shift_r) - c3_r / alpha_r) * chain_y     (the true-class term, formed in fp32 from the fp32
+//                                                                    target logit, not from the rounded stored value)
+__global__ void exp_store_fixup_kernel(const uint16_t* x, long long ld_x, int hidden, int fmt, int n_rows,
+                                       const long long* target, long long ignore_index, long long vocab, const float* lse,
+                                       const float* shift, const float* target_logit, const float* c1, const float* c3,
+                                       float inv_softcap, float clamp, uint16_t* slab, long long ld_slab, float* alpha,
+                                       uint16_t* xs, long long ld_xs) {
+  const int row = blockIdx.x;
+  if (row >= n_rows) return;
+  const long long y = target[row];
+  const bool live = y != ignore_index;
+  const float a = live ? c1[row] * ex2_approx((shift[row] - lse[row]) * kLog2e) : 0.f;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ld_x);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(row) * ld_xs);
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+    const uint4 raw = src[v];
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float2 f;
+      if (fmt == kOutBf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[q]));
+      else f = __half22float2(*reinterpret_cast<const __half2*>(&words[q]));
+      o[q] = pack2(f.x * a, f.y * a, fmt);
+    }
+    dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (threadIdx.x == 0) {
+    alpha[row] = a;
+    if (live && y >= 0 && y < vocab) {
+      const float sy = target_logit[row];
+      float chain = 1.f;
+      if (inv_softcap > 0.f) {
+        const float th = sy * inv_softcap;
+        chain = fmaf(-th, th, 1.f);
+      }
+      const float e = ex2_approx(fminf((sy - shift[row]) * kLog2e, clamp * kLog2e));
+      const float val = (a != 0.f) ? (e - c3[row] / a) * chain : 0.f;
+      if (fmt == kOutBf16) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(val);
+        slab[static_cast<size_t>(row) * ld_slab + y] = *reinterpret_cast<const uint16_t*>(&h);
+      } else {
+        const __half h = __float2half_rn(val);
+        slab[static_cast<size_t>(row) * ld_slab + y] = *reinterpret_cast<const uint16_t*>(&h);
+      }
+    }
+  }
+}
+
+// out[c] (+)= sum over rows of scale[r] * mat[r, c] for a 16-bit matrix (scale null = 1), in two ordered stages:
+// stage 1 (grid = column blocks of 64 x kColsumSplits row ranges) leaves partial sums in scratch[split][c],
+// stage 2 adds them up in a fixed order.  Used for sum_j w_j W[j, :] and sum_r c2_r x[r, :] (label smoothing).
+constexpr int kColsumSplits = 32;
+__global__ void scaled_colsum_stage1_kernel(const uint16_t* mat, long long ld, int n_rows, int n_cols, int fmt, const float* scale,
+                                            float* scratch) {
+  __shared__ float part[16][64];
+  const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;   // 64 x 16
+  const int col = blockIdx.x * 64 + cx;
+  const int per = (n_rows + kColsumSplits - 1) / kColsumSplits;
+  const int r_begin = blockIdx.y * per, r_end = min(n_rows, r_begin + per);
+  float s = 0.f;
+  if (col < n_cols) {
+    for (int r = r_begin + ry; r < r_end; r += 16) {
+      const uint16_t raw = mat[static_cast<size_t>(r) * ld + col];
+      const float v = (fmt == kOutBf16) ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw))
+                                        : __half2float(*reinterpret_cast<const __half*>(&raw));
+      s = fmaf(scale != nullptr ? scale[r] : 1.f, v, s);
+    }
+  }
+  part[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < n_cols) {
+    float t = 0.f;
+    for (int i = 0; i < 16; ++i) t += part[i][cx];
+    scratch[static_cast<size_t>(blockIdx.y) * n_cols + col] = t;
+  }
+}
+__global__ void scaled_colsum_stage2_kernel(const float* scratch, int n_cols, float* out, int accumulate) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n_cols) return;
+  float t = accumulate ? out[col] : 0.f;
+  for (int i = 0; i < kColsumSplits; ++i) t += scratch[static_cast<size_t>(i) * n_cols + col];
+  out[col] = t;
 }
 
 // data[i] *= *scale unless *scale == 1 (checked on the device: no host synchronisation); 16-bit or fp32 elements
@@ -259,9 +430,11 @@ __global__ void scale_inplace_kernel(void* data, long long n, int fmt, const flo
 }
 
 // out[j] += sum over rows of slab column j (bias gradient across token chunks); one block per 64 columns
+// (rows at and beyond *active_rows, when given, were never written by the sweep and are left out)
 __global__ void colsum_accumulate_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out,
-                                         int accumulate) {
+                                         int accumulate, const int* active_rows = nullptr, int active_base = 0) {
   __shared__ float part[16][64];
+  if (active_rows != nullptr) m_rows = min(m_rows, max(0, *active_rows - active_base));
   const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
   const int col = blockIdx.x * 64 + cx;
   float s = 0.f;
@@ -389,8 +562,11 @@ __global__ void split_fp32_kernel(const float* src, long long rows, long long co
 }
 
 // grad_bias[j] (+)= sum over rows of the 16-bit slab column j; one block per 64 columns, ordered sum
-__global__ void colsum_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out) {
+// (rows at and beyond *active_rows, when given, were never written by the sweep and are left out)
+__global__ void colsum_kernel(const uint16_t* dz, long long ld, int m_rows, int n_cols, int fmt, float* out,
+                              const int* active_rows = nullptr) {
   __shared__ float part[16][64];
+  if (active_rows != nullptr) m_rows = min(m_rows, max(0, *active_rows));
   const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;  // 64 x 16
   const int col = blockIdx.x * 64 + cx;
   float s = 0.f;

@@ -21,8 +21,13 @@ struct GemmShape {
   int poll_sleep_ns;   // back-off of the epilogue warps while they wait for an accumulator
   // Optional device-resident row count (rows that matter come first, e.g. after ignored tokens were moved to the end):
   // role 1 limits the m-tiles to those that contain such rows, role 2 limits the k-blocks (when K runs over rows).
+  // active_base is the index of this launch's first row in the numbering active_rows counts in (a token chunk).
   const int* active_rows;
   int active_role;
+  int active_base;
+  // Optional device-resident switch: when it points at 0 the whole launch returns at once (a pass that only some
+  // inputs need is enqueued unconditionally and decides on the device, without a host synchronisation).
+  const int* gate;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& mt, int& nt) {

@@ -106,7 +106,11 @@ class FusedArgs(C.Structure):
     _fields_ = [
         ("out", C.POINTER(ForwardOut)), ("norm", C.c_void_p), ("grad_dtype", C.c_int32),
         ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
+        ("norm_given", C.c_int32), ("store_mode", C.c_int32),
     ]
+
+
+STORE_AUTO, STORE_LOGITS, STORE_EXP = 0, 1, 2
 
 
 def _load():

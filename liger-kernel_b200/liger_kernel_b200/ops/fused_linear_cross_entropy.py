@@ -9,10 +9,12 @@ memory and the current stream only.  There is no CPU or eager fallback.
 Two execution modes (``MODE`` below, or the environment variable ``LIGER_B200_FLCE_MODE``):
 * ``"recompute"``: forward computes only the loss (sweep 1); ``backward`` recomputes the logits tile by tile
   (sweep 2) with the upstream gradient folded in.  8.N.H.V tensor FLOPs, smallest memory, any reduction.
-* ``"single_sweep"``: when a gradient is required and the reduction is mean or sum, forward also forms the
-  gradients, as the reference does (``ops/fused_linear_cross_entropy.py:395-435``), from a bounded 16-bit copy of each
-  token chunk's logits: 6.N.H.V tensor FLOPs.  The first ``backward`` hands the stored gradients off (scaled on the
-  device if the upstream gradient is not 1); a repeated ``backward`` falls back to the recompute sweep.
+* ``"single_sweep"``: when a gradient is required, the reduction is mean or sum and the operands are 16-bit, forward
+  also forms the gradients, as the reference does (``ops/fused_linear_cross_entropy.py:395-435``), from a bounded 16-bit
+  copy of each token chunk's logits: 6.N.H.V tensor FLOPs.  The first ``backward`` hands the stored gradients off
+  (scaled on the device if the upstream gradient is not 1); a repeated ``backward`` falls back to the recompute sweep.
+* ``"auto"`` (default): ``single_sweep`` wherever it applies, ``recompute`` elsewhere (``reduction="none"``, fp32
+  operands, forward-only calls).
 
 Differences from the reference that a caller can observe:
 * logits stay fp32 from accumulator to loss (the reference rounds them to the input dtype).
@@ -23,6 +25,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
+import threading
 from typing import Optional
 
 import torch
@@ -37,13 +40,17 @@ _REDUCTIONS = {"mean": _lib.FLCE_MEAN, "sum": _lib.FLCE_SUM, "none": _lib.FLCE_N
 SLAB_BUDGET_BYTES = 1 << 30
 # bytes of logits copy the single-sweep mode may use (chunk rows x V, 16-bit)
 CHUNK_BUDGET_BYTES = 5 << 29
-MODE = os.environ.get("LIGER_B200_FLCE_MODE", "recompute")
+MODE = os.environ.get("LIGER_B200_FLCE_MODE", "auto")
+# What the single-sweep mode keeps of a chunk's logits: "auto" (their exponentials wherever that form applies, else the
+# logits), "logits" or "exp" (see flce_store_mode_t in include/flce_b200.h).
+STORE_MODE = os.environ.get("LIGER_B200_FLCE_STORE", "auto")
+_STORE_MODES = {"auto": _lib.STORE_AUTO, "logits": _lib.STORE_LOGITS, "exp": _lib.STORE_EXP}
 # Read back the count of out-of-range targets after forward and raise, as the reference's stand-alone cross-entropy and
 # its sm_100 FLCE do (``ops/cross_entropy.py:389-392``).  Costs a host synchronisation, so it is off by default.
 CHECK_TARGETS = os.environ.get("LIGER_B200_CHECK_TARGETS", "0") == "1"
 # Move rows whose target is ignore_index to the end (on the device, no host sync) and let the sweeps skip the token
-# tiles that hold none of the others: the tensor work shrinks by the ignored fraction.  Recompute mode, 16-bit inputs.
-SKIP_IGNORED = os.environ.get("LIGER_B200_FLCE_SKIP_IGNORED", "0") == "1"
+# tiles that hold none of the others: the tensor work shrinks by the ignored fraction.  16-bit inputs, both modes.
+SKIP_IGNORED = os.environ.get("LIGER_B200_FLCE_SKIP_IGNORED", "1") == "1"
 
 
 def _raise_on_bad_targets(norm, vocab):
@@ -292,9 +299,10 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
 
 
 def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True, need_bias=False, grad_dtype=None,
-                             chunk_budget=None):
+                             chunk_budget=None, norm_in=None):
     """Loss and gradients (for an upstream gradient of 1) in one pass over token chunks.
-    Returns (outputs dict, norm, grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``."""
+    Returns (outputs dict, norm, grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``.
+    ``norm_in``: normalisers counted elsewhere (a token-sharded caller passes the all-reduced ones)."""
     dev = prep.device
     gd = prep.dtype if grad_dtype is None else grad_dtype
     budget = CHUNK_BUDGET_BYTES if chunk_budget is None else int(chunk_budget)
@@ -313,6 +321,10 @@ def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True,
         args.grad_input = None if gx is None else gx.data_ptr()
         args.grad_weight = None if gw is None else gw.data_ptr()
         args.grad_bias = None if gb is None else gb.data_ptr()
+        args.store_mode = _STORE_MODES[STORE_MODE]
+        if norm_in is not None:
+            norm.copy_(norm_in)
+            args.norm_given = 1
         ws = prep.workspace(_lib.PHASE_FUSED, budget)
         check(lib.flce_b200_forward_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
     return out, norm, gx, gw, gb
@@ -355,11 +367,7 @@ def fused_linear_cross_entropy_forward(
                      softcap, use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens,
                      allow_compact=True)
     out, norm, _rowstats = flce_forward_device(prep)
-    if prep.compacted:  # per-row results back to token order (lse / target_prob stay compact: backward works there)
-        saved_lse, saved_prob = out["lse"], out["target_prob"]
-        out = dict(out, loss_rows=prep.to_token_order(out["loss_rows"]), z_loss_rows=prep.to_token_order(out["z_loss_rows"]),
-                   correct_rows=prep.to_token_order(out["correct_rows"]),
-                   predicted_tokens=prep.to_token_order(out["predicted_tokens"], fill=-1), lse=saved_lse, target_prob=saved_prob)
+    out = _results_to_token_order(prep, out)   # lse / target_prob stay in compact order: backward works there
     if CHECK_TARGETS:
         _raise_on_bad_targets(norm, prep.vocab)
     if reduction == "none":
@@ -392,9 +400,40 @@ def fused_linear_cross_entropy_backward(grad_output, saved, need_input=True, nee
     return gx, gw, gb
 
 
+def _results_to_token_order(prep: _Prepared, out):
+    """Per-row results of a compacted call back in token order (lse / target_prob stay compact: backward works there)."""
+    if not prep.compacted:
+        return out
+    return dict(out, loss_rows=prep.to_token_order(out["loss_rows"]), z_loss_rows=prep.to_token_order(out["z_loss_rows"]),
+                correct_rows=prep.to_token_order(out["correct_rows"]),
+                predicted_tokens=prep.to_token_order(out["predicted_tokens"], fill=-1))
+
+
+_grad_mode = threading.local()
+
+
+def _use_single_sweep(reduction, needs, dtype) -> bool:
+    return MODE in ("single_sweep", "auto") and reduction in ("mean", "sum") and any(needs) and dtype != torch.float32
+
+
 class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
     """Drop-in for the reference class of the same name (``ops/fused_linear_cross_entropy.py:339-487``):
-    same 15 positional arguments, same 4-tuple result, same gradient slots."""
+    same 15 positional arguments, same 4-tuple result, same gradient slots.
+
+    What backward needs is kept with ``ctx.save_for_backward`` (the operands as the caller passed them, the targets, the
+    per-row log-sum-exp, target probability and normalisers), as the reference does (``:417,431``): saved-tensor hooks,
+    activation offload and torch's check for in-place changes between forward and backward all apply.  The padded,
+    compacted or term-split copies the kernels read are rebuilt from those in backward."""
+
+    @classmethod
+    def apply(cls, *args, **kwargs):
+        # grad mode is always off inside forward(): note here whether the caller is recording, so that an evaluation
+        # loop under torch.no_grad() does not pay for gradients nobody will ask for
+        _grad_mode.enabled = torch.is_grad_enabled()
+        try:
+            return super().apply(*args, **kwargs)
+        finally:
+            _grad_mode.enabled = True
 
     @staticmethod
     def forward(
@@ -402,36 +441,44 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
         label_smoothing=0.0, reduction="mean", softcap=None, return_z_loss: bool = False, accum_dtype=None,
         use_token_scaling: bool = False, return_token_accuracy: bool = False, return_predicted_tokens: bool = False,
     ):
+        assert isinstance(return_z_loss, bool), f"return_z_loss must be True or False. Got: {return_z_loss}"
+        assert isinstance(return_token_accuracy, bool), f"return_token_accuracy must be True or False. Got: {return_token_accuracy}"
+        assert isinstance(return_predicted_tokens, bool), f"return_predicted_tokens must be True or False. Got: {return_predicted_tokens}"
         ctx.in_dtypes = (_input.dtype, weight.dtype, None if bias is None else bias.dtype)
         x, w, b = _autocast_operands(_input, weight, bias)
         ctx.stored_grads = None
-        needs = (_input.requires_grad, weight.requires_grad, bias is not None and bias.requires_grad)
-        if MODE == "single_sweep" and reduction in ("mean", "sum") and any(needs) and x.dtype != torch.float32:
-            assert isinstance(return_z_loss, bool), f"return_z_loss must be True or False. Got: {return_z_loss}"
-            prep = _Prepared(x, w, target, b, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
-                             use_token_scaling, want_argmax=return_token_accuracy or return_predicted_tokens)
+        ctx.has_bias = bias is not None
+        ctx.flce_params = dict(ignore_index=ignore_index, lse_square_scale=lse_square_scale, label_smoothing=label_smoothing,
+                               reduction=reduction, softcap=softcap, use_token_scaling=use_token_scaling)
+        # what autograd will ask for: nothing under torch.no_grad(), whatever the tensors' flags say
+        recording = getattr(_grad_mode, "enabled", True)
+        needs = (recording and ctx.needs_input_grad[0], recording and ctx.needs_input_grad[1],
+                 recording and bias is not None and ctx.needs_input_grad[3])
+        want_argmax = return_token_accuracy or return_predicted_tokens
+        prep = _Prepared(x, w, target, b, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
+                         use_token_scaling, want_argmax=want_argmax, allow_compact=True)
+        if _use_single_sweep(reduction, needs, x.dtype):
             out, norm, gx, gw, gb = flce_single_sweep_device(prep, needs[0], needs[1], needs[2])
-            if CHECK_TARGETS:
-                _raise_on_bad_targets(norm, prep.vocab)
+            gx = prep.rows_to_token_order(gx)
             ctx.stored_grads = (gx, gw, gb)
-            ctx.flce_saved = (prep, out["lse"], out["target_prob"], norm)
-            ctx.has_bias = bias is not None
+        else:
+            out, norm, _rowstats = flce_forward_device(prep)
+        lse, target_prob = out["lse"], out["target_prob"]
+        out = _results_to_token_order(prep, out)
+        if CHECK_TARGETS:
+            _raise_on_bad_targets(norm, prep.vocab)
+        if reduction == "none":
+            loss = out["loss_rows"]
+            z_loss = out["z_loss_rows"].to(prep.dtype) if return_z_loss else None
+            token_accuracy = out["correct_rows"] if return_token_accuracy else None
+        else:
             loss = out["scalars"][0]
             z_loss = out["scalars"][1].to(prep.dtype) if return_z_loss else None
             token_accuracy = out["scalars"][2] if return_token_accuracy else None
-            predicted_tokens = out["predicted_tokens"] if return_predicted_tokens else None
-            nondiff = [t for t in (z_loss, token_accuracy, predicted_tokens) if t is not None]
-            if nondiff:
-                ctx.mark_non_differentiable(*nondiff)
-            return loss, z_loss, token_accuracy, predicted_tokens
-        loss, z_loss, token_accuracy, predicted_tokens, saved = fused_linear_cross_entropy_forward(
-            x, w, target, ce_weight=ce_weight, bias=b, ignore_index=ignore_index, lse_square_scale=lse_square_scale,
-            label_smoothing=label_smoothing, reduction=reduction, softcap=softcap, return_z_loss=return_z_loss,
-            accum_dtype=accum_dtype, use_token_scaling=use_token_scaling, return_token_accuracy=return_token_accuracy,
-            return_predicted_tokens=return_predicted_tokens,
-        )
-        ctx.flce_saved = saved
-        ctx.has_bias = bias is not None
+        predicted_tokens = out["predicted_tokens"] if return_predicted_tokens else None
+        ctx.flce_hidden = prep.hidden
+        ctx.flce_autocast = (x.dtype, w.dtype)
+        ctx.save_for_backward(_input, weight, target, bias, ce_weight, lse, target_prob, norm)
         nondiff = [t for t in (z_loss, token_accuracy, predicted_tokens) if t is not None]
         if nondiff:
             ctx.mark_non_differentiable(*nondiff)
@@ -441,13 +488,13 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
     def backward(ctx, grad_output, grad_output2=None, grad_output3=None, grad_output4=None):
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         need_b = ctx.has_bias and ctx.needs_input_grad[3]
+        h = ctx.flce_hidden
         if ctx.stored_grads is not None:
             # single-sweep mode, first backward: hand the stored gradients off (scaled on the device when needed)
             gx, gw, gb = ctx.stored_grads
             ctx.stored_grads = None
-            prep = ctx.flce_saved[0]
-            go = grad_output.detach().to(device=prep.device, dtype=torch.float32).reshape(1)
-            h = prep.hidden
+            dev = (gx if gx is not None else gw if gw is not None else gb).device
+            go = grad_output.detach().to(device=dev, dtype=torch.float32).reshape(1)
             gx = scale_gradient_(gx, go)
             gw = scale_gradient_(gw, go)
             gb = scale_gradient_(gb, go)
@@ -456,7 +503,14 @@ class LigerFusedLinearCrossEntropyFunction(torch.autograd.Function):
             if gw is not None and gw.shape[1] != h:
                 gw = gw[:, :h].contiguous()
         else:
-            gx, gw, gb = fused_linear_cross_entropy_backward(grad_output, ctx.flce_saved, need_x, need_w, need_b)
+            _input, weight, target, bias, ce_weight, lse, target_prob, norm = ctx.saved_tensors
+            x = _input.to(ctx.flce_autocast[0]) if _input.dtype != ctx.flce_autocast[0] else _input
+            w = weight.to(ctx.flce_autocast[1]) if weight.dtype != ctx.flce_autocast[1] else weight
+            b = bias if (bias is None or bias.dtype == ctx.flce_autocast[0]) else bias.to(ctx.flce_autocast[0])
+            kw = ctx.flce_params
+            prep = _Prepared(x, w, target, b, ce_weight, kw["ignore_index"], kw["lse_square_scale"], kw["label_smoothing"],
+                             kw["reduction"], kw["softcap"], kw["use_token_scaling"], want_argmax=False, allow_compact=True)
+            gx, gw, gb = fused_linear_cross_entropy_backward(grad_output, (prep, lse, target_prob, norm), need_x, need_w, need_b)
         dx, dw, db = ctx.in_dtypes
         gx = None if gx is None else gx.to(dx)
         gw = None if gw is None else gw.to(dw)

@@ -292,21 +292,30 @@ int emu_split_fp32(const float* src, long long rows, long long cols, long long l
 // the single-sweep mode's in-place logit gradient over one token chunk (launch geometry of flce_b200_forward_backward)
 int emu_dz_inplace(void* slab, long long ld, long long rows, long long vocab, int fmt, const long long* target,
                    long long vocab_offset, const float* lse, const float* c1, const float* c2, const float* c3,
-                   const float* col_weight, float inv_softcap) {
-  const int tpb = 256;
-  const emu::Dim3 grid(static_cast<unsigned>(ceil_div(ceil_div(vocab, 8), tpb)), static_cast<unsigned>(rows), 1);
-  emu::launch_serial(grid, tpb, [&]() {
+                   const float* col_weight, float inv_softcap, const int* active_rows, int active_base) {
+  const emu::Dim3 grid(static_cast<unsigned>(ceil_div(vocab, kDzInplaceCols)), static_cast<unsigned>(rows), 1);
+  emu::launch_serial(grid, kDzInplaceThreads, [&]() {
     dz_inplace_kernel(static_cast<uint16_t*>(slab), ld, static_cast<int>(rows), static_cast<int>(vocab), fmt, target,
-                      vocab_offset, lse, c1, c2, c3, col_weight, inv_softcap);
+                      vocab_offset, lse, c1, c2, c3, col_weight, inv_softcap, active_rows, active_base);
+  });
+  return 0;
+}
+
+// the ordered sums over all rows at the end of flce_b200_forward_backward
+int emu_reduce_rows(long long n_rows, const float* loss_rows, const float* z_rows, const float* correct_rows, const float* norm,
+                    float* scalars) {
+  emu::launch(1, kRedThreads, [&]() {
+    reduce_rows_kernel(static_cast<int>(n_rows), loss_rows, z_rows, correct_rows, norm, scalars);
   });
   return 0;
 }
 
 // bias gradient: column sums of a 16-bit slab, optionally accumulated
-int emu_colsum(const void* dz, long long ld, long long rows, long long cols, int fmt, float* out, int accumulate) {
+int emu_colsum(const void* dz, long long ld, long long rows, long long cols, int fmt, float* out, int accumulate,
+               const int* active_rows, int active_base) {
   emu::launch(static_cast<unsigned>(ceil_div(cols, 64)), 1024, [&]() {
     colsum_accumulate_kernel(static_cast<const uint16_t*>(dz), ld, static_cast<int>(rows), static_cast<int>(cols), fmt, out,
-                             accumulate);
+                             accumulate, active_rows, active_base);
   });
   return 0;
 }
@@ -395,8 +404,9 @@ int emu_limit_to_active_rows(int m_tiles, int k_blocks, int role, int active_row
 int emu_sweep_stats(const void* x, const void* w, int dtype, int m, int vocab, int k, long long ld_x, long long ld_w,
                     const long long* target, const float* bias, const float* col_weight, float softcap, long long vocab_offset,
                     float* pmax, float* psum, float* plogit_sum, float* pamax_val, int* pamax_idx, float* target_logit,
-                    void* logits_out, long long ld_logits, int logits_fmt, int m_tile_limit) {
-  StatsEpilogue::Params ep;
+                    void* logits_out, long long ld_logits, int logits_fmt, int m_tile_limit, const float* shift,
+                    long long ignore_index) {
+  StatsEpilogue::Params ep{};
   ep.target = target;
   ep.bias = bias;
   ep.col_weight = col_weight;
@@ -414,6 +424,8 @@ int emu_sweep_stats(const void* x, const void* w, int dtype, int m, int vocab, i
   ep.logits_out = logits_out;
   ep.ld_logits = ld_logits;
   ep.logits_fmt = logits_fmt;
+  ep.shift = shift;
+  ep.ignore_index = ignore_index;
   run_tiles<StatsEpilogue>(ep, x, w, dtype, m, vocab, k, ld_x, ld_w, m_tile_limit);
   return 0;
 }
@@ -447,7 +459,7 @@ int emu_sweep_dz(const void* x, const void* w, int dtype, int m, int vocab, int 
 // StoreEpilogue: D = A . B^T (+ acc) with both operands K-major; acc (fp32, in/out) and out (out_fmt) may each be null
 int emu_gemm_store(const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a, long long ld_b, float* acc,
                    long long ld_acc, void* out, long long ld_out, int out_fmt) {
-  StoreEpilogue::Params ep;
+  StoreEpilogue::Params ep{};
   ep.m_rows = m;
   ep.n_cols = n;
   ep.acc_in = acc;
@@ -457,6 +469,76 @@ int emu_gemm_store(const void* a, const void* b, int dtype, int m, int n, int k,
   ep.ld_out = ld_out;
   ep.out_fmt = out_fmt;
   run_tiles<StoreEpilogue>(ep, a, b, dtype, m, n, k, ld_a, ld_b);
+  return 0;
+}
+
+// StoreEpilogue with every option: separate fp32 partial in / out, per-row scale, rank-1 correction (all nullable)
+int emu_gemm_store_ex(const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a, long long ld_b,
+                      const float* acc_in, float* acc_out, long long ld_acc, void* out, long long ld_out, int out_fmt,
+                      const float* row_scale, const float* r1_row, const float* r1_col) {
+  StoreEpilogue::Params ep{};
+  ep.m_rows = m;
+  ep.n_cols = n;
+  ep.acc_in = acc_in;
+  ep.acc_out = acc_out;
+  ep.ld_acc = ld_acc;
+  ep.out = out;
+  ep.ld_out = ld_out;
+  ep.out_fmt = out_fmt;
+  ep.row_scale = row_scale;
+  ep.r1_row = r1_row;
+  ep.r1_col = r1_col;
+  run_tiles<StoreEpilogue>(ep, a, b, dtype, m, n, k, ld_a, ld_b);
+  return 0;
+}
+
+// the exp-store form of the single-sweep mode: reference points, per-chunk fix-up, ordered scaled column sums
+// (launch geometry of flce_b200_forward_backward)
+int emu_target_shift(const void* x, long long ld_x, const void* w, long long ld_w, int fmt, int n_rows, int hidden,
+                     const long long* target, long long ignore_index, long long vocab, const float* bias, float softcap,
+                     float* shift) {
+  const int warps = 8;
+  emu::launch(static_cast<unsigned>(ceil_div(n_rows, warps)), warps * 32, [&]() {
+    target_shift_kernel(static_cast<const uint16_t*>(x), ld_x, static_cast<const uint16_t*>(w), ld_w, fmt, n_rows, hidden,
+                        target, ignore_index, vocab, bias, softcap, softcap > 0.f ? 1.f / softcap : 0.f, kExpStoreOffset, shift);
+  });
+  return 0;
+}
+
+int emu_exp_store_fixup(const void* x, long long ld_x, int hidden, int fmt, int n_rows, const long long* target,
+                        long long ignore_index, long long vocab, const float* lse, const float* shift,
+                        const float* target_logit, const float* c1, const float* c3, float softcap, void* slab,
+                        long long ld_slab, float* alpha, void* xs, long long ld_xs) {
+  emu::launch_serial(static_cast<unsigned>(n_rows), 256, [&]() {
+    exp_store_fixup_kernel(static_cast<const uint16_t*>(x), ld_x, hidden, fmt, n_rows, target, ignore_index, vocab, lse, shift,
+                           target_logit, c1, c3, softcap > 0.f ? 1.f / softcap : 0.f, kExpStoreClamp,
+                           static_cast<uint16_t*>(slab), ld_slab, alpha, static_cast<uint16_t*>(xs), ld_xs);
+  });
+  return 0;
+}
+
+// returns the chunk's redo flag; when it is raised the reference points have been moved onto the log-sum-exp
+int emu_exp_store_check(int n_rows, const long long* target, long long ignore_index, const float* lse, float* shift) {
+  int flag = 0;
+  const int threads = 256;
+  emu::launch_serial(static_cast<unsigned>(ceil_div(n_rows, threads)), threads, [&]() {
+    exp_store_check_kernel(n_rows, target, ignore_index, lse, shift, kExpStoreRedoLimit, &flag);
+  });
+  emu::launch_serial(static_cast<unsigned>(ceil_div(n_rows, threads)), threads, [&]() {
+    exp_store_reshift_kernel(n_rows, lse, &flag, shift);
+  });
+  return flag;
+}
+
+int emu_scaled_colsum(const void* mat, long long ld, int n_rows, int n_cols, int fmt, const float* scale, float* scratch,
+                      float* out, int accumulate) {
+  const emu::Dim3 grid(static_cast<unsigned>(ceil_div(n_cols, 64)), kColsumSplits, 1);
+  emu::launch(grid, 1024, [&]() {
+    scaled_colsum_stage1_kernel(static_cast<const uint16_t*>(mat), ld, n_rows, n_cols, fmt, scale, scratch);
+  });
+  emu::launch_serial(static_cast<unsigned>(ceil_div(n_cols, 256)), 256, [&]() {
+    scaled_colsum_stage2_kernel(scratch, n_cols, out, accumulate);
+  });
   return 0;
 }
 
@@ -514,7 +596,7 @@ int emu_sce_forward(const void* x, const void* w, int dtype, int m, int vocab, i
                     float* nll, float* entropy, float* lse) {
   const int n_tiles = static_cast<int>(ceil_div(vocab, kBlockN));
   const size_t plane = static_cast<size_t>(n_tiles) * m;
-  EntropyStatsEpilogue::Params ep;
+  EntropyStatsEpilogue::Params ep{};
   ep.target = target;
   ep.scale = 1.f / temperature;
   ep.n_cols = vocab;

@@ -54,8 +54,9 @@ def load():
         "emu_compact_rows": [P, LL, LL, LL, P, LL, P, P, P, P],
         "emu_scatter_rows": [P, LL, P, P, LL, P],
         "emu_split_fp32": [P, LL, LL, LL, P, LL, LL, P, I, I],
-        "emu_dz_inplace": [P, LL, LL, LL, I, P, LL, P, P, P, P, P, F],
-        "emu_colsum": [P, LL, LL, LL, I, P, I],
+        "emu_dz_inplace": [P, LL, LL, LL, I, P, LL, P, P, P, P, P, F, P, I],
+        "emu_reduce_rows": [LL, P, P, P, P, P],
+        "emu_colsum": [P, LL, LL, LL, I, P, I, P, I],
         "emu_scale_inplace": [P, LL, I, P],
         "emu_merge_partials": [LL, I, P, P, P, P, P, P],
         "emu_scaled_ce_rows": [P, LL, I, LL, LL, P, LL, F, P, P, P],
@@ -64,7 +65,12 @@ def load():
         "emu_tile_schedule": [I, I, I, I, I, P, P],
         "emu_sce_forward": [P, P, I, I, I, I, LL, LL, P, LL, F, P, P, P, P, P],
         "emu_sce_sweep_dz": [P, P, I, I, I, I, LL, LL, P, LL, F, LL, P, P, P, P, P, LL, I],
-        "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I, I],
+        "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I, I, P, LL],
+        "emu_gemm_store_ex": [P, P, I, I, I, I, LL, LL, P, P, LL, P, LL, I, P, P, P],
+        "emu_target_shift": [P, LL, P, LL, I, I, I, P, LL, LL, P, F, P],
+        "emu_exp_store_fixup": [P, LL, I, I, I, P, LL, LL, P, P, P, P, P, F, P, LL, P, P, LL],
+        "emu_scaled_colsum": [P, LL, I, I, I, P, P, P, I],
+        "emu_exp_store_check": [I, P, LL, P, P],
         "emu_sweep_dz": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, LL, I, I],
         "emu_gemm_store": [P, P, I, I, I, I, LL, LL, P, LL, P, LL, I],
         "emu_coef": [LL, LL, F, F, I, I, LL, LL, LL, P, P, P, P, P, P, I, P, P, P],
@@ -181,7 +187,7 @@ class EmuLib(fake_lib.FakeLib):
         rc = self.emu.emu_sweep_stats(prob.x, prob.w, prob.dtype, n, v, prob.hidden, prob.ld_x, prob.ld_w, prob.target, prob.bias,
                                       prob.ce_weight, cap, prob.vocab_offset, planes[0].data_ptr(), planes[1].data_ptr(),
                                       planes[2].data_ptr(), planes[3].data_ptr(), pidx.data_ptr(), _addr(rowstats) + 2 * n * 4,
-                                      None, 0, 0, limit)
+                                      None, 0, 0, limit, None, 0)
         self.emu.emu_merge_partials(n, n_tiles, planes[0].data_ptr(), planes[1].data_ptr(), planes[2].data_ptr(),
                                     planes[3].data_ptr(), pidx.data_ptr(), _addr(rowstats))
         return rc
@@ -266,6 +272,128 @@ class EmuLib(fake_lib.FakeLib):
             if a.grad_bias:
                 gb = dzf[:k_rows].sum(0) + (0 if lof is None else lof[:k_rows].sum(0))
                 fake_lib.float_array(a.grad_bias + v0 * 4, cols)[:] = gb.numpy()
+        return 0
+
+    # ---- single-sweep mode: the host sequence of flce_b200_forward_backward restated around the emulated pieces
+    CHUNK_ROWS = 256             # rows per token chunk here (the library sizes chunks from a byte budget, in multiples of 256)
+
+    def flce_b200_forward_backward(self, p, args, ws, ws_bytes, budget, stream):
+        self.calls.append("flce_b200_forward_backward")
+        prob, a = p._obj, args._obj
+        self.structs.setdefault("flce_b200_forward_backward", []).append(prob)
+        fo = a.out.contents
+        tdt = {0: torch.bfloat16, 1: torch.float16}[prob.dtype]
+        gdt = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}[a.grad_dtype]
+        gfmt = a.grad_dtype
+        n, h, v = prob.n_rows, prob.hidden, prob.vocab
+        smoothing = prob.label_smoothing > 0
+        cap = float(prob.softcap)
+        exp_ok = not (smoothing and cap > 0) and not a.grad_bias and prob.dtype == 0
+        if a.store_mode == 2 and not exp_ok:
+            return 2
+        exp_store = exp_ok and a.store_mode != 1
+        self.store_modes = getattr(self, "store_modes", []) + ["exp" if exp_store else "logits"]
+        if not a.norm_given:
+            self.emu.emu_count(prob.target, n, prob.ignore_index, prob.ce_weight, v, prob.vocab_offset, float(prob.vocab_total), a.norm)
+        active = int(fake_lib._array(prob.active_rows, C.c_int32, 1)[0]) if prob.active_rows else None
+        active_ptr = prob.active_rows if prob.active_rows else None
+        W16 = self._matrix(prob.w, v, h, prob.ld_w, tdt)
+        Wt = W16.t().contiguous()                                   # [h, v]: B operand of grad_input, K (= vocabulary) contiguous
+        n_tiles = (v + 255) // 256
+        ld_slab = (v + 63) // 64 * 64
+        nan = float("nan")
+        dw_acc = torch.full((v, h), nan)
+        gb = torch.zeros(v)
+        shift = torch.full((n,), nan)
+        w_sum, x_sum = torch.full((h,), nan), torch.full((h,), nan)
+        scratch = torch.full((32, h), nan)
+        if exp_store:
+            self.emu.emu_target_shift(prob.x, prob.ld_x, prob.w, prob.ld_w, prob.dtype, n, h, prob.target, prob.ignore_index, v,
+                                      prob.bias, cap, shift.data_ptr())
+            if smoothing and a.grad_input:
+                self.emu.emu_scaled_colsum(prob.w, prob.ld_w, v, h, prob.dtype, prob.ce_weight, scratch.data_ptr(), w_sum.data_ptr(), 0)
+        off = lambda base, rows, size: (base + rows * size) if base else None      # noqa: E731
+        chunks = list(range(0, n, self.CHUNK_ROWS))
+        for r0 in chunks:
+            first, last = r0 == chunks[0], r0 == chunks[-1]
+            rows = min(self.CHUNK_ROWS, n - r0)
+            live = rows if active is None else min(rows, max(0, active - r0))
+            pairs = (live + self.PAIR_ROWS - 1) // self.PAIR_ROWS
+            limit = -1 if active is None else pairs * (self.PAIR_ROWS // 128)
+            row_limit = rows if active is None else min(rows, pairs * self.PAIR_ROWS)
+            k_rows = rows if active is None else min(rows, (live + 63) // 64 * 64)
+            x_c = prob.x + r0 * prob.ld_x * 2
+            t_c = prob.target + r0 * 8
+            planes = [torch.full((n_tiles, rows), nan) for _ in range(4)]
+            pidx = torch.zeros((n_tiles, rows), dtype=torch.int32)
+            stats = torch.full((6, rows), nan)
+            stats[2] = 0.0
+            slab = torch.full((rows, ld_slab), nan).to(tdt)        # what the sweep does not write stays poisoned
+            self.emu.emu_sweep_stats(x_c, prob.w, prob.dtype, rows, v, h, prob.ld_x, prob.ld_w, t_c, prob.bias, prob.ce_weight, cap,
+                                     prob.vocab_offset, planes[0].data_ptr(), planes[1].data_ptr(), planes[2].data_ptr(),
+                                     planes[3].data_ptr(), pidx.data_ptr(), stats[2].data_ptr(), slab.data_ptr(), ld_slab,
+                                     prob.dtype, limit, shift[r0:].data_ptr() if exp_store else None, prob.ignore_index)
+            self.emu.emu_merge_partials(rows, n_tiles, planes[0].data_ptr(), planes[1].data_ptr(), planes[2].data_ptr(),
+                                        planes[3].data_ptr(), pidx.data_ptr(), stats.data_ptr())
+            self.emu.emu_finalize(rows, prob.ignore_index, prob.label_smoothing, prob.lse_square_scale, int(prob.reduction == 0),
+                                  prob.use_token_scaling, v, prob.vocab_total, prob.vocab_offset, t_c, prob.ce_weight,
+                                  stats.data_ptr(), a.norm, off(fo.lse, r0, 4), off(fo.target_prob, r0, 4), off(fo.loss_rows, r0, 4),
+                                  off(fo.z_loss_rows, r0, 4), off(fo.correct_rows, r0, 4), off(fo.predicted_tokens, r0, 8), None)
+            c = torch.zeros(3, rows)
+            self.emu.emu_coef(rows, prob.ignore_index, prob.label_smoothing, prob.lse_square_scale, int(prob.reduction == 0),
+                              prob.use_token_scaling, v, prob.vocab_total, prob.vocab_offset, t_c, prob.ce_weight, off(fo.lse, r0, 4),
+                              off(fo.target_prob, r0, 4), a.norm, None, 0, c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr())
+            alpha = torch.full((rows,), nan)
+            xs = torch.full((rows, h), nan).to(tdt)
+            if exp_store:
+                redo = self.emu.emu_exp_store_check(rows, t_c, prob.ignore_index, off(fo.lse, r0, 4), shift[r0:].data_ptr())
+                self.redo_chunks = getattr(self, "redo_chunks", 0) + int(redo)
+                if redo:      # the gated repeat of sweep 1 with the reference points on the log-sum-exp
+                    tl = torch.zeros(rows)
+                    self.emu.emu_sweep_stats(x_c, prob.w, prob.dtype, rows, v, h, prob.ld_x, prob.ld_w, t_c, prob.bias,
+                                             prob.ce_weight, cap, prob.vocab_offset, planes[0].data_ptr(), planes[1].data_ptr(),
+                                             planes[2].data_ptr(), planes[3].data_ptr(), pidx.data_ptr(), tl.data_ptr(),
+                                             slab.data_ptr(), ld_slab, prob.dtype, limit, shift[r0:].data_ptr(), prob.ignore_index)
+                self.emu.emu_exp_store_fixup(x_c, prob.ld_x, h, prob.dtype, rows, t_c, prob.ignore_index, v, off(fo.lse, r0, 4),
+                                             shift[r0:].data_ptr(), stats[2].data_ptr(), c[0].data_ptr(), c[2].data_ptr(), cap,
+                                             slab.data_ptr(), ld_slab, alpha.data_ptr(), xs.data_ptr(), h)
+                if smoothing and a.grad_weight:
+                    self.emu.emu_scaled_colsum(x_c, prob.ld_x, rows, h, prob.dtype, c[1].data_ptr(), scratch.data_ptr(),
+                                               x_sum.data_ptr(), int(not first))
+            else:
+                self.emu.emu_dz_inplace(slab.data_ptr(), ld_slab, rows, v, prob.dtype, t_c, prob.vocab_offset, off(fo.lse, r0, 4),
+                                        c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr(), prob.ce_weight,
+                                        1.0 / cap if cap > 0 else 0.0, active_ptr, r0)
+            if a.grad_input and row_limit > 0:
+                # grad_input[chunk] = dZ . W through the library's store epilogue (per-row factor and rank-1 term in exp-store form)
+                gi = a.grad_input + r0 * h * (4 if gfmt == 2 else 2)
+                self.emu.emu_gemm_store_ex(slab.data_ptr(), Wt.data_ptr(), prob.dtype, row_limit, h, v, ld_slab, v, None, None, 0,
+                                           gi, h, gfmt, alpha.data_ptr() if exp_store else None,
+                                           c[1].data_ptr() if (exp_store and smoothing) else None,
+                                           w_sum.data_ptr() if (exp_store and smoothing) else None)
+            if a.grad_weight:
+                X16 = xs if exp_store else self._matrix(x_c, rows, h, prob.ld_x, tdt)
+                At = slab[:k_rows, :v].t().contiguous()             # [v, k_rows]
+                Bt = X16[:k_rows].t().contiguous()                  # [h, k_rows]
+                kk = k_rows
+                if kk == 0:                                         # nothing accumulated: the kernel's k_blocks == 0 path
+                    At, Bt, kk = torch.zeros(v, 8).to(tdt), torch.zeros(h, 8).to(tdt), 8
+                r1 = exp_store and smoothing and last
+                out_ptr = a.grad_weight if (last and gfmt != 2) else None
+                acc_out = dw_acc if (gfmt == 2 or not last) else None
+                if gfmt == 2:
+                    acc_out = self._matrix(a.grad_weight, v, h, h, torch.float32)
+                acc_in = None if first else (acc_out if gfmt == 2 else dw_acc)
+                self.emu.emu_gemm_store_ex(At.data_ptr(), Bt.data_ptr(), prob.dtype, v, h, kk, kk, kk,
+                                           None if acc_in is None else acc_in.data_ptr(),
+                                           None if acc_out is None else acc_out.data_ptr(), h, out_ptr, h, prob.dtype,
+                                           None, prob.ce_weight if r1 else None, x_sum.data_ptr() if r1 else None)
+            if a.grad_bias:
+                self.emu.emu_colsum(slab.data_ptr(), ld_slab, rows, v, prob.dtype, gb.data_ptr(), int(r0 != 0), active_ptr, r0)
+        if a.grad_bias:
+            fake_lib.float_array(a.grad_bias, v)[:] = gb.numpy()
+        if fo.scalars:
+            self.emu.emu_reduce_rows(n, fo.loss_rows, fo.z_loss_rows, fo.correct_rows, a.norm, fo.scalars)
         return 0
 
     # ---- scaled cross-entropy on the two sweeps: the library's epilogues tile by tile, its slab loop restated here

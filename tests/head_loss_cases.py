@@ -25,6 +25,12 @@ def _tols(dtype, vocab=0):
         # the largest gradient entry holds up to V = 32k, 5e-4 beyond (measured 2e-4 at V = 128256).  Both are inside the
         # reference's own fp32 bar, atol 1e-5 absolute / rtol 5e-4 (test/transformers/test_fused_linear_jsd.py:94).
         return 2e-5, 2e-5, (2e-5 if vocab <= 32768 else 5e-4), 5e-4
+    if dtype == torch.float16 and vocab > 100000:
+        # the logit gradients of a mean over a few hundred tokens at V = 128k are about 3e-8, at fp16's smallest
+        # subnormal (6e-8): an element of the 16-bit slab is 0 or one step, and a last-bit difference between the
+        # kernel's approximate exp2 and the oracle's exp flips it.  The sum over V averages the flips out to ~2 % of
+        # the largest gradient entry (the reference stores its chunk gradients in fp16 as well).
+        return 1e-2, 1e-2, 3e-2, 5e-2
     return 1e-2, 1e-2, 1e-2, 5e-2
 
 

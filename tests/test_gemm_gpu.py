@@ -47,3 +47,45 @@ def test_gemm_exact(M, N, K, a_mn, b_mn, pair):
 def test_gemm_16bit_output(dtype):
     D, ref = _run(0, 0, 0, 300, 264, 136, dtype=dtype, out_dtype=dtype)
     assert torch.equal(D.float(), ref.to(dtype).float())
+
+
+# K >= 2048 and N >= 1024 with CTA pairs select the 256 x 512 tile (two MMAs per K slice, one accumulator stage)
+WIDE_SHAPES = [(256, 1024, 2048), (300, 1032, 2056), (1000, 1304, 2120), (2048, 4096, 2048), (520, 2560, 4160)]
+
+
+@pytest.mark.parametrize("a_mn,b_mn", VARIANTS)
+@pytest.mark.parametrize("M,N,K", WIDE_SHAPES)
+def test_gemm_wide_tiles_exact(M, N, K, a_mn, b_mn):
+    from liger_kernel_b200 import _lib
+
+    D, ref = _run(a_mn, b_mn, 1, M, N, K)
+    assert torch.equal(D, ref), f"{int((D != ref).sum())} of {D.numel()} entries differ"
+    _lib.set_option("wide_tiles", 0)
+    try:
+        D2, _ = _run(a_mn, b_mn, 1, M, N, K)
+    finally:
+        _lib.set_option("wide_tiles", 1)
+    assert torch.equal(D2, ref)
+
+
+def test_gemm_wide_tiles_accumulate_across_calls():
+    """fp32 partial results carried from call to call (the weight gradient over token chunks) with the wide tile."""
+    from liger_kernel_b200 import _lib
+
+    lib = _lib.lib
+    M, N, K = 700, 1536, 2304
+    g = torch.Generator(device="cuda").manual_seed(5)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    acc = torch.zeros((M, N), device="cuda", dtype=torch.float32)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ref = torch.zeros((M, N), device="cuda", dtype=torch.float32)
+    for it in range(3):
+        A = torch.randint(-2, 3, (K, M), device="cuda", generator=g).to(torch.bfloat16)      # MN-major, as dZ^T
+        B = torch.randint(-2, 3, (K, N), device="cuda", generator=g).to(torch.bfloat16)      # MN-major, as X
+        _lib.check(lib.flce_b200_gemm_accumulate(C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), C.c_void_p(acc.data_ptr()),
+                                                 C.c_void_p(out.data_ptr()), M, N, K, A.stride(0), B.stride(0), acc.stride(0),
+                                                 out.stride(0), 0, 0, 1, 1, 1, st))
+        ref += A.float().t() @ B.float()
+    _lib.check(lib.flce_b200_check_device_status(st))
+    assert torch.equal(acc, ref)
+    assert torch.equal(out.float(), ref.bfloat16().float())

@@ -24,6 +24,8 @@ def test_recompute_mode_calls_and_shapes(monkeypatch):
     import liger_kernel_b200.ops.fused_linear_cross_entropy as fl
 
     with fake_lib.installed(monkeypatch) as fake:
+        monkeypatch.setattr(fl, "MODE", "recompute")
+        monkeypatch.setattr(fl, "SKIP_IGNORED", False)
         x, w, t = _inputs()
         b = torch.zeros(50, dtype=torch.bfloat16, requires_grad=True)
         loss, z, acc, pred = fl.LigerFusedLinearCrossEntropyFunction.apply(x, w, t, b, None, -100, 1e-4, 0.1, "mean", 30.0, True,
@@ -52,6 +54,7 @@ def test_single_sweep_mode_hands_off_then_recomputes(monkeypatch):
 
     with fake_lib.installed(monkeypatch) as fake:
         monkeypatch.setattr(fl, "MODE", "single_sweep")
+        monkeypatch.setattr(fl, "SKIP_IGNORED", False)
         x, w, t = _inputs(H=32)
         loss = fl.LigerFusedLinearCrossEntropyFunction.apply(x, w, t)[0]
         assert fake.calls == ["flce_b200_workspace_bytes", "flce_b200_forward_backward"]
@@ -63,6 +66,35 @@ def test_single_sweep_mode_hands_off_then_recomputes(monkeypatch):
         del fake.calls[:]
         fl.LigerFusedLinearCrossEntropyFunction.apply(x, w, t, None, None, -100, 0.0, 0.0, "none")
         assert "flce_b200_forward_backward" not in fake.calls and "flce_b200_forward" in fake.calls
+
+
+def test_default_mode_compacts_rows_and_forms_gradients_in_forward(monkeypatch):
+    """Defaults: ignored rows are moved out of the way and, for mean / sum with 16-bit operands and a gradient wanted,
+    forward already forms the gradients; grad_input comes back in token order; backward only scales."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as fl
+
+    with fake_lib.installed(monkeypatch) as fake:
+        assert fl.MODE == "auto" and fl.SKIP_IGNORED
+        x, w, t = _inputs(H=32)
+        loss = fl.LigerFusedLinearCrossEntropyFunction.apply(x, w, t)[0]
+        assert fake.calls == ["flce_b200_compact_rows", "flce_b200_workspace_bytes", "flce_b200_forward_backward",
+                              "flce_b200_scatter_rows"]
+        prob = fake.structs["flce_b200_forward_backward"][0]
+        assert prob.active_rows is not None
+        loss.backward()
+        assert fake.calls[4:] == ["flce_b200_scale_gradient", "flce_b200_scale_gradient"]
+        assert x.grad.shape == (12, 32) and w.grad.shape == (50, 32)
+        # forward-only and reduction "none" use the two-sweep path
+        del fake.calls[:]
+        with torch.no_grad():
+            fl.LigerFusedLinearCrossEntropyFunction.apply(x, w, t)
+        assert "flce_b200_forward_backward" not in fake.calls and "flce_b200_forward" in fake.calls
+        # an in-place change of a saved operand between forward and backward is caught by autograd
+        loss = fl.LigerFusedLinearCrossEntropyFunction.apply(x, w, t, None, None, -100, 0.0, 0.0, "none")[0]
+        with torch.no_grad():
+            w.mul_(2.0)
+        with pytest.raises(RuntimeError, match="modified by an inplace operation"):
+            loss.sum().backward()
 
 
 def test_fp32_inputs_use_term_splits_and_fp32_gradients(monkeypatch):

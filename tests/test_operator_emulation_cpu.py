@@ -128,6 +128,34 @@ def test_logit_gaps_of_several_hundred_stay_finite(emulated):
         gpu_tests._check(res, ora, torch.bfloat16, "mean", 70)
 
 
+def test_exp_store_form_where_it_applies_and_the_redo_path(emulated, monkeypatch):
+    """Default single-sweep calls keep exponentials (bf16, no bias gradient, no smoothing under a soft-cap) and logits
+    otherwise; ordinary inputs never take the second pass over a chunk, peaked ones do; both forms agree with the oracle."""
+    import liger_kernel_b200.ops.fused_linear_cross_entropy as mod
+
+    x, w, t, b, cw = make_inputs(300, 40, 600, torch.bfloat16, seed=11, bias=True, ce_weight=True)
+    cases = [(dict(), None, None, "exp"), (dict(label_smoothing=0.1, lse_square_scale=1e-4), None, cw, "exp"),
+             (dict(softcap=20.0), None, None, "exp"), (dict(softcap=20.0, label_smoothing=0.1), None, None, "logits"),
+             (dict(), b, None, "logits"), (dict(use_token_scaling=True, label_smoothing=0.05), None, None, "exp")]
+    for kw, bias, weights, form in cases:
+        emulated.store_modes, emulated.redo_chunks = [], 0
+        res = run_cuda(x, w, t, bias=bias, ce_weight=weights, **kw)
+        assert emulated.store_modes == [form] and emulated.redo_chunks == 0, (kw, emulated.store_modes, emulated.redo_chunks)
+        gpu_tests._check(res, oracle_for(x, w, t, bias=bias, ce_weight=weights, **kw), torch.bfloat16, "mean", 300)
+    emulated.store_modes = []
+    run_cuda(x.half(), w.half(), t)
+    assert emulated.store_modes == ["logits"]                       # fp16 cannot hold the exponentials' range
+    monkeypatch.setattr(mod, "STORE_MODE", "logits")
+    emulated.store_modes = []
+    res = run_cuda(x, w, t)
+    assert emulated.store_modes == ["logits"]
+    gpu_tests._check(res, oracle_for(x, w, t), torch.bfloat16, "mean", 300)
+    monkeypatch.setattr(mod, "STORE_MODE", "auto")
+    emulated.redo_chunks = 0
+    test_logit_gaps_of_several_hundred_stay_finite(emulated)
+    assert emulated.redo_chunks >= 1
+
+
 @pytest.mark.parametrize("ignore_frac", [0.0, 0.5, 0.97])
 def test_skip_ignored_gpu_bodies(emulated, monkeypatch, ignore_frac):
     """The bodies of tests/test_flce_skip_ignored_gpu.py at a size the emulation handles."""

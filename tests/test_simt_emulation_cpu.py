@@ -203,7 +203,7 @@ def test_dz_inplace_kernel(emu, fmt, softcap):
         want = want * (1 - (sf / softcap) ** 2)
     slab = s.clone()
     emu.emu_dz_inplace(slab.data_ptr(), ld, rows, vocab, fmt, t.data_ptr(), off, lse.data_ptr(), c1.data_ptr(), c2.data_ptr(),
-                       c3.data_ptr(), colw.data_ptr(), 1.0 / softcap if softcap > 0 else 0.0)
+                       c3.data_ptr(), colw.data_ptr(), 1.0 / softcap if softcap > 0 else 0.0, None, 0)
     got = slab[:, :vocab].double()
     tol = 2.0 ** -8 if fmt == 0 else 2.0 ** -10
     assert float(((got - want).abs() - tol * want.abs()).max()) <= 1e-6
@@ -215,9 +215,9 @@ def test_colsum_and_scale_and_merge(emu):
     rows, cols, ld = 70, 130, 136
     dz = torch.randn(rows, ld, generator=g).bfloat16()
     out = torch.ones(cols)
-    emu.emu_colsum(dz.data_ptr(), ld, rows, cols, 0, out.data_ptr(), 1)
+    emu.emu_colsum(dz.data_ptr(), ld, rows, cols, 0, out.data_ptr(), 1, None, 0)
     np.testing.assert_allclose(out.numpy(), 1.0 + dz[:, :cols].float().sum(0).numpy(), rtol=1e-5, atol=1e-5)
-    emu.emu_colsum(dz.data_ptr(), ld, rows, cols, 0, out.data_ptr(), 0)
+    emu.emu_colsum(dz.data_ptr(), ld, rows, cols, 0, out.data_ptr(), 0, None, 0)
     np.testing.assert_allclose(out.numpy(), dz[:, :cols].float().sum(0).numpy(), rtol=1e-5, atol=1e-5)
     # scaling: bf16, fp32, and the no-op when the factor is exactly one
     for t, fmt in ((torch.randn(1000, generator=g).bfloat16(), 0), (torch.randn(1000, generator=g).half(), 1),

@@ -47,7 +47,7 @@ def flce_on_emulated_tiles(emu, x, w, t, bias=None, ce_weight=None, ignore_index
     pidx = torch.zeros(n_tiles, N, dtype=torch.int32)
     rowstats = torch.zeros(6, N)
     emu.emu_sweep_stats(_p(x), _p(w), FMT[dtype], N, V, H, x.stride(0), w.stride(0), _p(t), _p(bias32), _p(cw), cap, vocab_offset,
-                        _p(planes[0]), _p(planes[1]), _p(planes[2]), _p(planes[3]), _p(pidx), rowstats[2].data_ptr(), None, 0, 0, -1)
+                        _p(planes[0]), _p(planes[1]), _p(planes[2]), _p(planes[3]), _p(pidx), rowstats[2].data_ptr(), None, 0, 0, -1, None, 0)
     emu.emu_merge_partials(N, n_tiles, _p(planes[0]), _p(planes[1]), _p(planes[2]), _p(planes[3]), _p(pidx), _p(rowstats))
     f = lambda: torch.zeros(N)                                                    # noqa: E731
     lse, prob, loss_rows, z_rows, correct = f(), f(), f(), f(), f()
