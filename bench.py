@@ -320,6 +320,130 @@ def run_comparators(args, timeout_s):
     return out
 
 
+def multi_gpu_extras(args, rank, world, device, peaks):
+    """At N > 1 GPUs, after the weak-scaling line: the fixed-problem (strong scaling) configurations the workload list
+    names as multi-GPU, each timed on all ranks and, for the efficiency, on rank 0 alone in the same invocation;
+    the collectives' own device time; the spread of the ranks' kernel time; and a bare all-reduce of a grad_weight-sized
+    buffer.  Returns a dict of extra keys for the JSON line (rank 0) or None."""
+    import torch.distributed as dist
+
+    import liger_kernel_b200.sharded as sharded
+    from liger_kernel_b200 import _lib
+    from liger_kernel_b200.transformers.functional import liger_fused_linear_cross_entropy
+
+    steps, warmup = 3, 2
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, participate=True):
+        ms = 0.0
+        if participate:
+            for _ in range(warmup):
+                step_fn()
+            torch.cuda.synchronize()
+        barrier()
+        if participate:
+            _lib.profile_enable(True)
+            sharded.COLLECTIVE_EVENTS = []
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step_fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+        barrier()
+        out = dict(ms=ms, kernels_ms=0.0, collectives={})
+        if participate:
+            prof = _lib.profile_read(reset=True)
+            _lib.profile_enable(False)
+            out["kernels_ms"] = sum(v[0] for v in prof.values()) / steps
+            for name, a, b in sharded.COLLECTIVE_EVENTS:
+                out["collectives"][name] = out["collectives"].get(name, 0.0) + a.elapsed_time(b) / steps
+            sharded.COLLECTIVE_EVENTS = None
+        return out
+
+    def gather_max(v):
+        t = torch.tensor([v], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather_min(v):
+        t = torch.tensor([v], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return float(t.item())
+
+    extras = {}
+    # ---- a bare all-reduce of a grad_weight-sized bf16 buffer (C2: 1.05 GB)
+    spec = WORKLOADS[args.workload]
+    buf = torch.zeros(spec["V"], spec["H"], device=device, dtype=torch.bfloat16)
+    r = timed(lambda: dist.all_reduce(buf))
+    ms = gather_max(r["ms"])
+    nbytes = buf.numel() * 2
+    extras["allreduce_alone"] = {"bytes": nbytes, "ms": ms, "algbw_gbs": nbytes / ms / 1e6,
+                                 "busbw_gbs": nbytes / ms / 1e6 * 2 * (world - 1) / world}
+    del buf
+    single_gpu_ms = {}
+    for key, wl, mode in (("c5_strong_token", "c5", "token"), ("c5_vocab", "c5", "vocab"), ("c4_vocab", "c4", "vocab")):
+        try:
+            spec = WORKLOADS[wl]
+            N, H, V = spec["N"], spec["H"], spec["V"]
+            kw = {k: v for k, v in spec["kw"].items() if k != "return_z_loss"}
+            x, w, t = make_inputs(spec, device, 4321)        # the same full problem on every rank
+            if wl not in single_gpu_ms:
+                w1 = w.clone().requires_grad_(True)
+
+                def one_gpu():
+                    xin = x.detach().requires_grad_(True)
+                    w1.grad = None
+                    out = liger_fused_linear_cross_entropy(xin, w1, t, **kw)
+                    (out if torch.is_tensor(out) else out.loss).backward()
+
+                r1 = timed(one_gpu, participate=(rank == 0))
+                single_gpu_ms[wl] = gather_max(r1["ms"])
+                del w1
+            if mode == "token":
+                n_loc = N // world
+                xs, ts = x[rank * n_loc:(rank + 1) * n_loc].clone(), t[rank * n_loc:(rank + 1) * n_loc].clone()
+                ws = w.clone().requires_grad_(True)
+
+                def step():
+                    xin = xs.detach().requires_grad_(True)
+                    ws.grad = None
+                    sharded.token_sharded_fused_linear_cross_entropy(xin, ws, ts, **kw).backward()
+            else:
+                per = (V + world - 1) // world
+                lo = rank * per
+                ws = w[lo:min(V, lo + per)].clone().requires_grad_(True)
+
+                def step():
+                    xin = x.detach().requires_grad_(True)
+                    ws.grad = None
+                    sharded.vocab_sharded_fused_linear_cross_entropy(xin, ws, t, lo, V, **kw).backward()
+            del w
+            r = timed(step)
+            ms = gather_max(r["ms"])
+            colls = {}
+            for name in sorted(r["collectives"]):
+                colls[name] = gather_max(r["collectives"][name])
+            extras[key] = {
+                "workload": NAMES[wl], "sharding": mode, "scaling": "strong", "ms_per_step": ms,
+                "tokens_per_s": N / (ms * 1e-3), "single_gpu_ms_per_step": single_gpu_ms[wl],
+                "efficiency_vs_n1": single_gpu_ms[wl] / (world * ms),
+                "collective_ms_max_over_ranks": colls,
+                "rank_kernel_ms": {"min": gather_min(r["kernels_ms"]), "max": gather_max(r["kernels_ms"])},
+                "steps": steps, "warmup": warmup,
+            }
+            del x, t, ws
+            torch.cuda.empty_cache()
+        except Exception as e:  # noqa: BLE001
+            extras[key] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+            barrier()
+    return extras if rank == 0 else None
+
+
 def run_ours(args, spec, rank, world, local_rank):
     import torch.distributed as dist
 
@@ -330,7 +454,11 @@ def run_ours(args, spec, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # the all-reduce of grad_weight runs beside the last grad_input GEMM, which leaves it 20 SMs
+        # (liger_kernel_b200.sharded.RESERVE_SMS_FOR_COLLECTIVE): keep NCCL's kernels within that
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")
+        import datetime
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     if args.cta_pair is not None:
         _lib.set_option("cta_pair", args.cta_pair)
     if args.raster_mb is not None:
@@ -342,6 +470,10 @@ def run_ours(args, spec, rank, world, local_rank):
         flce_op.STORE_MODE = args.store
     if args.wide_tiles is not None:
         _lib.set_option("wide_tiles", args.wide_tiles)
+    if args.poll_sleep_ns is not None:
+        _lib.set_option("poll_sleep_ns", args.poll_sleep_ns)
+    if args.chunk_gib is not None:
+        flce_op.CHUNK_BUDGET_BYTES = int(args.chunk_gib * (1 << 30))
     peaks = load_peaks()
     from liger_kernel_b200.sharded import vocab_sharded_fused_linear_cross_entropy
 
@@ -438,6 +570,9 @@ def run_ours(args, spec, rank, world, local_rank):
     barrier()
     ms_e2e = max_over_ranks(e2.elapsed_time(e3))
 
+    extras = None
+    if world > 1 and not args.no_variants and args.sharding == "token" and not args.strong:
+        extras = multi_gpu_extras(args, rank, world, device, peaks)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -530,6 +665,8 @@ def run_ours(args, spec, rank, world, local_rank):
             "value": rate, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"first {rows} rows with the full H and V, fp32 torch Linear+CrossEntropy with autograd, {secs:.1f} s",
         }
+    if extras:
+        result.update(extras)
     if world == 1 and not args.no_comparators:
         comps = run_comparators(args, args.comparator_timeout)
         result["comparators"] = comps
@@ -554,6 +691,9 @@ def main():
     ap.add_argument("--mode", default=None, choices=["recompute", "single_sweep", "auto"])
     ap.add_argument("--store", default=None, choices=["auto", "logits", "exp"], help="what the single-sweep mode keeps of a chunk")
     ap.add_argument("--wide-tiles", type=int, default=None, dest="wide_tiles")
+    ap.add_argument("--poll-sleep-ns", type=int, default=None, dest="poll_sleep_ns")
+    ap.add_argument("--chunk-gib", type=float, default=None, dest="chunk_gib",
+                    help="bytes (GiB) of the bounded 16-bit copy of a token chunk in the single-sweep mode (default 2.5)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true", dest="no_variants")
     ap.add_argument("--no-comparators", action="store_true", dest="no_comparators",

@@ -119,6 +119,15 @@ typedef struct flce_fused_args {
   float* grad_bias;              /* [vocab] fp32, or NULL                                                     */
   int32_t norm_given;            /* 1: norm is an input (already counted, e.g. all-reduced over token shards)  */
   int32_t store_mode;            /* flce_store_mode_t: what the bounded 16-bit copy of a chunk holds          */
+  /* Optional hook for a caller that sums grad_weight over token shards.  When set, the last token chunk forms
+   * grad_weight before grad_input; right after the launch that completes grad_weight has been enqueued the library
+   * calls after_grad_weight(user) on the calling thread (the caller records an event on the stream and enqueues its
+   * all-reduce on another one), and the one GEMM still to come leaves reserve_sms SMs free so that the collective's
+   * kernel finds room beside it.  Takes the place of the separate all-reduce a data-parallel wrapper issues after the
+   * reference's backward (the reference leaves it to DDP / FSDP). */
+  void (*after_grad_weight)(void* user);
+  void* after_grad_weight_user;
+  int32_t reserve_sms;
 } flce_fused_args_t;
 
 /* The single-sweep mode keeps a bounded 16-bit copy of each token chunk's logits.  FLCE_STORE_LOGITS keeps the

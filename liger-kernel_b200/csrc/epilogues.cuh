@@ -98,7 +98,7 @@ struct StatsEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
     float s[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(acc[j]);
@@ -263,7 +263,7 @@ struct DzEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
     if (!row_ok) return;
     float g[32];
 #pragma unroll
@@ -373,7 +373,7 @@ struct EntropyStatsEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
     float s[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(acc[j]) * p.scale;
@@ -464,7 +464,7 @@ struct ScaledDzEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
     if (!row_ok) return;
     float g[32];
 #pragma unroll
@@ -528,8 +528,13 @@ struct StoreEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col) {
-    if (!row_ok) return;
+  // The accumulators arrive one output row per thread.  Written out like that, every load / store instruction of the
+  // warp touches 32 different rows, 16 bytes each; with an fp32 partial to read and to write per element that costs
+  // more than the main loop of a short-K tile saves.  So the 32 x 32 patch goes through the warp's shared-memory
+  // stage: afterwards 8 lanes cover 32 consecutive columns of one row, 4 rows per instruction, and every global access
+  // is a whole 128-byte (fp32) or 64-byte (16-bit) row segment.
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* stage) {
+    const int lane = threadIdx.x & 31;
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
@@ -541,49 +546,40 @@ struct StoreEpilogue {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = fmaf(-r1, __ldg(p.r1_col + min(col + j, p.n_cols - 1)), v[j]);
     }
-    if (p.acc_in != nullptr) {
-      const float4* src = reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(row) * p.ld_acc + col);
+    float4* mine = reinterpret_cast<float4*>(stage + lane * 36);
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        if (col + 4 * q < p.n_cols) {
-          const float4 a = src[q];
-          v[4 * q + 0] += a.x;
-          v[4 * q + 1] += a.y;
-          v[4 * q + 2] += a.z;
-          v[4 * q + 3] += a.w;
+    for (int q = 0; q < 8; ++q) mine[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    __syncwarp();
+    const int row0 = row - lane;                 // first row of this warp's patch
+    const int c4 = (lane & 7) * 4;               // this lane's four columns inside the patch
+    const bool col_ok = col + c4 < p.n_cols;     // n_cols is a multiple of 8: a group of four is in or out as a whole
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3);
+      const int grow = row0 + r;
+      if (grow < p.m_rows && col_ok) {
+        float4 a = *reinterpret_cast<const float4*>(stage + r * 36 + c4);
+        if (p.acc_in != nullptr) {
+          const float4 b = *reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(grow) * p.ld_acc + col + c4);
+          a.x += b.x;
+          a.y += b.y;
+          a.z += b.z;
+          a.w += b.w;
         }
-      }
-    }
-    if (p.acc_out != nullptr) {
-      float4* dst = reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(row) * p.ld_acc + col);
-#pragma unroll
-      for (int q = 0; q < 8; ++q)
-        if (col + 4 * q < p.n_cols) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-    }
-    if (p.out != nullptr) {
-      if (p.out_fmt == kOutFp32) {
-        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          if (col + 4 * q < p.n_cols) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-      } else if (col + 32 <= p.n_cols) {
-        store32_16bit(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col),
-                      v, p.out_fmt);
-      } else {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (col + 8 * q < p.n_cols) {
-            uint4 o;
-            o.x = pack2(v[8 * q + 0], v[8 * q + 1], p.out_fmt);
-            o.y = pack2(v[8 * q + 2], v[8 * q + 3], p.out_fmt);
-            o.z = pack2(v[8 * q + 4], v[8 * q + 5], p.out_fmt);
-            o.w = pack2(v[8 * q + 6], v[8 * q + 7], p.out_fmt);
-            dst[q] = o;
+        if (p.acc_out != nullptr) *reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(grow) * p.ld_acc + col + c4) = a;
+        if (p.out != nullptr) {
+          if (p.out_fmt == kOutFp32) {
+            *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = a;
+          } else {
+            uint2 o;
+            o.x = pack2(a.x, a.y, p.out_fmt);
+            o.y = pack2(a.z, a.w, p.out_fmt);
+            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = o;
           }
         }
       }
     }
+    __syncwarp();                                // the stage is rewritten by the next chunk
   }
 
   __device__ __forceinline__ void end(const Params&) {}

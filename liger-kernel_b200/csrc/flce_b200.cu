@@ -164,7 +164,7 @@ template <int kCtas, int kAMajor, int kBMajor, class Epi, int kNSub = 1>
 static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, const Operand& b, int dtype, long long M,
                             long long N, long long K, long long raster_row_bytes, bool n_fastest,
                             const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows, int active_role,
-                            int active_base, const int* gate) {
+                            int active_base, const int* gate, int reserve_sms) {
   using Cfg = StageCfg<kCtas, kNSub>;
   CUtensorMap map_a, map_b;
   int rc = operand_map(&map_a, a, dtype, kBlockM);
@@ -201,7 +201,9 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
     shape.group = static_cast<int>(g);
   }
   const long long tiles = static_cast<long long>(shape.m_tiles) * shape.n_tiles;
-  long long units = dev.sm_count / kCtas;
+  // reserve_sms: SMs left free for a kernel of the caller's that should run beside this one (a collective)
+  long long units = (dev.sm_count - reserve_sms) / kCtas;
+  if (units < 1) units = 1;
   if (units > tiles) units = tiles;
   auto kernel = gemm_tcgen05_kernel<kCtas, kAMajor, kBMajor, Epi, kNSub>;
   FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -230,7 +232,7 @@ template <int kAMajor, int kBMajor, class Epi>
 static int launch_gemm(const DeviceState& dev, int kind, bool pair, const Operand& a, const Operand& b, int dtype, long long M,
                        long long N, long long K, long long raster_row_bytes, bool n_fastest,
                        const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows = nullptr,
-                       int active_role = 0, int active_base = 0, const int* gate = nullptr) {
+                       int active_role = 0, int active_base = 0, const int* gate = nullptr, int reserve_sms = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "empty GEMM %lld x %lld x %lld", M, N, K);
   if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll)
     return fail(FLCE_ERR_INVALID_ARGUMENT, "GEMM extent does not fit 32 bits");
@@ -238,13 +240,13 @@ static int launch_gemm(const DeviceState& dev, int kind, bool pair, const Operan
     // long K, light epilogue, enough columns to fill 512-wide tiles: the wide form moves a quarter less data per product
     if (pair && g_wide_tiles && K >= 2048 && N >= 1024)
       return launch_gemm_impl<2, kAMajor, kBMajor, Epi, 2>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep,
-                                                           stream, active_rows, active_role, active_base, gate);
+                                                           stream, active_rows, active_role, active_base, gate, reserve_sms);
   }
   if (pair)
     return launch_gemm_impl<2, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes * 2, n_fastest, ep, stream,
-                                                      active_rows, active_role, active_base, gate);
+                                                      active_rows, active_role, active_base, gate, reserve_sms);
   return launch_gemm_impl<1, kAMajor, kBMajor, Epi>(dev, kind, a, b, dtype, M, N, K, raster_row_bytes, n_fastest, ep, stream,
-                                                    active_rows, active_role, active_base, gate);
+                                                    active_rows, active_role, active_base, gate, reserve_sms);
 }
 
 // (the small SIMT kernels live in row_kernels.cuh)
@@ -1093,7 +1095,8 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       ++g_kernel_launches;
     }
     // ---- grad_input[chunk] = dZ . W          (M = rows, N = hidden, K = vocab; B is MN-major)
-    if (args->grad_input != nullptr) {
+    auto grad_input_gemm = [&](int reserve_sms) -> int {
+      if (args->grad_input == nullptr) return FLCE_OK;
       StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(rows);
       ep.n_cols = static_cast<int>(p->hidden);
@@ -1109,12 +1112,12 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       }
       Operand a{slab, rows, p->vocab, plan.ld_slab, 0};
       Operand b{p->w, p->hidden, p->vocab, p->ld_w, 1};
-      rc = launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, rows, p->hidden, p->vocab, 0, true,
-                                                         ep, stream, p->active_rows, 1, base);
-      if (rc != FLCE_OK) return rc;
-    }
+      return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindDx, pair, a, b, p->dtype, rows, p->hidden, p->vocab, 0, true,
+                                                           ep, stream, p->active_rows, 1, base, nullptr, reserve_sms);
+    };
     // ---- grad_weight (+)= dZ^T . X[chunk]    (M = vocab, N = hidden, K = rows; both operands MN-major)
-    if (args->grad_weight != nullptr) {
+    auto grad_weight_gemm = [&]() -> int {
+      if (args->grad_weight == nullptr) return FLCE_OK;
       StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(p->vocab);
       ep.n_cols = static_cast<int>(p->hidden);
@@ -1132,8 +1135,21 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       Operand a{slab, p->vocab, rows, plan.ld_slab, 1};
       Operand b{exp_store ? static_cast<const void*>(xs) : static_cast<const void*>(x_chunk), p->hidden, rows,
                 exp_store ? p->hidden : p->ld_x, 1};
-      rc = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0, true,
-                                                          ep, stream, p->active_rows, 2, base);
+      return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0, true,
+                                                            ep, stream, p->active_rows, 2, base);
+    };
+    if (last && args->after_grad_weight != nullptr) {
+      // grad_weight is complete after this launch: let the caller enqueue what consumes it (an all-reduce on another
+      // stream), then form the last chunk's grad_input beside it on the SMs that are left
+      rc = grad_weight_gemm();
+      if (rc != FLCE_OK) return rc;
+      args->after_grad_weight(args->after_grad_weight_user);
+      rc = grad_input_gemm(args->reserve_sms > 0 ? args->reserve_sms : 0);
+      if (rc != FLCE_OK) return rc;
+    } else {
+      rc = grad_input_gemm(0);
+      if (rc != FLCE_OK) return rc;
+      rc = grad_weight_gemm();
       if (rc != FLCE_OK) return rc;
     }
     if (args->grad_bias != nullptr) {

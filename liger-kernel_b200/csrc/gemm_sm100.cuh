@@ -62,15 +62,20 @@ struct StageCfg {
   static constexpr int kStages = (kNSub == 2) ? 4 : ((kCtas == 1) ? 4 : 6);
   static constexpr int kAccStages = (kNSub == 2) ? 1 : 2;            // accumulators in flight (tensor memory: 512 columns)
   static constexpr int kRingBytes = kStages * kStageBytes;
-  // ring + barriers + bookkeeping, plus 1 KiB so the ring can be aligned to the swizzle atom
-  static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
+  // per epilogue warp, a 32 x 32 fp32 patch (pitch 36 floats) for epilogues that turn their row-per-thread registers
+  // into row-contiguous global accesses
+  static constexpr int kEpiStageFloats = 32 * 36;
+  static constexpr int kEpiStageBytes = kNumEpilogueWarps * kEpiStageFloats * 4;
+  // ring + barriers + bookkeeping + epilogue staging, plus 1 KiB so the ring can be aligned to the swizzle atom
+  static constexpr int kSmemBytes = kRingBytes + 1024 + 256 + kEpiStageBytes;
 };
 
 // Epilogue concept:
 //   struct Epi {
 //     struct Params {...};                                  // trivially copyable, passed by value
 //     __device__ void begin(const Params&, int row, int col0, int n_tile, bool row_ok);
-//     __device__ void chunk(const Params&, const uint32_t (&acc)[32], int col);   // fp32 bit patterns
+//     __device__ void chunk(const Params&, const uint32_t (&acc)[32], int col, float* stage);   // fp32 bit patterns;
+//                         // stage: this warp's 32 x 36 float patch of shared memory; called by all 32 lanes together
 //     __device__ void end(const Params&);
 //   };
 template <int kCtas, int kAMajor, int kBMajor, class Epi, int kNSub = 1>
@@ -97,6 +102,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* tmem_empty_bar = tmem_full_bar + 2; // [2]        accumulator drained
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  float* epi_stage = reinterpret_cast<float*>(smem + Cfg::kRingBytes + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -278,6 +284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;                         // tensor-memory lanes this warp may read
     const int row_in_tile = quarter * 32 + lane;
+    float* stage = epi_stage + quarter * Cfg::kEpiStageFloats;
     uint32_t acc_phase[2] = {0, 0};
     int local_tile = 0;
     bool ok = true;
@@ -313,7 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) va[j] = 0u;
         }
-        epi.chunk(ep, va, col0 + c * 32);
+        epi.chunk(ep, va, col0 + c * 32, stage);
         if (c + 1 < n_chunks) {
           tmem_ld_wait();
           tmem_ld_fence(vb);
@@ -322,7 +329,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) vb[j] = 0u;
           }
-          epi.chunk(ep, vb, col0 + (c + 1) * 32);
+          epi.chunk(ep, vb, col0 + (c + 1) * 32, stage);
         }
       }
       epi.end(ep);

@@ -107,7 +107,11 @@ class FusedArgs(C.Structure):
         ("out", C.POINTER(ForwardOut)), ("norm", C.c_void_p), ("grad_dtype", C.c_int32),
         ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
         ("norm_given", C.c_int32), ("store_mode", C.c_int32),
+        ("after_grad_weight", C.c_void_p), ("after_grad_weight_user", C.c_void_p), ("reserve_sms", C.c_int32),
     ]
+
+
+AFTER_GRAD_WEIGHT_FN = C.CFUNCTYPE(None, C.c_void_p)
 
 
 STORE_AUTO, STORE_LOGITS, STORE_EXP = 0, 1, 2

@@ -299,10 +299,12 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
 
 
 def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True, need_bias=False, grad_dtype=None,
-                             chunk_budget=None, norm_in=None):
+                             chunk_budget=None, norm_in=None, after_grad_weight=None, reserve_sms=0):
     """Loss and gradients (for an upstream gradient of 1) in one pass over token chunks.
     Returns (outputs dict, norm, grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``.
-    ``norm_in``: normalisers counted elsewhere (a token-sharded caller passes the all-reduced ones)."""
+    ``norm_in``: normalisers counted elsewhere (a token-sharded caller passes the all-reduced ones).
+    ``after_grad_weight(grad_weight)``: called on this thread once the launch that completes grad_weight is enqueued,
+    before the last grad_input GEMM, which then leaves ``reserve_sms`` SMs free (room for the caller's collective)."""
     dev = prep.device
     gd = prep.dtype if grad_dtype is None else grad_dtype
     budget = CHUNK_BUDGET_BYTES if chunk_budget is None else int(chunk_budget)
@@ -325,8 +327,14 @@ def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True,
         if norm_in is not None:
             norm.copy_(norm_in)
             args.norm_given = 1
+        hook = None
+        if after_grad_weight is not None and gw is not None:
+            hook = _lib.AFTER_GRAD_WEIGHT_FN(lambda _user: after_grad_weight(gw))     # kept alive until the call returns
+            args.after_grad_weight = C.cast(hook, C.c_void_p)
+            args.reserve_sms = int(reserve_sms)
         ws = prep.workspace(_lib.PHASE_FUSED, budget)
         check(lib.flce_b200_forward_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
+        del hook
     return out, norm, gx, gw, gb
 
 

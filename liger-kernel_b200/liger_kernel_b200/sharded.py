@@ -5,8 +5,11 @@ peer's memory: the collectives land in local HBM and the kernels only ever see l
 
 Token-sharded (data parallel; the reference leaves this to DDP/FSDP, ``README.md:117``): every rank holds its
 own rows of X / target and the whole W.  Exchanges: the normalisers (count of non-ignored rows, class-weight
-sum) before the per-row losses are formed, the scalar loss, and grad_weight (summed; issued slab by slab on
-a side stream so it overlaps the remaining slabs' GEMMs, when asked to; by default once, after the last slab).
+sum) before the per-row losses are formed, the scalar loss, and grad_weight (summed).  With mean / sum reduction
+and 16-bit operands the gradients are formed in forward (``ops/fused_linear_cross_entropy.py``, single-sweep
+mode) with the all-reduced normalisers; the last token chunk forms grad_weight first, the all-reduce starts on a
+side stream as soon as that GEMM is done, and the chunk's grad_input GEMM runs beside it on the SMs it leaves
+free.  Otherwise (``reduction="none"``, fp32) backward recomputes the logits and all-reduces grad_weight after it.
 
 Vocabulary-sharded (tensor parallel; the math and collective pattern follow the reference's
 ``ops/vocab_parallel_cross_entropy.py:235-303``): every rank holds rows ``[vocab_start, vocab_start+V_r)`` of W and
@@ -35,10 +38,17 @@ class CudaBackend:
     """Local FLCE pieces on the current GPU through libflce_b200.so."""
 
     def prepare(self, x, w, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction, softcap,
-                use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=False):
+                use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=False, allow_compact=False):
         return _op._Prepared(x, w, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing, reduction,
                              softcap, use_token_scaling, vocab_total=vocab_total, vocab_offset=vocab_offset,
-                             want_argmax=want_argmax)
+                             want_argmax=want_argmax, allow_compact=allow_compact)
+
+    def single_sweep(self, prep, norm, need_input, need_weight, after_grad_weight=None, reserve_sms=0):
+        """Loss rows / scalars and the gradients for an upstream gradient of 1, with the given (global) normalisers."""
+        out, _, gx, gw, _ = _op.flce_single_sweep_device(prep, need_input, need_weight, False, norm_in=norm,
+                                                         after_grad_weight=after_grad_weight, reserve_sms=reserve_sms)
+        gx = prep.rows_to_token_order(gx)
+        return _op._results_to_token_order(prep, out), gx, gw
 
     def count(self, prep):
         norm = torch.empty(4, dtype=torch.float32, device=prep.device)
@@ -87,16 +97,81 @@ def _world(group):
     return dist.get_world_size(group) if dist.is_initialized() else 1
 
 
+# Optional device timing of the collectives: set to a list and every collective issued by the operators below appends
+# (name, start_event, end_event), recorded on the stream that issues it (a benchmark reads them after a synchronise).
+COLLECTIVE_EVENTS = None
+
+
+class _timed:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if COLLECTIVE_EVENTS is not None and torch.cuda.is_available():
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if COLLECTIVE_EVENTS is not None and torch.cuda.is_available():
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            COLLECTIVE_EVENTS.append((self.name, self.start, end))
+
+
+# SMs the last grad_input GEMM of a token-sharded call leaves to the grad_weight all-reduce that runs beside it
+RESERVE_SMS_FOR_COLLECTIVE = 20
+
+
 class _TokenSharded(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, target, group, backend, overlap, kw):
-        prep = backend.prepare(x.detach(), w.detach(), target, None, kw.get("ce_weight"), kw["ignore_index"],
-                               kw["lse_square_scale"], kw["label_smoothing"], kw["reduction"], kw["softcap"], False)
+        recording = kw.get("recording", True)
+        needs = (recording and ctx.needs_input_grad[0], recording and ctx.needs_input_grad[1])
+        single = hasattr(backend, "single_sweep") and _op._use_single_sweep(kw["reduction"], needs, x.dtype)
+        ctx.stored = None
+        world = _world(group)
+        if single:
+            prep = backend.prepare(x.detach(), w.detach(), target, None, kw.get("ce_weight"), kw["ignore_index"],
+                                   kw["lse_square_scale"], kw["label_smoothing"], kw["reduction"], kw["softcap"], False,
+                                   allow_compact=True)
+        else:
+            prep = backend.prepare(x.detach(), w.detach(), target, None, kw.get("ce_weight"), kw["ignore_index"],
+                                   kw["lse_square_scale"], kw["label_smoothing"], kw["reduction"], kw["softcap"], False)
         norm = backend.count(prep)
-        if _world(group) > 1:
+        if world > 1:
             counts = norm[:2].clone()          # norm[2] (sum of all class weights) is the same on every rank
-            dist.all_reduce(counts, group=group)
+            with _timed("all_reduce normalisers"):
+                dist.all_reduce(counts, group=group)
             norm = torch.cat([counts, norm[2:]])
+        if single:
+            pending = []
+            hook = None
+            if world > 1 and needs[1]:
+                comm = torch.cuda.Stream(device=prep.device)
+
+                def hook(gw):
+                    done = torch.cuda.Event()
+                    done.record()
+                    comm.wait_event(done)
+                    with torch.cuda.stream(comm):
+                        with _timed("all_reduce grad_weight (beside the last grad_input GEMM)"):
+                            work = dist.all_reduce(gw, group=group, async_op=True)
+                            work.wait()              # comm waits for the collective; the compute stream does so in backward
+                        pending.append(work)
+
+            out, gx, gw = backend.single_sweep(prep, norm, needs[0], needs[1], after_grad_weight=hook,
+                                               reserve_sms=RESERVE_SMS_FOR_COLLECTIVE if hook is not None else 0)
+            ctx.stored = (gx, gw, pending)
+            ctx.hidden = prep.hidden
+            ctx.in_dtypes = (x.dtype, w.dtype)
+            ctx.group = group
+            loss = out["scalars"][0].clone()
+            if world > 1:
+                with _timed("all_reduce loss"):
+                    dist.all_reduce(loss, group=group)
+            ctx.comm = comm if hook is not None else None
+            return loss
         out = backend.finalize(prep, backend.forward_stats(prep), norm)
         ctx.saved = (prep, out["lse"], out["target_prob"], norm)
         ctx.group, ctx.backend, ctx.overlap = group, backend, overlap
@@ -110,6 +185,19 @@ class _TokenSharded(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
+        if ctx.stored is not None:
+            gx, gw, pending = ctx.stored
+            ctx.stored = None
+            if ctx.comm is not None:             # the compute stream waits for the all-reduce of grad_weight
+                torch.cuda.current_stream().wait_stream(ctx.comm)
+            dev = (gx if gx is not None else gw).device
+            go = grad_output.detach().to(device=dev, dtype=torch.float32).reshape(1)
+            gx = _op.scale_gradient_(gx, go)
+            gw = _op.scale_gradient_(gw, go)
+            h = ctx.hidden
+            gx = None if gx is None else gx[:, :h].to(ctx.in_dtypes[0])
+            gw = None if gw is None else gw[:, :h].to(ctx.in_dtypes[1])
+            return gx, gw, None, None, None, None, None
         prep, lse, prob, norm = ctx.saved
         group, backend = ctx.group, ctx.backend
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
@@ -129,7 +217,8 @@ class _TokenSharded(torch.autograd.Function):
         gx, gw = backend.backward(prep, lse, prob, norm, grad_output, need_x, need_w, slab_hook=hook)
         if world > 1 and need_w:
             if hook is None:
-                dist.all_reduce(gw, group=group)
+                with _timed("all_reduce grad_weight (after backward)"):
+                    dist.all_reduce(gw, group=group)
             else:
                 for work in pending:
                     work.wait()
@@ -152,7 +241,8 @@ class _VocabSharded(torch.autograd.Function):
         if world > 1:
             planes, n = stats.shape
             gathered = torch.empty((world * planes, n), dtype=stats.dtype, device=stats.device)
-            dist.all_gather_into_tensor(gathered, stats.contiguous(), group=group)
+            with _timed("all_gather row statistics"):
+                dist.all_gather_into_tensor(gathered, stats.contiguous(), group=group)
             stats = merge_rowstats(gathered.view(world, planes, n))
         out = backend.finalize(prep, stats, norm)
         ctx.saved = (prep, out["lse"], out["target_prob"], norm)
@@ -168,7 +258,8 @@ class _VocabSharded(torch.autograd.Function):
         # partial grad_input in fp32 so that the cross-rank sum is formed before the single rounding
         gx, gw = ctx.backend.backward(prep, lse, prob, norm, grad_output, need_x, need_w, grad_dtype=torch.float32)
         if need_x and _world(ctx.group) > 1:
-            dist.all_reduce(gx, group=ctx.group)
+            with _timed("all_reduce grad_input (fp32 partials)"):
+                dist.all_reduce(gx, group=ctx.group)
         h = prep.hidden
         gx = None if gx is None else gx[:, :h].to(ctx.in_dtypes[0])
         gw = None if gw is None else gw[:, :h].to(ctx.in_dtypes[1])
@@ -189,12 +280,15 @@ def token_sharded_fused_linear_cross_entropy(input, weight, target, ignore_index
     Returns the loss over the *global* batch (identical on every rank; per-row for ``reduction="none"``).
     ``weight.grad`` receives the sum over ranks; ``input.grad`` is local.
 
-    ``overlap_grad_weight=True`` all-reduces each finished vocabulary slab of ``weight.grad`` on a side stream while the
-    next slabs are computed.  It is off by default: the persistent GEMM kernels fill every SM with a static tile
-    schedule, so a collective kernel that takes a few SMs mid-way delays whole launches; measured on 2 GPUs the
-    overlapped form cost 7 ms per step against about 1.4 ms for one all-reduce after the last slab."""
-    return _TokenSharded.apply(input, weight, target, group, backend or CudaBackend(), overlap_grad_weight,
-                               _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap, ce_weight))
+    With mean / sum reduction and 16-bit operands the gradients are formed in forward and the all-reduce of
+    ``weight.grad`` runs beside the last grad_input GEMM (see the module docstring); a repeated backward of the same
+    graph is not supported there.  ``overlap_grad_weight`` concerns the two-sweep path only (``reduction="none"``, fp32):
+    True all-reduces each finished vocabulary slab of ``weight.grad`` on a side stream while the next slabs are
+    computed.  It is off by default: those persistent GEMM kernels fill every SM, so a collective kernel that takes a
+    few SMs mid-way delays whole launches (measured on 2 GPUs: 7 ms per step lost)."""
+    kw = _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap, ce_weight)
+    kw["recording"] = torch.is_grad_enabled()
+    return _TokenSharded.apply(input, weight, target, group, backend or CudaBackend(), overlap_grad_weight, kw)
 
 
 def vocab_sharded_fused_linear_cross_entropy(input, weight_shard, target, vocab_start, vocab_total, ignore_index=-100,

@@ -191,11 +191,47 @@ void run_tiles(const typename Epi::Params& ep, const void* a, const void* b, int
               for (int kk = 0; kk < k; ++kk) v = fmaf(arow[kk], load16(b, static_cast<long long>(col) * ld_b + kk, dtype), v);
             acc[j] = __float_as_uint(v);
           }
-          epi.chunk(ep, acc, col0 + c * 32);
+          epi.chunk(ep, acc, col0 + c * 32, nullptr);
         }
         epi.end(ep);
       }
     }
+}
+
+// StoreEpilogue passes its accumulators through a warp-wide shared-memory patch, so its 32 rows run together: one
+// emulated warp per group of 32 rows, driven over the n-tiles the way an epilogue warp of the kernel is.
+void run_tiles_store(const StoreEpilogue::Params& ep, const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a,
+                     long long ld_b, int tile_n) {
+  const int groups = static_cast<int>(ceil_div(m, kBlockM)) * (kBlockM / 32);
+  const int n_tiles = static_cast<int>(ceil_div(n, tile_n));
+  static float stage[32 * 36];
+  for (int g = 0; g < groups; ++g) {
+    emu::launch(1, 32, [&]() {
+      const int lane = static_cast<int>(threadIdx.x);
+      const int row = g * 32 + lane;
+      const bool ok = row < m;
+      std::vector<float> arow(k);
+      for (int kk = 0; kk < k; ++kk) arow[kk] = ok ? load16(a, static_cast<long long>(row) * ld_a + kk, dtype) : 0.f;
+      for (int nt = 0; nt < n_tiles; ++nt) {
+        const int col0 = nt * tile_n;
+        StoreEpilogue epi;
+        epi.begin(ep, row, col0, nt, ok);
+        const int n_chunks = std::min(tile_n / 32, (n - col0 + 31) / 32);
+        for (int c = 0; c < n_chunks; ++c) {
+          uint32_t acc[32];
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + c * 32 + j;
+            float v = 0.f;
+            if (ok && col < n)
+              for (int kk = 0; kk < k; ++kk) v = fmaf(arow[kk], load16(b, static_cast<long long>(col) * ld_b + kk, dtype), v);
+            acc[j] = __float_as_uint(v);
+          }
+          epi.chunk(ep, acc, col0 + c * 32, stage);
+        }
+        epi.end(ep);
+      }
+    });
+  }
 }
 
 }  // namespace
@@ -468,7 +504,7 @@ int emu_gemm_store(const void* a, const void* b, int dtype, int m, int n, int k,
   ep.out = out;
   ep.ld_out = ld_out;
   ep.out_fmt = out_fmt;
-  run_tiles<StoreEpilogue>(ep, a, b, dtype, m, n, k, ld_a, ld_b);
+  run_tiles_store(ep, a, b, dtype, m, n, k, ld_a, ld_b, kBlockN);
   return 0;
 }
 
@@ -488,7 +524,7 @@ int emu_gemm_store_ex(const void* a, const void* b, int dtype, int m, int n, int
   ep.row_scale = row_scale;
   ep.r1_row = r1_row;
   ep.r1_col = r1_col;
-  run_tiles<StoreEpilogue>(ep, a, b, dtype, m, n, k, ld_a, ld_b);
+  run_tiles_store(ep, a, b, dtype, m, n, k, ld_a, ld_b, 2 * kBlockN);   // the 512-column tile of the gradient GEMMs
   return 0;
 }
 

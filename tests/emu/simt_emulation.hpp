@@ -203,6 +203,11 @@ T shuffle_from(T v, unsigned src_lane) {
 #define gridDim (emu::g_grid_dim)
 
 inline void __syncthreads() { emu::barrier_wait(emu::t_ctx->block_bar); }
+// warp-level barrier: supported for blocks of exactly one warp (launch()), where it is the block barrier; a no-op
+// under launch_serial(), whose kernels must not depend on it
+inline void __syncwarp(unsigned = 0xffffffffu) {
+  if (emu::t_ctx != nullptr) emu::barrier_wait(emu::t_ctx->block_bar);
+}
 
 template <typename T>
 T __shfl_xor_sync(unsigned, T v, int lane_mask) {

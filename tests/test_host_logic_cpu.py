@@ -190,10 +190,20 @@ def test_sharded_operators_single_process_path(monkeypatch):
 
     with fake_lib.installed(monkeypatch) as fake:
         x, w, t = _inputs(H=32)
+        # mean reduction, 16-bit: rows compacted, normalisers counted (and all-reduced when there are ranks), gradients
+        # formed in forward with the given normalisers, grad_input back in token order; backward only scales
         loss = sharded.token_sharded_fused_linear_cross_entropy(x, w, t, label_smoothing=0.1)
         assert [c for c in fake.calls if c != "flce_b200_workspace_bytes"] == [
-            "flce_b200_count", "flce_b200_forward_stats", "flce_b200_forward_finalize"]
+            "flce_b200_compact_rows", "flce_b200_count", "flce_b200_forward_backward", "flce_b200_scatter_rows"]
         loss.backward()
+        assert fake.calls[-1] == "flce_b200_scale_gradient" and w.grad.shape == (50, 32)
+        # per-token losses: the two-sweep path
+        del fake.calls[:]
+        x.grad = w.grad = None
+        rows = sharded.token_sharded_fused_linear_cross_entropy(x, w, t, reduction="none")
+        assert [c for c in fake.calls if c != "flce_b200_workspace_bytes"] == [
+            "flce_b200_count", "flce_b200_forward_stats", "flce_b200_forward_finalize"]
+        rows.sum().backward()
         assert fake.calls[-1] == "flce_b200_backward" and w.grad.shape == (50, 32)
         del fake.calls[:]
         w_shard = w.detach()[10:30].clone().requires_grad_(True)
