@@ -355,6 +355,14 @@ int flce_b200_jsd_rows(void* student, int64_t ld_student, const void* teacher, i
  * since the last call (FLCE_ERR_DEVICE_TIMEOUT) and clears the record.  For tests and debugging. */
 int flce_b200_check_device_status(void* stream);
 
+/* Exercises the give-up path of the library's bounded device waits without disturbing a real kernel: a one-thread
+ * kernel waits on a barrier that can never complete, with a limit of limit_ns nanoseconds (1 .. 1e8).  The wait runs
+ * out, the thread records the time-out in the device status word exactly as the tensor-core kernels' roles do, writes
+ * 2 to *outcome (device memory; 1 would mean the wait completed) and the kernel returns.  The next
+ * flce_b200_check_device_status() reports FLCE_ERR_DEVICE_TIMEOUT once and clears it.  No counterpart in the
+ * reference (its Triton kernels have no device-side waits). */
+int flce_b200_selftest_wait_expiry(int64_t limit_ns, int32_t* outcome, void* stream);
+
 /* Per-kernel timing for benchmarks; no counterpart in the reference (its benchmarks time whole calls,
  * benchmark/scripts/utils.py:115-172).  While enabled, each tensor-core launch is bracketed by CUDA
  * events on the caller's stream.  profile_read waits for the recorded events and returns, per kernel

@@ -1693,6 +1693,21 @@ int flce_b200_debug_clock_trace(unsigned long long* out, int n_words) {
 }
 #endif
 
+int flce_b200_selftest_wait_expiry(int64_t limit_ns, int32_t* outcome, void* stream_) {
+  if (limit_ns <= 0 || limit_ns > 100000000ll)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "limit_ns must be in (0, 1e8] (at most a tenth of a second)");
+  if (outcome == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "outcome is NULL");
+  DeviceState* dev = nullptr;
+  int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  FLCE_CUDA(cudaMemsetAsync(outcome, 0, sizeof(int32_t), stream));
+  wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned long long>(limit_ns), dev->status, outcome);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
 int flce_b200_check_device_status(void* stream) {
   DeviceState* dev = nullptr;
   int rc = device_state(&dev);

@@ -358,4 +358,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+// Self-test of the bounded wait: one thread waits on a barrier that expects two arrivals and gets one, so the wait can
+// only end by running out of time (limit_ns, about a millisecond in the test).  It then does what the roles of the
+// main loop do: raises the CTA's abort flag, leaves kDevTimeoutSelfTest in the status word and returns.  No tensor
+// memory, no TMA, nothing in flight: the kernel always terminates and the context stays usable.
+__global__ void wait_expiry_selftest_kernel(unsigned long long limit_ns, int* status, int* returned) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 2);
+    fence_barrier_init();
+    mbar_arrive(smem_u32(&bar));
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, status, kDevTimeoutSelfTest, 0, limit_ns);
+    *returned = ok ? 1 : 2;     // 2: the wait gave up and the thread carried on
+  }
+}
+
 }  // namespace flce

@@ -19,6 +19,7 @@ enum DeviceStatus : int {
   kDevTimeoutTmemFull = 3,       // epilogue never saw an accumulator complete
   kDevTimeoutTmemEmpty = 4,      // MMA warp never got an accumulator back
   kDevTimeoutPeer = 5,           // 2-CTA pair partner never answered
+  kDevTimeoutSelfTest = 6,       // the wait of the self-test kernel ran out, as it is meant to
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -86,7 +87,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // thread ran out of time (it then raises *abort_flag and records `code`) or
 // because another thread of the CTA already raised the flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code, uint32_t sleep_ns = 0) {
+                                          int code, uint32_t sleep_ns = 0, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
@@ -97,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

@@ -14,6 +14,8 @@ FLCE_MEAN, FLCE_SUM, FLCE_NONE = 0, 1, 2
 PHASE_FORWARD, PHASE_BACKWARD, PHASE_FUSED, PHASE_BACKWARD_SPLIT = 0, 1, 2, 3
 ROWSTAT_PLANES = 6
 FLAG_ARGMAX = 1
+# flce_status_t
+FLCE_OK, FLCE_ERR_INVALID_ARGUMENT, FLCE_ERR_UNSUPPORTED, FLCE_ERR_WORKSPACE, FLCE_ERR_CUDA, FLCE_ERR_DEVICE_TIMEOUT = range(6)
 
 EXPORTS = (
     "flce_b200_workspace_bytes",
@@ -33,6 +35,7 @@ EXPORTS = (
     "flce_b200_ce_backward",
     "flce_b200_gemm",
     "flce_b200_gemm_accumulate",
+    "flce_b200_selftest_wait_expiry",
     "flce_b200_scaled_ce_rows",
     "flce_b200_scaled_ce_grad",
     "flce_b200_jsd_rows",
@@ -170,6 +173,8 @@ def _load():
     lib.flce_b200_sce_backward.argtypes = [SP, vp, vp, vp, vp, i32, vp, vp, vp, sz, sz, vp]
     lib.flce_b200_sce_backward.restype = C.c_int
     lib.flce_b200_check_device_status.argtypes = [vp]
+    lib.flce_b200_selftest_wait_expiry.argtypes = [i64, vp, vp]
+    lib.flce_b200_selftest_wait_expiry.restype = C.c_int
     lib.flce_b200_set_option.argtypes = [C.c_char_p, i64]
     lib.flce_b200_profile_enable.argtypes = [C.c_int]
     lib.flce_b200_profile_enable.restype = C.c_int
