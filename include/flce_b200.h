@@ -128,6 +128,24 @@ typedef struct flce_fused_args {
   void (*after_grad_weight)(void* user);
   void* after_grad_weight_user;
   int32_t reserve_sms;
+  /* Optional hooks for a caller whose problem is one vocabulary shard of a larger one (vocab < vocab_total; every
+   * rank holds all rows and its own columns; the pattern of the reference's
+   * src/liger_kernel/ops/vocab_parallel_cross_entropy.py:235-303).  A shard alone cannot finish a row's softmax, so
+   * this mode needs all three; each is called on the calling thread, between launches, with device pointers, and does
+   * its cross-rank exchange on the same stream (or behind an event recorded on it):
+   *   exchange_shift(user, shift, n_rows): shift[r] is the row's reference point where this shard owns the target and
+   *       -inf elsewhere: replace it by the maximum over ranks (exp-store form only);
+   *   exchange_rowstats(user, rowstats, rows, first_row): the chunk's [FLCE_ROWSTAT_PLANES][rows] statistics of this
+   *       shard: replace them by the merge over ranks (max; sum-exp rescaled to it; target logit and logit sum added;
+   *       arg-max by value, lowest class on ties);
+   *   after_grad_input(user, grad_input_chunk, rows, first_row): this shard's partial grad_input rows of the chunk
+   *       (dense [rows, hidden] in grad_dtype, which should be FLCE_FP32 so that the sum over ranks is rounded once)
+   *       are complete once the stream reaches this point: start their sum over ranks; the chunk's grad_weight GEMM,
+   *       enqueued next, leaves reserve_sms SMs free for it. */
+  void (*exchange_shift)(void* user, float* shift, int64_t n_rows);
+  void (*exchange_rowstats)(void* user, float* rowstats, int64_t rows, int64_t first_row);
+  void (*after_grad_input)(void* user, void* grad_input_chunk, int64_t rows, int64_t first_row);
+  void* exchange_user;
 } flce_fused_args_t;
 
 /* The single-sweep mode keeps a bounded 16-bit copy of each token chunk's logits.  FLCE_STORE_LOGITS keeps the

@@ -923,9 +923,12 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
   if (p->reduction == FLCE_NONE)
     return fail(FLCE_ERR_UNSUPPORTED, "single-sweep mode forms gradients before the upstream gradient is known; "
                                       "reduction 'none' needs the two-sweep path");
-  if (p->vocab != p->vocab_total || p->vocab_offset != 0)
-    return fail(FLCE_ERR_UNSUPPORTED, "single-sweep mode needs the whole vocabulary (a vocabulary shard does not know the "
-                                      "row's log-sum-exp before the cross-rank merge): use the two-sweep path");
+  const bool sharded = p->vocab != p->vocab_total || p->vocab_offset != 0;
+  if (sharded && (args->exchange_shift == nullptr || args->exchange_rowstats == nullptr || args->after_grad_input == nullptr))
+    return fail(FLCE_ERR_UNSUPPORTED, "a vocabulary shard does not know a row's log-sum-exp on its own: single-sweep mode "
+                                      "needs the three exchange hooks of flce_fused_args_t there (or use the two-sweep path)");
+  if (sharded && args->grad_bias != nullptr)
+    return fail(FLCE_ERR_UNSUPPORTED, "grad_bias is not formed on a vocabulary shard");
   if (args->grad_dtype != p->dtype && args->grad_dtype != FLCE_FP32)
     return fail(FLCE_ERR_UNSUPPORTED, "gradients must be in the input dtype or fp32");
   if (args->store_mode < FLCE_STORE_AUTO || args->store_mode > FLCE_STORE_EXP)
@@ -987,10 +990,17 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
     const int warps = 8;
     target_shift_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, warps)), warps * 32, 0, stream>>>(
         static_cast<const uint16_t*>(p->x), p->ld_x, static_cast<const uint16_t*>(p->w), p->ld_w, fmt16,
-        static_cast<int>(p->n_rows), static_cast<int>(p->hidden), target_all, p->ignore_index, p->vocab, p->bias, p->softcap,
-        inv_softcap, kExpStoreOffset, shift);
+        static_cast<int>(p->n_rows), static_cast<int>(p->hidden), target_all, p->ignore_index, p->vocab, p->vocab_offset,
+        sharded ? 1 : 0, p->bias, p->softcap, inv_softcap, kExpStoreOffset, shift);
     FLCE_CUDA(cudaGetLastError());
     ++g_kernel_launches;
+    if (sharded) {
+      args->exchange_shift(args->exchange_user, shift, p->n_rows);
+      shift_fill_kernel<<<static_cast<unsigned>(ceil_div(p->n_rows, threads)), threads, 0, stream>>>(
+          static_cast<int>(p->n_rows), kExpStoreOffset, shift);
+      FLCE_CUDA(cudaGetLastError());
+      ++g_kernel_launches;
+    }
     if (smoothing && args->grad_input != nullptr) {
       rc = launch_scaled_colsum(p->w, p->ld_w, p->vocab, p->hidden, fmt16, p->ce_weight, colsum_scratch, w_sum, false, stream);
       if (rc != FLCE_OK) return rc;
@@ -1045,6 +1055,7 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
     };
     rc = sweep1(nullptr);
     if (rc != FLCE_OK) return rc;
+    if (sharded) args->exchange_rowstats(args->exchange_user, chunk_stats, rows, r0);
     // ---- per-row losses, then the gradient coefficients (upstream gradient = 1)
     finalize_rows_kernel<<<static_cast<unsigned>(ceil_div(rows, threads)), threads, 0, stream>>>(
         static_cast<int>(rows), rm, tgt, p->ce_weight, chunk_stats, args->norm, out->lse + r0, out->target_prob + r0,
@@ -1073,7 +1084,7 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       ProfileSlot* slot = profile_begin(kKindOther, stream);
       exp_store_fixup_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
           x_chunk, p->ld_x, static_cast<int>(p->hidden), fmt16, static_cast<int>(rows), tgt, p->ignore_index, p->vocab,
-          out->lse + r0, shift + r0, chunk_stats + 2 * static_cast<size_t>(rows), c1, c3, inv_softcap, kExpStoreClamp, slab,
+          p->vocab_offset, out->lse + r0, shift + r0, chunk_stats + 2 * static_cast<size_t>(rows), c1, c3, inv_softcap, kExpStoreClamp, slab,
           plan.ld_slab, alpha, xs, p->hidden);
       profile_end(slot, stream);
       FLCE_CUDA(cudaGetLastError());
@@ -1116,7 +1127,7 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
                                                            ep, stream, p->active_rows, 1, base, nullptr, reserve_sms);
     };
     // ---- grad_weight (+)= dZ^T . X[chunk]    (M = vocab, N = hidden, K = rows; both operands MN-major)
-    auto grad_weight_gemm = [&]() -> int {
+    auto grad_weight_gemm = [&](int reserve_sms) -> int {
       if (args->grad_weight == nullptr) return FLCE_OK;
       StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(p->vocab);
@@ -1136,12 +1147,12 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       Operand b{exp_store ? static_cast<const void*>(xs) : static_cast<const void*>(x_chunk), p->hidden, rows,
                 exp_store ? p->hidden : p->ld_x, 1};
       return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0, true,
-                                                            ep, stream, p->active_rows, 2, base);
+                                                            ep, stream, p->active_rows, 2, base, nullptr, reserve_sms);
     };
     if (last && args->after_grad_weight != nullptr) {
       // grad_weight is complete after this launch: let the caller enqueue what consumes it (an all-reduce on another
       // stream), then form the last chunk's grad_input beside it on the SMs that are left
-      rc = grad_weight_gemm();
+      rc = grad_weight_gemm(0);
       if (rc != FLCE_OK) return rc;
       args->after_grad_weight(args->after_grad_weight_user);
       rc = grad_input_gemm(args->reserve_sms > 0 ? args->reserve_sms : 0);
@@ -1149,7 +1160,13 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
     } else {
       rc = grad_input_gemm(0);
       if (rc != FLCE_OK) return rc;
-      rc = grad_weight_gemm();
+      int reserve = 0;
+      if (sharded && args->grad_input != nullptr) {   // this shard's partial rows are on their way: let the caller start their sum
+        args->after_grad_input(args->exchange_user,
+                               static_cast<uint8_t*>(args->grad_input) + static_cast<size_t>(r0) * p->hidden * esize_out, rows, r0);
+        reserve = args->reserve_sms > 0 ? args->reserve_sms : 0;
+      }
+      rc = grad_weight_gemm(reserve);
       if (rc != FLCE_OK) return rc;
     }
     if (args->grad_bias != nullptr) {

@@ -286,15 +286,19 @@ __device__ __forceinline__ float dot8_16bit(const uint4& a, const uint4& b, int 
 // shift[r] = soft-capped logit of row r's target class + offset: x_r . W[y_r] (+ bias), one warp per row.
 // The log-sum-exp of a row is at least its target logit and exceeds it by the row's loss, so this point is within
 // [offset - loss, offset] of it without a pass over the vocabulary.  Rows without a usable target get the offset alone.
+// On a vocabulary shard (sharded != 0; w holds classes [vocab_offset, vocab_offset + vocab)) rows whose target lives
+// elsewhere get -inf: the caller takes the maximum over the shards and shift_fill_kernel settles the rows no shard owns.
 __global__ void target_shift_kernel(const uint16_t* x, long long ld_x, const uint16_t* w, long long ld_w, int fmt, int n_rows,
                                     int hidden, const long long* target, long long ignore_index, long long vocab,
-                                    const float* bias, float softcap, float inv_softcap, float offset, float* shift) {
+                                    long long vocab_offset, int sharded, const float* bias, float softcap, float inv_softcap,
+                                    float offset, float* shift) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
-  const long long y = target[row];
+  const long long t = target[row];
+  const long long y = t - vocab_offset;
   float z = 0.f;
-  if (y != ignore_index && y >= 0 && y < vocab) {
+  if (t != ignore_index && y >= 0 && y < vocab) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ld_x);
     const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<size_t>(y) * ld_w);
     float acc = 0.f;
@@ -303,8 +307,15 @@ __global__ void target_shift_kernel(const uint16_t* x, long long ld_x, const uin
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     z = acc + (bias != nullptr ? bias[y] : 0.f);
     if (softcap > 0.f) z = softcap * tanh_accurate(z * inv_softcap);
+  } else if (sharded) {
+    z = -INFINITY;
   }
   if (lane == 0) shift[row] = z + offset;
+}
+// rows whose target no shard owns (ignore_index, out of range): the offset alone, as in the unsharded case
+__global__ void shift_fill_kernel(int n_rows, float offset, float* shift) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row < n_rows && !(shift[row] > -3.0e38f)) shift[row] = offset;
 }
 
 // The stored exponentials are exact only while exp(s - shift) stays inside the clamp and the per-row factor inside fp32:
@@ -329,14 +340,16 @@ __global__ void exp_store_reshift_kernel(int n_rows, const float* lse, const int
 //   E[r, y_r] = (exp(s_y - shift_r) - c3_r / alpha_r) * chain_y     (the true-class term, formed in fp32 from the fp32
 //                                                                    target logit, not from the rounded stored value)
 __global__ void exp_store_fixup_kernel(const uint16_t* x, long long ld_x, int hidden, int fmt, int n_rows,
-                                       const long long* target, long long ignore_index, long long vocab, const float* lse,
-                                       const float* shift, const float* target_logit, const float* c1, const float* c3,
-                                       float inv_softcap, float clamp, uint16_t* slab, long long ld_slab, float* alpha,
-                                       uint16_t* xs, long long ld_xs) {
+                                       const long long* target, long long ignore_index, long long vocab,
+                                       long long vocab_offset, const float* lse, const float* shift,
+                                       const float* target_logit, const float* c1, const float* c3, float inv_softcap,
+                                       float clamp, uint16_t* slab, long long ld_slab, float* alpha, uint16_t* xs,
+                                       long long ld_xs) {
   const int row = blockIdx.x;
   if (row >= n_rows) return;
-  const long long y = target[row];
-  const bool live = y != ignore_index;
+  const long long t = target[row];
+  const long long y = t - vocab_offset;          // column of the target in this (shard of the) vocabulary, if it is here
+  const bool live = t != ignore_index;
   const float a = live ? c1[row] * ex2_approx((shift[row] - lse[row]) * kLog2e) : 0.f;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ld_x);
   uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(row) * ld_xs);

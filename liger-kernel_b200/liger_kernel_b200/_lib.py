@@ -111,10 +111,15 @@ class FusedArgs(C.Structure):
         ("grad_input", C.c_void_p), ("grad_weight", C.c_void_p), ("grad_bias", C.c_void_p),
         ("norm_given", C.c_int32), ("store_mode", C.c_int32),
         ("after_grad_weight", C.c_void_p), ("after_grad_weight_user", C.c_void_p), ("reserve_sms", C.c_int32),
+        ("exchange_shift", C.c_void_p), ("exchange_rowstats", C.c_void_p), ("after_grad_input", C.c_void_p),
+        ("exchange_user", C.c_void_p),
     ]
 
 
 AFTER_GRAD_WEIGHT_FN = C.CFUNCTYPE(None, C.c_void_p)
+EXCHANGE_SHIFT_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int64)
+EXCHANGE_ROWSTATS_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64)
+AFTER_GRAD_INPUT_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64)
 
 
 STORE_AUTO, STORE_LOGITS, STORE_EXP = 0, 1, 2

@@ -299,12 +299,15 @@ def flce_backward_device(prep: _Prepared, lse, target_prob, norm, grad_output, n
 
 
 def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True, need_bias=False, grad_dtype=None,
-                             chunk_budget=None, norm_in=None, after_grad_weight=None, reserve_sms=0):
+                             chunk_budget=None, norm_in=None, after_grad_weight=None, reserve_sms=0, shard_hooks=None):
     """Loss and gradients (for an upstream gradient of 1) in one pass over token chunks.
     Returns (outputs dict, norm, grad_input, grad_weight, grad_bias) in the padded hidden size of ``prep``.
     ``norm_in``: normalisers counted elsewhere (a token-sharded caller passes the all-reduced ones).
     ``after_grad_weight(grad_weight)``: called on this thread once the launch that completes grad_weight is enqueued,
-    before the last grad_input GEMM, which then leaves ``reserve_sms`` SMs free (room for the caller's collective)."""
+    before the last grad_input GEMM, which then leaves ``reserve_sms`` SMs free (room for the caller's collective).
+    ``shard_hooks``: for a vocabulary shard, a dict of the three exchanges (``flce_fused_args_t`` in include/flce_b200.h),
+    here with tensors instead of pointers: ``exchange_shift(shift[n_rows])``, ``exchange_rowstats(stats[6, rows], first_row)``
+    (both update their argument in place) and ``after_grad_input(grad_input[first_row:first_row+rows], first_row)``."""
     dev = prep.device
     gd = prep.dtype if grad_dtype is None else grad_dtype
     budget = CHUNK_BUDGET_BYTES if chunk_budget is None else int(chunk_budget)
@@ -333,8 +336,25 @@ def flce_single_sweep_device(prep: _Prepared, need_input=True, need_weight=True,
             args.after_grad_weight = C.cast(hook, C.c_void_p)
             args.reserve_sms = int(reserve_sms)
         ws = prep.workspace(_lib.PHASE_FUSED, budget)
+        keep = []
+        if shard_hooks is not None:
+            def view(ptr, count):          # `count` floats at a pointer the library hands out, as a tensor (no copy)
+                return _float_tensor_at(ptr, count, dev)
+
+            def on_shift(_user, ptr, n):
+                shard_hooks["exchange_shift"](view(ptr, n))
+
+            def on_rowstats(_user, ptr, rows, first_row):
+                shard_hooks["exchange_rowstats"](view(ptr, _lib.ROWSTAT_PLANES * rows).view(_lib.ROWSTAT_PLANES, rows), first_row)
+
+            def on_grad_input(_user, _ptr_unused, rows, first_row):
+                shard_hooks["after_grad_input"](gx[first_row:first_row + rows], first_row)
+
+            keep = [_lib.EXCHANGE_SHIFT_FN(on_shift), _lib.EXCHANGE_ROWSTATS_FN(on_rowstats), _lib.AFTER_GRAD_INPUT_FN(on_grad_input)]
+            args.exchange_shift, args.exchange_rowstats, args.after_grad_input = (C.cast(f, C.c_void_p) for f in keep)
+            args.reserve_sms = int(reserve_sms)
         check(lib.flce_b200_forward_backward(C.byref(prep.problem), C.byref(args), _ptr(ws), ws.numel(), budget, _stream(dev)))
-        del hook
+        del hook, keep
     return out, norm, gx, gw, gb
 
 
@@ -345,6 +365,19 @@ def scale_gradient_(t: Optional[torch.Tensor], scale: torch.Tensor):
     with _device_guard(t.device):
         check(lib.flce_b200_scale_gradient(_ptr(t), t.numel(), _DTYPES[t.dtype], _ptr(scale), _stream(t.device)))
     return t
+
+
+class _CudaFloats:
+    """fp32 device memory at a raw pointer, in the form torch.as_tensor understands (CUDA array interface)."""
+
+    def __init__(self, ptr, count):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def _float_tensor_at(ptr: int, count: int, device) -> torch.Tensor:
+    if device.type == "cuda":
+        return torch.as_tensor(_CudaFloats(ptr, count), device=device)
+    return torch.frombuffer((C.c_char * (count * 4)).from_address(ptr), dtype=torch.float32, count=count)
 
 
 def _autocast_operands(_input, weight, bias):

@@ -43,11 +43,13 @@ class CudaBackend:
                              softcap, use_token_scaling, vocab_total=vocab_total, vocab_offset=vocab_offset,
                              want_argmax=want_argmax, allow_compact=allow_compact)
 
-    def single_sweep(self, prep, norm, need_input, need_weight, after_grad_weight=None, reserve_sms=0):
-        """Loss rows / scalars and the gradients for an upstream gradient of 1, with the given (global) normalisers."""
+    def single_sweep(self, prep, norm, need_input, need_weight, after_grad_weight=None, reserve_sms=0, shard_hooks=None,
+                     grad_dtype=None):
+        """Loss rows / scalars and the gradients for an upstream gradient of 1, with the given (global) normalisers.
+        grad_input comes back in the compact row order of ``prep`` (``prep.rows_to_token_order`` undoes it)."""
         out, _, gx, gw, _ = _op.flce_single_sweep_device(prep, need_input, need_weight, False, norm_in=norm,
-                                                         after_grad_weight=after_grad_weight, reserve_sms=reserve_sms)
-        gx = prep.rows_to_token_order(gx)
+                                                         after_grad_weight=after_grad_weight, reserve_sms=reserve_sms,
+                                                         shard_hooks=shard_hooks, grad_dtype=grad_dtype)
         return _op._results_to_token_order(prep, out), gx, gw
 
     def count(self, prep):
@@ -147,10 +149,14 @@ class _TokenSharded(torch.autograd.Function):
         if single:
             pending = []
             hook = None
+            comm = None
             if world > 1 and needs[1]:
-                comm = torch.cuda.Stream(device=prep.device)
+                comm = torch.cuda.Stream(device=prep.device) if prep.device.type == "cuda" else None
 
                 def hook(gw):
+                    if comm is None:             # host tensors (tests on gloo ranks): nothing to overlap with
+                        dist.all_reduce(gw, group=group)
+                        return
                     done = torch.cuda.Event()
                     done.record()
                     comm.wait_event(done)
@@ -162,6 +168,7 @@ class _TokenSharded(torch.autograd.Function):
 
             out, gx, gw = backend.single_sweep(prep, norm, needs[0], needs[1], after_grad_weight=hook,
                                                reserve_sms=RESERVE_SMS_FOR_COLLECTIVE if hook is not None else 0)
+            gx = prep.rows_to_token_order(gx)
             ctx.stored = (gx, gw, pending)
             ctx.hidden = prep.hidden
             ctx.in_dtypes = (x.dtype, w.dtype)
@@ -170,7 +177,7 @@ class _TokenSharded(torch.autograd.Function):
             if world > 1:
                 with _timed("all_reduce loss"):
                     dist.all_reduce(loss, group=group)
-            ctx.comm = comm if hook is not None else None
+            ctx.comm = comm
             return loss
         out = backend.finalize(prep, backend.forward_stats(prep), norm)
         ctx.saved = (prep, out["lse"], out["target_prob"], norm)
@@ -229,9 +236,65 @@ class _TokenSharded(torch.autograd.Function):
         return gx, gw, None, None, None, None, None
 
 
+def _merge_rowstats_in_place(stats, world, group):
+    planes, n = stats.shape
+    gathered = torch.empty((world * planes, n), dtype=stats.dtype, device=stats.device)
+    with _timed("all_gather row statistics"):
+        dist.all_gather_into_tensor(gathered, stats.contiguous(), group=group)
+    stats.copy_(merge_rowstats(gathered.view(world, planes, n)))
+
+
 class _VocabSharded(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_shard, target, vocab_start, vocab_total, group, backend, kw):
+        recording = kw.get("recording", True)
+        needs = (recording and ctx.needs_input_grad[0], recording and ctx.needs_input_grad[1])
+        world = _world(group)
+        ctx.stored = None
+        if hasattr(backend, "single_sweep") and _op._use_single_sweep(kw["reduction"], needs, x.dtype):
+            # Gradients formed in forward on every shard: the three exchanges happen inside the sweep, between launches
+            # (reference points: max over shards; row statistics per token chunk: all-gather + merge; partial grad_input
+            # of a chunk: summed over the shards on a side stream while the chunk's grad_weight GEMM runs).
+            prep = backend.prepare(x.detach(), w_shard.detach(), target, None, None, kw["ignore_index"], kw["lse_square_scale"],
+                                   kw["label_smoothing"], kw["reduction"], kw["softcap"], False, vocab_total=vocab_total,
+                                   vocab_offset=vocab_start, want_argmax=True, allow_compact=True)
+            norm = backend.count(prep)          # targets are replicated: identical on every rank
+            on_gpu = prep.device.type == "cuda"
+            comm = torch.cuda.Stream(device=prep.device) if (on_gpu and world > 1) else None
+
+            def exchange_shift(shift):
+                if world > 1:
+                    with _timed("all_reduce(max) reference points"):
+                        dist.all_reduce(shift, op=dist.ReduceOp.MAX, group=group)
+
+            def exchange_rowstats(stats, first_row):
+                if world > 1:
+                    _merge_rowstats_in_place(stats, world, group)
+
+            def after_grad_input(gx_chunk, first_row):
+                if world == 1:
+                    return
+                if comm is None:
+                    dist.all_reduce(gx_chunk, group=group)
+                    return
+                done = torch.cuda.Event()
+                done.record()
+                comm.wait_event(done)
+                with torch.cuda.stream(comm):
+                    with _timed("all_reduce grad_input chunk (beside the grad_weight GEMM)"):
+                        dist.all_reduce(gx_chunk, group=group, async_op=True).wait()
+
+            hooks = dict(exchange_shift=exchange_shift, exchange_rowstats=exchange_rowstats, after_grad_input=after_grad_input)
+            out, gx, gw = backend.single_sweep(prep, norm, needs[0], needs[1], shard_hooks=hooks, grad_dtype=torch.float32,
+                                               reserve_sms=RESERVE_SMS_FOR_COLLECTIVE if comm is not None else 0)
+            if comm is not None:
+                torch.cuda.current_stream(prep.device).wait_stream(comm)
+            gx = prep.rows_to_token_order(gx)
+            ctx.stored = (gx, gw)
+            ctx.hidden = prep.hidden
+            ctx.in_dtypes = (x.dtype, w_shard.dtype)
+            ctx.extra = dict(predicted_tokens=out["predicted_tokens"], z_loss=out["scalars"][1])
+            return out["scalars"][0].clone()
         prep = backend.prepare(x.detach(), w_shard.detach(), target, None, None, kw["ignore_index"], kw["lse_square_scale"],
                                kw["label_smoothing"], kw["reduction"], kw["softcap"], False, vocab_total=vocab_total,
                                vocab_offset=vocab_start, want_argmax=True)
@@ -253,6 +316,17 @@ class _VocabSharded(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
+        if ctx.stored is not None:
+            gx, gw = ctx.stored
+            ctx.stored = None
+            dev = (gx if gx is not None else gw).device
+            go = grad_output.detach().to(device=dev, dtype=torch.float32).reshape(1)
+            gx = _op.scale_gradient_(gx, go)
+            gw = _op.scale_gradient_(gw, go)
+            h = ctx.hidden
+            gx = None if gx is None else gx[:, :h].to(ctx.in_dtypes[0])
+            gw = None if gw is None else gw[:, :h].to(ctx.in_dtypes[1])
+            return gx, gw, None, None, None, None, None, None
         prep, lse, prob, norm = ctx.saved
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         # partial grad_input in fp32 so that the cross-rank sum is formed before the single rounding
@@ -299,6 +373,7 @@ def vocab_sharded_fused_linear_cross_entropy(input, weight_shard, target, vocab_
 
     Returns the loss of the full problem on every rank; ``weight_shard.grad`` is local, ``input.grad`` is the sum over
     ranks (all-reduced)."""
+    kw = _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap)
+    kw["recording"] = torch.is_grad_enabled()
     return _VocabSharded.apply(input, weight_shard, target, int(vocab_start), int(vocab_total), group,
-                               backend or CudaBackend(),
-                               _kwargs(ignore_index, lse_square_scale, label_smoothing, reduction, softcap))
+                               backend or CudaBackend(), kw)

@@ -531,22 +531,28 @@ int emu_gemm_store_ex(const void* a, const void* b, int dtype, int m, int n, int
 // the exp-store form of the single-sweep mode: reference points, per-chunk fix-up, ordered scaled column sums
 // (launch geometry of flce_b200_forward_backward)
 int emu_target_shift(const void* x, long long ld_x, const void* w, long long ld_w, int fmt, int n_rows, int hidden,
-                     const long long* target, long long ignore_index, long long vocab, const float* bias, float softcap,
-                     float* shift) {
+                     const long long* target, long long ignore_index, long long vocab, long long vocab_offset, int sharded,
+                     const float* bias, float softcap, float* shift) {
   const int warps = 8;
   emu::launch(static_cast<unsigned>(ceil_div(n_rows, warps)), warps * 32, [&]() {
     target_shift_kernel(static_cast<const uint16_t*>(x), ld_x, static_cast<const uint16_t*>(w), ld_w, fmt, n_rows, hidden,
-                        target, ignore_index, vocab, bias, softcap, softcap > 0.f ? 1.f / softcap : 0.f, kExpStoreOffset, shift);
+                        target, ignore_index, vocab, vocab_offset, sharded, bias, softcap, softcap > 0.f ? 1.f / softcap : 0.f,
+                        kExpStoreOffset, shift);
   });
   return 0;
 }
 
+int emu_shift_fill(int n_rows, float* shift) {
+  emu::launch_serial(static_cast<unsigned>(ceil_div(n_rows, 256)), 256, [&]() { shift_fill_kernel(n_rows, kExpStoreOffset, shift); });
+  return 0;
+}
+
 int emu_exp_store_fixup(const void* x, long long ld_x, int hidden, int fmt, int n_rows, const long long* target,
-                        long long ignore_index, long long vocab, const float* lse, const float* shift,
+                        long long ignore_index, long long vocab, long long vocab_offset, const float* lse, const float* shift,
                         const float* target_logit, const float* c1, const float* c3, float softcap, void* slab,
                         long long ld_slab, float* alpha, void* xs, long long ld_xs) {
   emu::launch_serial(static_cast<unsigned>(n_rows), 256, [&]() {
-    exp_store_fixup_kernel(static_cast<const uint16_t*>(x), ld_x, hidden, fmt, n_rows, target, ignore_index, vocab, lse, shift,
+    exp_store_fixup_kernel(static_cast<const uint16_t*>(x), ld_x, hidden, fmt, n_rows, target, ignore_index, vocab, vocab_offset, lse, shift,
                            target_logit, c1, c3, softcap > 0.f ? 1.f / softcap : 0.f, kExpStoreClamp,
                            static_cast<uint16_t*>(slab), ld_slab, alpha, static_cast<uint16_t*>(xs), ld_xs);
   });

@@ -67,8 +67,9 @@ def load():
         "emu_sce_sweep_dz": [P, P, I, I, I, I, LL, LL, P, LL, F, LL, P, P, P, P, P, LL, I],
         "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I, I, P, LL],
         "emu_gemm_store_ex": [P, P, I, I, I, I, LL, LL, P, P, LL, P, LL, I, P, P, P],
-        "emu_target_shift": [P, LL, P, LL, I, I, I, P, LL, LL, P, F, P],
-        "emu_exp_store_fixup": [P, LL, I, I, I, P, LL, LL, P, P, P, P, P, F, P, LL, P, P, LL],
+        "emu_target_shift": [P, LL, P, LL, I, I, I, P, LL, LL, LL, I, P, F, P],
+        "emu_shift_fill": [I, P],
+        "emu_exp_store_fixup": [P, LL, I, I, I, P, LL, LL, LL, P, P, P, P, P, F, P, LL, P, P, LL],
         "emu_scaled_colsum": [P, LL, I, I, I, P, P, P, I],
         "emu_exp_store_check": [I, P, LL, P, P],
         "emu_sweep_dz": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, LL, I, I],
@@ -291,6 +292,10 @@ class EmuLib(fake_lib.FakeLib):
         exp_ok = not (smoothing and cap > 0) and not a.grad_bias and prob.dtype == 0
         if a.store_mode == 2 and not exp_ok:
             return 2
+        sharded = prob.vocab != prob.vocab_total or prob.vocab_offset != 0
+        if sharded and not (a.exchange_shift and a.exchange_rowstats and a.after_grad_input):
+            return 2
+        from liger_kernel_b200 import _lib as real_lib
         exp_store = exp_ok and a.store_mode != 1
         self.store_modes = getattr(self, "store_modes", []) + ["exp" if exp_store else "logits"]
         if not a.norm_given:
@@ -309,7 +314,10 @@ class EmuLib(fake_lib.FakeLib):
         scratch = torch.full((32, h), nan)
         if exp_store:
             self.emu.emu_target_shift(prob.x, prob.ld_x, prob.w, prob.ld_w, prob.dtype, n, h, prob.target, prob.ignore_index, v,
-                                      prob.bias, cap, shift.data_ptr())
+                                      prob.vocab_offset, int(sharded), prob.bias, cap, shift.data_ptr())
+            if sharded:
+                real_lib.EXCHANGE_SHIFT_FN(a.exchange_shift)(a.exchange_user, shift.data_ptr(), n)
+                self.emu.emu_shift_fill(n, shift.data_ptr())
             if smoothing and a.grad_input:
                 self.emu.emu_scaled_colsum(prob.w, prob.ld_w, v, h, prob.dtype, prob.ce_weight, scratch.data_ptr(), w_sum.data_ptr(), 0)
         off = lambda base, rows, size: (base + rows * size) if base else None      # noqa: E731
@@ -335,6 +343,8 @@ class EmuLib(fake_lib.FakeLib):
                                      prob.dtype, limit, shift[r0:].data_ptr() if exp_store else None, prob.ignore_index)
             self.emu.emu_merge_partials(rows, n_tiles, planes[0].data_ptr(), planes[1].data_ptr(), planes[2].data_ptr(),
                                         planes[3].data_ptr(), pidx.data_ptr(), stats.data_ptr())
+            if sharded:
+                real_lib.EXCHANGE_ROWSTATS_FN(a.exchange_rowstats)(a.exchange_user, stats.data_ptr(), rows, r0)
             self.emu.emu_finalize(rows, prob.ignore_index, prob.label_smoothing, prob.lse_square_scale, int(prob.reduction == 0),
                                   prob.use_token_scaling, v, prob.vocab_total, prob.vocab_offset, t_c, prob.ce_weight,
                                   stats.data_ptr(), a.norm, off(fo.lse, r0, 4), off(fo.target_prob, r0, 4), off(fo.loss_rows, r0, 4),
@@ -354,7 +364,8 @@ class EmuLib(fake_lib.FakeLib):
                                              prob.ce_weight, cap, prob.vocab_offset, planes[0].data_ptr(), planes[1].data_ptr(),
                                              planes[2].data_ptr(), planes[3].data_ptr(), pidx.data_ptr(), tl.data_ptr(),
                                              slab.data_ptr(), ld_slab, prob.dtype, limit, shift[r0:].data_ptr(), prob.ignore_index)
-                self.emu.emu_exp_store_fixup(x_c, prob.ld_x, h, prob.dtype, rows, t_c, prob.ignore_index, v, off(fo.lse, r0, 4),
+                self.emu.emu_exp_store_fixup(x_c, prob.ld_x, h, prob.dtype, rows, t_c, prob.ignore_index, v, prob.vocab_offset,
+                                             off(fo.lse, r0, 4),
                                              shift[r0:].data_ptr(), stats[2].data_ptr(), c[0].data_ptr(), c[2].data_ptr(), cap,
                                              slab.data_ptr(), ld_slab, alpha.data_ptr(), xs.data_ptr(), h)
                 if smoothing and a.grad_weight:
@@ -364,30 +375,44 @@ class EmuLib(fake_lib.FakeLib):
                 self.emu.emu_dz_inplace(slab.data_ptr(), ld_slab, rows, v, prob.dtype, t_c, prob.vocab_offset, off(fo.lse, r0, 4),
                                         c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr(), prob.ce_weight,
                                         1.0 / cap if cap > 0 else 0.0, active_ptr, r0)
-            if a.grad_input and row_limit > 0:
-                # grad_input[chunk] = dZ . W through the library's store epilogue (per-row factor and rank-1 term in exp-store form)
-                gi = a.grad_input + r0 * h * (4 if gfmt == 2 else 2)
-                self.emu.emu_gemm_store_ex(slab.data_ptr(), Wt.data_ptr(), prob.dtype, row_limit, h, v, ld_slab, v, None, None, 0,
-                                           gi, h, gfmt, alpha.data_ptr() if exp_store else None,
-                                           c[1].data_ptr() if (exp_store and smoothing) else None,
-                                           w_sum.data_ptr() if (exp_store and smoothing) else None)
-            if a.grad_weight:
-                X16 = xs if exp_store else self._matrix(x_c, rows, h, prob.ld_x, tdt)
-                At = slab[:k_rows, :v].t().contiguous()             # [v, k_rows]
-                Bt = X16[:k_rows].t().contiguous()                  # [h, k_rows]
-                kk = k_rows
-                if kk == 0:                                         # nothing accumulated: the kernel's k_blocks == 0 path
-                    At, Bt, kk = torch.zeros(v, 8).to(tdt), torch.zeros(h, 8).to(tdt), 8
-                r1 = exp_store and smoothing and last
-                out_ptr = a.grad_weight if (last and gfmt != 2) else None
-                acc_out = dw_acc if (gfmt == 2 or not last) else None
-                if gfmt == 2:
-                    acc_out = self._matrix(a.grad_weight, v, h, h, torch.float32)
-                acc_in = None if first else (acc_out if gfmt == 2 else dw_acc)
-                self.emu.emu_gemm_store_ex(At.data_ptr(), Bt.data_ptr(), prob.dtype, v, h, kk, kk, kk,
-                                           None if acc_in is None else acc_in.data_ptr(),
-                                           None if acc_out is None else acc_out.data_ptr(), h, out_ptr, h, prob.dtype,
-                                           None, prob.ce_weight if r1 else None, x_sum.data_ptr() if r1 else None)
+            def grad_input_part():
+                if a.grad_input and row_limit > 0:
+                    # grad_input[chunk] = dZ . W through the library's store epilogue (per-row factor and rank-1 term in exp-store form)
+                    gi = a.grad_input + r0 * h * (4 if gfmt == 2 else 2)
+                    self.emu.emu_gemm_store_ex(slab.data_ptr(), Wt.data_ptr(), prob.dtype, row_limit, h, v, ld_slab, v, None, None, 0,
+                                               gi, h, gfmt, alpha.data_ptr() if exp_store else None,
+                                               c[1].data_ptr() if (exp_store and smoothing) else None,
+                                               w_sum.data_ptr() if (exp_store and smoothing) else None)
+                if sharded and a.grad_input:
+                    real_lib.AFTER_GRAD_INPUT_FN(a.after_grad_input)(a.exchange_user, a.grad_input + r0 * h * (4 if gfmt == 2 else 2),
+                                                                     rows, r0)
+
+            def grad_weight_part():
+                if a.grad_weight:
+                    X16 = xs if exp_store else self._matrix(x_c, rows, h, prob.ld_x, tdt)
+                    At = slab[:k_rows, :v].t().contiguous()             # [v, k_rows]
+                    Bt = X16[:k_rows].t().contiguous()                  # [h, k_rows]
+                    kk = k_rows
+                    if kk == 0:                                         # nothing accumulated: the kernel's k_blocks == 0 path
+                        At, Bt, kk = torch.zeros(v, 8).to(tdt), torch.zeros(h, 8).to(tdt), 8
+                    r1 = exp_store and smoothing and last
+                    out_ptr = a.grad_weight if (last and gfmt != 2) else None
+                    acc_out = dw_acc if (gfmt == 2 or not last) else None
+                    if gfmt == 2:
+                        acc_out = self._matrix(a.grad_weight, v, h, h, torch.float32)
+                    acc_in = None if first else (acc_out if gfmt == 2 else dw_acc)
+                    self.emu.emu_gemm_store_ex(At.data_ptr(), Bt.data_ptr(), prob.dtype, v, h, kk, kk, kk,
+                                               None if acc_in is None else acc_in.data_ptr(),
+                                               None if acc_out is None else acc_out.data_ptr(), h, out_ptr, h, prob.dtype,
+                                               None, prob.ce_weight if r1 else None, x_sum.data_ptr() if r1 else None)
+
+            if last and a.after_grad_weight:          # the library's order when a caller sums grad_weight over token shards
+                grad_weight_part()
+                real_lib.AFTER_GRAD_WEIGHT_FN(a.after_grad_weight)(a.after_grad_weight_user)
+                grad_input_part()
+            else:
+                grad_input_part()
+                grad_weight_part()
             if a.grad_bias:
                 self.emu.emu_colsum(slab.data_ptr(), ld_slab, rows, v, prob.dtype, gb.data_ptr(), int(r0 != 0), active_ptr, r0)
         if a.grad_bias:

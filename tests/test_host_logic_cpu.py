@@ -207,10 +207,22 @@ def test_sharded_operators_single_process_path(monkeypatch):
         assert fake.calls[-1] == "flce_b200_backward" and w.grad.shape == (50, 32)
         del fake.calls[:]
         w_shard = w.detach()[10:30].clone().requires_grad_(True)
+        # a vocabulary shard, mean reduction: gradients formed in forward too, fp32 so that the sum over shards rounds once,
+        # with the three exchange hooks set
         loss = sharded.vocab_sharded_fused_linear_cross_entropy(x, w_shard, t, 10, 50)
+        prob, args = fake.structs["flce_b200_forward_backward"][-2:]
+        assert (prob.vocab, prob.vocab_total, prob.vocab_offset, prob.flags) == (20, 50, 10, 1)
+        assert args.grad_dtype == 2 and args.norm_given == 1
+        assert args.exchange_shift and args.exchange_rowstats and args.after_grad_input
+        loss.backward()
+        assert w_shard.grad.shape == (20, 32) and w_shard.grad.dtype == torch.bfloat16
+        # per-token losses: statistics merged across shards, then the two-sweep backward with fp32 partial grad_input
+        del fake.calls[:]
+        w_shard.grad = None
+        rows = sharded.vocab_sharded_fused_linear_cross_entropy(x, w_shard, t, 10, 50, reduction="none")
         prob = fake.structs["flce_b200_forward_stats"][-1]
         assert (prob.vocab, prob.vocab_total, prob.vocab_offset, prob.flags) == (20, 50, 10, 1)
-        loss.backward()
+        rows.sum().backward()
         assert fake.structs["flce_b200_backward"][-1].grad_dtype == 2 and w_shard.grad.shape == (20, 32)
 
 
