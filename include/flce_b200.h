@@ -194,7 +194,9 @@ int flce_b200_forward_stats(const flce_problem_t* p, float* rowstats, void* work
  *     current); make that first call before starting any stream capture.
  *   - All calls on a GPU share the one array, and it keeps the previous call's contents; nothing in it needs to
  *     start at zero.  Two calls whose kernels overlap on the same GPU (different streams or threads) race on it:
- *     serialise them. */
+ *     serialise them.
+ *   - p->active_rows is not used here: the sweep always covers all n_rows rows (results are the same, the rows a
+ *     caller moved to the end are merely not skipped). */
 int flce_b200_forward_stats_static(const flce_problem_t* p, float* rowstats, void* stream);
 
 /* Per-row losses and metrics from (possibly cross-rank merged) statistics, and their sums.

@@ -511,6 +511,9 @@ struct StoreEpilogue {
     const float* row_scale;
     const float* r1_row;
     const float* r1_col;
+    // 1: add into acc_out with vector reductions at L2 (no read in this kernel, nothing to wait for); acc_in must be null.
+    // Every element is owned by one thread of one launch, so the sum over launches keeps the stream's order.
+    int acc_add;
   };
 
   int row;
@@ -553,20 +556,35 @@ struct StoreEpilogue {
     const int row0 = row - lane;                 // first row of this warp's patch
     const int c4 = (lane & 7) * 4;               // this lane's four columns inside the patch
     const bool col_ok = col + c4 < p.n_cols;     // n_cols is a multiple of 8: a group of four is in or out as a whole
+    const int r_first = lane >> 3;
+    // all partial-sum loads of the patch first (independent, in flight together), then the arithmetic and the stores
+    float4 part[8];
+    if (p.acc_in != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int grow = row0 + i * 4 + r_first;
+        part[i] = (grow < p.m_rows && col_ok)
+                      ? *reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(grow) * p.ld_acc + col + c4)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const int r = i * 4 + (lane >> 3);
+      const int r = i * 4 + r_first;
       const int grow = row0 + r;
       if (grow < p.m_rows && col_ok) {
         float4 a = *reinterpret_cast<const float4*>(stage + r * 36 + c4);
         if (p.acc_in != nullptr) {
-          const float4 b = *reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(grow) * p.ld_acc + col + c4);
-          a.x += b.x;
-          a.y += b.y;
-          a.z += b.z;
-          a.w += b.w;
+          a.x += part[i].x;
+          a.y += part[i].y;
+          a.z += part[i].z;
+          a.w += part[i].w;
         }
-        if (p.acc_out != nullptr) *reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(grow) * p.ld_acc + col + c4) = a;
+        if (p.acc_out != nullptr) {
+          float4* dst = reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(grow) * p.ld_acc + col + c4);
+          if (p.acc_add) vector_add_f32x4(dst, a);
+          else *dst = a;
+        }
         if (p.out != nullptr) {
           if (p.out_fmt == kOutFp32) {
             *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = a;

@@ -1132,11 +1132,15 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       StoreEpilogue::Params ep{};
       ep.m_rows = static_cast<int>(p->vocab);
       ep.n_cols = static_cast<int>(p->hidden);
+      // One chunk: written once in the final dtype.  Several: the first chunk stores its fp32 part, the others add theirs
+      // with reductions at L2 (no read-modify-write in the epilogue), and a 16-bit result is converted after the last.
       float* acc = grads_fp32 ? static_cast<float*>(args->grad_weight) : dw_acc;
-      ep.acc_in = first ? nullptr : acc;
-      ep.acc_out = (grads_fp32 || !last) ? acc : nullptr;
+      const bool direct = plan.n_chunks == 1 && !grads_fp32;
+      ep.acc_in = nullptr;
+      ep.acc_out = direct ? nullptr : acc;
+      ep.acc_add = (!direct && !first) ? 1 : 0;
       ep.ld_acc = p->hidden;
-      ep.out = (!grads_fp32 && last) ? args->grad_weight : nullptr;
+      ep.out = direct ? args->grad_weight : nullptr;
       ep.ld_out = p->hidden;
       ep.out_fmt = fmt16;
       if (exp_store && smoothing && last) {   // the uniform term of every chunk at once: - w_j * sum_r c2_r x_r
@@ -1146,8 +1150,18 @@ int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t*
       Operand a{slab, p->vocab, rows, plan.ld_slab, 1};
       Operand b{exp_store ? static_cast<const void*>(xs) : static_cast<const void*>(x_chunk), p->hidden, rows,
                 exp_store ? p->hidden : p->ld_x, 1};
-      return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0, true,
-                                                            ep, stream, p->active_rows, 2, base, nullptr, reserve_sms);
+      int rc2 = launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindDw, pair, a, b, p->dtype, p->vocab, p->hidden, rows, 0,
+                                                               true, ep, stream, p->active_rows, 2, base, nullptr, reserve_sms);
+      if (rc2 != FLCE_OK) return rc2;
+      if (last && !direct && !grads_fp32) {
+        ProfileSlot* slot = profile_begin(kKindOther, stream);
+        convert_f32_kernel<<<dev->sm_count * 8, 256, 0, stream>>>(acc, static_cast<long long>(p->vocab) * p->hidden, fmt16,
+                                                                   static_cast<uint16_t*>(args->grad_weight));
+        profile_end(slot, stream);
+        FLCE_CUDA(cudaGetLastError());
+        ++g_kernel_launches;
+      }
+      return FLCE_OK;
     };
     if (last && args->after_grad_weight != nullptr) {
       // grad_weight is complete after this launch: let the caller enqueue what consumes it (an all-reduce on another

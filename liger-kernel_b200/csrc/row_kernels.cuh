@@ -424,6 +424,28 @@ __global__ void scaled_colsum_stage2_kernel(const float* scratch, int n_cols, fl
   out[col] = t;
 }
 
+// fp32 accumulator -> 16-bit result, once every token chunk has added its part (single-sweep weight gradient)
+__global__ void convert_f32_kernel(const float* src, long long n, int fmt, uint16_t* dst) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    if (i + 8 <= n) {
+      const float4 a = *reinterpret_cast<const float4*>(src + i);
+      const float4 b = *reinterpret_cast<const float4*>(src + i + 4);
+      uint4 o;
+      o.x = pack2(a.x, a.y, fmt);
+      o.y = pack2(a.z, a.w, fmt);
+      o.z = pack2(b.x, b.y, fmt);
+      o.w = pack2(b.z, b.w, fmt);
+      *reinterpret_cast<uint4*>(dst + i) = o;
+    } else {
+      for (long long j = i; j < n; ++j) {
+        const uint32_t two = pack2(src[j], 0.f, fmt);
+        dst[j] = static_cast<uint16_t>(two & 0xffffu);
+      }
+    }
+  }
+}
+
 // data[i] *= *scale unless *scale == 1 (checked on the device: no host synchronisation); 16-bit or fp32 elements
 __global__ void scale_inplace_kernel(void* data, long long n, int fmt, const float* scale) {
   const float s = *scale;

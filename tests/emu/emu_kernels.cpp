@@ -511,7 +511,7 @@ int emu_gemm_store(const void* a, const void* b, int dtype, int m, int n, int k,
 // StoreEpilogue with every option: separate fp32 partial in / out, per-row scale, rank-1 correction (all nullable)
 int emu_gemm_store_ex(const void* a, const void* b, int dtype, int m, int n, int k, long long ld_a, long long ld_b,
                       const float* acc_in, float* acc_out, long long ld_acc, void* out, long long ld_out, int out_fmt,
-                      const float* row_scale, const float* r1_row, const float* r1_col) {
+                      const float* row_scale, const float* r1_row, const float* r1_col, int acc_add) {
   StoreEpilogue::Params ep{};
   ep.m_rows = m;
   ep.n_cols = n;
@@ -524,7 +524,14 @@ int emu_gemm_store_ex(const void* a, const void* b, int dtype, int m, int n, int
   ep.row_scale = row_scale;
   ep.r1_row = r1_row;
   ep.r1_col = r1_col;
+  ep.acc_add = acc_add;
   run_tiles_store(ep, a, b, dtype, m, n, k, ld_a, ld_b, 2 * kBlockN);   // the 512-column tile of the gradient GEMMs
+  return 0;
+}
+
+// fp32 accumulator -> 16-bit weight gradient after the last token chunk
+int emu_convert_f32(const float* src, long long n, int fmt, void* dst) {
+  emu::launch_serial(8, 256, [&]() { convert_f32_kernel(src, n, fmt, static_cast<uint16_t*>(dst)); });
   return 0;
 }
 

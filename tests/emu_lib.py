@@ -66,7 +66,8 @@ def load():
         "emu_sce_forward": [P, P, I, I, I, I, LL, LL, P, LL, F, P, P, P, P, P],
         "emu_sce_sweep_dz": [P, P, I, I, I, I, LL, LL, P, LL, F, LL, P, P, P, P, P, LL, I],
         "emu_sweep_stats": [P, P, I, I, I, I, LL, LL, P, P, P, F, LL, P, P, P, P, P, P, P, LL, I, I, P, LL],
-        "emu_gemm_store_ex": [P, P, I, I, I, I, LL, LL, P, P, LL, P, LL, I, P, P, P],
+        "emu_gemm_store_ex": [P, P, I, I, I, I, LL, LL, P, P, LL, P, LL, I, P, P, P, I],
+        "emu_convert_f32": [P, LL, I, P],
         "emu_target_shift": [P, LL, P, LL, I, I, I, P, LL, LL, LL, I, P, F, P],
         "emu_shift_fill": [I, P],
         "emu_exp_store_fixup": [P, LL, I, I, I, P, LL, LL, LL, P, P, P, P, P, F, P, LL, P, P, LL],
@@ -382,7 +383,7 @@ class EmuLib(fake_lib.FakeLib):
                     self.emu.emu_gemm_store_ex(slab.data_ptr(), Wt.data_ptr(), prob.dtype, row_limit, h, v, ld_slab, v, None, None, 0,
                                                gi, h, gfmt, alpha.data_ptr() if exp_store else None,
                                                c[1].data_ptr() if (exp_store and smoothing) else None,
-                                               w_sum.data_ptr() if (exp_store and smoothing) else None)
+                                               w_sum.data_ptr() if (exp_store and smoothing) else None, 0)
                 if sharded and a.grad_input:
                     real_lib.AFTER_GRAD_INPUT_FN(a.after_grad_input)(a.exchange_user, a.grad_input + r0 * h * (4 if gfmt == 2 else 2),
                                                                      rows, r0)
@@ -396,15 +397,15 @@ class EmuLib(fake_lib.FakeLib):
                     if kk == 0:                                         # nothing accumulated: the kernel's k_blocks == 0 path
                         At, Bt, kk = torch.zeros(v, 8).to(tdt), torch.zeros(h, 8).to(tdt), 8
                     r1 = exp_store and smoothing and last
-                    out_ptr = a.grad_weight if (last and gfmt != 2) else None
-                    acc_out = dw_acc if (gfmt == 2 or not last) else None
-                    if gfmt == 2:
-                        acc_out = self._matrix(a.grad_weight, v, h, h, torch.float32)
-                    acc_in = None if first else (acc_out if gfmt == 2 else dw_acc)
-                    self.emu.emu_gemm_store_ex(At.data_ptr(), Bt.data_ptr(), prob.dtype, v, h, kk, kk, kk,
-                                               None if acc_in is None else acc_in.data_ptr(),
-                                               None if acc_out is None else acc_out.data_ptr(), h, out_ptr, h, prob.dtype,
-                                               None, prob.ce_weight if r1 else None, x_sum.data_ptr() if r1 else None)
+                    # one chunk: written once in the final dtype; several: first stores fp32, the others add, 16-bit converted at the end
+                    direct = len(chunks) == 1 and gfmt != 2
+                    acc_t = self._matrix(a.grad_weight, v, h, h, torch.float32) if gfmt == 2 else dw_acc
+                    self.emu.emu_gemm_store_ex(At.data_ptr(), Bt.data_ptr(), prob.dtype, v, h, kk, kk, kk, None,
+                                               None if direct else acc_t.data_ptr(), h, a.grad_weight if direct else None, h, prob.dtype,
+                                               None, prob.ce_weight if r1 else None, x_sum.data_ptr() if r1 else None,
+                                               int(not direct and not first))
+                    if last and not direct and gfmt != 2:
+                        self.emu.emu_convert_f32(dw_acc.data_ptr(), v * h, prob.dtype, a.grad_weight)
 
             if last and a.after_grad_weight:          # the library's order when a caller sums grad_weight over token shards
                 grad_weight_part()

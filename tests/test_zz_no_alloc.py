@@ -1,8 +1,10 @@
 """flce_b200_forward_stats_static: the forward-statistics sweep for callers that cannot allocate device memory
 (a host with a fixed memory plan, a latency-critical loop).  Its scratch is a 32 MiB array inside the library.
 Called through the C ABI and compared with flce_b200_forward_stats (caller-provided workspace) on the same
-inputs: the two run the same kernels on differently placed scratch, so the statistics must be identical.
-Two calls in a row with different shapes check that contents left behind by the first do not leak into the second.
+inputs: the two run the same kernels on differently placed scratch, so the statistics must be identical; the
+log-sum-exp they imply is also checked against the CPU oracle.  Two calls in a row with different shapes check that
+contents left behind by the first do not leak into the second.  "Allocates nothing" is checked two ways: torch's
+allocator counter, and the free device memory the CUDA runtime reports (which would see a cudaMalloc inside the library).
 This file is named to be collected last."""
 
 import ctypes as C
@@ -29,11 +31,29 @@ def _both(N, H, V, seed, **kw):
     ref = torch.full((_lib.ROWSTAT_PLANES, N), float("nan"), device="cuda")
     got = torch.full((_lib.ROWSTAT_PLANES, N), float("nan"), device="cuda")
     _lib.check(lib.flce_b200_forward_stats(C.byref(prep.problem), _ptr(ref), _ptr(ws), ws.numel(), _stream(x.device)))
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
     _lib.check(lib.flce_b200_forward_stats_static(C.byref(prep.problem), _ptr(got), _stream(x.device)))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
     assert torch.cuda.memory_allocated() == before
+    if _both.warm:       # (the very first call on a device may make the runtime load the kernel's module)
+        assert free_after == free_before, (free_before, free_after)
+    _both.warm = True
     _lib.check(lib.flce_b200_check_device_status(_stream(x.device)))
+    # the statistics against the oracle: lse = max + log(sum exp) per row, to 1e-5
+    from oracle.flce_oracle import flce_oracle
+
+    ora = flce_oracle(x.cpu(), w.cpu(), t.cpu(), label_smoothing=kw.get("label_smoothing", 0.0), softcap=kw.get("softcap"))
+    lse = (got[0] + torch.log(got[1])).double().cpu()
+    valid = (t != -100).cpu()          # (the oracle reports 0 on ignored rows)
+    err = ((lse - ora.lse).abs() / ora.lse.abs().clamp(min=1.0))[valid].max()
+    assert float(err) <= 1e-5, float(err)
     return ref, got, kw.get("want_argmax", False)
+
+
+_both.warm = False
 
 
 def _same(ref, got, with_argmax):
