@@ -74,6 +74,40 @@ __device__ __forceinline__ void ce_state_push(CeRowState& s, float v, float w, i
   }
 }
 
+// fold kVec consecutive in-range values at once: one running-max update and one rescale for the group instead of one per
+// element (half the exp2 work of ce_state_push)
+template <int kVec>
+__device__ __forceinline__ void ce_state_push_vec(CeRowState& s, const float (&v)[kVec], const float* w, int col0) {
+  float vmax = v[0];
+#pragma unroll
+  for (int j = 1; j < kVec; ++j) vmax = fmaxf(vmax, v[j]);
+  if (vmax > s.best) {  // strictly greater, and the first position inside the group: the lowest index wins ties
+    int idx = kVec - 1;
+#pragma unroll
+    for (int j = kVec - 2; j >= 0; --j) idx = (v[j] == vmax) ? j : idx;
+    s.best = vmax;
+    s.best_idx = col0 + idx;
+  }
+  if (w != nullptr) {
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) s.ss = fmaf(v[j], w[col0 + j], s.ss);
+  } else {
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) a += v[j];
+    s.ss += a;
+  }
+  const float m_new = fmaxf(s.m, vmax);
+  if (m_new != -INFINITY) {
+    const float ml2 = m_new * kLog2e;
+    float e = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) e += ex2_approx(fmaf(v[j], kLog2e, -ml2));
+    s.d = fmaf(s.d, ex2_approx((s.m - m_new) * kLog2e), e);
+    s.m = m_new;
+  }
+}
+
 // merge two partial states of the same row (either may be empty: m = -inf, d = 0)
 __device__ __forceinline__ void ce_state_merge(CeRowState& a, const CeRowState& b) {
   if (b.best > a.best || (b.best == a.best && b.best_idx < a.best_idx)) {
@@ -89,6 +123,7 @@ __device__ __forceinline__ void ce_state_merge(CeRowState& a, const CeRowState& 
 }
 
 constexpr int kCeThreads = 256;
+constexpr int kCeGradUnroll = 4;   // vectors per thread of ce_grad_kernel
 
 template <typename T, bool kVectorised>
 __global__ void __launch_bounds__(kCeThreads)
@@ -105,15 +140,27 @@ ce_stats_kernel(const T* logits, long long ld, int n_rows, int n_cols, const lon
   if constexpr (kVectorised) {
     const int n_vec = n_cols / kVec;
     tail_begin = n_vec * kVec;
-    for (int i = threadIdx.x; i < n_vec; i += kCeThreads) {
-      float v[kVec];
-      ce_load_vec<T>(x + i * kVec, v);
+    // four 16-byte loads per thread in flight before any of them is used: one CTA per row has to keep HBM busy
+    constexpr int kUnroll = 4;
+    for (int i0 = threadIdx.x; i0 < n_vec; i0 += kCeThreads * kUnroll) {
+      uint4 raw[kUnroll];
 #pragma unroll
-      for (int j = 0; j < kVec; ++j) {
-        const int col = i * kVec + j;
-        float s = v[j];
-        if (softcap > 0.f) s = softcap * tanh_accurate(s * inv_softcap);
-        ce_state_push(st, s, col_weight != nullptr ? col_weight[col] : 1.f, col);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int i = i0 + u * kCeThreads;
+        if (i < n_vec) raw[u] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(i) * kVec);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int i = i0 + u * kCeThreads;
+        if (i >= n_vec) break;
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+        float v[kVec];
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          v[j] = CeElem<T>::load(e + j);
+          if (softcap > 0.f) v[j] = softcap * tanh_accurate(v[j] * inv_softcap);
+        }
+        ce_state_push_vec<kVec>(st, v, col_weight, i * kVec);
       }
     }
   }
@@ -177,12 +224,10 @@ ce_grad_kernel(const T* logits, long long ld, T* grad, long long ld_grad, int n_
   const int row = blockIdx.x;   // rows on x: no 65535 limit
   if (row >= n_rows) return;
   constexpr int kVec = kVectorised ? CeElem<T>::kVec : 1;
-  const int col0 = (blockIdx.y * kCeThreads + threadIdx.x) * kVec;
-  if (col0 >= n_cols) return;
   const float l2 = lse[row] * kLog2e, a = c1[row], b = c2[row], c = c3[row];
   const long long t = target[row];
-  const T* x = logits + static_cast<size_t>(row) * ld + col0;
-  T* g = grad + static_cast<size_t>(row) * ld_grad + col0;
+  const T* xrow = logits + static_cast<size_t>(row) * ld;
+  T* grow = grad + static_cast<size_t>(row) * ld_grad;
   auto one = [&](float z, int col) {
     float s = z, chain = 1.f;
     if (softcap > 0.f) {
@@ -195,18 +240,35 @@ ce_grad_kernel(const T* logits, long long ld, T* grad, long long ld_grad, int n_
     if (static_cast<long long>(col) == t) v -= c;
     return v * chain;
   };
+  // a block covers kCeGradUnroll * kCeThreads vectors of one row; all of a thread's loads are issued before the math
+  const int base = blockIdx.y * (kCeThreads * kCeGradUnroll) * kVec + threadIdx.x * kVec;
   if constexpr (kVectorised) {
-    if (col0 + kVec <= n_cols) {
-      float v[CeElem<T>::kVec];
-      ce_load_vec<T>(x, v);
+    uint4 raw[kCeGradUnroll];
 #pragma unroll
-      for (int j = 0; j < CeElem<T>::kVec; ++j) v[j] = one(v[j], col0 + j);
-      ce_store_vec<T>(g, v);
-      return;
+    for (int u = 0; u < kCeGradUnroll; ++u) {
+      const int col0 = base + u * kCeThreads * kVec;
+      if (col0 + kVec <= n_cols) raw[u] = *reinterpret_cast<const uint4*>(xrow + col0);
     }
-    for (int j = 0; col0 + j < n_cols; ++j) CeElem<T>::store(g + j, one(CeElem<T>::load(x + j), col0 + j));
+#pragma unroll
+    for (int u = 0; u < kCeGradUnroll; ++u) {
+      const int col0 = base + u * kCeThreads * kVec;
+      if (col0 >= n_cols) break;
+      if (col0 + kVec <= n_cols) {
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+        float v[CeElem<T>::kVec];
+#pragma unroll
+        for (int j = 0; j < CeElem<T>::kVec; ++j) v[j] = one(CeElem<T>::load(e + j), col0 + j);
+        ce_store_vec<T>(grow + col0, v);
+      } else {
+        for (int j = 0; col0 + j < n_cols; ++j) CeElem<T>::store(grow + col0 + j, one(CeElem<T>::load(xrow + col0 + j), col0 + j));
+      }
+    }
   } else {
-    CeElem<T>::store(g, one(CeElem<T>::load(x), col0));
+#pragma unroll
+    for (int u = 0; u < kCeGradUnroll; ++u) {
+      const int col0 = base + u * kCeThreads;
+      if (col0 < n_cols) CeElem<T>::store(grow + col0, one(CeElem<T>::load(xrow + col0), col0));
+    }
   }
 }
 

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -35,12 +36,13 @@ static int fail(int code, const char* fmt, ...) {
   } while (0)
 
 // ------------------------------------------------------------------ process-wide options
-static long long g_raster_bytes = 32ll << 20;  // bytes of A tiles kept hot per raster group
-static int g_cta_pair = 1;                      // use CTA pairs (cta_group::2) for the FLCE GEMMs
-static int g_poll_sleep_ns = 0;                 // epilogue back-off while waiting for an accumulator
-static int g_l2_hints = 0;                      // 1: mark streamed operands evict-first and re-read ones evict-last
-static int g_n_group = 0;                       // n-fastest raster: n-tiles per group (0 = all)
-static int g_wide_tiles = 1;                    // 256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
+// (atomics: autograd calls backward from worker threads while another thread may still be setting options)
+static std::atomic<long long> g_raster_bytes{32ll << 20};  // bytes of A tiles kept hot per raster group
+static std::atomic<int> g_cta_pair{1};           // use CTA pairs (cta_group::2) for the FLCE GEMMs
+static std::atomic<int> g_poll_sleep_ns{0};      // epilogue back-off while waiting for an accumulator
+static std::atomic<int> g_l2_hints{0};           // 1: mark streamed operands evict-first and re-read ones evict-last
+static std::atomic<int> g_n_group{0};            // n-fastest raster: n-tiles per group (0 = all)
+static std::atomic<int> g_wide_tiles{1};         // 256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
 
 // ------------------------------------------------------------------ optional per-kernel timing
 // When enabled, every tensor-core launch is bracketed by a pair of CUDA events on the caller's stream;
@@ -55,7 +57,7 @@ static bool g_profile_on = false;
 static ProfileSlot g_profile[kMaxProfileSlots];
 static int g_profile_created = 0;  // events exist for slots [0, created)
 static int g_profile_used = 0;
-static long long g_kernel_launches = 0;
+static std::atomic<long long> g_kernel_launches{0};
 static std::mutex g_profile_mutex;
 
 static ProfileSlot* profile_begin(int kind, cudaStream_t stream) {
@@ -192,10 +194,11 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   }
   if (n_fastest) {
     shape.group_along_m = 0;
-    shape.group = (g_n_group > 0 && g_n_group < shape.n_tiles) ? g_n_group : shape.n_tiles;
+    const int n_group = g_n_group.load();
+    shape.group = (n_group > 0 && n_group < shape.n_tiles) ? n_group : shape.n_tiles;
   } else {
     shape.group_along_m = 1;
-    long long g = g_raster_bytes / (raster_row_bytes > 0 ? raster_row_bytes : 1);
+    long long g = g_raster_bytes.load() / (raster_row_bytes > 0 ? raster_row_bytes : 1);
     if (g < 1) g = 1;
     if (g > shape.m_tiles) g = shape.m_tiles;
     shape.group = static_cast<int>(g);
@@ -206,7 +209,15 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   if (units < 1) units = 1;
   if (units > tiles) units = tiles;
   auto kernel = gemm_tcgen05_kernel<kCtas, kAMajor, kBMajor, Epi, kNSub>;
-  FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  {  // once per instantiation and device
+    static std::atomic<bool> smem_set[64];
+    int ordinal = 0;
+    FLCE_CUDA(cudaGetDevice(&ordinal));
+    if (!smem_set[ordinal & 63].load(std::memory_order_acquire)) {
+      FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      smem_set[ordinal & 63].store(true, std::memory_order_release);
+    }
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(units * kCtas), 1, 1);
   cfg.blockDim = dim3(kNumThreads, 1, 1);
@@ -422,7 +433,8 @@ static void launch_ce_grad(const flce_ce_problem_t* p, void* grad, long long ld_
   const long long* tgt = reinterpret_cast<const long long*>(p->target);
   const bool vec = ce_rows_vectorisable(p->logits, p->ld, p->dtype) && ce_rows_vectorisable(grad, ld_grad, p->dtype);
   const long long per_thread = vec ? CeElem<T>::kVec : 1;
-  dim3 grid(static_cast<unsigned>(p->n_rows), static_cast<unsigned>(ceil_div(ceil_div(p->vocab, per_thread), kCeThreads)), 1);
+  dim3 grid(static_cast<unsigned>(p->n_rows),
+            static_cast<unsigned>(ceil_div(ceil_div(p->vocab, per_thread), kCeThreads * kCeGradUnroll)), 1);
   if (vec)
     ce_grad_kernel<T, true><<<grid, kCeThreads, 0, stream>>>(x, p->ld, static_cast<T*>(grad), ld_grad, static_cast<int>(p->n_rows),
                                                             static_cast<int>(p->vocab), tgt, p->ce_weight, p->softcap, inv, lse,

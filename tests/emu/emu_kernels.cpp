@@ -75,7 +75,7 @@ void run_ce_grad(const CeProblem& p, void* grad, long long ld_grad, const float*
   const bool vec = vectorisable(p.logits, p.ld, p.dtype) && vectorisable(grad, ld_grad, p.dtype);
   const long long per_thread = vec ? CeElem<T>::kVec : 1;
   const emu::Dim3 grid(static_cast<unsigned>(p.n_rows),
-                       static_cast<unsigned>(ceil_div(ceil_div(p.vocab, per_thread), kCeThreads)), 1);
+                       static_cast<unsigned>(ceil_div(ceil_div(p.vocab, per_thread), kCeThreads * kCeGradUnroll)), 1);
   emu::launch_serial(grid, emu::Dim3(kCeThreads), [&]() {
     if (vec)
       ce_grad_kernel<T, true>(x, p.ld, static_cast<T*>(grad), ld_grad, static_cast<int>(p.n_rows),
