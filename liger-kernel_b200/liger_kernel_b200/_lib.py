@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libflce_b200.so")
+# LIGER_B200_LIB selects another build of the same library (e.g. the cycle-accounting build, `build.py --trace`)
+LIB_PATH = os.environ.get("LIGER_B200_LIB") or os.path.join(_HERE, "libflce_b200.so")
 
 FLCE_BF16, FLCE_FP16, FLCE_FP32 = 0, 1, 2
 FLCE_MEAN, FLCE_SUM, FLCE_NONE = 0, 1, 2
