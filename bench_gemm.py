@@ -35,12 +35,19 @@ def main():
     ap.add_argument("--trace", action="store_true")
     ap.add_argument("--wide", type=int, default=None, help="1: 256x512 tiles (default of the library), 0: 256x256")
     ap.add_argument("--iters", type=int, default=8)
+    ap.add_argument("--seconds", type=float, default=0.0,
+                    help="time each kernel over a loop this long instead of --iters launches: the power cap settles (about a second) "
+                         "and the SM clock sampled meanwhile is printed, so the figures are the sustained ones")
+    ap.add_argument("--out", default="bf16", choices=["bf16", "fp32"], help="dtype of D (fp32: the first chunk of a weight gradient)")
     args = ap.parse_args()
     if args.trace:
         os.environ["LIGER_B200_LIB"] = os.path.join(PKG, "liger_kernel_b200", "libflce_b200_trace.so")
     sys.path.insert(0, PKG)
     import numpy as np
     import torch
+
+    sys.path.insert(0, ROOT)
+    from bench import ClockSampler
 
     from liger_kernel_b200 import _lib
 
@@ -66,28 +73,43 @@ def main():
             torch.manual_seed(0)
             A = (torch.randn((K, M) if a_mn else (M, K), device="cuda") * 0.1).bfloat16()
             B = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.1).bfloat16()
-            D = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+            D = torch.empty((M, N), device="cuda", dtype=torch.bfloat16 if args.out == "bf16" else torch.float32)
+            d_code = 0 if args.out == "bf16" else 2
 
             def ours():
                 _lib.check(lib.flce_b200_gemm(C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), C.c_void_p(D.data_ptr()), M, N, K,
-                                              A.stride(0), B.stride(0), D.stride(0), 0, 0, a_mn, b_mn, 1, st))
+                                              A.stride(0), B.stride(0), D.stride(0), 0, d_code, a_mn, b_mn, 1, st))
+
+            Dc = D if args.out == "bf16" else torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
 
             def cublas():
-                torch.matmul(A.t() if a_mn else A, B if b_mn else B.t(), out=D)
+                torch.matmul(A.t() if a_mn else A, B if b_mn else B.t(), out=Dc)
 
-            res = {}
+            res, clk = {}, {}
             for tag, fn in (("ours", ours), ("cublas", cublas)):
                 for _ in range(3):
                     fn()
                 torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(args.iters):
+                iters = args.iters
+                if args.seconds > 0:          # calibrate the launch count for the requested duration
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
                     fn()
-                e1.record()
-                torch.cuda.synchronize()
-                res[tag] = 2.0 * M * N * K / (e0.elapsed_time(e1) / args.iters) / 1e9
+                    e1.record()
+                    torch.cuda.synchronize()
+                    iters = max(4, int(args.seconds * 1e3 / e0.elapsed_time(e1)))
+                with ClockSampler(0) as sampler:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(iters):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                res[tag] = 2.0 * M * N * K / (e0.elapsed_time(e1) / iters) / 1e9
+                clk[tag] = sampler.summary()["sm_mhz"] if args.seconds > 0 else None
             line = f"{name} {M}x{N}x{K}: ours {res['ours']:.0f} TFLOP/s, cuBLAS {res['cublas']:.0f}, ratio {res['ours'] / res['cublas']:.3f}"
+            if args.seconds > 0:
+                line += f"  (SM clock under load: ours {clk['ours']} MHz, cuBLAS {clk['cublas']} MHz)"
             if args.trace:
                 ours()
                 torch.cuda.synchronize()

@@ -133,6 +133,9 @@ class _ScaledCrossEntropy(torch.autograd.Function):
         _validate_inputs(hidden_states, vocab_weights, input_ids)
         _validate_temperature(temperature)
         _fl._require_cuda(hidden_states)
+        # backward recomputes the logits from the operands: remember their versions so that an in-place change in
+        # between is reported (what ctx.save_for_backward would do) instead of mixing new logits with the old lse
+        ctx.sce_operands = ((hidden_states, hidden_states._version), (vocab_weights, vocab_weights._version))
         if MODE == "fused" and hidden_states.dtype in (torch.bfloat16, torch.float16):
             return _fused_forward(ctx, hidden_states, vocab_weights, input_ids, temperature, ignore_index, return_entropy)
         dev, dtype = hidden_states.device, hidden_states.dtype
@@ -162,6 +165,11 @@ class _ScaledCrossEntropy(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_nll, grad_entropy=None):
+        for tensor, version in ctx.sce_operands:
+            if tensor._version != version:
+                raise RuntimeError("one of the variables needed for gradient computation has been modified by an inplace "
+                                   f"operation: a {tuple(tensor.shape)} operand of the fused linear scaled cross-entropy is at "
+                                   f"version {tensor._version}, expected version {version}")
         if ctx.sce[0] == "fused":
             return _fused_backward(ctx, grad_nll, grad_entropy)
         head, target, lse, entropy, temperature, ignore_index, chunk_rows = ctx.sce
