@@ -457,7 +457,11 @@ def run_ours(args, spec, rank, world, local_rank):
     if world > 1:
         # the all-reduce of grad_weight runs beside the last grad_input GEMM, which leaves it 20 SMs
         # (liger_kernel_b200.sharded.RESERVE_SMS_FOR_COLLECTIVE): keep NCCL's kernels within that
-        os.environ.setdefault("NCCL_MAX_CTAS", "16")
+        import liger_kernel_b200.sharded as sharded_mod
+        if args.comm_overlap is not None:
+            sharded_mod.OVERLAP_COLLECTIVES = bool(args.comm_overlap)
+        if sharded_mod.OVERLAP_COLLECTIVES:
+            os.environ.setdefault("NCCL_MAX_CTAS", "16")
         import datetime
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     if args.cta_pair is not None:
@@ -535,6 +539,9 @@ def run_ours(args, spec, rank, world, local_rank):
     torch.cuda.reset_peak_memory_stats()
     launches0 = _lib.lib.flce_b200_kernel_launches()
     _lib.profile_enable(True)
+    import liger_kernel_b200.sharded as sharded_timing
+    if world > 1:
+        sharded_timing.COLLECTIVE_EVENTS = []
     barrier()
     with ClockSampler(local_rank) as clocks:
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
@@ -549,6 +556,15 @@ def run_ours(args, spec, rank, world, local_rank):
     step_quantiles = {f"p{q}": per_step[min(len(per_step) - 1, int(q / 100 * len(per_step)))] for q in (20, 50, 80)}
     prof = _lib.profile_read(reset=True)
     _lib.profile_enable(False)
+    collective_ms = None
+    if world > 1:
+        collective_ms = {}
+        for name, a, b in sharded_timing.COLLECTIVE_EVENTS:
+            collective_ms[name] = collective_ms.get(name, 0.0) + a.elapsed_time(b) / args.steps
+        sharded_timing.COLLECTIVE_EVENTS = None
+        collective_ms = {name: max_over_ranks(v) for name, v in sorted(collective_ms.items())}
+        kernel_sum = sum(v[0] for v in prof.values()) / args.steps
+        rank_kernel_ms = {"max": max_over_ranks(kernel_sum), "min": -max_over_ranks(-kernel_sum)}
     launches = _lib.lib.flce_b200_kernel_launches() - launches0
     peak_mem = torch.cuda.max_memory_allocated()
     clock_info = clocks.summary()
@@ -648,6 +664,9 @@ def run_ours(args, spec, rank, world, local_rank):
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * 2 + t_host.numel() * 8, "d2h_bytes_per_step": 4},
         "global_tokens_per_step": tokens,
+        "collective_ms_max_over_ranks": collective_ms,
+        "rank_kernel_ms": rank_kernel_ms if world > 1 else None,
+        "comm_overlap": (sharded_timing.OVERLAP_COLLECTIVES if world > 1 else None),
         "gpu_launches": int(launches),
         "peak_mem_gb": peak_mem / 1e9,
         "ms_per_step_quantiles": step_quantiles,
@@ -714,6 +733,9 @@ def main():
     ap.add_argument("--store", default=None, choices=["auto", "logits", "exp"], help="what the single-sweep mode keeps of a chunk")
     ap.add_argument("--wide-tiles", type=int, default=None, dest="wide_tiles")
     ap.add_argument("--poll-sleep-ns", type=int, default=None, dest="poll_sleep_ns")
+    ap.add_argument("--comm-overlap", type=int, default=None, dest="comm_overlap",
+                    help="multi-GPU: 1 = start the big collective beside the GEMM that follows (side stream, SMs reserved, NCCL "
+                         "capped at 16 CTAs), 0 = issue it after the sweep with every SM to itself")
     ap.add_argument("--chunk-gib", type=float, default=None, dest="chunk_gib",
                     help="bytes (GiB) of the bounded 16-bit copy of a token chunk in the single-sweep mode (default 2.5)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -3,6 +3,12 @@
 #pragma once
 
 #include "simt_common.cuh"
+#ifdef FLCE_HOST_EMULATION
+struct CUtensorMap_st;
+typedef struct CUtensorMap_st CUtensorMap;   // the host emulation never dereferences one
+#else
+#include "ptx_sm100.cuh"
+#endif
 
 namespace flce {
 
@@ -45,6 +51,7 @@ constexpr float kExpStoreRedoLimit = 50.f;
 // branch around a fully unrolled, branch-free pass over the 32 values.
 // =====================================================================================
 struct StatsEpilogue {
+  static constexpr bool kDeepPrefetch = false;
   struct Params {
     const long long* target;  // [M] global class ids
     const float* bias;        // [n_cols] or null
@@ -98,7 +105,7 @@ struct StatsEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/, const CUtensorMap* /*map_d*/) {
     float s[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(acc[j]);
@@ -225,6 +232,7 @@ struct StatsEpilogue {
 // class weight of the target, token scaling, upstream gradient, ignored rows = 0).
 // =====================================================================================
 struct DzEpilogue {
+  static constexpr bool kDeepPrefetch = false;
   struct Params {
     const long long* target;
     const float* bias;
@@ -263,7 +271,7 @@ struct DzEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/, const CUtensorMap* /*map_d*/) {
     if (!row_ok) return;
     float g[32];
 #pragma unroll
@@ -344,6 +352,7 @@ struct DzEpilogue {
 // which is d(nll * g_nll + entropy * g_ent) / dz.
 // =====================================================================================
 struct EntropyStatsEpilogue {
+  static constexpr bool kDeepPrefetch = false;
   struct Params {
     const long long* target;  // [M] class ids
     float scale;              // 1 / temperature
@@ -373,7 +382,7 @@ struct EntropyStatsEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/, const CUtensorMap* /*map_d*/) {
     float s[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(acc[j]) * p.scale;
@@ -422,6 +431,7 @@ struct EntropyStatsEpilogue {
 };
 
 struct ScaledDzEpilogue {
+  static constexpr bool kDeepPrefetch = false;
   struct Params {
     const long long* target;
     long long ignore_index;
@@ -464,7 +474,7 @@ struct ScaledDzEpilogue {
     }
   }
 
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* /*stage*/, const CUtensorMap* /*map_d*/) {
     if (!row_ok) return;
     float g[32];
 #pragma unroll
@@ -500,6 +510,7 @@ struct ScaledDzEpilogue {
 //                                                                  a rank-1 matrix, never formed)
 // =====================================================================================
 struct StoreEpilogue {
+  static constexpr bool kDeepPrefetch = true;
   struct Params {
     int m_rows, n_cols;
     const float* acc_in;
@@ -514,15 +525,26 @@ struct StoreEpilogue {
     // 1: add into acc_out with vector reductions at L2 (no read in this kernel, nothing to wait for); acc_in must be null.
     // Every element is owned by one thread of one launch, so the sum over launches keeps the stream's order.
     int acc_add;
+    // 1 (set by the launcher when exactly one of out / acc_out is written and nothing is read back): each 32 x 32 patch
+    // leaves through a TMA store (or TMA add, with acc_add) from the warp's shared-memory stage, described by the
+    // kernel's output tensor map; the warp only writes shared memory and issues one bulk copy per patch.
+    int bulk;
   };
 
-  int row;
+  int row, flip;
   bool row_ok;
   float scale, r1;
 
   __device__ __forceinline__ void begin(const Params& p, int row_, int, int, bool ok) {
     row = row_;
     row_ok = ok;
+    flip = 0;
+#ifndef FLCE_HOST_EMULATION
+    if (p.bulk) {   // both stage buffers are free again before this tile's first patch (tiles may end on either one)
+      if ((threadIdx.x & 31) == 0) bulk_wait_group_read<0>();
+      __syncwarp();
+    }
+#endif
     scale = 1.f;
     r1 = 0.f;
     if (ok) {
@@ -536,7 +558,8 @@ struct StoreEpilogue {
   // more than the main loop of a short-K tile saves.  So the 32 x 32 patch goes through the warp's shared-memory
   // stage: afterwards 8 lanes cover 32 consecutive columns of one row, 4 rows per instruction, and every global access
   // is a whole 128-byte (fp32) or 64-byte (16-bit) row segment.
-  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* stage) {
+  __device__ __forceinline__ void chunk(const Params& p, const uint32_t (&acc)[32], int col, float* stage,
+                                        const CUtensorMap* map_d) {
     const int lane = threadIdx.x & 31;
     float v[32];
 #pragma unroll
@@ -549,6 +572,52 @@ struct StoreEpilogue {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = fmaf(-r1, __ldg(p.r1_col + min(col + j, p.n_cols - 1)), v[j]);
     }
+    if (p.bulk) {
+      void* dst_base = p.acc_out != nullptr ? static_cast<void*>(p.acc_out) : p.out;
+      const long long ld = p.acc_out != nullptr ? p.ld_acc : p.ld_out;
+      const int fmt = p.acc_out != nullptr ? static_cast<int>(kOutFp32) : p.out_fmt;
+#ifdef FLCE_HOST_EMULATION
+      // what the bulk copy does, element by element: the patch clipped to the output's extents, stored or added
+      (void)stage;
+      (void)map_d;
+      if (row < p.m_rows) {
+        for (int j = 0; j < 32 && col + j < p.n_cols; ++j) {
+          const size_t at = static_cast<size_t>(row) * ld + col + j;
+          if (fmt == kOutFp32) {
+            float* d = static_cast<float*>(dst_base) + at;
+            *d = p.acc_add ? *d + v[j] : v[j];
+          } else {
+            static_cast<uint16_t*>(dst_base)[at] = static_cast<uint16_t>(pack2(v[j], 0.f, fmt) & 0xffffu);
+          }
+        }
+      }
+#else
+      (void)dst_base;
+      (void)ld;
+      uint8_t* buf = reinterpret_cast<uint8_t*>(stage) + (flip ? 4096 : 0);
+      flip ^= 1;
+      if (lane == 0) bulk_wait_group_read<1>();   // the copy that last read this buffer (two patches ago) is done with it
+      __syncwarp();
+      if (fmt == kOutFp32) {
+        // 128-byte rows under the 128-byte swizzle of the tensor map: 16-byte chunk q of row r sits at position q ^ (r & 7)
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+              make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        store32_16bit(reinterpret_cast<uint4*>(buf + lane * 64), v, fmt);   // dense 64-byte rows, no swizzle
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      const int row0 = row - lane;
+      if (lane == 0 && row0 < p.m_rows) {
+        if (p.acc_add) tma_reduce_add_2d(map_d, smem_u32(buf), col, row0);
+        else tma_store_2d(map_d, smem_u32(buf), col, row0);
+        bulk_commit_group();
+      }
+#endif
+      return;
+    }
     float4* mine = reinterpret_cast<float4*>(stage + lane * 36);
 #pragma unroll
     for (int q = 0; q < 8; ++q) mine[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -557,42 +626,46 @@ struct StoreEpilogue {
     const int c4 = (lane & 7) * 4;               // this lane's four columns inside the patch
     const bool col_ok = col + c4 < p.n_cols;     // n_cols is a multiple of 8: a group of four is in or out as a whole
     const int r_first = lane >> 3;
-    // all partial-sum loads of the patch first (independent, in flight together), then the arithmetic and the stores
-    float4 part[8];
-    if (p.acc_in != nullptr) {
+    // partial-sum loads four at a time (independent, in flight together), then the arithmetic and the stores: left in
+    // program order they would each wait for the store before them (acc_in and acc_out may be the same buffer)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int grow = row0 + i * 4 + r_first;
-        part[i] = (grow < p.m_rows && col_ok)
-                      ? *reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(grow) * p.ld_acc + col + c4)
-                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int half = 0; half < 2; ++half) {
+      float4 part[4];
+      if (p.acc_in != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int grow = row0 + (half * 4 + i) * 4 + r_first;
+          part[i] = (grow < p.m_rows && col_ok)
+                        ? *reinterpret_cast<const float4*>(p.acc_in + static_cast<size_t>(grow) * p.ld_acc + col + c4)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
-    }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = i * 4 + r_first;
-      const int grow = row0 + r;
-      if (grow < p.m_rows && col_ok) {
-        float4 a = *reinterpret_cast<const float4*>(stage + r * 36 + c4);
-        if (p.acc_in != nullptr) {
-          a.x += part[i].x;
-          a.y += part[i].y;
-          a.z += part[i].z;
-          a.w += part[i].w;
-        }
-        if (p.acc_out != nullptr) {
-          float4* dst = reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(grow) * p.ld_acc + col + c4);
-          if (p.acc_add) vector_add_f32x4(dst, a);
-          else *dst = a;
-        }
-        if (p.out != nullptr) {
-          if (p.out_fmt == kOutFp32) {
-            *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = a;
-          } else {
-            uint2 o;
-            o.x = pack2(a.x, a.y, p.out_fmt);
-            o.y = pack2(a.z, a.w, p.out_fmt);
-            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = o;
+      for (int i = 0; i < 4; ++i) {
+        const int r = (half * 4 + i) * 4 + r_first;
+        const int grow = row0 + r;
+        if (grow < p.m_rows && col_ok) {
+          float4 a = *reinterpret_cast<const float4*>(stage + r * 36 + c4);
+          if (p.acc_in != nullptr) {
+            a.x += part[i].x;
+            a.y += part[i].y;
+            a.z += part[i].z;
+            a.w += part[i].w;
+          }
+          if (p.acc_out != nullptr) {
+            float4* dst = reinterpret_cast<float4*>(p.acc_out + static_cast<size_t>(grow) * p.ld_acc + col + c4);
+            if (p.acc_add) vector_add_f32x4(dst, a);
+            else *dst = a;
+          }
+          if (p.out != nullptr) {
+            if (p.out_fmt == kOutFp32) {
+              *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = a;
+            } else {
+              uint2 o;
+              o.x = pack2(a.x, a.y, p.out_fmt);
+              o.y = pack2(a.z, a.w, p.out_fmt);
+              *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(grow) * p.ld_out + col + c4) = o;
+            }
           }
         }
       }

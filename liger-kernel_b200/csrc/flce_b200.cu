@@ -42,6 +42,7 @@ static std::atomic<int> g_cta_pair{1};           // use CTA pairs (cta_group::2)
 static std::atomic<int> g_poll_sleep_ns{0};      // epilogue back-off while waiting for an accumulator
 static std::atomic<int> g_l2_hints{0};           // 1: mark streamed operands evict-first and re-read ones evict-last
 static std::atomic<int> g_n_group{0};            // n-fastest raster: n-tiles per group (0 = all)
+static std::atomic<int> g_bulk_store{1};         // store epilogue through TMA stores / adds where it applies
 static std::atomic<int> g_wide_tiles{1};         // 256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
 
 // ------------------------------------------------------------------ optional per-kernel timing
@@ -145,6 +146,25 @@ static int make_map(CUtensorMap* map, const void* base, int dtype, long long inn
   return FLCE_OK;
 }
 
+// 2-D tensor map for TMA stores of 32 x 32 patches of a row-major output (fp32: 128-byte swizzle in shared memory;
+// 16-bit: dense 64-byte rows).  `fmt` is an OutFormat.
+static int make_store_map(CUtensorMap* map, void* base, int fmt, long long cols, long long rows, long long pitch) {
+  const int esize = fmt == kOutFp32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch * esize) % 16 != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "output base %p / pitch %lld elements is not 16-byte aligned", base, pitch);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch) * esize};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = fmt == kOutFp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : (fmt == kOutBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUresult r = g_encode(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        fmt == kOutFp32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FLCE_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
+  return FLCE_OK;
+}
+
 // An operand of D = A.B^T as the main loop wants it.
 struct Operand {
   const void* base;
@@ -168,11 +188,23 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
                             const typename Epi::Params& ep, cudaStream_t stream, const int* active_rows, int active_role,
                             int active_base, const int* gate, int reserve_sms) {
   using Cfg = StageCfg<kCtas, kNSub>;
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_d;
   int rc = operand_map(&map_a, a, dtype, kBlockM);
   if (rc != FLCE_OK) return rc;
   rc = operand_map(&map_b, b, dtype, kBlockN / kCtas);
   if (rc != FLCE_OK) return rc;
+  map_d = map_a;   // unused unless the epilogue stores through TMA
+  typename Epi::Params ep_launch = ep;
+  if constexpr (std::is_same<Epi, StoreEpilogue>::value) {
+    // one destination, nothing read back: the patches leave as TMA stores / adds
+    const bool one_dst = (ep.out != nullptr) != (ep.acc_out != nullptr);
+    ep_launch.bulk = (g_bulk_store.load() != 0 && ep.acc_in == nullptr && one_dst) ? 1 : 0;
+    if (ep_launch.bulk) {
+      if (ep.acc_out != nullptr) rc = make_store_map(&map_d, ep.acc_out, kOutFp32, ep.n_cols, ep.m_rows, ep.ld_acc);
+      else rc = make_store_map(&map_d, ep.out, ep.out_fmt, ep.n_cols, ep.m_rows, ep.ld_out);
+      if (rc != FLCE_OK) return rc;
+    }
+  }
   GemmShape shape;
   shape.M = static_cast<int>(M);
   shape.N = static_cast<int>(N);
@@ -232,7 +264,7 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   cfg.numAttrs = 1;
   const int fmt = (dtype == FLCE_BF16) ? 1 : 0;
   ProfileSlot* slot = profile_begin(kind, stream);
-  const cudaError_t launched = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, shape, fmt, ep, dev.status);
+  const cudaError_t launched = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_d, shape, fmt, ep_launch, dev.status);
   profile_end(slot, stream);
   if (launched != cudaSuccess) return fail(FLCE_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(launched));
   ++g_kernel_launches;
@@ -532,6 +564,10 @@ int flce_b200_set_option(const char* name, int64_t value) {
   }
   if (strcmp(name, "l2_hints") == 0) {
     g_l2_hints = value != 0;
+    return FLCE_OK;
+  }
+  if (strcmp(name, "bulk_store") == 0) {
+    g_bulk_store = value != 0;
     return FLCE_OK;
   }
   if (strcmp(name, "wide_tiles") == 0) {

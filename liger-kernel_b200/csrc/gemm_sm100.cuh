@@ -62,26 +62,29 @@ struct StageCfg {
   static constexpr int kStages = (kNSub == 2) ? 4 : ((kCtas == 1) ? 4 : 6);
   static constexpr int kAccStages = (kNSub == 2) ? 1 : 2;            // accumulators in flight (tensor memory: 512 columns)
   static constexpr int kRingBytes = kStages * kStageBytes;
-  // per epilogue warp, a 32 x 32 fp32 patch (pitch 36 floats) for epilogues that turn their row-per-thread registers
-  // into row-contiguous global accesses
-  static constexpr int kEpiStageFloats = 32 * 36;
+  // per epilogue warp, 8 KiB right behind the ring (so 1 KiB-aligned): two dense 32 x 32 fp32 patches that leave as TMA
+  // stores, or one 32 x 36-float patch for the epilogue form that reads partial sums back
+  static constexpr int kEpiStageFloats = 2048;
   static constexpr int kEpiStageBytes = kNumEpilogueWarps * kEpiStageFloats * 4;
-  // ring + barriers + bookkeeping + epilogue staging, plus 1 KiB so the ring can be aligned to the swizzle atom
-  static constexpr int kSmemBytes = kRingBytes + 1024 + 256 + kEpiStageBytes;
+  // ring + epilogue staging + barriers / bookkeeping, plus 1 KiB so the ring can be aligned to the swizzle atom
+  static constexpr int kSmemBytes = kRingBytes + kEpiStageBytes + 256 + 1024;
 };
 
 // Epilogue concept:
 //   struct Epi {
 //     struct Params {...};                                  // trivially copyable, passed by value
 //     __device__ void begin(const Params&, int row, int col0, int n_tile, bool row_ok);
-//     __device__ void chunk(const Params&, const uint32_t (&acc)[32], int col, float* stage);   // fp32 bit patterns;
-//                         // stage: this warp's 32 x 36 float patch of shared memory; called by all 32 lanes together
+//     static constexpr bool kDeepPrefetch;                  // keep two tensor-memory loads in flight (light epilogues)
+//     __device__ void chunk(const Params&, const uint32_t (&acc)[32], int col, float* stage, const CUtensorMap* map_d);
+//                         // fp32 bit patterns; stage: this warp's 8 KiB of shared memory; map_d: tensor map of the output
+//                         // (valid when the launcher set Params::bulk); called by all 32 lanes together
 //     __device__ void end(const Params&);
 //   };
 template <int kCtas, int kAMajor, int kBMajor, class Epi, int kNSub = 1>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmShape shape_arg, const int ab_format, const typename Epi::Params ep, int* status) {
+                    const __grid_constant__ CUtensorMap map_d, const GemmShape shape_arg, const int ab_format,
+                    const typename Epi::Params ep, int* status) {
   using Cfg = StageCfg<kCtas, kNSub>;
   constexpr int kTileN = kBlockN * kNSub;          // output columns per tile
   constexpr int kAccStages = Cfg::kAccStages;
@@ -95,14 +98,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring_a = smem;
   uint8_t* ring_b = smem + kStages * Cfg::kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes + Cfg::kEpiStageBytes);
   uint64_t* full_bar = bars;                    // [kStages]  TMA bytes landed
   uint64_t* empty_bar = bars + kStages;         // [kStages]  MMAs that read the stage retired
   uint64_t* tmem_full_bar = bars + 2 * kStages; // [2]        accumulator complete
   uint64_t* tmem_empty_bar = tmem_full_bar + 2; // [2]        accumulator drained
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  float* epi_stage = reinterpret_cast<float*>(smem + Cfg::kRingBytes + 256);
+  float* epi_stage = reinterpret_cast<float*>(smem + Cfg::kRingBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -307,8 +310,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       Epi epi;
       epi.begin(ep, row, col0, nt, row < shape.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kBlockN);
-      // two register buffers: the load of the next 32 columns is in flight while the current ones are consumed
       const int n_chunks = min(kTileN / 32, (shape.N - col0 + 31) / 32);   // uniform across the CTA
+      if constexpr (Epi::kDeepPrefetch) {
+        // light epilogues are bound by the latency of the tensor-memory loads: two 32-column loads are in flight while
+        // two are consumed (four register buffers)
+        uint32_t a0[32], a1[32], b0[32], b1[32];
+        tmem_ld_32x32(taddr, a0);
+        if (1 < n_chunks) tmem_ld_32x32(taddr + 32u, a1);
+#pragma unroll 1
+        for (int c = 0; c < n_chunks; c += 4) {
+          tmem_ld_wait();
+          tmem_ld_fence(a0);
+          tmem_ld_fence(a1);
+          if (c + 2 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 2) * 32), b0);
+          if (c + 3 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 3) * 32), b1);
+          if (shape.k_blocks == 0) {   // nothing was accumulated (no active rows): the product is zero
+#pragma unroll
+            for (int j = 0; j < 32; ++j) a0[j] = a1[j] = 0u;
+          }
+          epi.chunk(ep, a0, col0 + c * 32, stage, &map_d);
+          if (c + 1 < n_chunks) epi.chunk(ep, a1, col0 + (c + 1) * 32, stage, &map_d);
+          if (c + 2 < n_chunks) {
+            tmem_ld_wait();
+            tmem_ld_fence(b0);
+            tmem_ld_fence(b1);
+            if (c + 4 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 4) * 32), a0);
+            if (c + 5 < n_chunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 5) * 32), a1);
+            if (shape.k_blocks == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) b0[j] = b1[j] = 0u;
+            }
+            epi.chunk(ep, b0, col0 + (c + 2) * 32, stage, &map_d);
+            if (c + 3 < n_chunks) epi.chunk(ep, b1, col0 + (c + 3) * 32, stage, &map_d);
+          }
+        }
+      } else {
+      // two register buffers: the load of the next 32 columns is in flight while the current ones are consumed
       uint32_t va[32], vb[32];
       tmem_ld_32x32(taddr, va);
 #pragma unroll 1
@@ -320,7 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) va[j] = 0u;
         }
-        epi.chunk(ep, va, col0 + c * 32, stage);
+        epi.chunk(ep, va, col0 + c * 32, stage, &map_d);
         if (c + 1 < n_chunks) {
           tmem_ld_wait();
           tmem_ld_fence(vb);
@@ -329,8 +366,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) vb[j] = 0u;
           }
-          epi.chunk(ep, vb, col0 + (c + 1) * 32, stage);
+          epi.chunk(ep, vb, col0 + (c + 1) * 32, stage, &map_d);
         }
+      }
       }
       epi.end(ep);
       tcgen05_fence_before();
@@ -340,6 +378,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         else mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]), 0);
       }
       FLCE_TRACE_ADD(busy, t_b);
+    }
+    if constexpr (Epi::kDeepPrefetch) {
+      if (lane == 0) bulk_wait_group_all();   // this warp's TMA stores have left shared memory and landed
     }
     if (threadIdx.x == 64) {
       FLCE_TRACE_STORE(2, wait_tmem_full);

@@ -25,6 +25,7 @@ on CPU ranks (gloo) with a stand-in backend in the tests; the default backend is
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -123,6 +124,9 @@ class _timed:
 
 # SMs the last grad_input GEMM of a token-sharded call leaves to the grad_weight all-reduce that runs beside it
 RESERVE_SMS_FOR_COLLECTIVE = 20
+# 1: start a sharded call's big collective beside the GEMM that follows (side stream, SMs reserved); 0: issue it on the
+# compute stream once the sweep is enqueued, with every SM to itself (LIGER_B200_SHARDED_OVERLAP)
+OVERLAP_COLLECTIVES = os.environ.get("LIGER_B200_SHARDED_OVERLAP", "1") == "1"
 
 
 class _TokenSharded(torch.autograd.Function):
@@ -150,7 +154,7 @@ class _TokenSharded(torch.autograd.Function):
             pending = []
             hook = None
             comm = None
-            if world > 1 and needs[1]:
+            if world > 1 and needs[1] and OVERLAP_COLLECTIVES:
                 comm = torch.cuda.Stream(device=prep.device) if prep.device.type == "cuda" else None
 
                 def hook(gw):
@@ -167,7 +171,10 @@ class _TokenSharded(torch.autograd.Function):
                         pending.append(work)
 
             out, gx, gw = backend.single_sweep(prep, norm, needs[0], needs[1], after_grad_weight=hook,
-                                               reserve_sms=RESERVE_SMS_FOR_COLLECTIVE if hook is not None else 0)
+                                               reserve_sms=RESERVE_SMS_FOR_COLLECTIVE if comm is not None else 0)
+            if world > 1 and needs[1] and hook is None:
+                with _timed("all_reduce grad_weight (after the sweep)"):
+                    dist.all_reduce(gw, group=group)
             gx = prep.rows_to_token_order(gx)
             ctx.stored = (gx, gw, pending)
             ctx.hidden = prep.hidden
@@ -260,7 +267,7 @@ class _VocabSharded(torch.autograd.Function):
                                    vocab_offset=vocab_start, want_argmax=True, allow_compact=True)
             norm = backend.count(prep)          # targets are replicated: identical on every rank
             on_gpu = prep.device.type == "cuda"
-            comm = torch.cuda.Stream(device=prep.device) if (on_gpu and world > 1) else None
+            comm = torch.cuda.Stream(device=prep.device) if (on_gpu and world > 1 and OVERLAP_COLLECTIVES) else None
 
             def exchange_shift(shift):
                 if world > 1:

@@ -191,7 +191,7 @@ void run_tiles(const typename Epi::Params& ep, const void* a, const void* b, int
               for (int kk = 0; kk < k; ++kk) v = fmaf(arow[kk], load16(b, static_cast<long long>(col) * ld_b + kk, dtype), v);
             acc[j] = __float_as_uint(v);
           }
-          epi.chunk(ep, acc, col0 + c * 32, nullptr);
+          epi.chunk(ep, acc, col0 + c * 32, nullptr, nullptr);
         }
         epi.end(ep);
       }
@@ -204,7 +204,7 @@ void run_tiles_store(const StoreEpilogue::Params& ep, const void* a, const void*
                      long long ld_b, int tile_n) {
   const int groups = static_cast<int>(ceil_div(m, kBlockM)) * (kBlockM / 32);
   const int n_tiles = static_cast<int>(ceil_div(n, tile_n));
-  static float stage[32 * 36];
+  static float stage[2048];
   for (int g = 0; g < groups; ++g) {
     emu::launch(1, 32, [&]() {
       const int lane = static_cast<int>(threadIdx.x);
@@ -226,7 +226,7 @@ void run_tiles_store(const StoreEpilogue::Params& ep, const void* a, const void*
               for (int kk = 0; kk < k; ++kk) v = fmaf(arow[kk], load16(b, static_cast<long long>(col) * ld_b + kk, dtype), v);
             acc[j] = __float_as_uint(v);
           }
-          epi.chunk(ep, acc, col0 + c * 32, stage);
+          epi.chunk(ep, acc, col0 + c * 32, stage, nullptr);
         }
         epi.end(ep);
       }
@@ -525,6 +525,7 @@ int emu_gemm_store_ex(const void* a, const void* b, int dtype, int m, int n, int
   ep.r1_row = r1_row;
   ep.r1_col = r1_col;
   ep.acc_add = acc_add;
+  ep.bulk = (acc_in == nullptr && ((out != nullptr) != (acc_out != nullptr))) ? 1 : 0;   // the launcher's rule
   run_tiles_store(ep, a, b, dtype, m, n, k, ld_a, ld_b, 2 * kBlockN);   // the 512-column tile of the gradient GEMMs
   return 0;
 }

@@ -89,3 +89,22 @@ def test_gemm_wide_tiles_accumulate_across_calls():
     _lib.check(lib.flce_b200_check_device_status(st))
     assert torch.equal(acc, ref)
     assert torch.equal(out.float(), ref.bfloat16().float())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pair,M,N,K", [(1, 1000, 1304, 2120), (1, 296, 1032, 2056), (1, 200, 264, 136), (0, 300, 264, 136),
+                                        (1, 2048, 4096, 2048)])
+def test_gemm_store_through_tma_matches_plain_stores(pair, M, N, K, out_dtype):
+    """The store epilogue writes each 32 x 32 patch with one TMA store from shared memory (ragged edges clipped by the
+    tensor map); with the option off it writes the same patch with ordinary vector stores.  Both exact."""
+    from liger_kernel_b200 import _lib
+
+    D, ref = _run(0, 1, pair, M, N, K, out_dtype=out_dtype)
+    want = ref if out_dtype == torch.float32 else ref.to(out_dtype).float()
+    assert torch.equal(D.float(), want)
+    _lib.set_option("bulk_store", 0)
+    try:
+        D2, _ = _run(0, 1, pair, M, N, K, out_dtype=out_dtype)
+    finally:
+        _lib.set_option("bulk_store", 1)
+    assert torch.equal(D2.float(), want)
