@@ -27,6 +27,8 @@ SHAPES = [
     ("dX two-sweep  (dZ.W, one slab)   ", 0, 1, 32768, 4096, 16128),
     ("dW default    (E^T.X', one chunk)", 1, 1, 128256, 4096, 10880),
     ("dX default    (E.W, one chunk)   ", 0, 1, 10880, 4096, 128256),
+    ("dW default, X' stored transposed ", 1, 0, 128256, 4096, 10880),
+    ("sweep-1 shape (X.W^T), plain store", 0, 0, 10880, 128256, 4096),
 ]
 
 

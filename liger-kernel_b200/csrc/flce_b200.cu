@@ -1428,7 +1428,7 @@ int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, 
     return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
   if (!a_mn_major && b_mn_major)
     return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
-  return fail(FLCE_ERR_UNSUPPORTED, "A MN-major with B K-major is not instantiated");
+  return launch_gemm<kMajorMN, kMajorK, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
 }
 
 int flce_b200_gemm_accumulate(const void* a, const void* b, float* acc, void* out, int64_t m, int64_t n, int64_t k,
@@ -1471,7 +1471,7 @@ int flce_b200_gemm_accumulate(const void* a, const void* b, float* acc, void* ou
     return launch_gemm<kMajorMN, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
   if (!a_mn_major && b_mn_major)
     return launch_gemm<kMajorK, kMajorMN, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
-  return fail(FLCE_ERR_UNSUPPORTED, "A MN-major with B K-major is not instantiated");
+  return launch_gemm<kMajorMN, kMajorK, StoreEpilogue>(*dev, kKindOther, pair, oa, ob, ab_dtype, m, n, k, row_bytes, true, ep, stream);
 }
 
 // ------------------------------------------------------------------ chunked sibling losses: row kernels

@@ -11,7 +11,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [(0, 0), (0, 1), (1, 1)]  # (A MN-major?, B MN-major?) as used by logits / dX / dW
+VARIANTS = [(0, 0), (0, 1), (1, 1), (1, 0)]  # (A MN-major?, B MN-major?): logits / dX / dW / dW against a transposed X
 SHAPES = [(128, 256, 64), (256, 512, 256), (1000, 1304, 520), (136, 8, 72), (2048, 4096, 1024)]
 
 
