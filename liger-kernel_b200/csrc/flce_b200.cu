@@ -87,6 +87,7 @@ struct DeviceState {
   int* status = nullptr;  // device word written by abandoned waits
 };
 static DeviceState g_dev[64];
+static std::atomic<int> g_sm_count_hint{0};   // SM count of the first device seen (work-partition heuristics of the planners)
 static std::mutex g_dev_mutex;
 __device__ int g_device_status_word;
 
@@ -121,6 +122,8 @@ static int device_state(DeviceState** out) {
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     st.ready = true;
+    int expected = 0;
+    g_sm_count_hint.compare_exchange_strong(expected, st.sm_count);
   }
   *out = &st;
   return FLCE_OK;
@@ -390,6 +393,28 @@ static FusedPlan fused_plan(const flce_problem_t* p, size_t budget, bool need_ac
   if (max_rows > 65280) max_rows = 65280;  // the in-place gradient kernel puts the chunk's rows on grid.y
   f.n_chunks = static_cast<int>(ceil_div(p->n_rows, max_rows));
   f.chunk_rows = ceil_div(ceil_div(p->n_rows, f.n_chunks), 256) * 256;
+  if (f.n_chunks > 1) {
+    // The grad_input GEMM of a chunk has few, long tiles (K = vocabulary): (chunk rows / 256) x ceil(hidden / 512) of them on
+    // 74 CTA pairs.  Pick the chunk height, within 3/4 .. 1 of what the budget allows, that needs the fewest waves of such
+    // tiles over the whole problem (equal chunks of 8192 rows at the Llama-3-8B head: 4 x 4 waves with the last one 46 % full;
+    // chunks of 9472: 3 x 4 full waves + 2); ties go to the taller chunk.
+    const int sms = g_sm_count_hint.load();
+    const long long units = (sms > 1 ? sms : 148) / 2;
+    const long long n_wide = ceil_div(p->hidden, 2 * kBlockN);
+    long long best_rows = f.chunk_rows, best_waves = -1;
+    for (long long rows = max_rows; rows >= 256 && rows * 4 >= max_rows * 3; rows -= 256) {
+      long long waves = 0;
+      for (long long r0 = 0; r0 < p->n_rows; r0 += rows) {
+        const long long here = (p->n_rows - r0 < rows) ? p->n_rows - r0 : rows;
+        waves += ceil_div(ceil_div(here, 256) * n_wide, units);
+      }
+      if (best_waves < 0 || waves < best_waves) {
+        best_waves = waves;
+        best_rows = rows;
+      }
+    }
+    f.chunk_rows = best_rows;
+  }
   f.n_chunks = static_cast<int>(ceil_div(p->n_rows, f.chunk_rows));
   f.n_tiles = static_cast<int>(ceil_div(p->vocab, kBlockN));
   f.plane = align_up(static_cast<size_t>(f.n_tiles) * f.chunk_rows * sizeof(float), 256);
@@ -584,6 +609,10 @@ int flce_b200_set_option(const char* name, int64_t value) {
 
 size_t flce_b200_workspace_bytes(const flce_problem_t* p, int phase, size_t slab_budget_bytes) {
   if (check_problem(p) != FLCE_OK) return 0;
+  {  // the planners size work for the device's SM count: make sure it is known (a host without a GPU plans for 148)
+    DeviceState* dev = nullptr;
+    (void)device_state(&dev);
+  }
   if (phase == FLCE_PHASE_FORWARD) return forward_plan(p).total;
   if (phase == FLCE_PHASE_BACKWARD) return backward_plan(p, slab_budget_bytes, true).total;
   if (phase == FLCE_PHASE_FUSED) return fused_plan(p, slab_budget_bytes, true).total;
