@@ -291,6 +291,12 @@ int flce_b200_scale_gradient(void* data, int64_t n, int32_t dtype, const float* 
  * No counterpart in the reference (its loop is over token chunks, ops/fused_linear_cross_entropy.py:108). */
 int flce_b200_backward_plan(const flce_problem_t* p, size_t slab_budget_bytes, int32_t* n_slabs, int64_t* slab_cols);
 
+/* The token chunks flce_b200_forward_backward will use for this problem and budget: chunk c covers rows
+ * [c * chunk_rows, min(n_rows, (c+1) * chunk_rows)).  The height is the tallest one within the budget's last quarter
+ * that fills whole waves of grad_input tiles (few and long: K is the vocabulary).  The reference fixes its chunk
+ * count from the shapes alone (src/liger_kernel/ops/fused_linear_cross_entropy.py:56-62). */
+int flce_b200_forward_backward_plan(const flce_problem_t* p, size_t slab_budget_bytes, int32_t* n_chunks, int64_t* chunk_rows);
+
 /* Plain D = A . B^T on the same main loop (fp32 or 16-bit output), for unit-testing the tensor-core
  * path in isolation.  a_mn_major / b_mn_major select which dimension is contiguous in memory:
  * 0: A is [M, K] (K contiguous), 1: A is [K, M] (M contiguous); likewise B is [N, K] or [K, N].

@@ -1427,6 +1427,20 @@ int flce_b200_backward_plan(const flce_problem_t* p, size_t slab_budget_bytes, i
   return FLCE_OK;
 }
 
+int flce_b200_forward_backward_plan(const flce_problem_t* p, size_t slab_budget_bytes, int32_t* n_chunks, int64_t* chunk_rows) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (n_chunks == nullptr || chunk_rows == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL output");
+  {
+    DeviceState* dev = nullptr;
+    (void)device_state(&dev);
+  }
+  const FusedPlan plan = fused_plan(p, slab_budget_bytes, true);
+  *n_chunks = plan.n_chunks;
+  *chunk_rows = plan.chunk_rows;
+  return FLCE_OK;
+}
+
 int flce_b200_gemm(const void* a, const void* b, void* d, int64_t m, int64_t n, int64_t k, int64_t ld_a, int64_t ld_b,
                    int64_t ld_d, int32_t ab_dtype, int32_t d_dtype, int32_t a_mn_major, int32_t b_mn_major,
                    int32_t cta_pair, void* stream_) {

@@ -27,6 +27,7 @@ EXPORTS = (
     "flce_b200_forward",
     "flce_b200_backward",
     "flce_b200_backward_plan",
+    "flce_b200_forward_backward_plan",
     "flce_b200_forward_backward",
     "flce_b200_scale_gradient",
     "flce_b200_split_fp32",
@@ -161,6 +162,8 @@ def _load():
     lib.flce_b200_scatter_rows.restype = C.c_int
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
+    lib.flce_b200_forward_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
+    lib.flce_b200_forward_backward_plan.restype = C.c_int
     lib.flce_b200_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]
     f32 = C.c_float
     lib.flce_b200_gemm_accumulate.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp]

@@ -56,6 +56,18 @@ def test_host_side_argument_errors_without_gpu():
     n_slabs, cols = C.c_int32(), C.c_int64()
     assert lib.flce_b200_backward_plan(C.byref(p), 64 * 2 * 256, C.byref(n_slabs), C.byref(cols)) == 0
     assert (n_slabs.value, cols.value) == (1, 256)
+    # token chunks of the default mode: the height that fills whole waves of the few, long grad_input tiles
+    # (hidden / 512 tiles per 256 rows on 74 CTA pairs), within the last quarter of what the 2.5 GiB default allows
+    n_chunks, rows = C.c_int32(), C.c_int64()
+    for (n, h, v), want in (((32768, 4096, 128256), (4, 9472)),     # 37 x 8 = 4 x 74 tiles per chunk
+                            ((32768, 3584, 152064), (5, 7936)),     # 31 x 7 = 217 tiles: 3 waves
+                            ((65536, 8192, 128256), (7, 9472)),
+                            ((4096, 4096, 128256), (1, 4096))):
+        q = _lib.Problem()
+        q.n_rows, q.hidden, q.vocab, q.vocab_total, q.ld_x, q.ld_w = n, h, v, v, h, h
+        q.x = q.w = q.target = 16
+        assert lib.flce_b200_forward_backward_plan(C.byref(q), 0, C.byref(n_chunks), C.byref(rows)) == 0
+        assert (n_chunks.value, rows.value) == want, (n, h, v, n_chunks.value, rows.value)
     p.dtype = _lib.FLCE_FP32 + 5
     assert lib.flce_b200_workspace_bytes(C.byref(p), 0, 0) == 0
     assert lib.flce_b200_set_option(b"no_such_option", 1) == 1
