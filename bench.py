@@ -458,9 +458,11 @@ def run_ours(args, spec, rank, world, local_rank):
         # the all-reduce of grad_weight runs beside the last grad_input GEMM, which leaves it 20 SMs
         # (liger_kernel_b200.sharded.RESERVE_SMS_FOR_COLLECTIVE): keep NCCL's kernels within that
         import liger_kernel_b200.sharded as sharded_mod
-        if args.comm_overlap is not None:
+        if args.comm_overlap is not None:      # 0: nothing overlapped; 1: also grad_weight of the token-sharded main line
             sharded_mod.OVERLAP_COLLECTIVES = bool(args.comm_overlap)
-        if sharded_mod.OVERLAP_COLLECTIVES:
+            sharded_mod.OVERLAP_GRAD_WEIGHT = bool(args.comm_overlap)
+        if sharded_mod.OVERLAP_COLLECTIVES or sharded_mod.OVERLAP_GRAD_WEIGHT:
+            # a collective that runs beside a GEMM gets 20 SMs (liger_kernel_b200.sharded.RESERVE_SMS_FOR_COLLECTIVE)
             os.environ.setdefault("NCCL_MAX_CTAS", "16")
         import datetime
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
@@ -666,7 +668,8 @@ def run_ours(args, spec, rank, world, local_rank):
         "global_tokens_per_step": tokens,
         "collective_ms_max_over_ranks": collective_ms,
         "rank_kernel_ms": rank_kernel_ms if world > 1 else None,
-        "comm_overlap": (sharded_timing.OVERLAP_COLLECTIVES if world > 1 else None),
+        "comm_overlap": ({"grad_input_of_vocab_shards": sharded_timing.OVERLAP_COLLECTIVES,
+                          "grad_weight_of_token_shards": sharded_timing.OVERLAP_GRAD_WEIGHT} if world > 1 else None),
         "gpu_launches": int(launches),
         "peak_mem_gb": peak_mem / 1e9,
         "ms_per_step_quantiles": step_quantiles,
@@ -734,8 +737,9 @@ def main():
     ap.add_argument("--wide-tiles", type=int, default=None, dest="wide_tiles")
     ap.add_argument("--poll-sleep-ns", type=int, default=None, dest="poll_sleep_ns")
     ap.add_argument("--comm-overlap", type=int, default=None, dest="comm_overlap",
-                    help="multi-GPU: 1 = start the big collective beside the GEMM that follows (side stream, SMs reserved, NCCL "
-                         "capped at 16 CTAs), 0 = issue it after the sweep with every SM to itself")
+                    help="multi-GPU: 1 = start every big collective beside the GEMM that follows (side stream, SMs reserved, NCCL "
+                         "capped at 16 CTAs), 0 = issue them after the sweep with every SM to themselves; default: only the "
+                         "partial grad_input of vocabulary shards is overlapped")
     ap.add_argument("--chunk-gib", type=float, default=None, dest="chunk_gib",
                     help="bytes (GiB) of the bounded 16-bit copy of a token chunk in the single-sweep mode (default 2.5)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -7,9 +7,10 @@ Token-sharded (data parallel; the reference leaves this to DDP/FSDP, ``README.md
 own rows of X / target and the whole W.  Exchanges: the normalisers (count of non-ignored rows, class-weight
 sum) before the per-row losses are formed, the scalar loss, and grad_weight (summed).  With mean / sum reduction
 and 16-bit operands the gradients are formed in forward (``ops/fused_linear_cross_entropy.py``, single-sweep
-mode) with the all-reduced normalisers; the last token chunk forms grad_weight first, the all-reduce starts on a
-side stream as soon as that GEMM is done, and the chunk's grad_input GEMM runs beside it on the SMs it leaves
-free.  Otherwise (``reduction="none"``, fp32) backward recomputes the logits and all-reduces grad_weight after it.
+mode) with the all-reduced normalisers, and grad_weight is all-reduced right after the sweep.  Optionally
+(``OVERLAP_GRAD_WEIGHT``) the last token chunk forms grad_weight first, the all-reduce starts on a side stream as
+soon as that GEMM is done, and the chunk's grad_input GEMM runs beside it on the SMs it leaves free.  Otherwise
+(``reduction="none"``, fp32) backward recomputes the logits and all-reduces grad_weight after it.
 
 Vocabulary-sharded (tensor parallel; the math and collective pattern follow the reference's
 ``ops/vocab_parallel_cross_entropy.py:235-303``): every rank holds rows ``[vocab_start, vocab_start+V_r)`` of W and
@@ -124,9 +125,15 @@ class _timed:
 
 # SMs the last grad_input GEMM of a token-sharded call leaves to the grad_weight all-reduce that runs beside it
 RESERVE_SMS_FOR_COLLECTIVE = 20
-# 1: start a sharded call's big collective beside the GEMM that follows (side stream, SMs reserved); 0: issue it on the
-# compute stream once the sweep is enqueued, with every SM to itself (LIGER_B200_SHARDED_OVERLAP)
+# Whether a sharded call's big collective starts beside the GEMM that follows it (side stream, SMs reserved) or is issued on
+# the compute stream with every SM to itself.  Measured on 2 GPUs, NCCL beside one of this library's GEMMs moves 40 - 80 GB/s
+# against 240 GB/s alone, so hiding pays only where the GEMM window is long:
+# * vocabulary shards: each chunk's partial grad_input (a few hundred MB) rides behind that chunk's grad_weight GEMM: on by
+#   default (LIGER_B200_SHARDED_OVERLAP=0 turns it off);
+# * token shards: grad_weight (as large as the weight) would have only the last chunk's grad_input GEMM to hide behind: off by
+#   default (LIGER_B200_SHARDED_OVERLAP_GRAD_WEIGHT=1 turns it on).
 OVERLAP_COLLECTIVES = os.environ.get("LIGER_B200_SHARDED_OVERLAP", "1") == "1"
+OVERLAP_GRAD_WEIGHT = os.environ.get("LIGER_B200_SHARDED_OVERLAP_GRAD_WEIGHT", "0") == "1"
 
 
 class _TokenSharded(torch.autograd.Function):
@@ -154,7 +161,7 @@ class _TokenSharded(torch.autograd.Function):
             pending = []
             hook = None
             comm = None
-            if world > 1 and needs[1] and OVERLAP_COLLECTIVES:
+            if world > 1 and needs[1] and OVERLAP_GRAD_WEIGHT:
                 comm = torch.cuda.Stream(device=prep.device) if prep.device.type == "cuda" else None
 
                 def hook(gw):
