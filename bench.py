@@ -48,11 +48,16 @@ NAMES = {
 }
 
 
-# DRAM bytes per (token row x vocabulary column) of one launch, from the ncu --set full capture of the profiling case
-# (dram__bytes_read.sum + dram__bytes_write.sum over N x V = 8192 x 32768 units; summary under profiles/).  Traffic of a
-# full-size launch is this figure times the units that launch covers; it grows with the units for a fixed raster.
-NCU_DRAM_BYTES_PER_UNIT = {"stats": 0.7325e9 / (8192 * 32768), "dz": 1.4562e9 / (8192 * 32768),
-                           "dw": 2.9133e9 / (8192 * 32768), "dx": 3.4928e9 / (8192 * 32768)}
+# DRAM bytes per (live token row x vocabulary column) of one launch, from the ncu --set full capture of the profiling
+# case (dram__bytes_read.sum + dram__bytes_write.sum over 10336 live rows x 32768 columns, one token chunk of the C2
+# height; summary under profiles/).  Traffic of a full-size launch is this figure times the units that launch covers:
+# the store of the chunk and the streamed operand grow with the units for a fixed raster.
+_PROFILE_UNITS = 10336 * 32768
+NCU_DRAM_BYTES_PER_UNIT = {"stats": (1.655e9 + 0.6876e9) / _PROFILE_UNITS, "dz": 0.0,
+                           "dw": (2.170e9 + 0.2583e9) / _PROFILE_UNITS, "dx": (2.362e9 + 0.0811e9) / _PROFILE_UNITS}
+
+
+BESIDE_GEMM_GROUP = None   # set in main() at N > 1: the NCCL group for collectives that run beside a GEMM
 
 
 def load_peaks():
@@ -413,7 +418,8 @@ def multi_gpu_extras(args, rank, world, device, peaks):
                 def step():
                     xin = xs.detach().requires_grad_(True)
                     ws.grad = None
-                    sharded.token_sharded_fused_linear_cross_entropy(xin, ws, ts, **kw).backward()
+                    sharded.token_sharded_fused_linear_cross_entropy(
+                        xin, ws, ts, group=BESIDE_GEMM_GROUP if sharded.OVERLAP_GRAD_WEIGHT else None, **kw).backward()
             else:
                 per = (V + world - 1) // world
                 lo = rank * per
@@ -422,7 +428,9 @@ def multi_gpu_extras(args, rank, world, device, peaks):
                 def step():
                     xin = x.detach().requires_grad_(True)
                     ws.grad = None
-                    sharded.vocab_sharded_fused_linear_cross_entropy(xin, ws, t, lo, V, **kw).backward()
+                    sharded.vocab_sharded_fused_linear_cross_entropy(
+                        xin, ws, t, lo, V, group=BESIDE_GEMM_GROUP if sharded.OVERLAP_COLLECTIVES else None,
+                        **kw).backward()
             del w
             r = timed(step)
             ms = gather_max(r["ms"])
@@ -461,11 +469,15 @@ def run_ours(args, spec, rank, world, local_rank):
         if args.comm_overlap is not None:      # 0: nothing overlapped; 1: also grad_weight of the token-sharded main line
             sharded_mod.OVERLAP_COLLECTIVES = bool(args.comm_overlap)
             sharded_mod.OVERLAP_GRAD_WEIGHT = bool(args.comm_overlap)
-        if sharded_mod.OVERLAP_COLLECTIVES or sharded_mod.OVERLAP_GRAD_WEIGHT:
-            # a collective that runs beside a GEMM gets 20 SMs (liger_kernel_b200.sharded.RESERVE_SMS_FOR_COLLECTIVE)
-            os.environ.setdefault("NCCL_MAX_CTAS", "16")
         import datetime
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
+        # calls whose collectives run beside a GEMM (which leaves them RESERVE_SMS_FOR_COLLECTIVE SMs) go through a
+        # second group limited to 16 thread blocks; a collective with the GPU to itself uses the default group
+        global BESIDE_GEMM_GROUP
+        BESIDE_GEMM_GROUP = None
+        if sharded_mod.OVERLAP_COLLECTIVES or sharded_mod.OVERLAP_GRAD_WEIGHT:
+            BESIDE_GEMM_GROUP = sharded_mod.new_group_for_collectives_beside_gemm(
+                max_ctas=16, timeout=datetime.timedelta(seconds=180), device_id=device)
     if args.cta_pair is not None:
         _lib.set_option("cta_pair", args.cta_pair)
     if args.raster_mb is not None:
@@ -479,6 +491,8 @@ def run_ours(args, spec, rank, world, local_rank):
         _lib.set_option("wide_tiles", args.wide_tiles)
     if args.poll_sleep_ns is not None:
         _lib.set_option("poll_sleep_ns", args.poll_sleep_ns)
+    if args.n_group is not None:
+        _lib.set_option("raster_n_group", args.n_group)
     if args.chunk_gib is not None:
         flce_op.CHUNK_BUDGET_BYTES = int(args.chunk_gib * (1 << 30))
     peaks = load_peaks()
@@ -517,7 +531,9 @@ def run_ours(args, spec, rank, world, local_rank):
         elif world > 1:
             # global-batch loss; grad_weight is all-reduced over NCCL inside backward
             skw = {k: v for k, v in kw.items() if k != "return_z_loss"}
-            loss = token_sharded_fused_linear_cross_entropy(xin, w, tin, overlap_grad_weight=args.overlap, **skw)
+            loss = token_sharded_fused_linear_cross_entropy(
+                xin, w, tin, overlap_grad_weight=args.overlap,
+                group=BESIDE_GEMM_GROUP if sharded_mod.OVERLAP_GRAD_WEIGHT else None, **skw)
         else:
             out = liger_fused_linear_cross_entropy(xin, w, tin, **kw)
             loss = out if torch.is_tensor(out) else out.loss
@@ -661,7 +677,7 @@ def run_ours(args, spec, rank, world, local_rank):
                      "peak_kind": f"sustained bf16 GEMM, {peaks['source']}",
                      "flops_basis": "executed: 2 x live rows x H x V per step for this kernel kind",
                      "traffic": NCU_DRAM_BYTES_PER_UNIT[dom] * live_here * w.shape[0] * args.steps / max(1, dom_launches),
-                     "traffic_note": "ncu capture of the N=8192,V=32768 case scaled by rows x columns per launch"},
+                     "traffic_note": "ncu capture of the N=10880 (10336 live), V=32768 case scaled by live rows x columns per launch"},
         "kernels": per_kind,
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * 2 + t_host.numel() * 8, "d2h_bytes_per_step": 4},
@@ -736,6 +752,8 @@ def main():
     ap.add_argument("--store", default=None, choices=["auto", "logits", "exp"], help="what the single-sweep mode keeps of a chunk")
     ap.add_argument("--wide-tiles", type=int, default=None, dest="wide_tiles")
     ap.add_argument("--poll-sleep-ns", type=int, default=None, dest="poll_sleep_ns")
+    ap.add_argument("--n-group", type=int, default=None, dest="n_group",
+                    help="gradient GEMMs: n-tiles per raster group (0 = all: the re-read operand is the whole of B)")
     ap.add_argument("--comm-overlap", type=int, default=None, dest="comm_overlap",
                     help="multi-GPU: 1 = start every big collective beside the GEMM that follows (side stream, SMs reserved, NCCL "
                          "capped at 16 CTAs), 0 = issue them after the sweep with every SM to themselves; default: only the "

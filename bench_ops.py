@@ -94,7 +94,9 @@ def make_step(op, impl, case, n_calls):
 def work_per_step(op, rows, hidden, vocab, element_size):
     """(bound, algorithmic units per step): HBM bytes for ce, tensor FLOPs for the two fused heads."""
     if op == "ce":
-        return "hbm", 3.0 * rows * vocab * element_size                    # read for the statistics, read + write for the gradient
+        # every logit read once, every gradient written once: what both implementations need from HBM when a row stays on
+        # chip between its two passes (ours: in a cluster's shared memory; the reference: in L2)
+        return "hbm", 2.0 * rows * vocab * element_size
     if op == "jsd":
         return "tensor", 2.0 * rows * vocab * (hidden // 2 + hidden) + 4.0 * rows * vocab * (hidden // 2)
     return "tensor", 8.0 * rows * hidden * vocab                           # logits twice (recomputed in backward) + two projections
@@ -160,6 +162,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=None)
     ap.add_argument("--vocab", type=int, default=None)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library tuning option (flce_b200_set_option), ours only; may be repeated")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -168,8 +172,17 @@ def main():
         raise SystemExit("bench_ops.py needs a CUDA device (sm_100a); there is no CPU path")
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
+    if args.option and args.impl == "ours":
+        sys.path.insert(0, os.path.join(ROOT, "liger-kernel_b200"))
+        from liger_kernel_b200 import _lib
+
+        for item in args.option:
+            name, value = item.split("=", 1)
+            _lib.set_option(name, int(value))
     out = run(args.op, args.impl, args.rows or d["rows"], args.hidden if args.hidden is not None else d["hidden"],
               args.vocab or d["vocab"], getattr(torch, args.dtype), args.steps, args.warmup, device)
+    if args.option:
+        out["options"] = args.option
     print(json.dumps(out))
 
 

@@ -257,6 +257,22 @@ int flce_b200_ce_backward(const flce_ce_problem_t* p, const float* lse, const fl
                           int32_t grad_output_per_row, void* grad_logits, int64_t ld_grad, float* coef_scratch,
                           void* stream);
 
+/* Forward and backward in one launch: the reference's own form (its forward kernel leaves the logit gradient, for an
+ * upstream gradient of 1, in the logits buffer: src/liger_kernel/ops/cross_entropy.py:41-336, :428-466).  Each row is held
+ * in the shared memory of a thread-block cluster between the statistics pass and the gradient pass, so HBM traffic is
+ * 2 * n_rows * vocab * sizeof(element).  grad_logits ([n_rows, ld_grad], the logits' dtype) may alias p->logits.  Outputs as
+ * flce_b200_ce_forward; rows with target == ignore_index are not read (lse 0, gradient 0).  Returns FLCE_ERR_UNSUPPORTED,
+ * before anything is launched, when a row is longer than eight CTAs' shared memory (1.6 MB), vocab is not a multiple of the
+ * 16-byte vector or rows are not 16-byte aligned: the two entry points above cover those. */
+int flce_b200_ce_forward_backward(const flce_ce_problem_t* p, float* norm, float* rowstats, const flce_forward_out_t* out,
+                                  void* grad_logits, int64_t ld_grad, void* stream);
+
+/* grad_logits *= grad_output (a device scalar, or one value per row): the reference's cross_entropy_backward
+ * (src/liger_kernel/ops/cross_entropy.py:484-502).  A scalar equal to 1 is recognised on the device and costs one empty
+ * launch, no host synchronisation. */
+int flce_b200_ce_scale_gradient(void* grad_logits, int64_t ld_grad, int64_t n_rows, int64_t vocab, int32_t dtype,
+                                const float* grad_output, int32_t grad_output_per_row, void* stream);
+
 /* fp32 inputs on 16-bit tensor cores: writes 16-bit terms of src (term 0 = round(v), term 1 = round(v - term 0),
  * term 2 = round of what is left) side by side: block b of dst, columns [b*block_cols, b*block_cols + cols), holds
  * term pattern[b] (host array of n_blocks <= 8 entries in {0,1,2}); padding columns are zero.  With X split as

@@ -10,6 +10,7 @@
 #include <mutex>
 #include <type_traits>
 
+#include "ce_fused_sm100.cuh"
 #include "ce_kernels.cuh"
 #include "epilogues.cuh"
 #include "gemm_sm100.cuh"
@@ -43,6 +44,9 @@ static std::atomic<int> g_poll_sleep_ns{0};      // epilogue back-off while wait
 static std::atomic<int> g_l2_hints{0};           // 1: mark streamed operands evict-first and re-read ones evict-last
 static std::atomic<int> g_n_group{0};            // n-fastest raster: n-tiles per group (0 = all)
 static std::atomic<int> g_bulk_store{1};         // store epilogue through TMA stores / adds where it applies
+static std::atomic<int> g_ce_store_exp{1};       // one-launch cross-entropy: keep the exponentials of the statistics pass
+static std::atomic<int> g_ce_small_slice{kCeFusedSmallSliceBytes};   // slice size the one-launch cross-entropy aims for
+static std::atomic<int> g_ce_warps{8};           // warps per CTA of the one-launch cross-entropy: 8 or 16
 static std::atomic<int> g_wide_tiles{1};         // 256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
 
 // ------------------------------------------------------------------ optional per-kernel timing
@@ -502,6 +506,57 @@ static void launch_ce_grad(const flce_ce_problem_t* p, void* grad, long long ld_
                                                              p->ce_weight, p->softcap, inv, lse, c1, c2, c3);
 }
 
+// Cluster size and slice (in 16-byte vectors) of ce_fused_kernel for a row of `vocab` elements, or false when the row does not
+// qualify: prefers slices small enough for three CTAs per SM, then one CTA per SM, over at most eight CTAs.
+static bool ce_fused_geometry(long long vocab, long long esize, int* cluster, int* slice_vecs) {
+  const long long per_vec = 16 / esize;
+  if (vocab % per_vec != 0) return false;
+  const long long n_vec = vocab / per_vec;
+  for (const long long limit : {static_cast<long long>(g_ce_small_slice.load()), static_cast<long long>(kCeFusedMaxSliceBytes)})
+    for (int c = 1; c <= kCeFusedMaxCluster; c *= 2) {
+      const long long sv = ceil_div(n_vec, c);
+      if (sv * 16 <= limit) {
+        *cluster = c;
+        *slice_vecs = static_cast<int>(sv);
+        return true;
+      }
+    }
+  return false;
+}
+
+template <typename T, bool kStoreExp, int kWarps>
+static int launch_ce_fused(const flce_ce_problem_t* p, void* grad, long long ld_grad, const float* norm, const CeFusedOut& out,
+                           int cluster, int slice_vecs, const DeviceState& dev, cudaStream_t stream) {
+  auto* kernel = ce_fused_kernel<T, kStoreExp, kWarps>;
+  {  // once per instantiation and device
+    static std::atomic<bool> smem_set[64];
+    int ordinal = 0;
+    FLCE_CUDA(cudaGetDevice(&ordinal));
+    if (!smem_set[ordinal & 63].load(std::memory_order_acquire)) {
+      FLCE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCeFusedMaxSliceBytes));
+      smem_set[ordinal & 63].store(true, std::memory_order_release);
+    }
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(p->n_rows * cluster), 1, 1);
+  cfg.blockDim = dim3(kWarps * 32, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(slice_vecs) * 16;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float inv = p->softcap > 0.f ? 1.f / p->softcap : 0.f;
+  FLCE_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<const T*>(p->logits), static_cast<long long>(p->ld), static_cast<T*>(grad),
+                               ld_grad, static_cast<int>(p->n_rows), static_cast<int>(p->vocab), slice_vecs,
+                               reinterpret_cast<const long long*>(p->target), p->ce_weight, p->softcap, inv, ce_row_math(p), norm,
+                               out, dev.status));
+  return FLCE_OK;
+}
+
 // ---- launchers of the chunked sibling losses' row kernels (head_loss_kernels.cuh)
 template <typename T>
 static void launch_scaled_ce_rows(const void* logits, int64_t ld, int32_t dtype, int64_t n_rows, int64_t vocab,
@@ -597,6 +652,20 @@ int flce_b200_set_option(const char* name, int64_t value) {
   }
   if (strcmp(name, "wide_tiles") == 0) {
     g_wide_tiles = value != 0;
+    return FLCE_OK;
+  }
+  if (strcmp(name, "ce_store_exp") == 0) {
+    g_ce_store_exp = value != 0;
+    return FLCE_OK;
+  }
+  if (strcmp(name, "ce_warps") == 0) {
+    if (value != 8 && value != 16) return fail(FLCE_ERR_INVALID_ARGUMENT, "ce_warps must be 8 or 16");
+    g_ce_warps = static_cast<int>(value);
+    return FLCE_OK;
+  }
+  if (strcmp(name, "ce_slice_bytes") == 0) {
+    if (value < 16 || value > kCeFusedMaxSliceBytes) return fail(FLCE_ERR_INVALID_ARGUMENT, "ce_slice_bytes out of range");
+    g_ce_small_slice = static_cast<int>(value);
     return FLCE_OK;
   }
   if (strcmp(name, "raster_n_group") == 0) {
@@ -1337,6 +1406,94 @@ int flce_b200_ce_backward(const flce_ce_problem_t* p, const float* lse, const fl
   if (p->dtype == FLCE_FP32) launch_ce_grad<float>(p, grad_logits, ld_grad, lse, c1, c2, c3, stream);
   else if (p->dtype == FLCE_BF16) launch_ce_grad<__nv_bfloat16>(p, grad_logits, ld_grad, lse, c1, c2, c3, stream);
   else launch_ce_grad<__half>(p, grad_logits, ld_grad, lse, c1, c2, c3, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_ce_forward_backward(const flce_ce_problem_t* p, float* norm, float* rowstats, const flce_forward_out_t* out,
+                                  void* grad_logits, int64_t ld_grad, void* stream_) {
+  int rc = check_ce_problem(p);
+  if (rc != FLCE_OK) return rc;
+  if (norm == nullptr || rowstats == nullptr || out == nullptr || grad_logits == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "norm, rowstats, out and grad_logits must not be NULL");
+  if (out->scalars != nullptr && out->loss_rows == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "scalars requires loss_rows");
+  if (ld_grad < p->vocab) return fail(FLCE_ERR_INVALID_ARGUMENT, "ld_grad smaller than vocab");
+  const long long esize = p->dtype == FLCE_FP32 ? 4 : 2;
+  int cluster = 0, slice_vecs = 0;
+  if (!ce_fused_geometry(p->vocab, esize, &cluster, &slice_vecs))
+    return fail(FLCE_ERR_UNSUPPORTED,
+                "row of %lld elements does not fit a cluster's shared memory or is not a multiple of 16 bytes: use the "
+                "two-pass entry points", (long long)p->vocab);
+  if (!ce_rows_vectorisable(p->logits, p->ld, p->dtype) || !ce_rows_vectorisable(grad_logits, ld_grad, p->dtype))
+    return fail(FLCE_ERR_UNSUPPORTED, "logits / gradient rows are not 16-byte aligned: use the two-pass entry points");
+  if (p->n_rows * cluster > 0x7fffffffll) return fail(FLCE_ERR_UNSUPPORTED, "too many rows for one launch");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long* tgt = reinterpret_cast<const long long*>(p->target);
+  count_kernel<<<1, kRedThreads, 0, stream>>>(tgt, p->n_rows, p->ignore_index, p->ce_weight, p->vocab, 0,
+                                             static_cast<float>(p->vocab), norm);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  CeFusedOut fo;
+  fo.rowstats = rowstats;
+  fo.lse = out->lse;
+  fo.target_prob = out->target_prob;
+  fo.loss_rows = out->loss_rows;
+  fo.z_rows = out->z_loss_rows;
+  fo.correct_rows = out->correct_rows;
+  fo.predicted = reinterpret_cast<long long*>(out->predicted_tokens);
+  // without a soft-cap the exponentials of the statistics pass are kept and reused for the gradient
+  const bool store_exp = !(p->softcap > 0.f) && g_ce_store_exp.load() != 0;
+  auto launch = [&](auto tag) {
+    using T = decltype(tag);
+    if (g_ce_warps.load() == 16)
+      return store_exp ? launch_ce_fused<T, true, 16>(p, grad_logits, ld_grad, norm, fo, cluster, slice_vecs, *dev, stream)
+                       : launch_ce_fused<T, false, 16>(p, grad_logits, ld_grad, norm, fo, cluster, slice_vecs, *dev, stream);
+    return store_exp ? launch_ce_fused<T, true, 8>(p, grad_logits, ld_grad, norm, fo, cluster, slice_vecs, *dev, stream)
+                     : launch_ce_fused<T, false, 8>(p, grad_logits, ld_grad, norm, fo, cluster, slice_vecs, *dev, stream);
+  };
+  if (p->dtype == FLCE_FP32) rc = launch(float{});
+  else if (p->dtype == FLCE_BF16) rc = launch(__nv_bfloat16{});
+  else rc = launch(__half{});
+  if (rc != FLCE_OK) return rc;
+  ++g_kernel_launches;
+  if (out->scalars != nullptr) {
+    reduce_rows_kernel<<<1, kRedThreads, 0, stream>>>(static_cast<int>(p->n_rows), out->loss_rows, out->z_loss_rows,
+                                                     out->correct_rows, norm, out->scalars);
+    FLCE_CUDA(cudaGetLastError());
+    ++g_kernel_launches;
+  }
+  return FLCE_OK;
+}
+
+int flce_b200_ce_scale_gradient(void* grad_logits, int64_t ld_grad, int64_t n_rows, int64_t vocab, int32_t dtype,
+                                const float* grad_output, int32_t grad_output_per_row, void* stream_) {
+  if (grad_logits == nullptr || grad_output == nullptr) return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL argument");
+  if (n_rows <= 0 || vocab <= 0 || ld_grad < vocab || n_rows > 0x7fffffffll || vocab > 0x7fffffffll)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad gradient shape (n_rows=%lld vocab=%lld ld=%lld)", (long long)n_rows,
+                (long long)vocab, (long long)ld_grad);
+  if (dtype < FLCE_BF16 || dtype > FLCE_FP32) return fail(FLCE_ERR_UNSUPPORTED, "gradient must be bf16, fp16 or fp32");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long per_thread = dtype == FLCE_FP32 ? 4 : 8;
+  DeviceState* dev = nullptr;
+  const int rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  const long long items = n_rows * ceil_div(ceil_div(vocab, per_thread), 256);
+  const long long resident = static_cast<long long>(dev->sm_count) * 8;      // eight 256-thread blocks per SM
+  dim3 grid(static_cast<unsigned>(items < resident ? items : resident), 1, 1);
+  if (dtype == FLCE_FP32)
+    ce_scale_gradient_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(grad_logits), ld_grad, static_cast<int>(n_rows),
+                                                             static_cast<int>(vocab), grad_output, grad_output_per_row);
+  else if (dtype == FLCE_BF16)
+    ce_scale_gradient_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(grad_logits), ld_grad,
+                                                                     static_cast<int>(n_rows), static_cast<int>(vocab),
+                                                                     grad_output, grad_output_per_row);
+  else
+    ce_scale_gradient_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<__half*>(grad_logits), ld_grad, static_cast<int>(n_rows),
+                                                              static_cast<int>(vocab), grad_output, grad_output_per_row);
   FLCE_CUDA(cudaGetLastError());
   ++g_kernel_launches;
   return FLCE_OK;

@@ -98,17 +98,11 @@ struct RowMath {
   long long vocab, vocab_offset;
 };
 
-// per-row loss / metrics (src/liger_kernel/ops/cross_entropy.py:289-336 of the reference)
-__global__ void finalize_rows_kernel(int m_rows, RowMath rm, const long long* target, const float* ce_weight,
-                                     const float* rowstats, const float* norm, float* lse_out, float* prob_out,
-                                     float* loss_rows, float* z_rows, float* correct_rows, long long* predicted) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= m_rows) return;
-  const size_t n = static_cast<size_t>(m_rows);
-  const float m = rowstats[0 * n + row], d = rowstats[1 * n + row], xy = rowstats[2 * n + row];
-  const float ss = rowstats[3 * n + row];
-  const int amax = reinterpret_cast<const int*>(rowstats)[5 * n + row];
-  const long long t = target[row];
+// per-row loss / metrics (src/liger_kernel/ops/cross_entropy.py:289-336 of the reference) from the row's statistics:
+// m, d = running maximum and sum of exponentials, xy = target logit, ss = (weighted) logit sum, amax = arg-max
+__device__ __forceinline__ void finalize_row(int row, const RowMath& rm, long long t, const float* ce_weight, float m, float d,
+                                             float xy, float ss, int amax, const float* norm, float* lse_out, float* prob_out,
+                                             float* loss_rows, float* z_rows, float* correct_rows, long long* predicted) {
   const bool valid = t != rm.ignore_index;
   const float lse = m + logf(d);
   if (lse_out != nullptr) lse_out[row] = lse;
@@ -146,6 +140,17 @@ __global__ void finalize_rows_kernel(int m_rows, RowMath rm, const long long* ta
   if (predicted != nullptr) predicted[row] = pred;
 }
 
+__global__ void finalize_rows_kernel(int m_rows, RowMath rm, const long long* target, const float* ce_weight,
+                                     const float* rowstats, const float* norm, float* lse_out, float* prob_out,
+                                     float* loss_rows, float* z_rows, float* correct_rows, long long* predicted) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= m_rows) return;
+  const size_t n = static_cast<size_t>(m_rows);
+  finalize_row(row, rm, target[row], ce_weight, rowstats[0 * n + row], rowstats[1 * n + row], rowstats[2 * n + row],
+               rowstats[3 * n + row], reinterpret_cast<const int*>(rowstats)[5 * n + row], norm, lse_out, prob_out, loss_rows,
+               z_rows, correct_rows, predicted);
+}
+
 // scalars[0] = sum loss_rows, [1] = sum z_rows, [2] = sum correct / n_non_ignore, [3] = n_non_ignore
 __global__ void reduce_rows_kernel(int m_rows, const float* loss_rows, const float* z_rows, const float* correct_rows,
                                    const float* norm, float* scalars) {
@@ -167,31 +172,34 @@ __global__ void reduce_rows_kernel(int m_rows, const float* loss_rows, const flo
   }
 }
 
-// per-row coefficients of the logit gradient (see DzEpilogue)
+// per-row coefficients of the logit gradient (see DzEpilogue): go = upstream gradient of the row, prob = exp(xy - lse)
+__device__ __forceinline__ void row_coefs(const RowMath& rm, long long t, const float* ce_weight, float lse, float prob,
+                                          const float* norm, float go, float& a, float& b, float& c) {
+  a = b = c = 0.f;
+  if (t == rm.ignore_index) return;
+  if (rm.token_scaling) go *= prob;
+  float wy = 1.f;
+  if (rm.weighted) {
+    const long long l = t - rm.vocab_offset;
+    wy = (l >= 0 && l < rm.vocab) ? ce_weight[l] : 0.f;
+  }
+  const float inv_s = rm.mean ? 1.f / norm[1] : 1.f;
+  const float inv_n = rm.mean ? 1.f / norm[0] : 1.f;
+  const float sum_w = norm[2];
+  a = go * (((1.f - rm.alpha) * wy + rm.eps * sum_w) * inv_s + 2.f * rm.lambda * lse * inv_n);
+  b = go * rm.eps * inv_s;
+  c = go * (1.f - rm.alpha) * wy * inv_s;
+}
+
 __global__ void coef_kernel(int m_rows, RowMath rm, const long long* target, const float* ce_weight, const float* lse,
                             const float* prob, const float* norm, const float* grad_output, int per_row, float* c1,
                             float* c2, float* c3) {
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= m_rows) return;
-  const long long t = target[row];
-  float a = 0.f, b = 0.f, c = 0.f;
-  if (t != rm.ignore_index) {
-    float go = 1.f;
-    if (grad_output != nullptr) go = per_row ? grad_output[row] : grad_output[0];
-    if (rm.token_scaling) go *= prob[row];
-    float wy = 1.f;
-    if (rm.weighted) {
-      const long long l = t - rm.vocab_offset;
-      wy = (l >= 0 && l < rm.vocab) ? ce_weight[l] : 0.f;
-    }
-    const float inv_s = rm.mean ? 1.f / norm[1] : 1.f;
-    const float inv_n = rm.mean ? 1.f / norm[0] : 1.f;
-    const float sum_w = norm[2];
-    const float l = lse[row];
-    a = go * (((1.f - rm.alpha) * wy + rm.eps * sum_w) * inv_s + 2.f * rm.lambda * l * inv_n);
-    b = go * rm.eps * inv_s;
-    c = go * (1.f - rm.alpha) * wy * inv_s;
-  }
+  float go = 1.f;
+  if (grad_output != nullptr) go = per_row ? grad_output[row] : grad_output[0];
+  float a, b, c;
+  row_coefs(rm, target[row], ce_weight, lse[row], rm.token_scaling ? prob[row] : 0.f, norm, go, a, b, c);
   c1[row] = a;
   c2[row] = b;
   c3[row] = c;

@@ -35,6 +35,8 @@ EXPORTS = (
     "flce_b200_scatter_rows",
     "flce_b200_ce_forward",
     "flce_b200_ce_backward",
+    "flce_b200_ce_forward_backward",
+    "flce_b200_ce_scale_gradient",
     "flce_b200_gemm",
     "flce_b200_gemm_accumulate",
     "flce_b200_selftest_wait_expiry",
@@ -156,6 +158,10 @@ def _load():
     lib.flce_b200_ce_forward.restype = C.c_int
     lib.flce_b200_ce_backward.argtypes = [CP, vp, vp, vp, i32, vp, i64, vp, vp]
     lib.flce_b200_ce_backward.restype = C.c_int
+    lib.flce_b200_ce_forward_backward.argtypes = [CP, vp, vp, F, vp, i64, vp]
+    lib.flce_b200_ce_forward_backward.restype = C.c_int
+    lib.flce_b200_ce_scale_gradient.argtypes = [vp, i64, i64, i64, i32, vp, i32, vp]
+    lib.flce_b200_ce_scale_gradient.restype = C.c_int
     lib.flce_b200_compact_rows.argtypes = [P, vp, vp, vp, vp, vp]
     lib.flce_b200_compact_rows.restype = C.c_int
     lib.flce_b200_scatter_rows.argtypes = [vp, i64, vp, vp, i64, vp, vp]

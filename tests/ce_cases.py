@@ -13,12 +13,14 @@ FEATURES = [dict(), dict(label_smoothing=0.1), dict(lse_square_scale=1e-3), dict
             dict(label_smoothing=0.1, ignore_index=42, lse_square_scale=1e-4, softcap=30.0)]
 
 
-def run_ce(logits, t, device, weight=None, grad_output=None, inplace=False, **kw):
+def run_ce(logits, t, device, weight=None, grad_output=None, inplace=False, mode=None, **kw):
     import liger_kernel_b200.ops.cross_entropy as mod
     from liger_kernel_b200.ops.cross_entropy import LigerCrossEntropyFunction as Fn
 
-    before = mod.INPLACE_GRADIENT
+    before, mode_before = mod.INPLACE_GRADIENT, mod.MODE
     mod.INPLACE_GRADIENT = inplace
+    if mode is not None:
+        mod.MODE = mode
     try:
         x = logits.to(device).clone().requires_grad_(True)
         loss, z, acc, pred = Fn.apply(x, t.to(device), None if weight is None else weight.to(device), kw.get("ignore_index", -100),
@@ -30,7 +32,7 @@ def run_ce(logits, t, device, weight=None, grad_output=None, inplace=False, **kw
             go = torch.as_tensor(grad_output, dtype=loss.dtype).to(device).expand_as(loss).contiguous()
         loss.backward(go)
     finally:
-        mod.INPLACE_GRADIENT = before
+        mod.INPLACE_GRADIENT, mod.MODE = before, mode_before
     return dict(loss=loss.detach().float().cpu(), z_loss=z.float().cpu(), token_accuracy=acc.cpu(), predicted=pred.cpu(),
                 grad=x.grad.float().cpu())
 
@@ -55,10 +57,10 @@ def random_case(N, V, dtype, feat):
     return logits, t
 
 
-def case_correctness(device, N, V, dtype, reduction, feat):
+def case_correctness(device, N, V, dtype, reduction, feat, mode=None):
     logits, t = random_case(N, V, dtype, feat)
     kw = dict(reduction=reduction, **feat)
-    check_ce(run_ce(logits, t, device, **kw), ce_oracle(logits, t, **kw), dtype)
+    check_ce(run_ce(logits, t, device, mode=mode, **kw), ce_oracle(logits, t, **kw), dtype)
 
 
 def case_weights_none_reduction_upstream_gradient_and_inplace(device, N=300, V=1000):

@@ -114,6 +114,33 @@ class EmuLib(fake_lib.FakeLib):
         return self.emu.emu_ce_backward(*self._ce_args(p._obj), _addr(lse), _addr(norm), _addr(go) or None, per_row, _addr(grad),
                                         ld_grad, _addr(scratch))
 
+    def flce_b200_ce_forward_backward(self, p, norm, rowstats, out, grad, ld_grad, stream):
+        # host restatement of the one-launch form: the two emulated passes, the second with an upstream gradient of 1
+        self.calls.append("flce_b200_ce_forward_backward")
+        prob, fo = p._obj, out._obj
+        self.structs.setdefault("flce_b200_ce_forward_backward", []).append(prob)
+        rc = self.emu.emu_ce_forward(*self._ce_args(prob), _addr(norm), _addr(rowstats), fo.lse, fo.target_prob, fo.loss_rows,
+                                     fo.z_loss_rows, fo.correct_rows, fo.predicted_tokens, fo.scalars)
+        if rc != 0:
+            return rc
+        scratch = (C.c_float * (3 * prob.n_rows))()
+        return self.emu.emu_ce_backward(*self._ce_args(prob), fo.lse, _addr(norm), None, 0, _addr(grad), ld_grad,
+                                        C.addressof(scratch))
+
+    def flce_b200_ce_scale_gradient(self, grad, ld_grad, n_rows, vocab, dtype, go, per_row, stream):
+        self.calls.append("flce_b200_ce_scale_gradient")
+        import torch
+
+        tdtype = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}[dtype]
+        esize = 4 if dtype == 2 else 2
+        raw = (C.c_char * (((n_rows - 1) * ld_grad + vocab) * esize)).from_address(_addr(grad))
+        flat = torch.frombuffer(raw, dtype=tdtype)
+        g = torch.as_strided(flat, (n_rows, vocab), (ld_grad, 1))
+        scale = torch.frombuffer((C.c_char * (4 * (n_rows if per_row else 1))).from_address(_addr(go)), dtype=torch.float32)
+        if per_row or float(scale[0]) != 1.0:
+            g.copy_((g.float() * (scale[:, None] if per_row else scale[0])).to(tdtype))
+        return 0
+
     def flce_b200_count(self, p, norm, stream):
         self.calls.append("flce_b200_count")
         prob = p._obj

@@ -23,7 +23,7 @@ def test_bench_ops_record(monkeypatch, op, rows, hidden, vocab):
     assert rec["roofline"]["bound"] == ("hbm" if op == "ce" else "tensor")
     bound, units = bench_ops.work_per_step(op, rows, hidden, vocab, 2)
     if op == "ce":
-        assert units == 3 * rows * vocab * 2
+        assert units == 2 * rows * vocab * 2          # each logit read once, each gradient written once
     elif op == "jsd":
         assert units == 2 * rows * vocab * (hidden // 2 + hidden) + 4 * rows * vocab * (hidden // 2)
     else:

@@ -159,6 +159,8 @@ def test_stand_alone_cross_entropy_operator(monkeypatch):
     import liger_kernel_b200.ops.cross_entropy as ce
 
     with fake_lib.installed(monkeypatch) as fake:
+        # two-pass form: forward leaves the logits alone, backward writes the gradient over them
+        monkeypatch.setattr(ce, "MODE", "two_pass")
         logits = torch.randn(6, 40, dtype=torch.bfloat16, requires_grad=True)
         holder = logits * 1.0
         t = torch.tensor([1, 2, -100, 3, 4, 5])
@@ -183,6 +185,45 @@ def test_stand_alone_cross_entropy_operator(monkeypatch):
         rows = lk.liger_cross_entropy(logits * 1.0, t, reduction="none")
         rows.backward(torch.ones(6))
         assert seen["per_row"] == 1 and seen["grad"] != holder.data_ptr()
+
+        # default form: the gradient is formed in forward (over the logits), backward only folds the upstream gradient in;
+        # nothing is formed when nobody records or the logits need no gradient, or when the rows do not qualify
+        monkeypatch.setattr(ce, "MODE", "auto")
+        monkeypatch.setattr(ce, "INPLACE_GRADIENT", True)
+        del fake.calls[:]
+        holder = logits * 1.0
+        formed = {}
+
+        def ce_forward_backward(p, norm, rowstats, out_, grad, ld_grad, stream):
+            formed.update(grad=fake_lib._addr(grad), ld=ld_grad, logits=p._obj.logits)
+            return 0
+
+        def ce_scale(grad, ld_grad, n_rows, vocab, dtype, go, per_row, stream):
+            formed.update(scaled=fake_lib._addr(grad), shape=(n_rows, vocab, dtype), per_row=per_row)
+            return 0
+
+        fake.hooks["flce_b200_ce_forward_backward"] = ce_forward_backward
+        fake.hooks["flce_b200_ce_scale_gradient"] = ce_scale
+        loss = lk.liger_cross_entropy(holder, t)
+        assert fake.calls == ["flce_b200_ce_forward_backward"]
+        assert formed == dict(grad=holder.data_ptr(), ld=40, logits=holder.data_ptr())
+        loss.backward(retain_graph=True)
+        assert fake.calls == ["flce_b200_ce_forward_backward", "flce_b200_ce_scale_gradient"]
+        assert formed["scaled"] == holder.data_ptr() and formed["shape"] == (6, 40, 0) and formed["per_row"] == 0
+        with pytest.raises(RuntimeError, match="overwritten"):
+            loss.backward()
+        del fake.calls[:]
+        with torch.no_grad():
+            lk.liger_cross_entropy(logits * 1.0, t)
+        lk.liger_cross_entropy(logits.detach(), t)
+        odd = torch.randn(6, 41, dtype=torch.bfloat16, requires_grad=True)        # 82-byte rows: not a multiple of 16 bytes
+        lk.liger_cross_entropy(odd * 1.0, t)
+        assert fake.calls == ["flce_b200_ce_forward"] * 3
+        monkeypatch.setattr(ce, "INPLACE_GRADIENT", False)
+        holder = logits * 1.0
+        rows = lk.liger_cross_entropy(holder, t, reduction="none")
+        rows.backward(torch.ones(6))
+        assert formed["per_row"] == 1 and formed["grad"] != holder.data_ptr() and formed["scaled"] == formed["grad"]
 
 
 def test_sharded_operators_single_process_path(monkeypatch):
