@@ -493,6 +493,9 @@ def run_ours(args, spec, rank, world, local_rank):
         _lib.set_option("poll_sleep_ns", args.poll_sleep_ns)
     if args.n_group is not None:
         _lib.set_option("raster_n_group", args.n_group)
+    for item in args.option:
+        name, value = item.split("=", 1)
+        _lib.set_option(name, int(value))
     if args.chunk_gib is not None:
         flce_op.CHUNK_BUDGET_BYTES = int(args.chunk_gib * (1 << 30))
     peaks = load_peaks()
@@ -752,6 +755,8 @@ def main():
     ap.add_argument("--store", default=None, choices=["auto", "logits", "exp"], help="what the single-sweep mode keeps of a chunk")
     ap.add_argument("--wide-tiles", type=int, default=None, dest="wide_tiles")
     ap.add_argument("--poll-sleep-ns", type=int, default=None, dest="poll_sleep_ns")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library tuning option (flce_b200_set_option); may be repeated")
     ap.add_argument("--n-group", type=int, default=None, dest="n_group",
                     help="gradient GEMMs: n-tiles per raster group (0 = all: the re-read operand is the whole of B)")
     ap.add_argument("--comm-overlap", type=int, default=None, dest="comm_overlap",

@@ -52,6 +52,7 @@ constexpr float kExpStoreRedoLimit = 50.f;
 // =====================================================================================
 struct StatsEpilogue {
   static constexpr bool kDeepPrefetch = false;
+  static constexpr bool kSplitK = false;
   struct Params {
     const long long* target;  // [M] global class ids
     const float* bias;        // [n_cols] or null
@@ -233,6 +234,7 @@ struct StatsEpilogue {
 // =====================================================================================
 struct DzEpilogue {
   static constexpr bool kDeepPrefetch = false;
+  static constexpr bool kSplitK = false;
   struct Params {
     const long long* target;
     const float* bias;
@@ -353,6 +355,7 @@ struct DzEpilogue {
 // =====================================================================================
 struct EntropyStatsEpilogue {
   static constexpr bool kDeepPrefetch = false;
+  static constexpr bool kSplitK = false;
   struct Params {
     const long long* target;  // [M] class ids
     float scale;              // 1 / temperature
@@ -432,6 +435,7 @@ struct EntropyStatsEpilogue {
 
 struct ScaledDzEpilogue {
   static constexpr bool kDeepPrefetch = false;
+  static constexpr bool kSplitK = false;
   struct Params {
     const long long* target;
     long long ignore_index;
@@ -511,6 +515,13 @@ struct ScaledDzEpilogue {
 // =====================================================================================
 struct StoreEpilogue {
   static constexpr bool kDeepPrefetch = true;
+  // a tile's K range may be cut in two, the second part added to what the first one wrote (fp32 accumulator output only)
+  static constexpr bool kSplitK = true;
+  template <class P>
+  __device__ static P accumulating(P p) {
+    p.acc_add = 1;
+    return p;
+  }
   struct Params {
     int m_rows, n_cols;
     const float* acc_in;

@@ -47,6 +47,7 @@ static std::atomic<int> g_bulk_store{1};         // store epilogue through TMA s
 static std::atomic<int> g_ce_store_exp{1};       // one-launch cross-entropy: keep the exponentials of the statistics pass
 static std::atomic<int> g_ce_small_slice{kCeFusedSmallSliceBytes};   // slice size the one-launch cross-entropy aims for
 static std::atomic<int> g_ce_warps{8};           // warps per CTA of the one-launch cross-entropy: 8 or 16
+static std::atomic<int> g_stagger_pct{0};        // wide fp32-accumulating GEMMs: spread of the units' first-tile cut, % of K (0 = off)
 static std::atomic<int> g_wide_tiles{1};         // 256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
 
 // ------------------------------------------------------------------ optional per-kernel timing
@@ -224,6 +225,11 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   shape.active_role = active_rows != nullptr ? active_role : 0;
   shape.active_base = active_base;
   shape.gate = gate;
+  shape.stagger = 0;
+  if constexpr (std::is_same<Epi, StoreEpilogue>::value && kNSub == 2) {
+    // fp32 accumulator output, nothing read back: the first tile of every unit may be cut in two (tile_schedule.cuh)
+    if (ep.acc_out != nullptr && ep.acc_in == nullptr && ep.out == nullptr) shape.stagger = g_stagger_pct.load();
+  }
   shape.hint_a = 0;
   shape.hint_b = 0;
   if (g_l2_hints) {
@@ -652,6 +658,11 @@ int flce_b200_set_option(const char* name, int64_t value) {
   }
   if (strcmp(name, "wide_tiles") == 0) {
     g_wide_tiles = value != 0;
+    return FLCE_OK;
+  }
+  if (strcmp(name, "stagger_pct") == 0) {
+    if (value < 0 || value > 100) return fail(FLCE_ERR_INVALID_ARGUMENT, "stagger_pct must be 0 .. 100");
+    g_stagger_pct = static_cast<int>(value);
     return FLCE_OK;
   }
   if (strcmp(name, "ce_store_exp") == 0) {
@@ -1657,6 +1668,11 @@ int flce_b200_gemm_accumulate(const void* a, const void* b, float* acc, void* ou
   ep.n_cols = static_cast<int>(n);
   ep.acc_in = acc;
   ep.acc_out = acc;
+  if (acc != nullptr && out == nullptr) {
+    // only the running sum is wanted: add into it at L2, nothing is read back
+    ep.acc_in = nullptr;
+    ep.acc_add = 1;
+  }
   ep.ld_acc = ld_acc;
   ep.out = out;
   ep.ld_out = ld_out;

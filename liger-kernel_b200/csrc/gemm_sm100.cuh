@@ -114,6 +114,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int unit = blockIdx.x / kCtas;          // tile-owning unit (CTA or CTA pair)
   const int num_units = gridDim.x / kCtas;
   const int num_tiles = shape.m_tiles * shape.n_tiles;
+  // the first tile of this unit as two parts [0, split_kb) and [split_kb, k_blocks), the second added to the first's output
+  int split_kb = 0;
+  if constexpr (kNSub == 2 && Epi::kSplitK) split_kb = stagger_split(shape, unit, num_units);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -236,6 +239,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       FLCE_TRACE_DECL(wait_tmem_empty);
       for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local_tile) {
         const int acc = (kAccStages == 2) ? (local_tile & 1) : 0;
+        const int parts = (local_tile == 0 && split_kb > 0) ? 2 : 1;    // split_kb > 0 only with a single accumulator
+        for (int part = 0; part < parts && ok; ++part) {
+        const int kb_begin = part == 0 ? 0 : split_kb;
+        const int kb_end = (parts == 2 && part == 0) ? split_kb : shape.k_blocks;
         FLCE_TRACE_BEGIN(t_e);
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase[acc] ^ 1u, abort_flag, status, kDevTimeoutTmemEmpty);
         FLCE_TRACE_ADD(wait_tmem_empty, t_e);
@@ -243,7 +250,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         acc_phase[acc] ^= 1u;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
-        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           FLCE_TRACE_BEGIN(t_f);
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, status, kDevTimeoutFullBarrier);
           FLCE_TRACE_ADD(wait_full, t_f);
@@ -257,7 +264,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < kNSub; ++j)
               umma_f16<kCtas>(tmem_d + static_cast<uint32_t>(j * kBlockN), desc_a + static_cast<uint64_t>(k * kStepA),
-                              desc_b + static_cast<uint64_t>(k * kStepB + j * kSubStepB), idesc, (kb | k) != 0 ? 1u : 0u);
+                              desc_b + static_cast<uint64_t>(k * kStepB + j * kSubStepB), idesc,
+                              (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           if constexpr (kCtas == 1) umma_commit(smem_u32(&empty_bar[stage]));
           else umma_commit_pair(smem_u32(&empty_bar[stage]), 0x3);
@@ -278,6 +286,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         } else {
           umma_commit_pair(smem_u32(&tmem_full_bar[acc]), 0x3);
         }
+        }  // part
       }
       FLCE_TRACE_STORE(0, wait_full);
       FLCE_TRACE_STORE(1, wait_tmem_empty);
@@ -299,6 +308,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int acc = (kAccStages == 2) ? (local_tile & 1) : 0;
       const int row = (mt * kCtas + static_cast<int>(cta_rank)) * kBlockM + row_in_tile;
       const int col0 = nt * kTileN;
+      const int parts = (local_tile == 0 && split_kb > 0) ? 2 : 1;
+      for (int part = 0; part < parts && ok; ++part) {
+      typename Epi::Params ep_part = ep;
+      if constexpr (Epi::kSplitK) {
+        if (part == 1) {
+          // what part 0 stored must have landed before anything is added to it
+          if (lane == 0) bulk_wait_group_all();
+          __syncwarp();
+          ep_part = Epi::accumulating(ep);
+        }
+      }
       FLCE_TRACE_BEGIN(t_w);
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase[acc], abort_flag, status, kDevTimeoutTmemFull,
                      static_cast<uint32_t>(shape.poll_sleep_ns));
@@ -308,7 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       acc_phase[acc] ^= 1u;
       tcgen05_fence_after();
       Epi epi;
-      epi.begin(ep, row, col0, nt, row < shape.M);
+      epi.begin(ep_part, row, col0, nt, row < shape.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kBlockN);
       const int n_chunks = min(kTileN / 32, (shape.N - col0 + 31) / 32);   // uniform across the CTA
       if constexpr (Epi::kDeepPrefetch) {
@@ -328,8 +348,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) a0[j] = a1[j] = 0u;
           }
-          epi.chunk(ep, a0, col0 + c * 32, stage, &map_d);
-          if (c + 1 < n_chunks) epi.chunk(ep, a1, col0 + (c + 1) * 32, stage, &map_d);
+          epi.chunk(ep_part, a0, col0 + c * 32, stage, &map_d);
+          if (c + 1 < n_chunks) epi.chunk(ep_part, a1, col0 + (c + 1) * 32, stage, &map_d);
           if (c + 2 < n_chunks) {
             tmem_ld_wait();
             tmem_ld_fence(b0);
@@ -340,8 +360,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
               for (int j = 0; j < 32; ++j) b0[j] = b1[j] = 0u;
             }
-            epi.chunk(ep, b0, col0 + (c + 2) * 32, stage, &map_d);
-            if (c + 3 < n_chunks) epi.chunk(ep, b1, col0 + (c + 3) * 32, stage, &map_d);
+            epi.chunk(ep_part, b0, col0 + (c + 2) * 32, stage, &map_d);
+            if (c + 3 < n_chunks) epi.chunk(ep_part, b1, col0 + (c + 3) * 32, stage, &map_d);
           }
         }
       } else {
@@ -357,7 +377,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) va[j] = 0u;
         }
-        epi.chunk(ep, va, col0 + c * 32, stage, &map_d);
+        epi.chunk(ep_part, va, col0 + c * 32, stage, &map_d);
         if (c + 1 < n_chunks) {
           tmem_ld_wait();
           tmem_ld_fence(vb);
@@ -366,11 +386,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) vb[j] = 0u;
           }
-          epi.chunk(ep, vb, col0 + (c + 1) * 32, stage, &map_d);
+          epi.chunk(ep_part, vb, col0 + (c + 1) * 32, stage, &map_d);
         }
       }
       }
-      epi.end(ep);
+      epi.end(ep_part);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -378,6 +398,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         else mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]), 0);
       }
       FLCE_TRACE_ADD(busy, t_b);
+      }  // part
     }
     if constexpr (Epi::kDeepPrefetch) {
       if (lane == 0) bulk_wait_group_all();   // this warp's TMA stores have left shared memory and landed

@@ -28,7 +28,19 @@ struct GemmShape {
   // Optional device-resident switch: when it points at 0 the whole launch returns at once (a pass that only some
   // inputs need is enqueued unconditionally and decides on the device, without a host synchronisation).
   const int* gate;
+  // Per cent of a tile's K range over which the units' first tiles are cut in two at unit-dependent points (0 = never).
+  // All units of a persistent grid otherwise finish their equally long tiles at the same moment, and their epilogues
+  // (fp32 read-modify-write of the whole output wave) hit memory as one burst while every tensor core waits.
+  int stagger;
 };
+
+// k-block at which unit `unit` cuts its first tile (0: not cut)
+__device__ __forceinline__ int stagger_split(const GemmShape& s, int unit, int num_units) {
+  if (s.stagger <= 0 || s.k_blocks < 16 || num_units < 2) return 0;
+  const long long span = static_cast<long long>(s.k_blocks) * s.stagger / 100;
+  const int cut = 1 + static_cast<int>(span * (2 * unit + 1) / (2 * num_units));
+  return cut < s.k_blocks ? cut : s.k_blocks - 1;
+}
 
 __device__ __forceinline__ void decode_tile(const GemmShape& s, int tile, int& mt, int& nt) {
   if (s.group_along_m) {

@@ -91,6 +91,33 @@ def test_gemm_wide_tiles_accumulate_across_calls():
     assert torch.equal(out.float(), ref.bfloat16().float())
 
 
+@pytest.mark.parametrize("stagger", [0, 25, 100])
+@pytest.mark.parametrize("M,N,K", [(2048, 2048, 4096), (8192, 4096, 2048), (1000, 1304, 2120)])
+def test_gemm_accumulate_with_staggered_first_tiles(M, N, K, stagger):
+    """Running fp32 sum only (no 16-bit copy): partial products are added at L2, and every CTA pair cuts its first tile's K
+    range in two at its own point so that the pairs' epilogues do not all hit memory at once.  Exact for small integers,
+    whatever the cut (none, spread over a quarter of K, over all of K)."""
+    from liger_kernel_b200 import _lib
+
+    lib = _lib.lib
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    acc = torch.zeros((M, N), device="cuda", dtype=torch.float32)
+    ref = torch.zeros((M, N), device="cuda", dtype=torch.float32)
+    _lib.set_option("stagger_pct", stagger)
+    try:
+        for it in range(2):
+            A = torch.randint(-2, 3, (K, M), device="cuda", generator=g).to(torch.bfloat16)
+            B = torch.randint(-2, 3, (K, N), device="cuda", generator=g).to(torch.bfloat16)
+            _lib.check(lib.flce_b200_gemm_accumulate(C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), C.c_void_p(acc.data_ptr()),
+                                                     None, M, N, K, A.stride(0), B.stride(0), acc.stride(0), 0, 0, 0, 1, 1, 1, st))
+            ref += A.float().t() @ B.float()
+    finally:
+        _lib.set_option("stagger_pct", 0)
+    _lib.check(lib.flce_b200_check_device_status(st))
+    assert torch.equal(acc, ref)
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("pair,M,N,K", [(1, 1000, 1304, 2120), (1, 296, 1032, 2056), (1, 200, 264, 136), (0, 300, 264, 136),
                                         (1, 2048, 4096, 2048)])
