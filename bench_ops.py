@@ -28,7 +28,9 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 DEFAULTS = {"ce": dict(rows=8192, hidden=0, vocab=128256), "jsd": dict(rows=4096, hidden=4096, vocab=128256),
-            "scaled_ce": dict(rows=8192, hidden=4096, vocab=128256)}
+            "scaled_ce": dict(rows=8192, hidden=4096, vocab=128256),
+            # final RMSNorm + lm_head + cross-entropy; --impl ours_unfused = torch's RMSNorm formula + this library's fused head
+            "rmsnorm_head": dict(rows=32768, hidden=4096, vocab=128256)}
 
 
 def make_case(op, rows, hidden, vocab, dtype, device, seed=1234):
@@ -41,6 +43,9 @@ def make_case(op, rows, hidden, vocab, dtype, device, seed=1234):
     target = torch.where(torch.rand(rows, generator=g, device=device) < 0.05, torch.full_like(target, -100), target)
     if op == "ce":
         return dict(logits=rand(rows, vocab, scale=2.0), target=target)
+    if op == "rmsnorm_head":
+        return dict(h=rand(rows, hidden, scale=3.0), gamma=(torch.rand(hidden, generator=g, device=device) + 0.5).to(dtype),
+                    w=rand(vocab, hidden, scale=0.02), target=target)
     if op == "jsd":
         return dict(xs=rand(rows, hidden // 2), ws=rand(vocab, hidden // 2, scale=0.02), xt=rand(rows, hidden),
                     wt=rand(vocab, hidden, scale=0.02), target=target)
@@ -52,7 +57,7 @@ def make_step(op, impl, case, n_calls):
     """Returns a callable running one forward + backward; gradients are dropped between steps.  Both cross-entropy
     implementations write the gradient over the logits they are given, so that operator gets a fresh copy per call,
     made before the clock starts."""
-    if impl == "ours":
+    if impl in ("ours", "ours_unfused"):
         import liger_kernel_b200 as lk
 
         ce, jsd, sce = lk.liger_cross_entropy, lk.LigerFusedLinearJSD(), lk.LigerFusedLinearScaledCrossEntropyFunction.apply
@@ -63,6 +68,30 @@ def make_step(op, impl, case, n_calls):
         from liger_kernel.transformers.fused_linear_jsd import LigerFusedLinearJSD
 
         jsd, sce = LigerFusedLinearJSD(), LigerFusedLinearScaledCrossEntropyFunction.apply
+    if op == "rmsnorm_head":
+        h, gamma, w = case["h"].requires_grad_(True), case["gamma"].requires_grad_(True), case["w"].requires_grad_(True)
+        if impl == "ours":
+            def head(hh):
+                return lk.liger_fused_rmsnorm_linear_cross_entropy(hh, gamma, w, case["target"], eps=1e-6)
+        elif impl == "ours_unfused":
+            def head(hh):
+                hf = hh.float()
+                y = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6)).to(hh.dtype) * gamma
+                return lk.liger_fused_linear_cross_entropy(y, w, case["target"])
+        else:
+            from liger_kernel.ops.rms_norm import LigerRMSNormFunction
+            from liger_kernel.transformers.functional import liger_fused_linear_cross_entropy as liger_flce
+
+            def head(hh):
+                y = LigerRMSNormFunction.apply(hh, gamma, 1e-6, 0.0, "llama", False)
+                return liger_flce(y, w, case["target"])
+
+        def step():
+            h.grad = gamma.grad = w.grad = None
+            loss = head(h)
+            loss.backward()
+            return loss
+        return step
     if op == "ce":
         pool = [case["logits"].clone().requires_grad_(True) for _ in range(n_calls)]
 
@@ -97,6 +126,8 @@ def work_per_step(op, rows, hidden, vocab, element_size):
         # every logit read once, every gradient written once: what both implementations need from HBM when a row stays on
         # chip between its two passes (ours: in a cluster's shared memory; the reference: in L2)
         return "hbm", 2.0 * rows * vocab * element_size
+    if op == "rmsnorm_head":
+        return "tensor", 8.0 * rows * hidden * vocab                           # the head's credited FLOPs; the norm is HBM work
     if op == "jsd":
         return "tensor", 2.0 * rows * vocab * (hidden // 2 + hidden) + 4.0 * rows * vocab * (hidden // 2)
     return "tensor", 8.0 * rows * hidden * vocab                           # logits twice (recomputed in backward) + two projections
@@ -126,7 +157,7 @@ def run(op, impl, rows, hidden, vocab, dtype, steps, warmup, device):
     case = make_case(op, rows, hidden, vocab, dtype, device)
     step = make_step(op, impl, case, steps + warmup)
     launches_before = 0
-    if impl == "ours":
+    if impl in ("ours", "ours_unfused"):
         from liger_kernel_b200._lib import lib
         launches_before = lib.flce_b200_kernel_launches()
     if device.type == "cuda":
@@ -137,7 +168,7 @@ def run(op, impl, rows, hidden, vocab, dtype, steps, warmup, device):
         ms, loss = time_steps(step, steps, warmup, device)
         clocks = None
     launches = None
-    if impl == "ours":
+    if impl in ("ours", "ours_unfused"):
         launches = (lib.flce_b200_kernel_launches() - launches_before) * steps // (steps + warmup)
     bound, units = work_per_step(op, rows, hidden, vocab, torch.empty((), dtype=dtype).element_size())
     peaks = load_peaks()
@@ -157,7 +188,7 @@ def run(op, impl, rows, hidden, vocab, dtype, steps, warmup, device):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True, choices=sorted(DEFAULTS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "liger"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "ours_unfused", "liger"])
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--hidden", type=int, default=None)
     ap.add_argument("--vocab", type=int, default=None)

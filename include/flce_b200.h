@@ -229,6 +229,29 @@ int flce_b200_backward(const flce_problem_t* p, const flce_backward_args_t* args
 int flce_b200_forward_backward(const flce_problem_t* p, const flce_fused_args_t* args, void* workspace,
                                size_t workspace_bytes, size_t slab_budget_bytes, void* stream);
 
+/* ---- The caller in front of the path: the decoder's final RMSNorm, folded into the two row moves ------------------
+ * The hidden states that reach the fused operator come out of the model's final norm
+ * (src/liger_kernel/transformers/model/llama.py:95-98); the reference runs that norm as its own kernel pair
+ * (src/liger_kernel/ops/rms_norm.py:59-139 forward, :143-235 backward) and has no fused counterpart of what follows.
+ * flce_b200_compact_rows_rmsnorm is flce_b200_compact_rows with p->x holding the *raw* hidden states: the gather writes
+ * y = x * rstd * (offset + gamma) (casting_mode 0 "llama": x * rstd rounded to the input dtype first;
+ * 1 "gemma": everything in fp32, one rounding at the end) into x_compact and rstd[i] = 1 / rms of compact row i.  16-bit dtypes, hidden a multiple of 8, at most 16384. */
+int flce_b200_compact_rows_rmsnorm(const flce_problem_t* p, const void* gamma, float eps, float offset, int32_t casting_mode,
+                                   void* x_compact, int64_t* target_compact, int32_t* perm, int32_t* active_rows, float* rstd,
+                                   void* stream);
+
+/* floats of scratch flce_b200_rmsnorm_scatter_backward needs for a hidden size */
+int64_t flce_b200_rmsnorm_partial_floats(int64_t hidden);
+
+/* flce_b200_scatter_rows with the norm's backward applied on the way: grad_normed [n_rows, ld_g] is the gradient with respect
+ * to the normalised rows in compact order (what the fused operator returns as grad_input), hidden_states the raw rows in token
+ * order; grad_hidden row perm[i] receives dx of compact row i (zeros for i >= *active_rows), grad_gamma [hidden] (fp32) the sum
+ * over the rows of dy * (x * rstd).  perm / active_rows may be NULL (rows not moved, all of them live). */
+int flce_b200_rmsnorm_scatter_backward(const void* grad_normed, int64_t ld_g, const void* hidden_states, int64_t ld_x,
+                                       int32_t dtype, int64_t n_rows, int64_t hidden, const void* gamma, const float* rstd,
+                                       const int32_t* perm, const int32_t* active_rows, float offset, int32_t casting_mode,
+                                       void* grad_hidden, int64_t ld_gx, float* grad_gamma, float* partials, void* stream);
+
 /* ---- Stand-alone cross-entropy on materialised logits (the operator beside the fused path) ----------------------
  * Replaces cross_entropy_forward / cross_entropy_backward and the same Triton kernel
  * (src/liger_kernel/ops/cross_entropy.py:351-502).  Forward reads the logits once and leaves them untouched;

@@ -15,6 +15,7 @@
 #include "epilogues.cuh"
 #include "gemm_sm100.cuh"
 #include "head_loss_kernels.cuh"
+#include "rmsnorm_rows.cuh"
 #include "row_kernels.cuh"
 
 namespace flce {
@@ -608,6 +609,42 @@ static void launch_jsd_rows(int sm_count, void* student, int64_t ld_s, const voi
   else
     jsd_rows_kernel<T, false><<<grid, kJsdThreads, 0, stream>>>(xs, ld_s, xt, ld_t, static_cast<int>(n_rows), static_cast<int>(vocab),
                                                               labels, ignore_index, beta, inv_t, count, fixed_count, loss_rows);
+}
+
+// ---- the final RMSNorm folded into the two row moves (rmsnorm_rows.cuh)
+static int check_rmsnorm(int32_t dtype, int64_t hidden, int32_t casting_mode, const void* gamma) {
+  if (dtype != FLCE_BF16 && dtype != FLCE_FP16) return fail(FLCE_ERR_UNSUPPORTED, "the fused RMSNorm takes bf16 or fp16 hidden states");
+  if (hidden <= 0 || hidden % 8 != 0) return fail(FLCE_ERR_UNSUPPORTED, "the fused RMSNorm needs a hidden size that is a multiple of 8");
+  if (hidden > 512ll * kRmsMaxVecs * 8) return fail(FLCE_ERR_UNSUPPORTED, "the fused RMSNorm handles hidden sizes up to 16384");
+  if (casting_mode != kRmsModeLlama && casting_mode != kRmsModeGemma)
+    return fail(FLCE_ERR_UNSUPPORTED, "casting_mode must be 0 (llama) or 1 (gemma)");
+  if (gamma == nullptr || (reinterpret_cast<uintptr_t>(gamma) & 15) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "the norm weight must be given and 16-byte aligned");
+  return FLCE_OK;
+}
+
+static int rmsnorm_partial_blocks() {
+  int sms = g_sm_count_hint.load();
+  if (sms <= 0) sms = 148;
+  return 2 * sms;
+}
+
+template <typename T>
+static void launch_rmsnorm_backward(const void* gy, long long ld_g, const void* x, long long ld_x, const void* gamma,
+                                    const float* rstd, const int* perm, const int* active, long long n_rows, long long hidden,
+                                    float offset, int mode, void* gx, long long ld_gx, float* partials, int blocks,
+                                    cudaStream_t stream) {
+  const long long n_vec = hidden / 8;
+  const int threads = n_vec <= 256 * kRmsMaxVecs ? 256 : 512;
+  const long long per_thread = ceil_div(n_vec, threads);
+  auto go = [&](auto kernel) {
+    kernel<<<blocks, threads, 0, stream>>>(static_cast<const T*>(gy), ld_g, static_cast<const T*>(x), ld_x,
+                                          static_cast<const T*>(gamma), rstd, perm, active, static_cast<int>(n_rows),
+                                          static_cast<int>(hidden), offset, mode, static_cast<T*>(gx), ld_gx, partials);
+  };
+  if (per_thread <= 1) go(rmsnorm_backward_scatter_kernel<T, 1>);
+  else if (per_thread <= 2) go(rmsnorm_backward_scatter_kernel<T, 2>);
+  else go(rmsnorm_backward_scatter_kernel<T, 4>);
 }
 
 }  // namespace flce
@@ -1551,6 +1588,86 @@ int flce_b200_compact_rows(const flce_problem_t* p, void* x_compact, int64_t* ta
   gather_rows_kernel<<<static_cast<unsigned>(p->n_rows), 256, 0, stream>>>(
       static_cast<const uint8_t*>(p->x), p->ld_x * 2, perm, static_cast<uint8_t*>(x_compact), p->hidden * 2,
       reinterpret_cast<const long long*>(p->target), reinterpret_cast<long long*>(target_compact));
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int flce_b200_compact_rows_rmsnorm(const flce_problem_t* p, const void* gamma, float eps, float offset, int32_t casting_mode,
+                                   void* x_compact, int64_t* target_compact, int32_t* perm, int32_t* active_rows, float* rstd,
+                                   void* stream_) {
+  int rc = check_problem(p);
+  if (rc != FLCE_OK) return rc;
+  rc = check_rmsnorm(p->dtype, p->hidden, casting_mode, gamma);
+  if (rc != FLCE_OK) return rc;
+  if (x_compact == nullptr || target_compact == nullptr || perm == nullptr || active_rows == nullptr || rstd == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL output");
+  if ((reinterpret_cast<uintptr_t>(x_compact) & 15) != 0 || (reinterpret_cast<uintptr_t>(p->x) & 15) != 0 || p->ld_x % 8 != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "x and x_compact must be 16-byte aligned with a row pitch that is a multiple of 8");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  compact_plan_kernel<<<1, kRedThreads, 0, stream>>>(reinterpret_cast<const long long*>(p->target), static_cast<int>(p->n_rows),
+                                                    p->ignore_index, perm, active_rows);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  const unsigned grid = static_cast<unsigned>(p->n_rows);
+  const long long* tgt = reinterpret_cast<const long long*>(p->target);
+  long long* tgt_out = reinterpret_cast<long long*>(target_compact);
+  if (p->dtype == FLCE_BF16)
+    rmsnorm_gather_rows_kernel<__nv_bfloat16><<<grid, kRmsThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(p->x), p->ld_x, perm, static_cast<__nv_bfloat16*>(x_compact), p->hidden,
+        static_cast<int>(p->hidden), static_cast<const __nv_bfloat16*>(gamma), eps, offset, casting_mode, rstd, tgt, tgt_out);
+  else
+    rmsnorm_gather_rows_kernel<__half><<<grid, kRmsThreads, 0, stream>>>(
+        static_cast<const __half*>(p->x), p->ld_x, perm, static_cast<__half*>(x_compact), p->hidden, static_cast<int>(p->hidden),
+        static_cast<const __half*>(gamma), eps, offset, casting_mode, rstd, tgt, tgt_out);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  return FLCE_OK;
+}
+
+int64_t flce_b200_rmsnorm_partial_floats(int64_t hidden) {
+  {  // make sure the device's SM count is known (a host without a GPU plans for 148)
+    DeviceState* dev = nullptr;
+    (void)device_state(&dev);
+  }
+  return hidden > 0 ? static_cast<int64_t>(rmsnorm_partial_blocks()) * hidden : 0;
+}
+
+int flce_b200_rmsnorm_scatter_backward(const void* grad_normed, int64_t ld_g, const void* hidden_states, int64_t ld_x,
+                                       int32_t dtype, int64_t n_rows, int64_t hidden, const void* gamma, const float* rstd,
+                                       const int32_t* perm, const int32_t* active_rows, float offset, int32_t casting_mode,
+                                       void* grad_hidden, int64_t ld_gx, float* grad_gamma, float* partials, void* stream_) {
+  int rc = check_rmsnorm(dtype, hidden, casting_mode, gamma);
+  if (rc != FLCE_OK) return rc;
+  if (grad_normed == nullptr || hidden_states == nullptr || rstd == nullptr || grad_hidden == nullptr || grad_gamma == nullptr ||
+      partials == nullptr)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "NULL argument");
+  if (n_rows <= 0 || n_rows > 0x7fffffffll || ld_g < hidden || ld_x < hidden || ld_gx < hidden || ld_g % 8 != 0 || ld_x % 8 != 0 ||
+      ld_gx % 8 != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "bad shapes (n_rows=%lld hidden=%lld pitches %lld %lld %lld)", (long long)n_rows,
+                (long long)hidden, (long long)ld_g, (long long)ld_x, (long long)ld_gx);
+  if (((reinterpret_cast<uintptr_t>(grad_normed) | reinterpret_cast<uintptr_t>(hidden_states) |
+        reinterpret_cast<uintptr_t>(grad_hidden)) & 15) != 0)
+    return fail(FLCE_ERR_INVALID_ARGUMENT, "matrices must be 16-byte aligned");
+  DeviceState* dev = nullptr;
+  rc = device_state(&dev);
+  if (rc != FLCE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int blocks = rmsnorm_partial_blocks();
+  if (blocks > n_rows) blocks = static_cast<int>(n_rows);
+  if (dtype == FLCE_BF16)
+    launch_rmsnorm_backward<__nv_bfloat16>(grad_normed, ld_g, hidden_states, ld_x, gamma, rstd, perm, active_rows, n_rows, hidden,
+                                           offset, casting_mode, grad_hidden, ld_gx, partials, blocks, stream);
+  else
+    launch_rmsnorm_backward<__half>(grad_normed, ld_g, hidden_states, ld_x, gamma, rstd, perm, active_rows, n_rows, hidden, offset,
+                                    casting_mode, grad_hidden, ld_gx, partials, blocks, stream);
+  FLCE_CUDA(cudaGetLastError());
+  ++g_kernel_launches;
+  rmsnorm_dgamma_reduce_kernel<<<static_cast<unsigned>(ceil_div(hidden, 256)), 256, 0, stream>>>(partials, blocks,
+                                                                                               static_cast<int>(hidden), grad_gamma);
   FLCE_CUDA(cudaGetLastError());
   ++g_kernel_launches;
   return FLCE_OK;

@@ -9,6 +9,8 @@ from .ops.cross_entropy import LigerCrossEntropyFunction  # noqa: F401
 from .ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction  # noqa: F401
 from .ops.fused_linear_jsd import LigerFusedLinearJSDFunction  # noqa: F401
 from .ops.fused_linear_scaled_cross_entropy import LigerFusedLinearScaledCrossEntropyFunction  # noqa: F401
+from .ops.fused_rmsnorm_linear_cross_entropy import LigerFusedRMSNormLinearCrossEntropyFunction  # noqa: F401
+from .ops.fused_rmsnorm_linear_cross_entropy import liger_fused_rmsnorm_linear_cross_entropy  # noqa: F401
 from .transformers.cross_entropy import LigerCrossEntropyLoss  # noqa: F401
 from .transformers.functional import liger_cross_entropy  # noqa: F401
 from .transformers.functional import CrossEntropyOutput  # noqa: F401

@@ -33,6 +33,9 @@ EXPORTS = (
     "flce_b200_split_fp32",
     "flce_b200_compact_rows",
     "flce_b200_scatter_rows",
+    "flce_b200_compact_rows_rmsnorm",
+    "flce_b200_rmsnorm_partial_floats",
+    "flce_b200_rmsnorm_scatter_backward",
     "flce_b200_ce_forward",
     "flce_b200_ce_backward",
     "flce_b200_ce_forward_backward",
@@ -166,6 +169,13 @@ def _load():
     lib.flce_b200_compact_rows.restype = C.c_int
     lib.flce_b200_scatter_rows.argtypes = [vp, i64, vp, vp, i64, vp, vp]
     lib.flce_b200_scatter_rows.restype = C.c_int
+    f32 = C.c_float
+    lib.flce_b200_compact_rows_rmsnorm.argtypes = [P, vp, f32, f32, i32, vp, vp, vp, vp, vp, vp]
+    lib.flce_b200_compact_rows_rmsnorm.restype = C.c_int
+    lib.flce_b200_rmsnorm_partial_floats.argtypes = [i64]
+    lib.flce_b200_rmsnorm_partial_floats.restype = C.c_int64
+    lib.flce_b200_rmsnorm_scatter_backward.argtypes = [vp, i64, vp, i64, i32, i64, i64, vp, vp, vp, vp, f32, i32, vp, i64, vp, vp, vp]
+    lib.flce_b200_rmsnorm_scatter_backward.restype = C.c_int
     lib.flce_b200_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     lib.flce_b200_backward_plan.restype = C.c_int
     lib.flce_b200_forward_backward_plan.argtypes = [P, sz, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]

@@ -114,7 +114,9 @@ class _Prepared:
 
     def __init__(self, _input, weight, target, bias, ce_weight, ignore_index, lse_square_scale, label_smoothing,
                  reduction, softcap, use_token_scaling, vocab_total=None, vocab_offset=0, want_argmax=True,
-                 allow_compact=False):
+                 allow_compact=False, rms_norm=None):
+        # rms_norm: dict(weight, eps, offset, casting_mode) when ``_input`` holds the hidden states *before* the decoder's
+        # final RMSNorm; the norm is then applied by the gather that moves the rows that matter to the front
         _require_cuda(_input)
         if _input.dim() != 2 or weight.dim() != 2 or _input.shape[1] != weight.shape[1]:
             raise ValueError(f"expected _input [BT, H] and weight [V, H], got {tuple(_input.shape)} and {tuple(weight.shape)}")
@@ -169,7 +171,21 @@ class _Prepared:
         p.ce_weight = None if self.ce_weight is None else self.ce_weight.data_ptr()
         self.problem = p
         self.compacted = False
-        if allow_compact and SKIP_IGNORED and not self.split:
+        self.rms_norm = None
+        if rms_norm is not None:
+            if self.split or self.hidden % 8 != 0 or self.hidden > 16384:
+                raise NotImplementedError("the fused RMSNorm needs bf16 / fp16 hidden states with a hidden size that is a "
+                                          "multiple of 8 and at most 16384")
+            mode = {"llama": 0, "gemma": 1}.get(rms_norm["casting_mode"])
+            if mode is None:
+                raise NotImplementedError(f"casting_mode must be 'llama' or 'gemma', got {rms_norm['casting_mode']!r}")
+            gamma = rms_norm["weight"].detach().to(device=self.device, dtype=self.dtype).contiguous()
+            if gamma.shape != (self.hidden,):
+                raise ValueError(f"the norm weight must be [H]={self.hidden}, got {tuple(gamma.shape)}")
+            self.rms_norm = dict(weight=gamma, eps=float(rms_norm["eps"]), offset=float(rms_norm["offset"]), mode=mode)
+            self.raw_hidden = self.x
+            self._compact()
+        elif allow_compact and SKIP_IGNORED and not self.split:
             self._compact()
 
     def _compact(self):
@@ -180,8 +196,15 @@ class _Prepared:
         self.perm = torch.empty(n, dtype=torch.int32, device=dev)
         self.active = torch.empty(1, dtype=torch.int32, device=dev)
         with _device_guard(dev):
-            check(lib.flce_b200_compact_rows(C.byref(self.problem), _ptr(xc), _ptr(tc), _ptr(self.perm), _ptr(self.active),
-                                             _stream(dev)))
+            if self.rms_norm is not None:
+                rn = self.rms_norm
+                self.rstd = torch.empty(n, dtype=torch.float32, device=dev)
+                check(lib.flce_b200_compact_rows_rmsnorm(C.byref(self.problem), _ptr(rn["weight"]), rn["eps"], rn["offset"],
+                                                         rn["mode"], _ptr(xc), _ptr(tc), _ptr(self.perm), _ptr(self.active),
+                                                         _ptr(self.rstd), _stream(dev)))
+            else:
+                check(lib.flce_b200_compact_rows(C.byref(self.problem), _ptr(xc), _ptr(tc), _ptr(self.perm), _ptr(self.active),
+                                                 _stream(dev)))
         self.x, self.target = xc, tc
         p = self.problem
         p.x, p.ld_x, p.target = xc.data_ptr(), xc.stride(0), tc.data_ptr()
@@ -208,6 +231,21 @@ class _Prepared:
             check(lib.flce_b200_scatter_rows(_ptr(m), m.shape[1] * m.element_size(), _ptr(self.perm), _ptr(self.active),
                                              m.shape[0], _ptr(out), _stream(self.device)))
         return out
+
+    def rmsnorm_backward(self, grad_normed: torch.Tensor):
+        """Gradient with respect to the normalised rows (compact order) -> (grad_hidden in token order, zeros on ignored rows;
+        grad of the norm weight, fp32)."""
+        rn, dev = self.rms_norm, self.device
+        raw = self.raw_hidden
+        grad_hidden = torch.empty_like(raw)
+        grad_gamma = torch.empty(self.hidden, dtype=torch.float32, device=dev)
+        partials = torch.empty(lib.flce_b200_rmsnorm_partial_floats(self.hidden), dtype=torch.float32, device=dev)
+        with _device_guard(dev):
+            check(lib.flce_b200_rmsnorm_scatter_backward(
+                _ptr(grad_normed), grad_normed.stride(0), _ptr(raw), raw.stride(0), _DTYPES[self.dtype], self.n_rows, self.hidden,
+                _ptr(rn["weight"]), _ptr(self.rstd), _ptr(self.perm), _ptr(self.active), rn["offset"], rn["mode"],
+                _ptr(grad_hidden), grad_hidden.stride(0), _ptr(grad_gamma), _ptr(partials), _stream(dev)))
+        return grad_hidden, grad_gamma
 
     def workspace(self, phase: int, budget: int = 0) -> torch.Tensor:
         nbytes = lib.flce_b200_workspace_bytes(C.byref(self.problem), phase, budget)

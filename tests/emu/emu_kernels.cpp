@@ -13,6 +13,7 @@
 #include "ce_kernels.cuh"
 #include "epilogues.cuh"
 #include "head_loss_kernels.cuh"
+#include "rmsnorm_rows.cuh"
 #include "row_kernels.cuh"
 #include "tile_schedule.cuh"
 
@@ -301,6 +302,46 @@ int emu_compact_rows(const void* x, long long ld_x, long long hidden, long long 
     gather_rows_kernel(static_cast<const uint8_t*>(x), ld_x * 2, perm, static_cast<uint8_t*>(x_compact), hidden * 2, target,
                        target_compact);
   });
+  return 0;
+}
+
+// flce_b200_compact_rows_rmsnorm (dtype: 0 bf16, 1 fp16)
+int emu_compact_rows_rmsnorm(const void* x, long long ld_x, long long hidden, long long n_rows, const long long* target,
+                             long long ignore_index, int dtype, const void* gamma, float eps, float offset, int mode,
+                             void* x_compact, long long* target_compact, int* perm, int* active, float* rstd) {
+  emu::launch(1, kRedThreads, [&]() { compact_plan_kernel(target, static_cast<int>(n_rows), ignore_index, perm, active); });
+  emu::launch(static_cast<unsigned>(n_rows), kRmsThreads, [&]() {
+    if (dtype == 0)
+      rmsnorm_gather_rows_kernel<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x), ld_x, perm,
+                                                static_cast<__nv_bfloat16*>(x_compact), hidden, static_cast<int>(hidden),
+                                                static_cast<const __nv_bfloat16*>(gamma), eps, offset, mode, rstd, target,
+                                                target_compact);
+    else
+      rmsnorm_gather_rows_kernel<__half>(static_cast<const __half*>(x), ld_x, perm, static_cast<__half*>(x_compact), hidden,
+                                         static_cast<int>(hidden), static_cast<const __half*>(gamma), eps, offset, mode, rstd,
+                                         target, target_compact);
+  });
+  return 0;
+}
+
+// flce_b200_rmsnorm_scatter_backward with `blocks` row-striding blocks of 256 threads (hidden <= 8192)
+int emu_rmsnorm_scatter_backward(const void* gy, long long ld_g, const void* x, long long ld_x, int dtype, long long n_rows,
+                                 long long hidden, const void* gamma, const float* rstd, const int* perm, const int* active,
+                                 float offset, int mode, void* gx, long long ld_gx, float* dgamma, float* partials, int blocks) {
+  if (hidden > 256 * 4 * 8) return 2;
+  emu::launch(static_cast<unsigned>(blocks), 256, [&]() {
+    if (dtype == 0)
+      rmsnorm_backward_scatter_kernel<__nv_bfloat16, 4>(
+          static_cast<const __nv_bfloat16*>(gy), ld_g, static_cast<const __nv_bfloat16*>(x), ld_x,
+          static_cast<const __nv_bfloat16*>(gamma), rstd, perm, active, static_cast<int>(n_rows), static_cast<int>(hidden), offset,
+          mode, static_cast<__nv_bfloat16*>(gx), ld_gx, partials);
+    else
+      rmsnorm_backward_scatter_kernel<__half, 4>(static_cast<const __half*>(gy), ld_g, static_cast<const __half*>(x), ld_x,
+                                                 static_cast<const __half*>(gamma), rstd, perm, active, static_cast<int>(n_rows),
+                                                 static_cast<int>(hidden), offset, mode, static_cast<__half*>(gx), ld_gx, partials);
+  });
+  emu::launch_serial(static_cast<unsigned>((hidden + 255) / 256), 256,
+                     [&]() { rmsnorm_dgamma_reduce_kernel(partials, blocks, static_cast<int>(hidden), dgamma); });
   return 0;
 }
 

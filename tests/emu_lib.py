@@ -53,6 +53,8 @@ def load():
         "emu_count": [P, LL, LL, P, LL, LL, F, P],
         "emu_compact_rows": [P, LL, LL, LL, P, LL, P, P, P, P],
         "emu_scatter_rows": [P, LL, P, P, LL, P],
+        "emu_compact_rows_rmsnorm": [P, LL, LL, LL, P, LL, I, P, F, F, I, P, P, P, P, P],
+        "emu_rmsnorm_scatter_backward": [P, LL, P, LL, I, LL, LL, P, P, P, P, F, I, P, LL, P, P, I],
         "emu_split_fp32": [P, LL, LL, LL, P, LL, LL, P, I, I],
         "emu_dz_inplace": [P, LL, LL, LL, I, P, LL, P, P, P, P, P, F, P, I],
         "emu_reduce_rows": [LL, P, P, P, P, P],
@@ -152,6 +154,23 @@ class EmuLib(fake_lib.FakeLib):
         prob = p._obj
         return self.emu.emu_compact_rows(prob.x, prob.ld_x, prob.hidden, prob.n_rows, prob.target, prob.ignore_index, _addr(xc),
                                          _addr(tc), _addr(perm), _addr(active))
+
+    def flce_b200_compact_rows_rmsnorm(self, p, gamma, eps, offset, mode, xc, tc, perm, active, rstd, stream):
+        self.calls.append("flce_b200_compact_rows_rmsnorm")
+        prob = p._obj
+        return self.emu.emu_compact_rows_rmsnorm(prob.x, prob.ld_x, prob.hidden, prob.n_rows, prob.target, prob.ignore_index,
+                                                 prob.dtype, _addr(gamma), eps, offset, mode, _addr(xc), _addr(tc), _addr(perm),
+                                                 _addr(active), _addr(rstd))
+
+    def flce_b200_rmsnorm_partial_floats(self, hidden):
+        return 8 * hidden
+
+    def flce_b200_rmsnorm_scatter_backward(self, gy, ld_g, x, ld_x, dtype, n_rows, hidden, gamma, rstd, perm, active, offset, mode,
+                                           gx, ld_gx, dgamma, partials, stream):
+        self.calls.append("flce_b200_rmsnorm_scatter_backward")
+        return self.emu.emu_rmsnorm_scatter_backward(_addr(gy), ld_g, _addr(x), ld_x, dtype, n_rows, hidden, _addr(gamma),
+                                                     _addr(rstd), _addr(perm) or None, _addr(active) or None, offset, mode,
+                                                     _addr(gx), ld_gx, _addr(dgamma), _addr(partials), min(8, n_rows))
 
     def flce_b200_scatter_rows(self, src, row_bytes, perm, active, n_rows, dst, stream):
         self.calls.append("flce_b200_scatter_rows")
