@@ -463,8 +463,6 @@ def run_ours(args, spec, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
-        # the all-reduce of grad_weight runs beside the last grad_input GEMM, which leaves it 20 SMs
-        # (liger_kernel_b200.sharded.RESERVE_SMS_FOR_COLLECTIVE): keep NCCL's kernels within that
         import liger_kernel_b200.sharded as sharded_mod
         if args.comm_overlap is not None:      # 0: nothing overlapped; 1: also grad_weight of the token-sharded main line
             sharded_mod.OVERLAP_COLLECTIVES = bool(args.comm_overlap)

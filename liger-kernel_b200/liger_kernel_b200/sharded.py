@@ -380,9 +380,9 @@ def token_sharded_fused_linear_cross_entropy(input, weight, target, ignore_index
     Returns the loss over the *global* batch (identical on every rank; per-row for ``reduction="none"``).
     ``weight.grad`` receives the sum over ranks; ``input.grad`` is local.
 
-    With mean / sum reduction and 16-bit operands the gradients are formed in forward and the all-reduce of
-    ``weight.grad`` runs beside the last grad_input GEMM (see the module docstring); a repeated backward of the same
-    graph is not supported there.  ``overlap_grad_weight`` concerns the two-sweep path only (``reduction="none"``, fp32):
+    With mean / sum reduction and 16-bit operands the gradients are formed in forward and ``weight.grad`` is all-reduced
+    right after the sweep (or, with ``OVERLAP_GRAD_WEIGHT``, beside the last grad_input GEMM: see the module docstring);
+    a repeated backward of the same graph is not supported there.  ``overlap_grad_weight`` concerns the two-sweep path only (``reduction="none"``, fp32):
     True all-reduces each finished vocabulary slab of ``weight.grad`` on a side stream while the next slabs are
     computed.  It is off by default: those persistent GEMM kernels fill every SM, so a collective kernel that takes a
     few SMs mid-way delays whole launches (measured on 2 GPUs: 7 ms per step lost)."""
