@@ -30,7 +30,9 @@ import torch  # noqa: E402
 DEFAULTS = {"ce": dict(rows=8192, hidden=0, vocab=128256), "jsd": dict(rows=4096, hidden=4096, vocab=128256),
             "scaled_ce": dict(rows=8192, hidden=4096, vocab=128256),
             # final RMSNorm + lm_head + cross-entropy; --impl ours_unfused = torch's RMSNorm formula + this library's fused head
-            "rmsnorm_head": dict(rows=32768, hidden=4096, vocab=128256)}
+            "rmsnorm_head": dict(rows=32768, hidden=4096, vocab=128256),
+            # DPO with a reference model on 8 chosen + 8 rejected sequences of rows / 16 tokens (chunked_loss/dpo_loss.py)
+            "dpo": dict(rows=16384, hidden=4096, vocab=128256)}
 
 
 def make_case(op, rows, hidden, vocab, dtype, device, seed=1234):
@@ -43,6 +45,12 @@ def make_case(op, rows, hidden, vocab, dtype, device, seed=1234):
     target = torch.where(torch.rand(rows, generator=g, device=device) < 0.05, torch.full_like(target, -100), target)
     if op == "ce":
         return dict(logits=rand(rows, vocab, scale=2.0), target=target)
+    if op == "dpo":
+        batch = 16
+        t = target.view(batch, rows // batch).clone()
+        t[:, : rows // batch // 4] = -100                                       # prompts
+        return dict(x=rand(batch, rows // batch, hidden), w=rand(vocab, hidden, scale=0.02),
+                    ref_x=rand(batch, rows // batch, hidden), ref_w=rand(vocab, hidden, scale=0.02), target=t)
     if op == "rmsnorm_head":
         return dict(h=rand(rows, hidden, scale=3.0), gamma=(torch.rand(hidden, generator=g, device=device) + 0.5).to(dtype),
                     w=rand(vocab, hidden, scale=0.02), target=target)
@@ -68,6 +76,20 @@ def make_step(op, impl, case, n_calls):
         from liger_kernel.transformers.fused_linear_jsd import LigerFusedLinearJSD
 
         jsd, sce = LigerFusedLinearJSD(), LigerFusedLinearScaledCrossEntropyFunction.apply
+    if op == "dpo":
+        x, w = case["x"].requires_grad_(True), case["w"].requires_grad_(True)
+        if impl == "ours":
+            from liger_kernel_b200.chunked_loss import LigerFusedLinearDPOLoss
+        else:
+            from liger_kernel.chunked_loss import LigerFusedLinearDPOLoss
+        loss_mod = LigerFusedLinearDPOLoss(beta=0.1, use_ref_model=True)
+
+        def step():
+            x.grad = w.grad = None
+            loss = loss_mod(w, x, case["target"], None, case["ref_x"], case["ref_w"], None)[0]
+            loss.backward()
+            return loss
+        return step
     if op == "rmsnorm_head":
         h, gamma, w = case["h"].requires_grad_(True), case["gamma"].requires_grad_(True), case["w"].requires_grad_(True)
         if impl == "ours":
@@ -126,6 +148,9 @@ def work_per_step(op, rows, hidden, vocab, element_size):
         # every logit read once, every gradient written once: what both implementations need from HBM when a row stays on
         # chip between its two passes (ours: in a cluster's shared memory; the reference: in L2)
         return "hbm", 2.0 * rows * vocab * element_size
+    if op == "dpo":
+        return "tensor", 8.0 * rows * hidden * vocab                           # policy: logits + two projections, credited like
+                                                                               # the head (plus the reference model's logits)
     if op == "rmsnorm_head":
         return "tensor", 8.0 * rows * hidden * vocab                           # the head's credited FLOPs; the norm is HBM work
     if op == "jsd":

@@ -1,0 +1,16 @@
+"""Preference losses of the reference's ``liger_kernel.chunked_loss`` on this library's fused head (see ``preference.py``)."""
+
+from .preference import LigerFusedLinearCPOFunction  # noqa: F401
+from .preference import LigerFusedLinearCPOLoss  # noqa: F401
+from .preference import LigerFusedLinearDPOFunction  # noqa: F401
+from .preference import LigerFusedLinearDPOLoss  # noqa: F401
+from .preference import LigerFusedLinearORPOFunction  # noqa: F401
+from .preference import LigerFusedLinearORPOLoss  # noqa: F401
+from .preference import LigerFusedLinearSimPOFunction  # noqa: F401
+from .preference import LigerFusedLinearSimPOLoss  # noqa: F401
+from .preference import per_token_logps  # noqa: F401
+
+liger_fused_linear_dpo = LigerFusedLinearDPOFunction.apply
+liger_fused_linear_orpo = LigerFusedLinearORPOFunction.apply
+liger_fused_linear_simpo = LigerFusedLinearSimPOFunction.apply
+liger_fused_linear_cpo = LigerFusedLinearCPOFunction.apply
