@@ -4,6 +4,8 @@ from .preference import LigerFusedLinearCPOFunction  # noqa: F401
 from .preference import LigerFusedLinearCPOLoss  # noqa: F401
 from .preference import LigerFusedLinearDPOFunction  # noqa: F401
 from .preference import LigerFusedLinearDPOLoss  # noqa: F401
+from .preference import LigerFusedLinearKTOFunction  # noqa: F401
+from .preference import LigerFusedLinearKTOLoss  # noqa: F401
 from .preference import LigerFusedLinearORPOFunction  # noqa: F401
 from .preference import LigerFusedLinearORPOLoss  # noqa: F401
 from .preference import LigerFusedLinearSimPOFunction  # noqa: F401
@@ -14,3 +16,4 @@ liger_fused_linear_dpo = LigerFusedLinearDPOFunction.apply
 liger_fused_linear_orpo = LigerFusedLinearORPOFunction.apply
 liger_fused_linear_simpo = LigerFusedLinearSimPOFunction.apply
 liger_fused_linear_cpo = LigerFusedLinearCPOFunction.apply
+liger_fused_linear_kto = LigerFusedLinearKTOFunction.apply

@@ -150,6 +150,50 @@ def cpo_loss_fn(chosen_logps, rejected_logps, pairs, beta=0.1, label_smoothing=0
     return loss, beta * chosen_logps, beta * rejected_logps
 
 
+def kto_loss_fn(log_probs, preference_labels, batch, ref_log_probs=None, beta=0.1, kl=None):
+    """Kahneman-Tversky optimisation on unpaired samples (``chunked_loss/kto_loss.py:8-70``): a desirable sample is pushed above
+    the KL reference point, an undesirable one below it."""
+    ratios = log_probs if ref_log_probs is None else log_probs - ref_log_probs
+    sign = torch.where(preference_labels, 1.0, -1.0)
+    z = ratios if kl is None else ratios - kl
+    loss = (1 - torch.sigmoid(beta * z * sign)).sum() / batch
+    rewards = beta * ratios
+    return loss, (rewards * preference_labels).sum(), (rewards * ~preference_labels).sum()
+
+
+def unpaired_preference_forward(loss_fn, _input, weight, target, preference_labels, bias=None, ignore_index=-100, beta=0.1,
+                                use_ref_model=False, ref_input=None, ref_weight=None, ref_bias=None, average_log_prob=False,
+                                **loss_kwargs):
+    """``LigerFusedLinearUnpairedPreferenceBase`` (``chunked_loss/fused_linear_unpaired_preference.py:9-341``) on the whole batch at
+    once: every sequence carries its own desirable / undesirable label.  The per-class sums are sums over the samples of that
+    class (what the reference's chunk loop accumulates with its default chunk size of one sample)."""
+    if _input.dim() != 3 or target.dim() != 2 or _input.shape[:2] != target.shape:
+        raise ValueError(f"expected _input [B, T, H] and target [B, T], got {tuple(_input.shape)} and {tuple(target.shape)}")
+    if preference_labels is None or preference_labels.shape != (_input.shape[0],):
+        raise ValueError("preference_labels must hold one boolean per sequence")
+    labels = preference_labels.to(device=_input.device, dtype=torch.bool)
+    mask = target != ignore_index
+    seq = per_token_logps(_input, weight, target, bias, ignore_index).sum(-1)
+    if average_log_prob:
+        seq = seq / mask.sum(-1)
+    if use_ref_model:
+        with torch.no_grad():
+            ref = per_token_logps(ref_input, ref_weight, target, ref_bias, ignore_index).sum(-1)
+            if average_log_prob:
+                ref = ref / mask.sum(-1)
+        loss_kwargs["ref_log_probs"] = ref
+    outputs = loss_fn(seq, labels, _input.shape[0], beta=beta, **loss_kwargs)
+    loss, aux = (outputs[0], list(outputs[1:])) if isinstance(outputs, tuple) else (outputs, [])
+    with torch.no_grad():
+        w_sum = weight.detach().float().sum(dim=0)
+        row_sums = _input.detach().float().sum(dim=1) @ w_sum                        # [B]: sum of all logits of a sequence
+        if bias is not None:
+            row_sums = row_sums + bias.detach().float().sum() * _input.shape[1]
+        chosen_logits_sum, rejected_logits_sum = (row_sums * labels).sum(), (row_sums * ~labels).sum()
+        chosen_logps_sum, rejected_logps_sum = (seq.detach() * labels).sum(), (seq.detach() * ~labels).sum()
+    return loss, (chosen_logps_sum, rejected_logps_sum, chosen_logits_sum, rejected_logits_sum, *[a.detach() for a in aux])
+
+
 # ---------------------------------------------------------------- call surface of the reference's classes
 class _ApplyMixin:
     """The reference exposes autograd Functions and calls them positionally through ``.apply``
@@ -193,6 +237,29 @@ class LigerFusedLinearCPOFunction(_ApplyMixin):
                 compute_nll_loss=True, compiled=True, average_log_prob=False, chunk_size=1):
         return preference_forward(cpo_loss_fn, _input, weight, target, bias, ignore_index, alpha, beta, compute_nll_loss,
                                   average_log_prob=average_log_prob, label_smoothing=label_smoothing)
+
+
+class LigerFusedLinearKTOFunction(_ApplyMixin):
+    @staticmethod
+    def forward(_input, weight, target, preference_labels, bias=None, ref_input=None, ref_weight=None, ref_bias=None, kl=None,
+                ignore_index=-100, beta=0.1, compiled=True, use_ref_model=True, average_log_prob=False, chunk_size=1):
+        return unpaired_preference_forward(kto_loss_fn, _input, weight, target, preference_labels, bias, ignore_index, beta,
+                                           use_ref_model, ref_input, ref_weight, ref_bias, average_log_prob, kl=kl)
+
+
+class LigerFusedLinearKTOLoss(torch.nn.Module):
+    """``chunked_loss/kto_loss.py:140-210``: note the argument order of ``forward`` (``_input`` before ``lin_weight``)."""
+
+    def __init__(self, ignore_index=-100, beta=0.1, compiled=True, use_ref_model=False, average_log_prob=False, chunk_size=1):
+        super().__init__()
+        self.ignore_index, self.beta, self.compiled = ignore_index, beta, compiled
+        self.use_ref_model, self.average_log_prob, self.chunk_size = use_ref_model, average_log_prob, chunk_size
+
+    def forward(self, _input, lin_weight, target, bias=None, preference_labels=None, ref_input=None, ref_weight=None,
+                ref_bias=None, kl=None):
+        return LigerFusedLinearKTOFunction.apply(_input, lin_weight, target, preference_labels, bias, ref_input, ref_weight,
+                                                 ref_bias, kl, self.ignore_index, self.beta, self.compiled, self.use_ref_model,
+                                                 self.average_log_prob, self.chunk_size)
 
 
 class LigerFusedLinearDPOLoss(torch.nn.Module):

@@ -131,3 +131,38 @@ def case(device, kind, dtype, pairs=3, seq=24, hidden=64, vocab=500, with_bias=F
         assert_close(got.float().cpu(), ref_g, (2e-2 if low else 2e-5) * float(ref_g.abs().max()), 5e-2 if low else 2e-3, name)
     # the prompt and the ignored positions take no part
     assert float(xd.grad[td == -100].abs().max()) == 0.0
+
+
+def case_kto(device, dtype, batch=5, seq=20, hidden=64, vocab=300, use_ref=True, with_kl=True, average=False, beta=0.3):
+    from liger_kernel_b200 import chunked_loss as cl
+
+    x, w, _, t = make_batch((batch + 1) // 2, seq, hidden, vocab, dtype)
+    x, t = x[:batch], t[:batch]
+    labels = torch.tensor([i % 3 != 1 for i in range(batch)])
+    g = torch.Generator().manual_seed(5)
+    kl = torch.rand(batch, generator=g) * 0.5 if with_kl else None
+    ref = make_batch((batch + 1) // 2, seq, hidden, vocab, dtype, seed=99)[:2] if use_ref else None
+    # torch, float64, materialised logits
+    xr, wr = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    seq_lp, _, _, logits = batch_logps(xr, wr, None, t, average)
+    ratios = seq_lp
+    if use_ref:
+        ratios = seq_lp - batch_logps(ref[0][:batch].double(), ref[1].double(), None, t, average)[0]
+    z = ratios - kl.double() if with_kl else ratios
+    want = (1 - torch.sigmoid(beta * z * torch.where(labels, 1.0, -1.0))).mean()
+    want.backward()
+    xd, wd = x.to(device).requires_grad_(True), w.to(device).requires_grad_(True)
+    mod = cl.LigerFusedLinearKTOLoss(beta=beta, use_ref_model=use_ref, average_log_prob=average)
+    loss, aux = mod(xd, wd, t.to(device), None, labels.to(device), None if ref is None else ref[0][:batch].to(device),
+                    None if ref is None else ref[1].to(device), None, None if kl is None else kl.to(device))
+    low = dtype != torch.float32
+    tol = 2e-2 if low else 2e-4
+    assert_close(loss.detach().float().cpu().reshape(()), want.detach().float(), tol, tol, "loss")
+    assert_close(aux[0].float().cpu().reshape(()), (seq_lp.detach() * labels).sum().float(), tol * float(seq_lp.detach().abs().sum()), tol,
+                 "chosen_logps_sum")
+    assert_close(aux[2].float().cpu().reshape(()), (logits.detach().sum((1, 2)) * labels).sum().float(),
+                 2e-2 * float(logits.detach().abs().sum()) ** 0.5 + 1.0, 5e-2, "chosen_logits_sum")
+    loss.backward()
+    for name, got, ref_g in (("grad_input", xd.grad, xr.grad), ("grad_weight", wd.grad, wr.grad)):
+        ref_g = ref_g.float()
+        assert_close(got.float().cpu(), ref_g, (2e-2 if low else 2e-5) * float(ref_g.abs().max()), 5e-2 if low else 2e-3, name)

@@ -35,3 +35,10 @@ def test_with_bias_and_rejections(monkeypatch):
             cl.LigerFusedLinearDPOLoss(loss_type="nope")
         with pytest.raises(NotImplementedError, match="ipo"):
             cl.liger_fused_linear_dpo(x, w, t, None, None, None, None, -100, 0.1, False, True, False, False, 1, "ipo")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("use_ref,with_kl,average", [(True, True, False), (False, False, True)])
+def test_kto(monkeypatch, dtype, use_ref, with_kl, average):
+    with emu_lib.installed(monkeypatch):
+        cases.case_kto("cpu", dtype, batch=5, seq=10, hidden=32, vocab=131, use_ref=use_ref, with_kl=with_kl, average=average)

@@ -27,3 +27,9 @@ def test_with_bias_and_a_wide_vocabulary():
     cases.case("cuda", "orpo", torch.bfloat16, pairs=2, seq=64, hidden=512, vocab=32001, with_bias=True)
     cases.case("cuda", "dpo", torch.bfloat16, pairs=2, seq=64, hidden=512, vocab=32001, use_ref=True, average=False,
                compute_nll=False)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("use_ref,with_kl,average", [(True, True, False), (False, False, True)])
+def test_kto(dtype, use_ref, with_kl, average):
+    cases.case_kto("cuda", dtype, batch=7, seq=48, hidden=256, vocab=4099, use_ref=use_ref, with_kl=with_kl, average=average)
