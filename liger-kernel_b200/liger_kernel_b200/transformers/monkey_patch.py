@@ -202,11 +202,37 @@ _INSTALL_SITES = {
 }
 
 
-def install(cross_entropy: bool = False, fused_linear_jsd: bool = False, fused_linear_scaled_cross_entropy: bool = False) -> bool:
+# where the reference binds its preference losses: the defining module, the package and (Functions only, as
+# ``liger_fused_linear_<name> = <Function>.apply``) ``chunked_loss/functional.py:10-17``
+_PREFERENCE_LOSSES = {"DPO": "dpo", "ORPO": "orpo", "SimPO": "simpo", "CPO": "cpo", "KTO": "kto"}
+
+
+def _install_preference_losses() -> bool:
+    from .. import chunked_loss as ours
+
+    try:
+        package = importlib.import_module("liger_kernel.chunked_loss")
+        functional = importlib.import_module("liger_kernel.chunked_loss.functional")
+        defining = {short: importlib.import_module(f"liger_kernel.chunked_loss.{short}_loss") for short in _PREFERENCE_LOSSES.values()}
+    except ImportError:
+        return False
+    for name, short in _PREFERENCE_LOSSES.items():
+        fn, loss = getattr(ours, f"LigerFusedLinear{name}Function"), getattr(ours, f"LigerFusedLinear{name}Loss")
+        setattr(defining[short], f"LigerFusedLinear{name}Function", fn)
+        setattr(defining[short], f"LigerFusedLinear{name}Loss", loss)
+        setattr(package, f"LigerFusedLinear{name}Loss", loss)
+        setattr(functional, f"LigerFusedLinear{name}Function", fn)
+        setattr(functional, f"liger_fused_linear_{short}", fn.apply)
+    return True
+
+
+def install(cross_entropy: bool = False, fused_linear_jsd: bool = False, fused_linear_scaled_cross_entropy: bool = False,
+            chunked_loss: bool = False) -> bool:
     """Rebind ``LigerFusedLinearCrossEntropyFunction`` inside an importable ``liger_kernel`` package
     at the three places that bind it at import time (``liger_kernel.ops``,
     ``liger_kernel.transformers.functional``, ``liger_kernel.transformers.fused_linear_cross_entropy``), and on request
-    the stand-alone cross-entropy, fused linear JSD and fused linear scaled cross-entropy operators at theirs.
+    the stand-alone cross-entropy, fused linear JSD and fused linear scaled cross-entropy operators at theirs;
+    ``chunked_loss=True`` also rebinds the DPO / ORPO / SimPO / CPO / KTO classes of ``liger_kernel.chunked_loss``.
     Returns False when no ``liger_kernel`` is installed."""
     from ..ops.cross_entropy import LigerCrossEntropyFunction
     from ..ops.fused_linear_jsd import LigerFusedLinearJSDFunction
@@ -226,4 +252,6 @@ def install(cross_entropy: bool = False, fused_linear_jsd: bool = False, fused_l
     for symbol, fn in wanted.items():
         for name in _INSTALL_SITES[symbol]:
             setattr(modules[name], symbol, fn)
+    if chunked_loss and not _install_preference_losses():
+        return False
     return True

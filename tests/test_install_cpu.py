@@ -52,6 +52,27 @@ def test_install_on_request_rebinds_the_sibling_operators(monkeypatch):
     assert lk.install() is True and not hasattr(mods2["liger_kernel.ops"], "LigerCrossEntropyFunction")
 
 
+def test_install_on_request_rebinds_the_preference_losses(monkeypatch):
+    import liger_kernel_b200 as lk
+    from liger_kernel_b200 import chunked_loss as ours
+
+    mods, _ = _fake_liger(monkeypatch)
+    names = ["liger_kernel.chunked_loss", "liger_kernel.chunked_loss.functional"] + [
+        f"liger_kernel.chunked_loss.{s}_loss" for s in ("dpo", "orpo", "simpo", "cpo", "kto")]
+    for n in names:
+        mods[n] = types.ModuleType(n)
+        monkeypatch.setitem(sys.modules, n, mods[n])
+    assert lk.install(chunked_loss=True) is True
+    assert mods["liger_kernel.chunked_loss"].LigerFusedLinearDPOLoss is ours.LigerFusedLinearDPOLoss
+    assert mods["liger_kernel.chunked_loss.kto_loss"].LigerFusedLinearKTOFunction is ours.LigerFusedLinearKTOFunction
+    assert mods["liger_kernel.chunked_loss.functional"].liger_fused_linear_simpo == ours.LigerFusedLinearSimPOFunction.apply
+    mods2, _ = _fake_liger(monkeypatch)                       # a liger_kernel without that sub-package: reported, not raised
+    for n in names:
+        monkeypatch.delitem(sys.modules, n)
+    monkeypatch.setattr(sys, "path", [p for p in sys.path if "baseline/_ref" not in p])
+    assert lk.install(chunked_loss=True) is False
+
+
 def test_install_without_liger_returns_false(monkeypatch):
     import liger_kernel_b200 as lk
 
