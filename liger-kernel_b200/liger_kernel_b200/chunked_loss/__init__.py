@@ -1,5 +1,9 @@
-"""Preference losses of the reference's ``liger_kernel.chunked_loss`` on this library's fused head (see ``preference.py``)."""
+"""Preference losses (``preference.py``) and GRPO (``grpo.py``) of the reference's ``liger_kernel.chunked_loss`` on this
+library's fused head."""
 
+from .grpo import LigerFusedLinearGRPOFunction  # noqa: F401
+from .grpo import LigerFusedLinearGRPOLoss  # noqa: F401
+from .grpo import selected_token_logps  # noqa: F401
 from .preference import LigerFusedLinearCPOFunction  # noqa: F401
 from .preference import LigerFusedLinearCPOLoss  # noqa: F401
 from .preference import LigerFusedLinearDPOFunction  # noqa: F401
@@ -17,3 +21,4 @@ liger_fused_linear_orpo = LigerFusedLinearORPOFunction.apply
 liger_fused_linear_simpo = LigerFusedLinearSimPOFunction.apply
 liger_fused_linear_cpo = LigerFusedLinearCPOFunction.apply
 liger_fused_linear_kto = LigerFusedLinearKTOFunction.apply
+liger_fused_linear_grpo = LigerFusedLinearGRPOFunction.apply
