@@ -58,7 +58,7 @@ def test_install_on_request_rebinds_the_preference_losses(monkeypatch):
 
     mods, _ = _fake_liger(monkeypatch)
     names = ["liger_kernel.chunked_loss", "liger_kernel.chunked_loss.functional"] + [
-        f"liger_kernel.chunked_loss.{s}_loss" for s in ("dpo", "orpo", "simpo", "cpo", "kto")]
+        f"liger_kernel.chunked_loss.{s}_loss" for s in ("dpo", "orpo", "simpo", "cpo", "kto", "grpo")]
     for n in names:
         mods[n] = types.ModuleType(n)
         monkeypatch.setitem(sys.modules, n, mods[n])
