@@ -52,7 +52,7 @@ def test_out_of_range_targets_are_counted_and_optionally_raised(monkeypatch):
 
 
 FULL_SIZE = {
-    # BASELINE configs 3-5 at their full sizes (config 2 is covered by test_flce_gpu.py::test_full_size_properties)
+    # the benchmark configurations 3-5 at their full sizes (configuration 2 is covered by test_flce_gpu.py::test_full_size_properties)
     "c3_qwen_style": (32768, 3584, 152064, 0.20, dict(label_smoothing=0.1, lse_square_scale=1e-4)),
     "c4_gemma_style": (16384, 3584, 256000, 0.05, dict(softcap=30.0, reduction="sum")),
     "c5_llama70b_head": (65536, 8192, 128256, 0.05, dict()),

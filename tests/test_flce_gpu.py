@@ -428,7 +428,7 @@ def test_correctness_fp32(B, T, H, V, reduction, bias, feat):
 
 
 def test_config_c1_small_fp32_head():
-    """BASELINE config 1: N=1024 (B=2, T=512), H=1024, V=32000, fp32, X~N(0,1), W~N(0,1/H), 10 % ignored, mean."""
+    """Benchmark configuration 1: N=1024 (B=2, T=512), H=1024, V=32000, fp32, X~N(0,1), W~N(0,1/H), 10 % ignored, mean."""
     from liger_kernel_b200.ops.fused_linear_cross_entropy import _Prepared, flce_forward_device
 
     x, w, t, _, _ = make_inputs(1024, 1024, 32000, torch.float32, seed=1234 + 1, ignore_frac=0.10, wscale=1024 ** -0.5)
