@@ -441,7 +441,16 @@ int flce_b200_profile_read(double* ms_by_kind, int64_t* launches_by_kind, int re
 /* Kernels launched by this library in this process so far (host-side counter). */
 int64_t flce_b200_kernel_launches(void);
 
-/* Tunables (process-wide): raster group (m-tiles kept L2-resident per sweep), CTA pairing on/off. */
+/* Tunables (process-wide atomics, meant to be set once at start-up; unknown names are an error):
+ *   cta_pair (1)            CTA pairs (cta_group::2) or single CTAs for the tensor-core sweeps
+ *   raster_group_bytes      bytes of the re-read operand kept L2-resident per raster group of a sweep
+ *   raster_n_group (0)      gradient GEMMs: n-tiles per raster group (0 = all)
+ *   wide_tiles (1)          256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
+ *   bulk_store (1)          store epilogue through TMA stores / adds from shared memory instead of vector stores
+ *   stagger_pct (0)         wide fp32-accumulating GEMMs: cut each pair's first tile at its own K, spread over this % of K
+ *   l2_hints (0), poll_sleep_ns (0)   L2 eviction hints on operand loads; back-off of idle epilogue warps
+ *   ce_store_exp (1), ce_slice_bytes (73728), ce_warps (8)   one-launch cross-entropy: keep the exponentials of the
+ *                           statistics pass; slice of a row per CTA that the cluster size is chosen for; warps per CTA */
 int flce_b200_set_option(const char* name, int64_t value);
 
 const char* flce_b200_status_string(int status);
