@@ -1,6 +1,8 @@
-"""Preference losses (``preference.py``) and GRPO (``grpo.py``) of the reference's ``liger_kernel.chunked_loss`` on this
+"""Preference losses (``preference.py``), GRPO (``grpo.py``) and JSD distillation (``distillation.py``) of the reference's ``liger_kernel.chunked_loss`` on this
 library's fused head."""
 
+from .distillation import LigerFusedLinearJSDFunction  # noqa: F401
+from .distillation import LigerFusedLinearJSDLoss  # noqa: F401
 from .grpo import LigerFusedLinearGRPOFunction  # noqa: F401
 from .grpo import LigerFusedLinearGRPOLoss  # noqa: F401
 from .grpo import selected_token_logps  # noqa: F401
@@ -22,3 +24,4 @@ liger_fused_linear_simpo = LigerFusedLinearSimPOFunction.apply
 liger_fused_linear_cpo = LigerFusedLinearCPOFunction.apply
 liger_fused_linear_kto = LigerFusedLinearKTOFunction.apply
 liger_fused_linear_grpo = LigerFusedLinearGRPOFunction.apply
+liger_fused_linear_jsd = LigerFusedLinearJSDFunction.apply
