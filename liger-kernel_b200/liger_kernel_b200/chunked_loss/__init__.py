@@ -1,6 +1,8 @@
 """Preference losses (``preference.py``), GRPO (``grpo.py``) and JSD distillation (``distillation.py``) of the reference's ``liger_kernel.chunked_loss`` on this
 library's fused head."""
 
+from .distillation import LigerFusedLinearCosineSimilarityFunction  # noqa: F401
+from .distillation import LigerFusedLinearCosineSimilarityLoss  # noqa: F401
 from .distillation import LigerFusedLinearJSDFunction  # noqa: F401
 from .distillation import LigerFusedLinearJSDLoss  # noqa: F401
 from .grpo import LigerFusedLinearGRPOFunction  # noqa: F401
@@ -25,3 +27,4 @@ liger_fused_linear_cpo = LigerFusedLinearCPOFunction.apply
 liger_fused_linear_kto = LigerFusedLinearKTOFunction.apply
 liger_fused_linear_grpo = LigerFusedLinearGRPOFunction.apply
 liger_fused_linear_jsd = LigerFusedLinearJSDFunction.apply
+liger_fused_linear_cosine = LigerFusedLinearCosineSimilarityFunction.apply

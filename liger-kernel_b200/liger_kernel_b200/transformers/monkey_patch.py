@@ -204,7 +204,8 @@ _INSTALL_SITES = {
 
 # where the reference binds its preference losses: the defining module, the package and (Functions only, as
 # ``liger_fused_linear_<name> = <Function>.apply``) ``chunked_loss/functional.py:10-17``
-_PREFERENCE_LOSSES = {"DPO": "dpo", "ORPO": "orpo", "SimPO": "simpo", "CPO": "cpo", "KTO": "kto", "GRPO": "grpo"}
+_PREFERENCE_LOSSES = {"DPO": "dpo", "ORPO": "orpo", "SimPO": "simpo", "CPO": "cpo", "KTO": "kto", "GRPO": "grpo", "JSD": "jsd",
+                      "CosineSimilarity": "cosine_similarity"}
 
 
 def _install_preference_losses() -> bool:
@@ -222,7 +223,7 @@ def _install_preference_losses() -> bool:
         setattr(defining[short], f"LigerFusedLinear{name}Loss", loss)
         setattr(package, f"LigerFusedLinear{name}Loss", loss)
         setattr(functional, f"LigerFusedLinear{name}Function", fn)
-        setattr(functional, f"liger_fused_linear_{short}", fn.apply)
+        setattr(functional, f"liger_fused_linear_{short.split('_')[0]}", fn.apply)      # ..._cosine for cosine_similarity
     return True
 
 
@@ -232,7 +233,7 @@ def install(cross_entropy: bool = False, fused_linear_jsd: bool = False, fused_l
     at the three places that bind it at import time (``liger_kernel.ops``,
     ``liger_kernel.transformers.functional``, ``liger_kernel.transformers.fused_linear_cross_entropy``), and on request
     the stand-alone cross-entropy, fused linear JSD and fused linear scaled cross-entropy operators at theirs;
-    ``chunked_loss=True`` also rebinds the DPO / ORPO / SimPO / CPO / KTO / GRPO classes of ``liger_kernel.chunked_loss``.
+    ``chunked_loss=True`` also rebinds the DPO / ORPO / SimPO / CPO / KTO / GRPO / JSD / cosine-similarity classes of ``liger_kernel.chunked_loss``.
     Returns False when no ``liger_kernel`` is installed."""
     from ..ops.cross_entropy import LigerCrossEntropyFunction
     from ..ops.fused_linear_jsd import LigerFusedLinearJSDFunction

@@ -26,3 +26,10 @@ def test_rejections(monkeypatch):
             cl.liger_fused_linear_jsd(x, w, x, w, t, torch.zeros(50), None)
         with pytest.raises(NotImplementedError, match="vocabulary"):
             cl.liger_fused_linear_jsd(x, w, x, w[:40], t)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kw", [dict(), dict(wh=0.0, wsft=1.0, beta=1.0), dict(wh=1.0, wsft=0.3, beta=0.7)])
+def test_cosine_similarity_distillation(monkeypatch, kw, dtype):
+    with emu_lib.installed(monkeypatch):
+        cases.case_cosine("cpu", dtype, rows=24, hs=32, ht=48, vocab=131, **dict(kw))

@@ -58,7 +58,7 @@ def test_install_on_request_rebinds_the_preference_losses(monkeypatch):
 
     mods, _ = _fake_liger(monkeypatch)
     names = ["liger_kernel.chunked_loss", "liger_kernel.chunked_loss.functional"] + [
-        f"liger_kernel.chunked_loss.{s}_loss" for s in ("dpo", "orpo", "simpo", "cpo", "kto", "grpo")]
+        f"liger_kernel.chunked_loss.{s}_loss" for s in ("dpo", "orpo", "simpo", "cpo", "kto", "grpo", "jsd", "cosine_similarity")]
     for n in names:
         mods[n] = types.ModuleType(n)
         monkeypatch.setitem(sys.modules, n, mods[n])
@@ -66,6 +66,8 @@ def test_install_on_request_rebinds_the_preference_losses(monkeypatch):
     assert mods["liger_kernel.chunked_loss"].LigerFusedLinearDPOLoss is ours.LigerFusedLinearDPOLoss
     assert mods["liger_kernel.chunked_loss.kto_loss"].LigerFusedLinearKTOFunction is ours.LigerFusedLinearKTOFunction
     assert mods["liger_kernel.chunked_loss.functional"].liger_fused_linear_simpo == ours.LigerFusedLinearSimPOFunction.apply
+    assert (mods["liger_kernel.chunked_loss.functional"].liger_fused_linear_cosine
+            == ours.LigerFusedLinearCosineSimilarityFunction.apply)
     mods2, _ = _fake_liger(monkeypatch)                       # a liger_kernel without that sub-package: reported, not raised
     for n in names:
         monkeypatch.delitem(sys.modules, n)
