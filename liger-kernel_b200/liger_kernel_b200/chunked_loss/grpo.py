@@ -7,10 +7,10 @@ head with ``reduction="none"`` when the sampling temperature is 1, the fused *sc
 temperature inside the sweep's epilogue) otherwise.  The loss is arithmetic on ``[B, T]`` tensors in torch; autograd hands the
 per-token upstream gradients back to the operator's backward, which recomputes the logit tiles and projects them.
 
-Loss types: ``grpo``, ``bnpo``, ``dr_grpo``, ``dapo``, ``cispo``, ``luspo``, ``sapo``; token- or sequence-level importance
-ratios; KL penalty to a reference policy (k3 estimator) with or without the importance-sampling correction; the two-sided
-``delta`` clamp; the vLLM importance-sampling ratio.  ``vespo`` raises ``NotImplementedError``.  ``compiled`` and
-``chunk_size`` are accepted and mean nothing here.
+Loss types: ``grpo``, ``bnpo``, ``dr_grpo``, ``dapo``, ``cispo``, ``luspo``, ``sapo``, ``vespo``; token- or sequence-level
+importance ratios; KL penalty to a reference policy (k3 estimator) with or without the importance-sampling correction; the
+two-sided ``delta`` clamp; the vLLM importance-sampling ratio.  ``compiled`` and ``chunk_size`` are accepted and mean nothing
+here.
 """
 
 from __future__ import annotations
@@ -49,6 +49,24 @@ def _soft_gate(ratio, temperature):
     return torch.sigmoid(temperature * (ratio - 1)) * 4 / temperature
 
 
+@torch.no_grad()
+def _gamma_weights(advantages, log_ratio, mask, is_ratio, k_pos, lambda_pos, k_neg, lambda_neg):
+    """VESPO's sequence-level weight phi(w) = e^lambda * w^k * e^(-lambda w) of the importance ratio w (phi(1) = 1), evaluated in
+    log space and used as a constant (``grpo_loss.py:16-53``); shape ``[B, 1]``."""
+    import math
+
+    floor = math.log(1e-8)
+    seq = (torch.clamp(log_ratio, -20.0, 20.0) * mask).sum(-1, keepdim=True)
+    if is_ratio is not None:
+        seq = seq + torch.clamp(torch.log(is_ratio), floor, 20.0).sum(-1, keepdim=True)
+    log_w = torch.clamp(seq, floor, 20.0)
+    w = torch.exp(log_w)
+    nonneg = advantages.unsqueeze(-1) >= 0
+    k = torch.where(nonneg, k_pos, k_neg)
+    lam = torch.where(nonneg, lambda_pos, lambda_neg).clamp(min=1e-4)
+    return torch.exp(lam + k * log_w - lam * w).nan_to_num(nan=0.0, posinf=0.0, neginf=0.0)
+
+
 def _dapo_normalizer(attention_mask, num_items_in_batch):
     """Active tokens per process (``fused_linear_ppo.py:438-473``): given from outside, or counted over all ranks."""
     world = 1
@@ -68,7 +86,7 @@ def _dapo_normalizer(attention_mask, num_items_in_batch):
 def grpo_loss_fn(per_token_logps, attention_mask, advantages, ref_per_token_logps=None, old_per_token_logps=None,
                  epsilon_low=0.2, epsilon_high=0.2, beta=0.04, loss_type="dapo", max_completion_length=None,
                  importance_sampling_level="token", sapo_temperature_pos=1.0, sapo_temperature_neg=1.05, vllm_is_ratio=None,
-                 delta=None, use_bias_correction_kl=False, num_items_in_batch=None):
+                 delta=None, use_bias_correction_kl=False, num_items_in_batch=None, vespo=(2.0, 3.0, 3.0, 2.0)):
     """The clipped-ratio policy loss of GRPOTrainer on a whole batch (``grpo_loss.py:100-281``).  Returns
     ``(loss, [kl (if beta != 0), clip_ratio])``."""
     if importance_sampling_level not in ("token", "sequence"):
@@ -76,8 +94,6 @@ def grpo_loss_fn(per_token_logps, attention_mask, advantages, ref_per_token_logp
     if importance_sampling_level == "sequence" and loss_type in ("cispo", "sapo", "vespo"):
         raise ValueError(f"Sequence-level importance sampling is not supported for loss_type='{loss_type}'. "
                          "Use importance_sampling_level='token' instead.")
-    if loss_type == "vespo":
-        raise NotImplementedError("loss_type='vespo' is not built")
     mask = attention_mask.to(per_token_logps.dtype)
     adv = advantages.to(per_token_logps.dtype).unsqueeze(1)
     if ref_per_token_logps is None:
@@ -94,6 +110,9 @@ def grpo_loss_fn(per_token_logps, attention_mask, advantages, ref_per_token_logp
         clipped = torch.clamp(ratio, max=epsilon_high).detach()
         upper = ratio > epsilon_high
         per_token = -clipped * adv * per_token_logps
+    elif loss_type == "vespo":
+        phi = _gamma_weights(advantages.to(per_token_logps.dtype), log_ratio, mask, vllm_is_ratio, *vespo)
+        per_token = -phi * adv * per_token_logps
     elif loss_type == "sapo":
         positive = adv.expand_as(ratio) > 0
         per_token = -torch.where(positive, _soft_gate(ratio, sapo_temperature_pos), _soft_gate(ratio, sapo_temperature_neg)) * adv
@@ -103,7 +122,7 @@ def grpo_loss_fn(per_token_logps, attention_mask, advantages, ref_per_token_logp
         lower, upper = ratio < lo, ratio > hi
         unclipped = ratio if delta is None else torch.clamp(ratio, max=delta)
         per_token = -torch.min(unclipped * adv, clipped * adv)
-    if vllm_is_ratio is not None:
+    if vllm_is_ratio is not None and loss_type != "vespo":      # vespo folds that correction into its sequence weight
         per_token = per_token * vllm_is_ratio
     kl = None
     if beta != 0.0:
@@ -121,7 +140,7 @@ def grpo_loss_fn(per_token_logps, attention_mask, advantages, ref_per_token_logp
         if max_completion_length is None:
             raise ValueError("max_completion_length must be provided for loss_type 'dr_grpo'")
         loss = (per_token * mask).sum() / (rows * max_completion_length)
-    elif loss_type in ("dapo", "cispo"):
+    elif loss_type in ("dapo", "cispo", "vespo"):
         loss = (per_token * mask).sum() / _dapo_normalizer(attention_mask, num_items_in_batch)
     elif loss_type == "luspo":
         weighted = per_token * mask.sum(1, keepdim=True)
@@ -174,7 +193,8 @@ class LigerFusedLinearGRPOFunction(_ApplyMixin):
         loss, metrics = grpo_loss_fn(
             logps, attention_mask, advantages, ref_per_token_logps if use_ref_model else None, old_per_token_logps, epsilon_low,
             epsilon_high, beta, loss_type, max_completion_length, importance_sampling_level, sapo_temperature_pos,
-            sapo_temperature_neg, vllm_is_ratio, delta, use_bias_correction_kl, num_items_in_batch)
+            sapo_temperature_neg, vllm_is_ratio, delta, use_bias_correction_kl, num_items_in_batch,
+            (vespo_k_pos, vespo_lambda_pos, vespo_k_neg, vespo_lambda_neg))
         return loss, tuple(metrics)
 
 

@@ -2,6 +2,8 @@
 (tests/test_grpo_emulation_cpu.py) against torch in float64 with materialised logits, written the way GRPOTrainer and the
 reference's test (test/chunked_loss/test_grpo_loss.py: TorchLMHeadGRPO) write it."""
 
+import math
+
 import torch
 import torch.nn.functional as F
 
@@ -26,7 +28,14 @@ def torch_grpo(x, w, ids, mask, adv, ref=None, old=None, beta=0.04, eps_lo=0.2, 
         log_ratio = ((log_ratio * maskf).sum(-1) / maskf.sum(-1).clamp(min=1)).unsqueeze(-1)
     c1 = torch.exp(log_ratio)
     a = adv.double().unsqueeze(1)
-    if loss_type == "cispo":
+    if loss_type == "vespo":
+        with torch.no_grad():
+            seq = (torch.clamp(lp - old_lp, -20, 20) * maskf).sum(-1, keepdim=True).clamp(math.log(1e-8), 20.0)
+            pos = a >= 0
+            k, lam = torch.where(pos, 2.0, 3.0), torch.where(pos, 3.0, 2.0)
+            phi = torch.exp(lam + k * seq - lam * torch.exp(seq))
+        per_token = -phi * a * lp
+    elif loss_type == "cispo":
         per_token = -torch.clamp(c1, max=eps_hi).detach() * a * lp
     else:
         c2 = torch.clamp(c1, 1 - eps_lo, 1 + eps_hi)
@@ -43,7 +52,7 @@ def torch_grpo(x, w, ids, mask, adv, ref=None, old=None, beta=0.04, eps_lo=0.2, 
         loss = (per_token * maskf).sum() / maskf.sum().clamp(min=1)
     elif loss_type == "dr_grpo":
         loss = (per_token * maskf).sum() / (mask.shape[0] * max_len)
-    elif loss_type in ("dapo", "cispo"):
+    elif loss_type in ("dapo", "cispo", "vespo"):
         loss = (per_token * maskf).sum() / maskf.sum().clamp(min=1)
     elif loss_type == "luspo":
         loss = (per_token * maskf.sum(1, keepdim=True)).mean()

@@ -14,6 +14,7 @@ VARIANTS = [
     dict(loss_type="dr_grpo", max_completion_length=30, importance_sampling_level="sequence"),
     dict(loss_type="cispo", epsilon_high=1.2),
     dict(loss_type="luspo", temperature=0.7),
+    dict(loss_type="vespo", beta=0.02),
 ]
 
 
@@ -32,8 +33,8 @@ def test_on_policy_without_reference_and_rejections(monkeypatch):
         x = torch.randn(2, 4, 32).bfloat16()
         w = torch.randn(50, 32).bfloat16()
         ids, mask, adv = torch.zeros(2, 4, dtype=torch.long), torch.ones(2, 4, dtype=torch.long), torch.ones(2)
-        with pytest.raises(NotImplementedError, match="vespo"):
-            cl.LigerFusedLinearGRPOLoss(use_ref_model=False, loss_type="vespo")(x, w, ids, mask, adv)
+        with pytest.raises(ValueError, match="Unknown loss type"):
+            cl.LigerFusedLinearGRPOLoss(use_ref_model=False, loss_type="nope")(x, w, ids, mask, adv)
         with pytest.raises(ValueError, match="Sequence-level"):
             cl.LigerFusedLinearGRPOLoss(use_ref_model=False, loss_type="cispo", importance_sampling_level="sequence")(x, w, ids, mask, adv)
         with pytest.raises(AssertionError, match="ref_per_token_logps or ref_input"):
