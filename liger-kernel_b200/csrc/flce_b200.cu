@@ -191,6 +191,32 @@ static int operand_map(CUtensorMap* map, const Operand& op, int dtype, int tile_
 static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// n-tiles per raster group of an n-fastest GEMM, chosen by estimated DRAM traffic.  A group walks all m-tiles over g n-tiles, so
+// the g B panels (tile_n x K each) are what is re-read.  While they fit a third of L2 they stay resident and every A panel is
+// read once per group; otherwise a wave of `units` tiles touches units / g A panels and g B panels, and nothing survives to
+// the next wave.  Smaller groups re-read A more often, larger ones re-read B: the estimate picks between the halvings of n_tiles.
+static int raster_n_group_for(int m_tiles, int n_tiles, long long K, int tile_m, int tile_n, int units) {
+  const double a_panel = 2.0 * tile_m * K, b_panel = 2.0 * tile_n * K;
+  const double resident = 40.0 * 1024 * 1024;
+  const double waves = static_cast<double>(m_tiles) * n_tiles / (units > 0 ? units : 1);
+  int best = n_tiles;
+  double best_bytes = -1.0;
+  for (int g = n_tiles; g >= 1; g = (g + 1) / 2) {
+    double bytes;
+    if (g * b_panel <= resident)
+      bytes = a_panel * m_tiles * ((n_tiles + g - 1) / g) + b_panel * n_tiles;
+    else
+      bytes = (a_panel * (static_cast<double>(units) / g < m_tiles ? static_cast<double>(units) / g : m_tiles) + b_panel * g) *
+              (waves < 1.0 ? 1.0 : waves);
+    if (best_bytes < 0 || bytes < best_bytes * 0.97) {   // a smaller group has to win by 3 % to be taken
+      best_bytes = bytes;
+      best = g;
+    }
+    if (g == 1) break;
+  }
+  return best;
+}
+
 template <int kCtas, int kAMajor, int kBMajor, class Epi, int kNSub = 1>
 static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, const Operand& b, int dtype, long long M,
                             long long N, long long K, long long raster_row_bytes, bool n_fastest,
@@ -240,7 +266,9 @@ static int launch_gemm_impl(const DeviceState& dev, int kind, const Operand& a, 
   }
   if (n_fastest) {
     shape.group_along_m = 0;
-    const int n_group = g_n_group.load();
+    int n_group = g_n_group.load();
+    if (n_group < 0) n_group = raster_n_group_for(shape.m_tiles, shape.n_tiles, K, kBlockM * kCtas, kBlockN * kNSub,
+                                                   dev.sm_count / kCtas);
     shape.group = (n_group > 0 && n_group < shape.n_tiles) ? n_group : shape.n_tiles;
   } else {
     shape.group_along_m = 1;
@@ -717,7 +745,7 @@ int flce_b200_set_option(const char* name, int64_t value) {
     return FLCE_OK;
   }
   if (strcmp(name, "raster_n_group") == 0) {
-    if (value < 0) return fail(FLCE_ERR_INVALID_ARGUMENT, "raster_n_group must be >= 0");
+    if (value < -1) return fail(FLCE_ERR_INVALID_ARGUMENT, "raster_n_group must be >= -1 (-1: chosen per GEMM, 0: all)");
     g_n_group = static_cast<int>(value);
     return FLCE_OK;
   }
