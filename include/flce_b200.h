@@ -444,7 +444,7 @@ int64_t flce_b200_kernel_launches(void);
 /* Tunables (process-wide atomics, meant to be set once at start-up; unknown names are an error):
  *   cta_pair (1)            CTA pairs (cta_group::2) or single CTAs for the tensor-core sweeps
  *   raster_group_bytes      bytes of the re-read operand kept L2-resident per raster group of a sweep
- *   raster_n_group (0)      gradient GEMMs: n-tiles per raster group (0 = all)
+ *   raster_n_group (-1)     gradient GEMMs: n-tiles per raster group (-1 = chosen per GEMM by estimated DRAM traffic, 0 = all)
  *   wide_tiles (1)          256 x 512 tiles for the gradient GEMMs of CTA pairs when K is long
  *   bulk_store (1)          store epilogue through TMA stores / adds from shared memory instead of vector stores
  *   stagger_pct (0)         wide fp32-accumulating GEMMs: cut each pair's first tile at its own K, spread over this % of K

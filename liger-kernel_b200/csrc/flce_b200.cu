@@ -43,7 +43,7 @@ static std::atomic<long long> g_raster_bytes{32ll << 20};  // bytes of A tiles k
 static std::atomic<int> g_cta_pair{1};           // use CTA pairs (cta_group::2) for the FLCE GEMMs
 static std::atomic<int> g_poll_sleep_ns{0};      // epilogue back-off while waiting for an accumulator
 static std::atomic<int> g_l2_hints{0};           // 1: mark streamed operands evict-first and re-read ones evict-last
-static std::atomic<int> g_n_group{0};            // n-fastest raster: n-tiles per group (0 = all)
+static std::atomic<int> g_n_group{-1};           // n-fastest raster: n-tiles per group (-1 = chosen per GEMM, 0 = all)
 static std::atomic<int> g_bulk_store{1};         // store epilogue through TMA stores / adds where it applies
 static std::atomic<int> g_ce_store_exp{1};       // one-launch cross-entropy: keep the exponentials of the statistics pass
 static std::atomic<int> g_ce_small_slice{kCeFusedSmallSliceBytes};   // slice size the one-launch cross-entropy aims for
