@@ -48,13 +48,13 @@ NAMES = {
 }
 
 
-# DRAM bytes per (live token row x vocabulary column) of one launch, from the ncu --set full capture of the profiling
-# case (dram__bytes_read.sum + dram__bytes_write.sum over 10336 live rows x 32768 columns, one token chunk of the C2
-# height; summary under profiles/).  Traffic of a full-size launch is this figure times the units that launch covers:
-# the store of the chunk and the streamed operand grow with the units for a fixed raster.
+# DRAM bytes per (live token row x vocabulary column) of one launch, from an ncu capture of the profiling case with the DRAM
+# counters alone (dram__bytes_read.sum + dram__bytes_write.sum over 10336 live rows x 32768 columns, one token chunk of the C2
+# height; summary under profiles/).  Traffic of a full-size launch is this figure times the units that launch covers: the
+# store of the chunk and the streamed operand grow with the units for a fixed raster.
 _PROFILE_UNITS = 10336 * 32768
-NCU_DRAM_BYTES_PER_UNIT = {"stats": (1.655e9 + 0.6876e9) / _PROFILE_UNITS, "dz": 0.0,
-                           "dw": (2.170e9 + 0.2583e9) / _PROFILE_UNITS, "dx": (2.362e9 + 0.0811e9) / _PROFILE_UNITS}
+NCU_DRAM_BYTES_PER_UNIT = {"stats": (1.373e9 + 0.684e9) / _PROFILE_UNITS, "dz": 0.0,
+                           "dw": (2.033e9 + 0.264e9) / _PROFILE_UNITS, "dx": (2.173e9 + 0.081e9) / _PROFILE_UNITS}
 
 
 BESIDE_GEMM_GROUP = None   # set in main() at N > 1: the NCCL group for collectives that run beside a GEMM
